@@ -1,0 +1,161 @@
+"""Builds the native library and programs for sm_100a with nvcc and g++.
+
+    python build.py            # incremental build of everything
+    python build.py --clean    # remove build products first
+    python build.py --jobs 8
+
+Products (all inside this directory, never installed elsewhere):
+    lib/libswitchml_b200.so        core + CPU backends + CUDA backend + C interface
+    lib/libswitchml_gemm.so        tcgen05 weight-gradient GEMM (loaded on demand)
+    bin/switchml_switchd           stand-alone controller / software switch
+    bin/hello_world, bin/allreduce_benchmark, bin/dnn_benchmark, bin/core_tests
+
+The role of the reference's Makefiles (dev_root/Makefile, client_lib/Makefile,
+benchmarks/Makefile, examples/Makefile) with their DEBUG/DUMMY/... switches: DEBUG=1 in
+the environment builds with -O0 -g, SWITCHML_CHECKED=1 adds bounds checks in kernels.
+"""
+import argparse
+import concurrent.futures as cf
+import os
+import shutil
+import subprocess
+import sys
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+OBJ = os.path.join(ROOT, "build", "obj")
+LIB = os.path.join(ROOT, "lib")
+BIN = os.path.join(ROOT, "bin")
+CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+NVCC = os.path.join(CUDA_HOME, "bin", "nvcc")
+ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
+DEBUG = os.environ.get("DEBUG", "0") == "1"
+OPT = ["-O0", "-g"] if DEBUG else ["-O3"]
+DEFS = ["-DSWITCHML_CHECKED"] if os.environ.get("SWITCHML_CHECKED", "0") == "1" else []
+INCLUDES = ["-I" + os.path.join(ROOT, "include"), "-I" + os.path.join(ROOT, "csrc"),
+            "-I" + os.path.join(CUDA_HOME, "include")]
+
+LIB_SOURCES = [
+    "csrc/core/log.cc", "csrc/core/config.cc", "csrc/core/job.cc", "csrc/core/utils.cc",
+    "csrc/core/stats.cc", "csrc/core/scheduler.cc", "csrc/core/context.cc", "csrc/core/backend.cc",
+    "csrc/ppp/cpu_exponent_quantizer_ppp.cc",
+    "csrc/backends/dummy/dummy_backend.cc",
+    "csrc/backends/softswitch/soft_switch.cc", "csrc/backends/softswitch/udp_backend.cc",
+    "csrc/rendezvous/control.cc",
+    "csrc/backends/cuda/driver_api.cc", "csrc/backends/cuda/fd_channel.cc",
+    "csrc/backends/cuda/symmetric_memory.cc", "csrc/backends/cuda/cuda_backend.cc",
+    "csrc/kernels/allreduce_kernels.cu",
+    "csrc/capi/switchml_c.cc",
+]
+GEMM_SOURCES = ["csrc/kernels/wgrad_gemm.cu"]
+PROGRAMS = {
+    "switchml_switchd": ["controller/switchd.cc"],
+    "hello_world": ["examples/hello_world/main.cc"],
+    "allreduce_benchmark": ["benchmarks/allreduce_benchmark.cc"],
+    "dnn_benchmark": ["benchmarks/dnn_benchmark.cc"],
+    "core_tests": ["csrc/tests/core_tests.cc"],
+}
+
+
+def _headers_mtime():
+    newest = 0.0
+    for base in ("include", "csrc"):
+        for d, _, files in os.walk(os.path.join(ROOT, base)):
+            for f in files:
+                if f.endswith((".h", ".cuh", ".inc")):
+                    newest = max(newest, os.path.getmtime(os.path.join(d, f)))
+    return newest
+
+
+def _obj_path(src):
+    return os.path.join(OBJ, src.replace("/", "_") + ".o")
+
+
+def _compile(src, hdr_mtime, verbose):
+    path = os.path.join(ROOT, src)
+    obj = _obj_path(src)
+    if os.path.exists(obj) and os.path.getmtime(obj) > max(os.path.getmtime(path), hdr_mtime):
+        return obj, None
+    if src.endswith(".cu"):
+        cmd = [NVCC] + ARCH + ["-lineinfo", "-std=c++17", "-Xcompiler", "-fPIC,-Wall"] + OPT + DEFS + \
+              INCLUDES + ["-c", path, "-o", obj]
+    else:
+        cmd = ["g++", "-std=c++17", "-fPIC", "-Wall", "-Wextra", "-Wno-unused-parameter", "-pthread"] + \
+              OPT + DEFS + INCLUDES + ["-c", path, "-o", obj]
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        return obj, "FAILED: %s\n%s%s" % (" ".join(cmd), r.stdout, r.stderr)
+    if r.stderr.strip() and verbose:
+        print(r.stderr)
+    return obj, None
+
+
+def _link(cmd, verbose):
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("link failed: %s\n%s%s" % (" ".join(cmd), r.stdout, r.stderr))
+
+
+def build(jobs=None, verbose=False, programs=True):
+    """Compile whatever is out of date. Returns the path of the main library."""
+    for d in (OBJ, LIB, BIN):
+        os.makedirs(d, exist_ok=True)
+    jobs = jobs or max(1, (os.cpu_count() or 2))
+    hdr = _headers_mtime()
+    sources = list(LIB_SOURCES)
+    gemm = [s for s in GEMM_SOURCES if os.path.exists(os.path.join(ROOT, s))]
+    progs = {k: v for k, v in PROGRAMS.items()
+             if programs and all(os.path.exists(os.path.join(ROOT, s)) for s in v)}
+    every = sources + gemm + [s for v in progs.values() for s in v]
+    errors = []
+    with cf.ThreadPoolExecutor(max_workers=jobs) as ex:
+        for obj, err in ex.map(lambda s: _compile(s, hdr, verbose), every):
+            if err:
+                errors.append(err)
+    if errors:
+        raise RuntimeError("\n".join(errors))
+
+    def newer(target, objs):
+        return not os.path.exists(target) or any(os.path.getmtime(o) > os.path.getmtime(target) for o in objs)
+
+    main_lib = os.path.join(LIB, "libswitchml_b200.so")
+    objs = [_obj_path(s) for s in sources]
+    if newer(main_lib, objs):
+        # cudart is linked statically, so the library loads on machines without a driver.
+        _link([NVCC] + ARCH + ["-shared", "-o", main_lib] + objs + ["-lpthread", "-ldl", "-lrt"], verbose)
+    if gemm:
+        gemm_lib = os.path.join(LIB, "libswitchml_gemm.so")
+        gobjs = [_obj_path(s) for s in gemm]
+        if newer(gemm_lib, gobjs):
+            _link([NVCC] + ARCH + ["-shared", "-o", gemm_lib] + gobjs + ["-lpthread", "-ldl", "-lrt"], verbose)
+    for name, srcs in progs.items():
+        exe = os.path.join(BIN, name)
+        pobjs = [_obj_path(s) for s in srcs]
+        if newer(exe, pobjs + [main_lib]):
+            _link([NVCC] + ARCH + ["-o", exe] + pobjs +
+                  ["-L" + LIB, "-lswitchml_b200", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../lib",
+                   "-lpthread", "-ldl", "-lrt"], verbose)
+    return main_lib
+
+
+def clean():
+    for d in (os.path.join(ROOT, "build"), LIB, BIN):
+        shutil.rmtree(d, ignore_errors=True)
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--clean", action="store_true")
+    ap.add_argument("--jobs", type=int, default=None)
+    ap.add_argument("-v", "--verbose", action="store_true")
+    a = ap.parse_args()
+    if a.clean:
+        clean()
+    try:
+        print(build(a.jobs, a.verbose))
+    except RuntimeError as e:
+        print(e, file=sys.stderr)
+        sys.exit(1)

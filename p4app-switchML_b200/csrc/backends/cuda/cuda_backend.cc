@@ -1,0 +1,615 @@
+// See cuda_backend.h.
+#include "backends/cuda/cuda_backend.h"
+
+#include <cuda_runtime.h>
+
+#include <atomic>
+#include <chrono>
+#include <condition_variable>
+#include <cstdlib>
+#include <cstring>
+#include <deque>
+#include <mutex>
+#include <sstream>
+#include <thread>
+#include <vector>
+
+#include "backends/cuda/fd_channel.h"
+#include "backends/cuda/symmetric_memory.h"
+#include "kernels/allreduce_kernels.h"
+#include "rendezvous/control.h"
+#include "switchml/context.h"
+#include "switchml/log.h"
+
+namespace switchml {
+
+namespace {
+
+#define SML_CUDA_CHECK(call)                                                        \
+  do {                                                                              \
+    cudaError_t _e = (call);                                                        \
+    SML_CHECK(_e == cudaSuccess) << #call << ": " << cudaGetErrorString(_e);        \
+  } while (0)
+
+// Recycles CUDA events; shared with the jobs so that an event outlives the backend if a
+// caller still holds the job.
+struct EventPool {
+  std::mutex mu;
+  std::vector<cudaEvent_t> free_list;
+  cudaEvent_t Get() {
+    {
+      std::lock_guard<std::mutex> lk(mu);
+      if (!free_list.empty()) {
+        cudaEvent_t e = free_list.back();
+        free_list.pop_back();
+        return e;
+      }
+    }
+    cudaEvent_t e = nullptr;
+    cudaEventCreateWithFlags(&e, cudaEventDisableTiming);
+    return e;
+  }
+  void Put(cudaEvent_t e) {
+    if (!e) return;
+    std::lock_guard<std::mutex> lk(mu);
+    free_list.push_back(e);
+  }
+  ~EventPool() {
+    for (cudaEvent_t e : free_list) cudaEventDestroy(e);
+  }
+};
+
+struct EventState : public DeviceJobState {
+  cudaEvent_t done = nullptr;
+  std::shared_ptr<EventPool> pool;
+  ~EventState() override {
+    if (pool) pool->Put(done);
+  }
+  void StreamWait(void* stream) override {
+    cudaStreamWaitEvent(static_cast<cudaStream_t>(stream), done, 0);
+  }
+};
+
+struct InFlight {
+  std::shared_ptr<Job> job;
+  bool via_scheduler = false;
+  JobSlice slice;
+  cudaEvent_t done = nullptr;
+  cudaEvent_t ready = nullptr;
+  int status_slot = 0;
+  unsigned long long tiles = 0;
+  std::string launch_error;
+};
+
+static const int kStatusSlots = 4096;
+
+class CudaBackend : public CudaBackendInterface {
+ public:
+  CudaBackend(Context& context, Config& config) : CudaBackendInterface(context, config) {}
+  ~CudaBackend() override { CleanupWorker(); }
+
+  int NumSchedulerConsumers() const override { return 1; }
+
+  void SetupWorker() override;
+  void CleanupWorker() override;
+  bool OnSubmit(const std::shared_ptr<Job>& job) override;
+  std::string ExtraStatsJson() override;
+
+  void* SymmetricAlloc(size_t bytes) override;
+  void SymmetricReset() override;
+  bool UsesMultimem() const override { return ctx_.use_multimem != 0; }
+  int Device() const override { return device_; }
+  int RunWaitProbe(double budget_ms) override;
+
+ private:
+  void LauncherLoop();
+  void CompletionLoop();
+  // Enqueue the kernels of `job` on `stream`; fills `f`. Caller holds launch_mu_.
+  void LaunchJob(const std::shared_ptr<Job>& job, cudaStream_t stream, InFlight* f);
+  cudaEvent_t GetEvent() { return events_->Get(); }
+  void PutEvent(cudaEvent_t e) { events_->Put(e); }
+
+  int device_ = 0;
+  int rank_ = 0, n_ = 1;
+  bool inline_launch_ = false;
+  bool set_up_ = false;
+  std::unique_ptr<ControlServer> server_;
+  ControlClient client_;
+  FdChannel fds_;
+  std::unique_ptr<SymmetricAllocator> allocator_;
+  SymmetricRegion staging_;
+  SymmetricRegion heap_;
+  size_t heap_used_ = 0;
+  kernels::RankCtx ctx_;
+  int max_channels_ = 1;
+  cudaStream_t comm_stream_ = nullptr;
+  int* dev_status_ = nullptr;
+  unsigned long long* dev_counters_ = nullptr;
+  int* host_status_ = nullptr;  // pinned ring of status words
+
+  std::mutex launch_mu_;  // serialises launches: one job order on every rank
+  unsigned long long epoch_base_ = 0;
+  int oneshot_parity_ = 0;
+  unsigned long long launched_jobs_ = 0;
+
+  std::shared_ptr<EventPool> events_ = std::make_shared<EventPool>();
+
+  std::thread launcher_, completer_;
+  std::mutex q_mu_;
+  std::condition_variable q_cv_;
+  std::deque<InFlight> inflight_;
+  bool stop_completer_ = false;
+  std::atomic<bool> failed_{false};
+};
+
+void CudaBackend::SetupWorker() {
+  const GeneralConfig& g = config_.general_;
+  const CudaBackendConfig& c = config_.backend_.cuda;
+  rank_ = g.rank;
+  n_ = g.num_workers;
+  SML_CHECK(n_ <= kernels::kMaxRanks)
+      << "the cuda backend serves one NVSwitch domain of at most " << kernels::kMaxRanks
+      << " GPUs, got num_workers = " << n_;
+  inline_launch_ = c.launch == "inline";
+
+  int ndev = 0;
+  cudaError_t e = cudaGetDeviceCount(&ndev);
+  SML_CHECK(e == cudaSuccess && ndev > 0)
+      << "backend = cuda needs a GPU: " << cudaGetErrorString(e);
+  device_ = c.device;
+  if (device_ < 0) {
+    const char* lr = getenv("LOCAL_RANK");
+    device_ = (lr && *lr) ? atoi(lr) : static_cast<int>(g.rank);
+    device_ %= ndev;
+  }
+  SML_CHECK(device_ < ndev) << "backend.cuda.device " << device_ << " does not exist";
+  SML_CUDA_CHECK(cudaSetDevice(device_));
+  cudaDeviceProp prop;
+  SML_CUDA_CHECK(cudaGetDeviceProperties(&prop, device_));
+  SML_CHECK(prop.major >= 9) << "device " << device_ << " (" << prop.name << ", sm_" << prop.major
+                             << prop.minor << ") is too old for this library (built for sm_100a)";
+
+  uint64_t session = static_cast<uint64_t>(
+      std::chrono::duration_cast<std::chrono::nanoseconds>(
+          std::chrono::system_clock::now().time_since_epoch()).count());
+  if (n_ > 1) {
+    if (rank_ == 0) {
+      server_.reset(new ControlServer());
+      SML_CHECK(server_->Start(g.controller_ip_str, g.controller_port, 0))
+          << "cannot start the in-process controller on " << g.controller_ip_str << ":"
+          << g.controller_port;
+    }
+    SML_CHECK(client_.Connect(g.controller_ip_str, g.controller_port)) << "controller unreachable";
+    SML_CHECK(client_.Broadcast(n_, rank_, 0, &session)) << "session broadcast failed";
+    SML_CHECK(fds_.Listen(session, rank_, c.rendezvous_dir)) << "cannot open the fd channel";
+    SML_CHECK(client_.Barrier(n_)) << "barrier failed";
+  }
+  allocator_.reset(new SymmetricAllocator(rank_, n_, device_, &client_, &fds_));
+
+  // Co-residency bound: every CTA of a job must be able to run at the same time.
+  max_channels_ = prop.multiProcessorCount;
+  if (c.channels > 0 && static_cast<int>(c.channels) < max_channels_) max_channels_ = c.channels;
+  if (max_channels_ > kernels::kMaxChannels) max_channels_ = kernels::kMaxChannels;
+
+  memset(&ctx_, 0, sizeof(ctx_));
+  ctx_.rank = rank_;
+  ctx_.nranks = n_;
+  ctx_.slot_bytes = c.slot_bytes;
+  SML_CHECK(c.slot_bytes / 4 / g.packet_numel <= 8192)
+      << "backend.cuda.slot_bytes / packet_numel is too large (at most 8192 blocks per slot)";
+  ctx_.slots_per_channel = c.slots_per_channel;
+  ctx_.block_numel = static_cast<int>(g.packet_numel);
+  ctx_.oneshot_bytes = (c.oneshot_max_bytes + 255) / 256 * 256;
+  ctx_.timeout_ns = static_cast<unsigned long long>(c.wait_timeout_ms * 1e6);
+  size_t bytes = kernels::StagingBytes(ctx_.slot_bytes, ctx_.slots_per_channel, ctx_.block_numel,
+                                       max_channels_, ctx_.oneshot_bytes, n_, &ctx_.data_offset,
+                                       &ctx_.exp_offset, &ctx_.oneshot_offset);
+  bool want_mc = c.transport != "p2p";
+  std::string err;
+  SML_CHECK(allocator_->Create(bytes, want_mc, &staging_, &err))
+      << "cannot create the symmetric staging region (" << (bytes >> 20) << " MiB): " << err;
+  SML_CHECK(!(c.transport == "nvls" && n_ > 1 && !staging_.multicast))
+      << "backend.cuda.transport = nvls but NVLink multicast is not available";
+  for (int p = 0; p < n_; p++) ctx_.stage_peer[p] = static_cast<char*>(staging_.peers[p]);
+  ctx_.stage_mc = static_cast<char*>(staging_.multicast);
+  ctx_.use_multimem = staging_.multicast != nullptr;
+
+  if (c.symm_heap_mb > 0) {
+    SML_CHECK(allocator_->Create(static_cast<size_t>(c.symm_heap_mb) << 20, ctx_.use_multimem != 0,
+                                 &heap_, &err))
+        << "cannot create the symmetric heap: " << err;
+    if (ctx_.use_multimem && !heap_.multicast) {
+      SML_LOG(WARNING) << "symmetric heap has no multicast mapping; zero-copy jobs use peer loads";
+    }
+  }
+  heap_used_ = 0;
+
+  int lo = 0, hi = 0;
+  cudaDeviceGetStreamPriorityRange(&lo, &hi);
+  SML_CUDA_CHECK(cudaStreamCreateWithPriority(&comm_stream_, cudaStreamNonBlocking, hi));
+  SML_CUDA_CHECK(cudaMalloc(&dev_status_, sizeof(int)));
+  SML_CUDA_CHECK(cudaMalloc(&dev_counters_, 8 * sizeof(unsigned long long)));
+  SML_CUDA_CHECK(cudaMemset(dev_status_, 0, sizeof(int)));
+  SML_CUDA_CHECK(cudaMemset(dev_counters_, 0, 8 * sizeof(unsigned long long)));
+  SML_CUDA_CHECK(cudaHostAlloc(&host_status_, kStatusSlots * sizeof(int), cudaHostAllocDefault));
+  memset(host_status_, 0, kStatusSlots * sizeof(int));
+  ctx_.status = dev_status_;
+  ctx_.counters = dev_counters_;
+  epoch_base_ = 0;
+  oneshot_parity_ = 0;
+  launched_jobs_ = 0;
+  failed_ = false;
+  SML_CUDA_CHECK(cudaDeviceSynchronize());
+  if (n_ > 1) SML_CHECK(client_.Barrier(n_)) << "barrier failed";
+
+  SML_VLOG(0) << "cuda backend ready: rank " << rank_ << "/" << n_ << " on device " << device_
+              << " (" << prop.name << "), transport "
+              << (n_ == 1 ? "local" : (ctx_.use_multimem ? "nvls (multimem)" : "p2p (peer memory)"))
+              << ", staging " << (bytes >> 20) << " MiB, up to " << max_channels_ << " channels, launch "
+              << c.launch;
+  stop_completer_ = false;
+  set_up_ = true;
+  completer_ = std::thread(&CudaBackend::CompletionLoop, this);
+  if (!inline_launch_) launcher_ = std::thread(&CudaBackend::LauncherLoop, this);
+}
+
+void CudaBackend::CleanupWorker() {
+  if (!set_up_) return;
+  set_up_ = false;
+  if (launcher_.joinable()) launcher_.join();
+  {
+    std::lock_guard<std::mutex> lk(q_mu_);
+    stop_completer_ = true;
+  }
+  q_cv_.notify_all();
+  if (completer_.joinable()) completer_.join();
+  cudaSetDevice(device_);
+  cudaDeviceSynchronize();
+  bool peers_alive = !failed_.load();
+  if (heap_.local) allocator_->Destroy(&heap_, peers_alive);
+  if (staging_.local) allocator_->Destroy(&staging_, peers_alive);
+  if (comm_stream_) cudaStreamDestroy(comm_stream_);
+  comm_stream_ = nullptr;
+  if (dev_status_) cudaFree(dev_status_);
+  if (dev_counters_) cudaFree(dev_counters_);
+  if (host_status_) cudaFreeHost(host_status_);
+  dev_status_ = nullptr;
+  dev_counters_ = nullptr;
+  host_status_ = nullptr;
+  fds_.Close();
+  client_.Close();
+  if (server_) {
+    server_->Stop();
+    server_.reset();
+  }
+}
+
+void* CudaBackend::SymmetricAlloc(size_t bytes) {
+  if (!heap_.local) return nullptr;
+  size_t need = (bytes + 255) / 256 * 256;
+  std::lock_guard<std::mutex> lk(launch_mu_);
+  if (heap_used_ + need > heap_.bytes) return nullptr;
+  void* p = static_cast<char*>(heap_.local) + heap_used_;
+  heap_used_ += need;
+  return p;
+}
+
+void CudaBackend::SymmetricReset() {
+  std::lock_guard<std::mutex> lk(launch_mu_);
+  heap_used_ = 0;
+}
+
+void CudaBackend::LaunchJob(const std::shared_ptr<Job>& job, cudaStream_t stream, InFlight* f) {
+  const CudaBackendConfig& c = config_.backend_.cuda;
+  const Tensor& t = job->tensor_;
+  kernels::JobArgs a;
+  memset(&a, 0, sizeof(a));
+  a.in = t.in_ptr;
+  a.out = t.out_ptr;
+  a.numel = t.numel;
+  a.elem_type = t.data_type == FLOAT32 ? kernels::ELEM_F32
+              : t.data_type == INT32 ? kernels::ELEM_I32 : kernels::ELEM_BF16;
+  a.mode = (t.data_type != INT32 && c.mode == "int32_quant") ? kernels::MODE_QUANT : kernels::MODE_SUM;
+  a.post_scale = c.average && t.data_type != INT32 ? 1.0f / static_cast<float>(n_) : 1.0f;
+  a.epoch_base = epoch_base_;
+  size_t esz = DataTypeSize(t.data_type);
+  size_t bytes = t.numel * esz;
+
+  // Pick the algorithm (identically on every rank: it depends on sizes and on whether the
+  // pointers sit in the symmetric heap, which is allocated in lock step).
+  auto in_heap = [&](const void* p) {
+    return heap_.local && p >= heap_.local &&
+           static_cast<const char*>(p) + bytes <= static_cast<const char*>(heap_.local) + heap_.bytes;
+  };
+  bool heap_ok = in_heap(t.in_ptr) && in_heap(t.out_ptr) &&
+                 (reinterpret_cast<uintptr_t>(t.in_ptr) & 15) == 0 &&
+                 (reinterpret_cast<uintptr_t>(t.out_ptr) & 15) == 0 &&
+                 (!ctx_.use_multimem || heap_.multicast);
+  if (a.mode == kernels::MODE_SUM && heap_ok && n_ > 1) {
+    a.algo = kernels::ALGO_ZEROCOPY;
+    for (int p = 0; p < n_; p++) a.user_peer[p] = static_cast<char*>(heap_.peers[p]);
+    a.user_mc = static_cast<char*>(heap_.multicast);
+    a.in_offset = static_cast<const char*>(t.in_ptr) - static_cast<const char*>(heap_.local);
+    a.out_offset = static_cast<const char*>(t.out_ptr) - static_cast<const char*>(heap_.local);
+  } else if (bytes <= c.oneshot_max_bytes) {
+    a.algo = kernels::ALGO_ONESHOT;
+    a.oneshot_parity = oneshot_parity_;
+    oneshot_parity_ ^= 1;
+  } else {
+    a.algo = kernels::ALGO_STAGED;
+  }
+  kernels::LaunchPlan plan = kernels::PlanLaunch(ctx_, a, c.channels, max_channels_);
+  epoch_base_ += plan.epochs;
+  f->tiles = plan.tiles;
+  f->status_slot = static_cast<int>(launched_jobs_++ % kStatusSlots);
+  f->done = GetEvent();
+
+  cudaError_t e = cudaSuccess;
+  if (t.numel > 0) e = kernels::LaunchAllReduce(ctx_, a, plan, stream);
+  if (e == cudaSuccess) {
+    // Bring the status word home and clear it for the next job, in stream order.
+    e = cudaMemcpyAsync(host_status_ + f->status_slot, dev_status_, sizeof(int),
+                        cudaMemcpyDeviceToHost, stream);
+  }
+  if (e == cudaSuccess) e = cudaMemsetAsync(dev_status_, 0, sizeof(int), stream);
+  if (e == cudaSuccess) e = cudaEventRecord(f->done, stream);
+  if (e != cudaSuccess) {
+    f->launch_error = std::string("kernel launch failed: ") + cudaGetErrorString(e);
+    cudaGetLastError();
+  }
+  SML_VLOG(2) << "job " << job->id_ << ": " << t.numel << " x " << DataTypeName(t.data_type)
+              << " algo " << a.algo << " mode " << a.mode << " channels " << plan.channels
+              << " epochs " << plan.epochs;
+  auto st = std::make_shared<EventState>();
+  st->done = f->done;
+  st->pool = events_;
+  job->SetDeviceState(st);
+}
+
+bool CudaBackend::OnSubmit(const std::shared_ptr<Job>& job) {
+  if (job->job_type_ != ALLREDUCE) {
+    context_.NotifyJobCompletion(job, false, "only ALLREDUCE jobs are supported");
+    return true;
+  }
+  if (config_.general_.instant_job_completion) {
+    job->SetJobStatus(RUNNING);
+    context_.NotifyJobCompletion(job, true);
+    return true;
+  }
+  cudaSetDevice(device_);
+  if (!inline_launch_) {
+    // Remember where the producer stream is now; the launcher orders the job after it.
+    cudaEvent_t ready = GetEvent();
+    cudaEventRecord(ready, static_cast<cudaStream_t>(job->producer_stream_));
+    job->ready_event_ = ready;
+    return false;  // goes through the scheduler
+  }
+  InFlight f;
+  f.job = job;
+  {
+    std::lock_guard<std::mutex> lk(launch_mu_);
+    job->SetJobStatus(QUEUED);
+    job->SetJobStatus(RUNNING);
+    LaunchJob(job, static_cast<cudaStream_t>(job->producer_stream_), &f);
+  }
+  {
+    std::lock_guard<std::mutex> lk(q_mu_);
+    inflight_.push_back(std::move(f));
+  }
+  q_cv_.notify_all();
+  return true;
+}
+
+void CudaBackend::LauncherLoop() {
+  cudaSetDevice(device_);
+  JobSlice js;
+  while (context_.GetContextState() == Context::RUNNING && context_.GetJobSlice(0, js)) {
+    InFlight f;
+    f.job = js.job;
+    f.via_scheduler = true;
+    f.slice = js;
+    f.ready = static_cast<cudaEvent_t>(js.job->ready_event_);
+    {
+      std::lock_guard<std::mutex> lk(launch_mu_);
+      if (f.ready) cudaStreamWaitEvent(comm_stream_, f.ready, 0);
+      LaunchJob(js.job, comm_stream_, &f);
+    }
+    {
+      std::lock_guard<std::mutex> lk(q_mu_);
+      inflight_.push_back(std::move(f));
+    }
+    q_cv_.notify_all();
+    // The scheduler's barrier (one consumer) lets us take the next job at once: jobs are
+    // queued back to back on the stream and complete in order.
+  }
+}
+
+void CudaBackend::CompletionLoop() {
+  cudaSetDevice(device_);
+  Stats& stats = context_.GetStats();
+  for (;;) {
+    InFlight f;
+    {
+      std::unique_lock<std::mutex> lk(q_mu_);
+      q_cv_.wait(lk, [this] { return stop_completer_ || !inflight_.empty(); });
+      if (inflight_.empty()) return;  // stop requested and nothing left
+      f = std::move(inflight_.front());
+      inflight_.pop_front();
+    }
+    bool ok = f.launch_error.empty();
+    std::string why = f.launch_error;
+    if (ok) {
+      cudaError_t e = cudaEventSynchronize(f.done);
+      if (e != cudaSuccess) {
+        ok = false;
+        why = std::string("device error: ") + cudaGetErrorString(e);
+        failed_ = true;
+      } else {
+        int st = host_status_[f.status_slot];
+        if (st != kernels::STATUS_OK) {
+          ok = false;
+          std::ostringstream o;
+          if ((st & 0xf) == kernels::STATUS_TIMEOUT) {
+            o << "a peer did not arrive within " << config_.backend_.cuda.wait_timeout_ms
+              << " ms (channel " << (st >> 8) << ", phase " << ((st >> 4) & 0xf) << ")";
+            stats.AddTimeouts(0, 1);
+          } else {
+            o << "kernel status " << st;
+          }
+          why = o.str();
+          failed_ = true;
+        }
+      }
+    }
+    stats.AddTotalPktsSent(0, f.tiles);
+    if (ok) stats.AddCorrectPktsReceived(0, f.tiles);
+    PutEvent(f.ready);
+    // f.done belongs to the job's EventState and returns to the pool with the job.
+    if (f.via_scheduler) {
+      if (!ok) f.job->failure_reason_ = why;
+      context_.NotifyJobSliceCompletion(0, f.slice);
+    } else {
+      context_.NotifyJobCompletion(f.job, ok, why);
+    }
+  }
+}
+
+std::string CudaBackend::ExtraStatsJson() {
+  unsigned long long c[8] = {0};
+  if (dev_counters_) {
+    cudaSetDevice(device_);
+    cudaMemcpy(c, dev_counters_, sizeof(c), cudaMemcpyDeviceToHost);
+  }
+  std::ostringstream o;
+  o << "{\"device\":" << device_ << ",\"multimem\":" << (ctx_.use_multimem ? "true" : "false")
+    << ",\"tiles\":" << c[0] << ",\"wait_spins\":" << c[1] << ",\"device_timeouts\":" << c[2]
+    << ",\"jobs_launched\":" << launched_jobs_ << ",\"epoch\":" << epoch_base_ << "}";
+  return o.str();
+}
+
+int CudaBackend::RunWaitProbe(double budget_ms) {
+  cudaSetDevice(device_);
+  std::lock_guard<std::mutex> lk(launch_mu_);
+  kernels::RankCtx probe = ctx_;
+  probe.timeout_ns = static_cast<unsigned long long>(budget_ms * 1e6);
+  cudaStream_t s = comm_stream_;
+  int st = -1;
+  cudaError_t e = kernels::LaunchWaitProbe(probe, s);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(host_status_ + kStatusSlots - 1, dev_status_, sizeof(int), cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaMemsetAsync(dev_status_, 0, sizeof(int), s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  if (e == cudaSuccess) st = host_status_[kStatusSlots - 1];
+  return e == cudaSuccess ? st : -static_cast<int>(e);
+}
+
+}  // namespace
+
+Backend* CreateCudaBackend(Context& context, Config& config) {
+  return new CudaBackend(context, config);
+}
+
+// ---------------------------------------------------------------------------------------
+
+int EmulatedAllReduce(int nranks, void* const* in_ptrs, void* const* out_ptrs,
+                      unsigned long long numel, int elem_type, int mode, int algo, int block_numel,
+                      size_t slot_bytes, int slots_per_channel, int channels, float post_scale,
+                      int repeats, std::string* error) {
+  using namespace kernels;
+  auto fail = [&](const std::string& m, int code) {
+    if (error) *error = m;
+    return code;
+  };
+  if (nranks < 1 || nranks > kMaxRanks) return fail("nranks out of range", -1);
+  if (algo == ALGO_ZEROCOPY) return fail("zero-copy needs real symmetric memory", -1);
+  int dev = 0;
+  cudaGetDevice(&dev);
+  cudaDeviceProp prop;
+  if (cudaGetDeviceProperties(&prop, dev) != cudaSuccess) return fail("no CUDA device", -2);
+  int esz = elem_type == ELEM_BF16 ? 2 : 4;
+  size_t oneshot_bytes = algo == ALGO_ONESHOT ? (numel * esz + 255) / 256 * 256 : 256;
+  int max_channels = prop.multiProcessorCount / nranks;  // all virtual ranks share the GPU
+  if (max_channels < 1) max_channels = 1;
+  if (channels > 0 && channels < max_channels) max_channels = channels;
+
+  RankCtx proto;
+  memset(&proto, 0, sizeof(proto));
+  proto.nranks = nranks;
+  proto.slot_bytes = slot_bytes;
+  proto.slots_per_channel = slots_per_channel;
+  proto.block_numel = block_numel;
+  proto.oneshot_bytes = oneshot_bytes;
+  proto.timeout_ns = 2000000000ull;  // 2 s: generous for one GPU, still bounded
+  size_t bytes = StagingBytes(slot_bytes, slots_per_channel, block_numel, max_channels,
+                              oneshot_bytes, nranks, &proto.data_offset, &proto.exp_offset,
+                              &proto.oneshot_offset);
+  std::vector<char*> stage(nranks, nullptr);
+  int* status = nullptr;
+  unsigned long long* counters = nullptr;
+  RankCtx* d_ctx = nullptr;
+  JobArgs* d_job = nullptr;
+  int result = 0;
+  cudaError_t e = cudaSuccess;
+  auto cleanup = [&] {
+    for (char* p : stage) if (p) cudaFree(p);
+    if (status) cudaFree(status);
+    if (counters) cudaFree(counters);
+    if (d_ctx) cudaFree(d_ctx);
+    if (d_job) cudaFree(d_job);
+  };
+  for (int r = 0; r < nranks && e == cudaSuccess; r++) {
+    e = cudaMalloc(&stage[r], bytes);
+    if (e == cudaSuccess) e = cudaMemset(stage[r], 0, bytes);
+  }
+  if (e == cudaSuccess) e = cudaMalloc(&status, nranks * sizeof(int));
+  if (e == cudaSuccess) e = cudaMemset(status, 0, nranks * sizeof(int));
+  if (e == cudaSuccess) e = cudaMalloc(&counters, nranks * 8 * sizeof(unsigned long long));
+  if (e == cudaSuccess) e = cudaMemset(counters, 0, nranks * 8 * sizeof(unsigned long long));
+  if (e == cudaSuccess) e = cudaMalloc(&d_ctx, nranks * sizeof(RankCtx));
+  if (e == cudaSuccess) e = cudaMalloc(&d_job, nranks * sizeof(JobArgs));
+  if (e != cudaSuccess) {
+    cleanup();
+    return fail(std::string("allocation failed: ") + cudaGetErrorString(e), -3);
+  }
+  std::vector<RankCtx> ctxs(nranks, proto);
+  std::vector<JobArgs> jobs(nranks);
+  unsigned long long epoch = 0;
+  for (int it = 0; it < (repeats < 1 ? 1 : repeats) && result == 0; it++) {
+    LaunchPlan plan;
+    for (int r = 0; r < nranks; r++) {
+      ctxs[r].rank = r;
+      for (int p = 0; p < nranks; p++) ctxs[r].stage_peer[p] = stage[p];
+      ctxs[r].status = status + r;
+      ctxs[r].counters = counters + r * 8;
+      JobArgs& j = jobs[r];
+      memset(&j, 0, sizeof(j));
+      j.in = in_ptrs[r];
+      j.out = out_ptrs[r];
+      j.numel = numel;
+      j.elem_type = elem_type;
+      j.mode = mode;
+      j.algo = algo;
+      j.post_scale = post_scale;
+      j.epoch_base = epoch;
+      j.oneshot_parity = it & 1;
+    }
+    plan = PlanLaunch(ctxs[0], jobs[0], channels, max_channels);
+    epoch += plan.epochs;
+    cudaMemcpy(d_ctx, ctxs.data(), nranks * sizeof(RankCtx), cudaMemcpyHostToDevice);
+    cudaMemcpy(d_job, jobs.data(), nranks * sizeof(JobArgs), cudaMemcpyHostToDevice);
+    e = LaunchAllReduceEmulated(d_ctx, d_job, jobs[0], nranks, plan, 0);
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) {
+      result = fail(std::string("emulated launch failed: ") + cudaGetErrorString(e), -4);
+      break;
+    }
+    std::vector<int> st(nranks);
+    cudaMemcpy(st.data(), status, nranks * sizeof(int), cudaMemcpyDeviceToHost);
+    for (int r = 0; r < nranks; r++) {
+      if (st[r] != STATUS_OK) result = fail("kernel status " + std::to_string(st[r]) + " on rank " + std::to_string(r), st[r]);
+    }
+  }
+  cleanup();
+  return result;
+}
+
+}  // namespace switchml

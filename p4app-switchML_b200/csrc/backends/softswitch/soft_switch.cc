@@ -1,0 +1,203 @@
+// See soft_switch.h.
+#include "backends/softswitch/soft_switch.h"
+
+#include <arpa/inet.h>
+
+#include <cstring>
+#include <sstream>
+
+namespace switchml {
+
+SoftSwitch::SoftSwitch(uint32_t num_slots) : num_slots_(num_slots), rng_(0x5eed) {
+  sets_[0].resize(num_slots_);
+  sets_[1].resize(num_slots_);
+}
+
+void SoftSwitch::Reset(uint64_t session_id, int num_workers, int packet_numel) {
+  std::lock_guard<std::mutex> lk(mu_);
+  for (int k = 0; k < 2; k++) {
+    for (SlotSet& s : sets_[k]) s = SlotSet();
+  }
+  session_id_ = session_id;
+  num_workers_ = num_workers;
+  packet_numel_ = packet_numel;
+  registered_ = 0;
+  counters_ = SwitchCounters();
+  for (WorkerCounters& w : worker_counters_) w = WorkerCounters();
+}
+
+bool SoftSwitch::AddWorker(int rank) {
+  std::lock_guard<std::mutex> lk(mu_);
+  if (rank < 0 || rank >= num_workers_ || rank >= kMaxWorkers) return false;
+  registered_ |= 1u << rank;
+  return true;
+}
+
+void SoftSwitch::SetDropProbabilities(double ingress, double egress, uint64_t seed) {
+  std::lock_guard<std::mutex> lk(mu_);
+  drop_ingress_ = ingress < 0 ? 0 : (ingress > 1 ? 1 : ingress);
+  drop_egress_ = egress < 0 ? 0 : (egress > 1 ? 1 : egress);
+  if (seed) rng_.seed(seed);
+}
+
+void SoftSwitch::GetDropProbabilities(double* ingress, double* egress) const {
+  std::lock_guard<std::mutex> lk(mu_);
+  *ingress = drop_ingress_;
+  *egress = drop_egress_;
+}
+
+bool SoftSwitch::Roll(double p) {
+  if (p <= 0) return false;
+  return std::uniform_real_distribution<double>(0.0, 1.0)(rng_) < p;
+}
+
+void SoftSwitch::Emit(const SlotSet& s, uint16_t pool_index, int dest_worker, int dest_thread,
+                      uint8_t type, std::vector<SwitchOutput>* out) {
+  if (Roll(drop_egress_)) {
+    counters_.egress_dropped++;
+    return;
+  }
+  SwitchOutput o;
+  o.dest_worker = dest_worker;
+  o.dest_thread = dest_thread;
+  o.bytes.resize(sizeof(WireHeader) + s.numel * 4u);
+  WireHeader h;
+  h.magic = htonl(kWireMagic);
+  h.type = type;
+  h.job_tag = s.job_tag;
+  h.worker_id = htons(static_cast<uint16_t>(dest_worker));
+  h.pkt_id = htonl(s.pkt_id);
+  h.pool_index = htons(pool_index);
+  h.numel = htons(s.numel);
+  h.exponent = s.exponent;
+  h.thread_id = static_cast<uint8_t>(dest_thread);
+  h.session_lo = htons(static_cast<uint16_t>(session_id_));
+  memcpy(o.bytes.data(), &h, sizeof(h));
+  uint32_t* p = reinterpret_cast<uint32_t*>(o.bytes.data() + sizeof(h));
+  for (uint16_t i = 0; i < s.numel; i++) {
+    uint32_t be = htonl(static_cast<uint32_t>(s.values[i]));
+    memcpy(p + i, &be, 4);
+  }
+  worker_counters_[dest_worker].tx_packets++;
+  worker_counters_[dest_worker].tx_bytes += o.bytes.size();
+  out->push_back(std::move(o));
+}
+
+void SoftSwitch::Process(const uint8_t* data, size_t len, std::vector<SwitchOutput>* out) {
+  std::lock_guard<std::mutex> lk(mu_);
+  WireHeader h;
+  if (len < sizeof(h)) { counters_.malformed++; return; }
+  memcpy(&h, data, sizeof(h));
+  uint16_t numel = ntohs(h.numel);
+  int worker = ntohs(h.worker_id);
+  uint16_t pool_index = ntohs(h.pool_index);
+  if (ntohl(h.magic) != kWireMagic || h.type != WIRE_DATA || numel > kMaxPacketNumel ||
+      len != sizeof(h) + numel * 4u || worker >= num_workers_ || worker >= kMaxWorkers ||
+      !(registered_ & (1u << worker)) || ntohs(h.session_lo) != static_cast<uint16_t>(session_id_) ||
+      (pool_index & ~kSetBit) >= num_slots_) {
+    counters_.malformed++;
+    return;
+  }
+  worker_counters_[worker].rx_packets++;
+  worker_counters_[worker].rx_bytes += len;
+  if (Roll(drop_ingress_)) { counters_.ingress_dropped++; return; }
+
+  int k = (pool_index & kSetBit) ? 1 : 0;
+  uint32_t slot = pool_index & ~kSetBit;
+  SlotSet& cur = sets_[k][slot];
+  SlotSet& other = sets_[1 - k][slot];
+  uint32_t bit = 1u << worker;
+
+  // Bitmap stage: note the arrival in this set and acknowledge the other set.
+  bool seen = (cur.bitmap & bit) != 0;
+  cur.bitmap |= bit;
+  other.bitmap &= ~bit;
+
+  if (seen) {
+    // A retransmission. If the slot is finished the worker lost the result: send it again
+    // from the retained copy, to that worker only. Otherwise the first copy was already
+    // absorbed and the aggregate is still waiting for others: nothing to do.
+    if (cur.complete) {
+      counters_.retransmit++;
+      Emit(cur, pool_index, worker, h.thread_id, WIRE_RESULT_RETX, out);
+    } else {
+      counters_.ignored++;
+    }
+    return;
+  }
+
+  const uint8_t* payload = data + sizeof(h);
+  if (cur.remaining == 0) {
+    // First packet of a new use of this slot set: overwrite.
+    cur.values.resize(numel);
+    for (uint16_t i = 0; i < numel; i++) {
+      uint32_t be;
+      memcpy(&be, payload + 4 * i, 4);
+      cur.values[i] = static_cast<int32_t>(ntohl(be));
+    }
+    cur.exponent = h.exponent;
+    cur.numel = numel;
+    cur.pkt_id = ntohl(h.pkt_id);
+    cur.job_tag = h.job_tag;
+    cur.complete = false;
+    cur.remaining = static_cast<uint32_t>(num_workers_ - 1);
+  } else {
+    uint16_t n = numel < cur.numel ? numel : cur.numel;
+    for (uint16_t i = 0; i < n; i++) {
+      uint32_t be;
+      memcpy(&be, payload + 4 * i, 4);
+      // wrapping add, as the switch register ALUs do
+      cur.values[i] = static_cast<int32_t>(static_cast<uint32_t>(cur.values[i]) + ntohl(be));
+    }
+    if (h.exponent > cur.exponent) cur.exponent = h.exponent;
+    cur.remaining--;
+  }
+
+  if (cur.remaining == 0) {
+    cur.complete = true;
+    counters_.broadcast++;
+    for (int w = 0; w < num_workers_; w++) Emit(cur, pool_index, w, h.thread_id, WIRE_RESULT, out);
+  } else {
+    counters_.consumed++;
+  }
+}
+
+SwitchCounters SoftSwitch::counters() const {
+  std::lock_guard<std::mutex> lk(mu_);
+  return counters_;
+}
+
+WorkerCounters SoftSwitch::worker_counters(int rank) const {
+  std::lock_guard<std::mutex> lk(mu_);
+  return worker_counters_[rank];
+}
+
+uint32_t SoftSwitch::Bitmap(uint32_t slot, int set) const {
+  std::lock_guard<std::mutex> lk(mu_);
+  return sets_[set & 1][slot % num_slots_].bitmap;
+}
+
+std::string SoftSwitch::DescribeWorkers() const {
+  std::lock_guard<std::mutex> lk(mu_);
+  std::ostringstream o;
+  o << "session " << session_id_ << ": " << num_workers_ << " worker(s), packet_numel "
+    << packet_numel_ << "\n rank  registered  rx_pkts  rx_bytes  tx_pkts  tx_bytes\n";
+  for (int w = 0; w < num_workers_; w++) {
+    const WorkerCounters& c = worker_counters_[w];
+    o << " " << w << "  " << ((registered_ >> w) & 1 ? "yes" : "no") << "  " << c.rx_packets << "  "
+      << c.rx_bytes << "  " << c.tx_packets << "  " << c.tx_bytes << "\n";
+  }
+  return o.str();
+}
+
+std::string SoftSwitch::DescribeStatistics() const {
+  std::lock_guard<std::mutex> lk(mu_);
+  std::ostringstream o;
+  o << "broadcast " << counters_.broadcast << "\nretransmit " << counters_.retransmit
+    << "\nconsumed " << counters_.consumed << "\nignored " << counters_.ignored
+    << "\ningress_dropped " << counters_.ingress_dropped << "\negress_dropped "
+    << counters_.egress_dropped << "\nmalformed " << counters_.malformed << "\n";
+  return o.str();
+}
+
+}  // namespace switchml

@@ -1,0 +1,99 @@
+// SoftSwitch: the aggregation pipeline of the programmable switch as a CPU state machine.
+//
+// It reproduces, per incoming packet, what the reference P4 program does in its ingress
+// pipeline (p4/switchml.p4:96-192): drop simulator → worker bitmap update/check
+// (bitmap_checker.p4:82-154) → worker counter (workers_counter.p4:25-111) → exponent max
+// (exponents.p4:32-111) → 32-bit adders (processor.p4:32-127) → next step
+// (next_step_selector.p4:112-204): consume, multicast the finished slot, or answer a
+// retransmission from the retained copy of the slot. Every slot exists twice ("sets");
+// using one set acknowledges the other, which is what makes retransmissions idempotent.
+//
+// The class has no sockets: Process() takes one packet and appends the packets to emit.
+// The UDP front end lives in rendezvous/control_server.cc; tests drive it directly.
+#ifndef SWITCHML_SOFT_SWITCH_H_
+#define SWITCHML_SOFT_SWITCH_H_
+
+#include <cstdint>
+#include <mutex>
+#include <random>
+#include <string>
+#include <vector>
+
+#include "backends/softswitch/wire.h"
+
+namespace switchml {
+
+struct SwitchOutput {
+  int dest_worker;
+  int dest_thread;
+  std::vector<uint8_t> bytes;  // WireHeader + payload
+};
+
+struct SwitchCounters {
+  // per slot and set, like the counters behind the reference CLI's show_statistics
+  uint64_t broadcast = 0, retransmit = 0, consumed = 0, ignored = 0;
+  uint64_t ingress_dropped = 0, egress_dropped = 0, malformed = 0;
+};
+
+struct WorkerCounters {
+  uint64_t rx_packets = 0, rx_bytes = 0, tx_packets = 0, tx_bytes = 0;
+};
+
+class SoftSwitch {
+ public:
+  explicit SoftSwitch(uint32_t num_slots = 16384);
+
+  // Forget every worker and clear all registers (rank 0 does this when a session starts;
+  // reference controller/grpc_server.py:234-236,332-334).
+  void Reset(uint64_t session_id, int num_workers, int packet_numel);
+  // Register a worker in the current session; false if the rank is out of range.
+  bool AddWorker(int rank);
+  int num_workers() const { return num_workers_; }
+  uint64_t session_id() const { return session_id_; }
+
+  // Feed one datagram; results (0, 1 or num_workers packets) are appended to `out`.
+  void Process(const uint8_t* data, size_t len, std::vector<SwitchOutput>* out);
+
+  // Fault injection: probability in [0,1] of dropping a packet on ingress / each copy on
+  // egress (reference p4/drop_simulator.p4:24-71, controller/drop_simulator.py:45-93).
+  void SetDropProbabilities(double ingress, double egress, uint64_t seed = 0);
+  void GetDropProbabilities(double* ingress, double* egress) const;
+
+  SwitchCounters counters() const;
+  WorkerCounters worker_counters(int rank) const;
+  uint32_t Bitmap(uint32_t slot, int set) const;
+  // Human-readable tables for the CLI.
+  std::string DescribeWorkers() const;
+  std::string DescribeStatistics() const;
+
+ private:
+  struct SlotSet {
+    uint32_t bitmap = 0;     // workers whose packet for this use has been absorbed
+    uint32_t remaining = 0;  // packets still missing; 0 = idle or complete
+    int8_t exponent = 0;
+    uint16_t numel = 0;
+    uint32_t pkt_id = 0;
+    uint8_t job_tag = 0;
+    bool complete = false;   // values hold a finished aggregate (the retained copy)
+    std::vector<int32_t> values;  // host order
+  };
+
+  void Emit(const SlotSet& s, uint16_t pool_index, int dest_worker, int dest_thread, uint8_t type,
+            std::vector<SwitchOutput>* out);
+  bool Roll(double p);
+
+  mutable std::mutex mu_;
+  uint32_t num_slots_;
+  std::vector<SlotSet> sets_[2];
+  int num_workers_ = 0;
+  int packet_numel_ = 0;
+  uint64_t session_id_ = 0;
+  uint32_t registered_ = 0;
+  double drop_ingress_ = 0, drop_egress_ = 0;
+  std::mt19937_64 rng_;
+  SwitchCounters counters_;
+  WorkerCounters worker_counters_[kMaxWorkers];
+};
+
+}  // namespace switchml
+#endif  // SWITCHML_SOFT_SWITCH_H_

@@ -1,0 +1,242 @@
+// See udp_backend.h.
+#include "backends/softswitch/udp_backend.h"
+
+#include <arpa/inet.h>
+#include <errno.h>
+#include <netinet/in.h>
+#include <poll.h>
+#include <sys/socket.h>
+#include <unistd.h>
+
+#include <chrono>
+#include <cstring>
+
+#include "backends/slot_window.h"
+#include "backends/softswitch/wire.h"
+#include "backends/timeout_queue.h"
+#include "switchml/context.h"
+#include "switchml/log.h"
+#include "switchml/prepostprocessor.h"
+
+namespace switchml {
+
+namespace {
+
+class UdpTransport : public SlotTransport {
+ public:
+  UdpTransport(const Config& cfg, WorkerTid tid, int fd, uint64_t session_id, int window)
+      : cfg_(cfg), tid_(tid), fd_(fd), session_id_(session_id), window_(window),
+        set_bits_(window, 0), answered_(window, 0) {
+    buf_.resize(kWireMaxBytes + 64);
+  }
+
+  void BeginSlice(const JobSlice& js, uint64_t, int batch) override {
+    job_tag_ = static_cast<uint8_t>(js.job->id_ & 0xff);
+    batch_ = batch;
+    timers_.reset(new TimeoutQueue(batch, cfg_.general_.timeout, cfg_.general_.timeout_threshold,
+                                   cfg_.general_.timeout_threshold_increment));
+  }
+
+  void EndSlice() override {
+    // Later jobs start at a different place of the pool so that a late packet of this
+    // job cannot be mistaken for one of the next (reference dpdk_worker_thread.cc:100,392).
+    shift_ = (shift_ + batch_) % window_;
+  }
+
+  void Send(const SlotPacket& p, bool retransmission) override {
+    int phys = (p.slot + shift_) % window_;
+    if (!retransmission) {
+      set_bits_[phys] ^= 1;  // every new use takes the other set
+      answered_[p.slot] = 0;
+    }
+    uint16_t pool_index = static_cast<uint16_t>(tid_ * window_ + phys) |
+                          (set_bits_[phys] ? kSetBit : 0);
+    WireHeader h;
+    h.magic = htonl(kWireMagic);
+    h.type = WIRE_DATA;
+    h.job_tag = job_tag_;
+    h.worker_id = htons(cfg_.general_.rank);
+    h.pkt_id = htonl(p.pkt_id);
+    h.pool_index = htons(pool_index);
+    h.numel = htons(p.numel);
+    h.exponent = p.exponent;
+    h.thread_id = static_cast<uint8_t>(tid_);
+    h.session_lo = htons(static_cast<uint16_t>(session_id_));
+    memcpy(buf_.data(), &h, sizeof(h));
+    memcpy(buf_.data() + sizeof(h), p.payload, p.numel * 4u);
+    send(fd_, buf_.data(), sizeof(h) + p.numel * 4u, 0);
+    timers_->Push(p.slot, std::chrono::steady_clock::now());
+  }
+
+  bool Poll(std::vector<SlotPacket>& slots, std::vector<int>* ready) override {
+    struct pollfd pf = {fd_, POLLIN, 0};
+    int r = poll(&pf, 1, 1);
+    if (r < 0 && errno != EINTR) return false;
+    if (r <= 0) return true;
+    for (int burst = 0; burst < 64; burst++) {
+      ssize_t n = recv(fd_, buf_.data(), buf_.size(), MSG_DONTWAIT);
+      if (n <= 0) break;
+      WireHeader h;
+      if (static_cast<size_t>(n) < sizeof(h)) { ready->push_back(-1); continue; }
+      memcpy(&h, buf_.data(), sizeof(h));
+      uint16_t numel = ntohs(h.numel);
+      uint16_t pool_index = ntohs(h.pool_index);
+      int phys = static_cast<int>(pool_index & ~kSetBit) - tid_ * window_;
+      bool ok = ntohl(h.magic) == kWireMagic && (h.type == WIRE_RESULT || h.type == WIRE_RESULT_RETX) &&
+                static_cast<size_t>(n) == sizeof(h) + numel * 4u && phys >= 0 && phys < window_ &&
+                h.job_tag == job_tag_;
+      int s = -1;
+      if (ok) {
+        s = (phys - shift_ % window_ + window_) % window_;
+        ok = s < static_cast<int>(slots.size()) && !answered(s) &&
+             slots[s].pkt_id == ntohl(h.pkt_id) &&
+             ((pool_index & kSetBit) != 0) == (set_bits_[phys] != 0);
+      }
+      if (!ok) { ready->push_back(-1); continue; }  // duplicate, stale job or foreign packet
+      SlotPacket& p = slots[s];
+      memcpy(p.payload, buf_.data() + sizeof(h), numel * 4u);
+      p.exponent = h.exponent;
+      mark_answered(s);
+      ready->push_back(s);
+    }
+    return true;
+  }
+
+  void OnAnswered(int slot) override { timers_->Remove(slot); }
+
+  uint64_t OnIdle(std::vector<SlotPacket>& slots) override {
+    uint64_t fired = 0;
+    auto now = std::chrono::steady_clock::now();
+    for (int s = timers_->Check(now); s >= 0; s = timers_->Check(now)) {
+      SML_VLOG(3) << "worker thread " << tid_ << ": timeout on slot " << s << " pkt "
+                  << slots[s].pkt_id << ", retransmitting";
+      Send(slots[s], true);  // re-arms the timer
+      fired++;
+      now = std::chrono::steady_clock::now();
+    }
+    return fired;
+  }
+
+ private:
+  bool answered(int s) const { return answered_[s] != 0; }
+  void mark_answered(int s) { answered_[s] = 1; }
+
+  const Config& cfg_;
+  WorkerTid tid_;
+  int fd_;
+  uint64_t session_id_;
+  int window_;
+  int batch_ = 0;
+  int shift_ = 0;
+  uint8_t job_tag_ = 0;
+  std::vector<uint8_t> set_bits_;
+  std::vector<uint8_t> answered_;
+  std::vector<uint8_t> buf_;
+  std::unique_ptr<TimeoutQueue> timers_;
+};
+
+}  // namespace
+
+UdpBackend::UdpBackend(Context& context, Config& config) : Backend(context, config) {}
+UdpBackend::~UdpBackend() { CleanupWorker(); }
+
+void UdpBackend::SetupWorker() {
+  const GeneralConfig& g = config_.general_;
+  const UdpBackendConfig& u = config_.backend_.udp;
+  if (g.rank == 0 && u.spawn_switch) {
+    server_.reset(new ControlServer());
+    SML_CHECK(server_->Start(g.controller_ip_str, g.controller_port, u.switch_port))
+        << "cannot start the in-process controller/software switch";
+  }
+  SML_CHECK(client_.Connect(g.controller_ip_str, g.controller_port)) << "controller unreachable";
+
+  // Session id: rank 0's clock, shared through the controller (reference
+  // dpdk_backend.cc:78-93).
+  session_id_ = static_cast<uint64_t>(
+      std::chrono::duration_cast<std::chrono::nanoseconds>(
+          std::chrono::system_clock::now().time_since_epoch()).count());
+  SML_CHECK(client_.Broadcast(g.num_workers, g.rank, 0, &session_id_)) << "session broadcast failed";
+
+  // One socket per worker thread.
+  for (int t = 0; t < g.num_worker_threads; t++) {
+    int fd = socket(AF_INET, SOCK_DGRAM, 0);
+    SML_CHECK(fd >= 0) << "socket(): " << strerror(errno);
+    int big = 4 << 20;
+    setsockopt(fd, SOL_SOCKET, SO_RCVBUF, &big, sizeof(big));
+    sockaddr_in me;
+    memset(&me, 0, sizeof(me));
+    me.sin_family = AF_INET;
+    inet_pton(AF_INET, u.worker_ip_str.c_str(), &me.sin_addr);
+    me.sin_port = htons(u.worker_port ? static_cast<uint16_t>(u.worker_port + t) : 0);
+    SML_CHECK(bind(fd, reinterpret_cast<sockaddr*>(&me), sizeof(me)) == 0)
+        << "cannot bind worker UDP port " << u.worker_port + t << ": " << strerror(errno);
+    fds_.push_back(fd);
+  }
+
+  // Rank 0 opens the session (which clears the switch) before anybody else joins.
+  std::string sw_ip;
+  if (g.rank == 0) {
+    SML_CHECK(client_.CreateUdpSession(session_id_, g.rank, g.num_workers, g.packet_numel,
+                                       u.worker_ip_str, u.worker_port, g.num_worker_threads,
+                                       &sw_ip, &switch_udp_port_)) << "session setup failed";
+    SML_CHECK(client_.Barrier(g.num_workers)) << "barrier failed";
+  } else {
+    SML_CHECK(client_.Barrier(g.num_workers)) << "barrier failed";
+    SML_CHECK(client_.CreateUdpSession(session_id_, g.rank, g.num_workers, g.packet_numel,
+                                       u.worker_ip_str, u.worker_port, g.num_worker_threads,
+                                       &sw_ip, &switch_udp_port_)) << "session setup failed";
+  }
+  sockaddr_in sw;
+  memset(&sw, 0, sizeof(sw));
+  sw.sin_family = AF_INET;
+  inet_pton(AF_INET, u.switch_ip_str.c_str(), &sw.sin_addr);
+  sw.sin_port = htons(switch_udp_port_);
+  for (int fd : fds_) {
+    SML_CHECK(connect(fd, reinterpret_cast<sockaddr*>(&sw), sizeof(sw)) == 0)
+        << "connect to switch: " << strerror(errno);
+  }
+  SML_CHECK(client_.Barrier(g.num_workers)) << "barrier failed";
+
+  for (int t = 0; t < g.num_worker_threads; t++) {
+    threads_.emplace_back(&UdpBackend::WorkerLoop, this, static_cast<WorkerTid>(t), fds_[t]);
+  }
+}
+
+void UdpBackend::CleanupWorker() {
+  for (auto& t : threads_) {
+    if (t.joinable()) t.join();
+  }
+  threads_.clear();
+  for (int fd : fds_) close(fd);
+  fds_.clear();
+  client_.Close();
+  if (server_) {
+    server_->Stop();
+    server_.reset();
+  }
+}
+
+void UdpBackend::WorkerLoop(WorkerTid tid, int fd) {
+  const GeneralConfig& g = config_.general_;
+  int window = static_cast<int>(g.max_outstanding_packets / g.num_worker_threads);
+  int packet_numel = static_cast<int>(g.packet_numel);
+  auto ppp = PrePostProcessor::CreateInstance(config_, tid, g.packet_numel * 4, window);
+  UdpTransport transport(config_, tid, fd, session_id_, window);
+  std::vector<int32_t> pool;
+  Stats& stats = context_.GetStats();
+  auto running = [this] { return context_.GetContextState() == Context::RUNNING; };
+  JobSlice js;
+  while (running() && context_.GetJobSlice(tid, js)) {
+    if (js.slice.numel > 0 && !g.instant_job_completion) {
+      SlotWindowResult r = RunSlotWindow(js, *ppp, transport, window, packet_numel, pool, running);
+      stats.AddTotalPktsSent(tid, r.sent);
+      stats.AddCorrectPktsReceived(tid, r.received);
+      stats.AddWrongPktsReceived(tid, r.wrong);
+      stats.AddTimeouts(tid, r.timeouts);
+      if (!r.ok) js.job->failure_reason_ = "context stopped during the job";
+    }
+    context_.NotifyJobSliceCompletion(tid, js);
+  }
+}
+
+}  // namespace switchml

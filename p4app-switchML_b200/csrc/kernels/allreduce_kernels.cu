@@ -1,0 +1,698 @@
+// Aggregation kernels for sm_100a: see allreduce_kernels.h for the host interface.
+//
+// ALGO_STAGED — the streaming pipeline. A job is cut into contiguous per-channel ranges
+// (the analogue of the reference scheduler's static per-thread slices,
+// schedulers/fifo_scheduler.cc:92-109); a channel (one CTA on every rank) walks its range
+// in tiles of one staging slot. Per tile:
+//   MODE_QUANT   A  block max-abs -> exponent, published to the peers          [barrier 0]
+//                   global exponent = max over ranks (multimem.ld_reduce.max.s32 through
+//                   the switch, or peer loads); quantise own tile into the slot [barrier 1]
+//                B  owner of shard r: integer sum over ranks of its shard
+//                   (multimem.ld_reduce.add.s32 / peer loads), dequantise, broadcast
+//                   (multimem.st / peer stores) as float32                      [barrier 2]
+//                C  copy the finished tile from the slot to the output
+//   MODE_SUM     copy-in [barrier 1], B with a float/int add, [barrier 2], copy-out.
+// The barrier after B is also the acknowledgement that lets the slot be reused, the role
+// of the "other set" bitmap clear in the switch (p4/bitmap_checker.p4:82-123).
+//
+// ALGO_ONESHOT — for small messages: every rank pushes its input into a per-source buffer
+// on every rank (one multimem.st, or n peer stores), one barrier, then each rank reduces
+// the n copies locally (in QUANT mode with exactly the same integer arithmetic).
+//
+// ALGO_ZEROCOPY — tensors that live in symmetric memory are reduced in place: barrier,
+// shard-wise reduce+broadcast, barrier. No staging traffic at all.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "kernels/allreduce_kernels.h"
+#include "kernels/device_sync.cuh"
+#include "kernels/multimem.cuh"
+#include "switchml/quant_math.h"
+
+namespace switchml {
+namespace kernels {
+
+namespace {
+
+static const int kMaxBlocksPerSlot = 8192;  // scale factors kept in shared memory
+static const int kUnroll = 4;
+
+__device__ __forceinline__ bool Aligned16(const void* p) {
+  return (reinterpret_cast<uintptr_t>(p) & 15) == 0;
+}
+
+__device__ __forceinline__ uint4 LoadCg16(const void* p) {
+  return __ldcg(reinterpret_cast<const uint4*>(p));
+}
+
+// bf16 pair helpers -----------------------------------------------------------------
+__device__ __forceinline__ float2 Bf16x2ToFloat2(unsigned u) {
+  return make_float2(__uint_as_float(u << 16), __uint_as_float(u & 0xffff0000u));
+}
+__device__ __forceinline__ unsigned Float2ToBf16x2(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<unsigned*>(&h);
+}
+__device__ __forceinline__ float Bf16ToFloat(unsigned short u) {
+  return __uint_as_float(static_cast<unsigned>(u) << 16);
+}
+__device__ __forceinline__ unsigned short FloatToBf16(float f) {
+  __nv_bfloat16 h = __float2bfloat16_rn(f);
+  return *reinterpret_cast<unsigned short*>(&h);
+}
+
+// Plain byte-wise identical copy of `bytes` bytes (multiple of the element size `esz`).
+__device__ __forceinline__ void CopyBytes(void* dst, const void* src, size_t bytes, int esz) {
+  if (Aligned16(dst) && Aligned16(src)) {
+    size_t nvec = bytes / 16;
+    const uint4* s = reinterpret_cast<const uint4*>(src);
+    uint4* d = reinterpret_cast<uint4*>(dst);
+    size_t i = threadIdx.x;
+    for (; i + (kUnroll - 1) * blockDim.x < nvec; i += kUnroll * blockDim.x) {
+      uint4 v[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; u++) v[u] = s[i + u * blockDim.x];
+#pragma unroll
+      for (int u = 0; u < kUnroll; u++) d[i + u * blockDim.x] = v[u];
+    }
+    for (; i < nvec; i += blockDim.x) d[i] = s[i];
+    size_t done = nvec * 16;
+    if (esz == 4) {
+      for (size_t b = done + threadIdx.x * 4; b < bytes; b += blockDim.x * 4)
+        *reinterpret_cast<unsigned*>(static_cast<char*>(dst) + b) =
+            *reinterpret_cast<const unsigned*>(static_cast<const char*>(src) + b);
+    } else {
+      for (size_t b = done + threadIdx.x * 2; b < bytes; b += blockDim.x * 2)
+        *reinterpret_cast<unsigned short*>(static_cast<char*>(dst) + b) =
+            *reinterpret_cast<const unsigned short*>(static_cast<const char*>(src) + b);
+    }
+  } else if (esz == 4) {
+    const unsigned* s = reinterpret_cast<const unsigned*>(src);
+    unsigned* d = reinterpret_cast<unsigned*>(dst);
+    for (size_t i = threadIdx.x; i < bytes / 4; i += blockDim.x) d[i] = s[i];
+  } else {
+    const unsigned short* s = reinterpret_cast<const unsigned short*>(src);
+    unsigned short* d = reinterpret_cast<unsigned short*>(dst);
+    for (size_t i = threadIdx.x; i < bytes / 2; i += blockDim.x) d[i] = s[i];
+  }
+}
+
+// Element `i` of the input as float (QUANT mode reads f32 or bf16).
+template <int ELEM>
+__device__ __forceinline__ float LoadAsFloat(const void* in, size_t i) {
+  if (ELEM == ELEM_BF16) return Bf16ToFloat(reinterpret_cast<const unsigned short*>(in)[i]);
+  return reinterpret_cast<const float*>(in)[i];
+}
+
+// ------------------------------------------------------------------------------------
+// Reduce one 16-byte vector at byte offset `off` of the staging/user regions over all
+// ranks and return it post-scaled. `nvalid` is unused here; tails are handled by callers.
+template <int ELEM>
+__device__ __forceinline__ uint4 ReduceVec(const RankCtx& ctx, char* const* peers, char* mc,
+                                           size_t off, float post_scale) {
+  uint4 r;
+  if (ELEM == ELEM_F32) {
+    float4 a;
+    if (ctx.use_multimem) {
+      a = MultimemLdReduceAddF32x4(mc + off);
+    } else {
+      a = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int p = 0; p < ctx.nranks; p++) {
+        uint4 v = LoadCg16(peers[p] + off);
+        a.x += __uint_as_float(v.x);
+        a.y += __uint_as_float(v.y);
+        a.z += __uint_as_float(v.z);
+        a.w += __uint_as_float(v.w);
+      }
+    }
+    if (post_scale != 1.0f) { a.x *= post_scale; a.y *= post_scale; a.z *= post_scale; a.w *= post_scale; }
+    r = make_uint4(__float_as_uint(a.x), __float_as_uint(a.y), __float_as_uint(a.z), __float_as_uint(a.w));
+  } else if (ELEM == ELEM_I32) {
+    if (ctx.use_multimem) {
+      r.x = static_cast<unsigned>(MultimemLdReduceAddS32(mc + off));
+      r.y = static_cast<unsigned>(MultimemLdReduceAddS32(mc + off + 4));
+      r.z = static_cast<unsigned>(MultimemLdReduceAddS32(mc + off + 8));
+      r.w = static_cast<unsigned>(MultimemLdReduceAddS32(mc + off + 12));
+    } else {
+      r = make_uint4(0, 0, 0, 0);
+      for (int p = 0; p < ctx.nranks; p++) {
+        uint4 v = LoadCg16(peers[p] + off);
+        r.x += v.x; r.y += v.y; r.z += v.z; r.w += v.w;  // wrapping
+      }
+    }
+  } else {  // bf16: 8 values, float32 accumulation
+    float acc[8];
+    if (ctx.use_multimem) {
+      uint4 v = MultimemLdReduceAddBf16x8(mc + off);
+      if (post_scale == 1.0f) return v;
+      float2 t;
+      t = Bf16x2ToFloat2(v.x); acc[0] = t.x; acc[1] = t.y;
+      t = Bf16x2ToFloat2(v.y); acc[2] = t.x; acc[3] = t.y;
+      t = Bf16x2ToFloat2(v.z); acc[4] = t.x; acc[5] = t.y;
+      t = Bf16x2ToFloat2(v.w); acc[6] = t.x; acc[7] = t.y;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; j++) acc[j] = 0.f;
+      for (int p = 0; p < ctx.nranks; p++) {
+        uint4 v = LoadCg16(peers[p] + off);
+        float2 t;
+        t = Bf16x2ToFloat2(v.x); acc[0] += t.x; acc[1] += t.y;
+        t = Bf16x2ToFloat2(v.y); acc[2] += t.x; acc[3] += t.y;
+        t = Bf16x2ToFloat2(v.z); acc[4] += t.x; acc[5] += t.y;
+        t = Bf16x2ToFloat2(v.w); acc[6] += t.x; acc[7] += t.y;
+      }
+    }
+    if (post_scale != 1.0f) {
+#pragma unroll
+      for (int j = 0; j < 8; j++) acc[j] *= post_scale;
+    }
+    r.x = Float2ToBf16x2(acc[0], acc[1]);
+    r.y = Float2ToBf16x2(acc[2], acc[3]);
+    r.z = Float2ToBf16x2(acc[4], acc[5]);
+    r.w = Float2ToBf16x2(acc[6], acc[7]);
+  }
+  return r;
+}
+
+// Write one 16-byte vector to every rank's copy.
+__device__ __forceinline__ void BroadcastVec(const RankCtx& ctx, char* const* peers, char* mc,
+                                             size_t off, uint4 v) {
+  if (ctx.use_multimem) {
+    MultimemStore16(mc + off, v);
+  } else {
+    for (int p = 0; p < ctx.nranks; p++) *reinterpret_cast<uint4*>(peers[p] + off) = v;
+  }
+}
+
+// Integer-sum one vector of quantised values over all ranks.
+__device__ __forceinline__ uint4 ReduceQuantVec(const RankCtx& ctx, char* const* peers, char* mc,
+                                                size_t off) {
+  return ReduceVec<ELEM_I32>(ctx, peers, mc, off, 1.0f);
+}
+
+// Shard [begin,end) (elements) of a tile that has `len` elements; units of `unit`.
+__device__ __forceinline__ void ShardRange(size_t len, int nranks, int rank, size_t unit,
+                                           size_t* begin, size_t* end) {
+  size_t per = (len + nranks - 1) / nranks;
+  per = (per + unit - 1) / unit * unit;
+  size_t b = per * rank, e = b + per;
+  *begin = b < len ? b : len;
+  *end = e < len ? e : len;
+}
+
+// ------------------------------------------------------------------------------------
+template <int ELEM, int MODE>
+__device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
+                          unsigned long long elems_per_channel, int* s_failed, float* s_sf) {
+  const int in_esz = ELEM == ELEM_BF16 ? 2 : 4;
+  const int st_esz = MODE == MODE_QUANT ? 4 : in_esz;
+  const size_t slot_elems = ctx.slot_bytes / st_esz;
+  const size_t vec_elems = 16 / st_esz;
+  const size_t unit = MODE == MODE_QUANT ? static_cast<size_t>(ctx.block_numel) : 128;
+
+  unsigned long long c0 = static_cast<unsigned long long>(channel) * elems_per_channel;
+  if (c0 >= job.numel) return;
+  unsigned long long c1 = c0 + elems_per_channel;
+  if (c1 > job.numel) c1 = job.numel;
+
+  char* my_stage = ctx.stage_peer[ctx.rank];
+  const size_t blocks_per_slot = slot_elems / ctx.block_numel;
+  unsigned long long k = 0;
+  for (unsigned long long pos = c0; pos < c1; pos += slot_elems, ++k) {
+    const unsigned long long epoch = job.epoch_base + k + 1;
+    const size_t len = static_cast<size_t>(c1 - pos < slot_elems ? c1 - pos : slot_elems);
+    const int slot = static_cast<int>(k % ctx.slots_per_channel);
+    const size_t slot_index = static_cast<size_t>(channel) * ctx.slots_per_channel + slot;
+    const size_t slot_off = ctx.data_offset + slot_index * ctx.slot_bytes;  // same on all ranks
+    const char* in = static_cast<const char*>(job.in) + pos * in_esz;
+    char* out = static_cast<char*>(job.out) + pos * in_esz;
+
+    if (MODE == MODE_QUANT) {
+      // ---- A: exponents of my blocks ----
+      const size_t nblocks = (len + ctx.block_numel - 1) / ctx.block_numel;
+      const size_t exp_off = ctx.exp_offset + slot_index * blocks_per_slot * 4;
+      int* my_exp = reinterpret_cast<int*>(my_stage + exp_off);
+      const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+      for (size_t b = warp; b < nblocks; b += nwarps) {
+        size_t base = b * ctx.block_numel;
+        size_t n = len - base < static_cast<size_t>(ctx.block_numel) ? len - base : ctx.block_numel;
+        float m = 0.f;
+        for (size_t i = lane; i < n; i += 32) {
+          float v = fabsf(LoadAsFloat<ELEM>(in, base + i));
+          if (v > m) m = v;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          float t = __shfl_xor_sync(0xffffffffu, m, o);
+          if (t > m) m = t;
+        }
+        if (lane == 0) my_exp[b] = quant::LocalExponent(m);
+      }
+      if (!ChannelBarrier(ctx, channel, 0, epoch, s_failed)) return;
+      // ---- global exponents -> scale factors ----
+      for (size_t b = threadIdx.x; b < nblocks; b += blockDim.x) {
+        int e;
+        if (ctx.use_multimem) {
+          e = MultimemLdReduceMaxS32(ctx.stage_mc + exp_off + b * 4);
+        } else {
+          e = quant::kZeroExponent;
+          for (int p = 0; p < ctx.nranks; p++) {
+            int t = __ldcg(reinterpret_cast<const int*>(ctx.stage_peer[p] + exp_off) + b);
+            if (t > e) e = t;
+          }
+        }
+        s_sf[b] = quant::ScaleFactor(e, ctx.nranks);
+      }
+      __syncthreads();
+      // ---- quantise my tile into the slot ----
+      int* q = reinterpret_cast<int*>(my_stage + slot_off);
+      const int shift = 31 - __clz(ctx.block_numel);  // block_numel is a power of two
+      if (ELEM == ELEM_F32 && Aligned16(in)) {
+        const float4* in4 = reinterpret_cast<const float4*>(in);
+        size_t nvec = len / 4;
+        for (size_t i = threadIdx.x; i < nvec; i += blockDim.x) {
+          float4 x = in4[i];
+          float sf = s_sf[(i * 4) >> shift];  // a vector never straddles a block (>= 32)
+          int4 r;
+          r.x = quant::Quantize(x.x, sf);
+          r.y = quant::Quantize(x.y, sf);
+          r.z = quant::Quantize(x.z, sf);
+          r.w = quant::Quantize(x.w, sf);
+          reinterpret_cast<int4*>(q)[i] = r;
+        }
+        for (size_t i = nvec * 4 + threadIdx.x; i < len; i += blockDim.x)
+          q[i] = quant::Quantize(reinterpret_cast<const float*>(in)[i], s_sf[i >> shift]);
+      } else {
+        for (size_t i = threadIdx.x; i < len; i += blockDim.x)
+          q[i] = quant::Quantize(LoadAsFloat<ELEM>(in, i), s_sf[i >> shift]);
+      }
+    } else {
+      CopyBytes(my_stage + slot_off, in, len * in_esz, in_esz);
+    }
+    if (!ChannelBarrier(ctx, channel, 1, epoch, s_failed)) return;
+
+    // ---- B: reduce and broadcast my shard ----
+    {
+      size_t sb, se;
+      ShardRange(len, ctx.nranks, ctx.rank, unit, &sb, &se);
+      size_t v0 = sb / vec_elems, v1 = (se + vec_elems - 1) / vec_elems;
+      if (MODE == MODE_QUANT) {
+        const int shift = 31 - __clz(ctx.block_numel);
+        for (size_t v = v0 + threadIdx.x; v < v1; v += blockDim.x) {
+          size_t off = slot_off + v * 16;
+          uint4 s = ReduceQuantVec(ctx, ctx.stage_peer, ctx.stage_mc, off);
+          float sf = s_sf[(v * 4) >> shift];
+          float4 y;
+          y.x = quant::Dequantize(static_cast<int>(s.x), sf);
+          y.y = quant::Dequantize(static_cast<int>(s.y), sf);
+          y.z = quant::Dequantize(static_cast<int>(s.z), sf);
+          y.w = quant::Dequantize(static_cast<int>(s.w), sf);
+          if (job.post_scale != 1.0f) { y.x *= job.post_scale; y.y *= job.post_scale; y.z *= job.post_scale; y.w *= job.post_scale; }
+          BroadcastVec(ctx, ctx.stage_peer, ctx.stage_mc, off,
+                       make_uint4(__float_as_uint(y.x), __float_as_uint(y.y), __float_as_uint(y.z), __float_as_uint(y.w)));
+        }
+      } else {
+        size_t v = v0 + threadIdx.x;
+        for (; v + (kUnroll - 1) * blockDim.x < v1; v += kUnroll * blockDim.x) {
+          uint4 r[kUnroll];
+#pragma unroll
+          for (int u = 0; u < kUnroll; u++)
+            r[u] = ReduceVec<ELEM>(ctx, ctx.stage_peer, ctx.stage_mc, slot_off + (v + u * blockDim.x) * 16, job.post_scale);
+#pragma unroll
+          for (int u = 0; u < kUnroll; u++)
+            BroadcastVec(ctx, ctx.stage_peer, ctx.stage_mc, slot_off + (v + u * blockDim.x) * 16, r[u]);
+        }
+        for (; v < v1; v += blockDim.x) {
+          uint4 r = ReduceVec<ELEM>(ctx, ctx.stage_peer, ctx.stage_mc, slot_off + v * 16, job.post_scale);
+          BroadcastVec(ctx, ctx.stage_peer, ctx.stage_mc, slot_off + v * 16, r);
+        }
+      }
+    }
+    if (!ChannelBarrier(ctx, channel, 2, epoch, s_failed)) return;
+
+    // ---- C: copy the finished tile out ----
+    if (MODE == MODE_QUANT && ELEM == ELEM_BF16) {
+      const float* y = reinterpret_cast<const float*>(my_stage + slot_off);
+      unsigned short* o = reinterpret_cast<unsigned short*>(out);
+      for (size_t i = threadIdx.x; i < len; i += blockDim.x) o[i] = FloatToBf16(y[i]);
+    } else {
+      CopyBytes(out, my_stage + slot_off, len * in_esz, in_esz);
+    }
+    if (threadIdx.x == 0) atomicAdd(ctx.counters, 1ull);
+    // The next use of this slot (tile k + slots_per_channel) writes it only after this
+    // copy-out, because the same threads do both, separated by the barrier's syncs.
+    __syncthreads();
+  }
+}
+
+// ------------------------------------------------------------------------------------
+template <int ELEM, int MODE>
+__device__ void RunOneShot(const RankCtx& ctx, const JobArgs& job, int channel,
+                           unsigned long long elems_per_channel, int* s_failed) {
+  const int esz = ELEM == ELEM_BF16 ? 2 : 4;
+  unsigned long long c0 = static_cast<unsigned long long>(channel) * elems_per_channel;
+  if (c0 >= job.numel) return;
+  unsigned long long c1 = c0 + elems_per_channel;
+  if (c1 > job.numel) c1 = job.numel;
+  const size_t len = static_cast<size_t>(c1 - c0);
+  const unsigned long long epoch = job.epoch_base + 1;
+
+  // Buffer of source rank s (same offset on every rank).
+  auto buf_off = [&](int s) {
+    return ctx.oneshot_offset +
+           (static_cast<size_t>(job.oneshot_parity) * ctx.nranks + s) * ctx.oneshot_bytes + c0 * esz;
+  };
+  const char* in = static_cast<const char*>(job.in) + c0 * esz;
+  const size_t my_off = buf_off(ctx.rank);
+  const size_t bytes = len * esz;
+
+  // ---- push my range to everybody ----
+  if (Aligned16(in)) {
+    size_t nvec = bytes / 16;
+    for (size_t i = threadIdx.x; i < nvec; i += blockDim.x) {
+      uint4 v = reinterpret_cast<const uint4*>(in)[i];
+      BroadcastVec(ctx, ctx.stage_peer, ctx.stage_mc, my_off + i * 16, v);
+    }
+    for (size_t b = nvec * 16 + threadIdx.x * esz; b < bytes; b += blockDim.x * esz) {
+      for (int p = 0; p < ctx.nranks; p++) {
+        if (esz == 4) *reinterpret_cast<unsigned*>(ctx.stage_peer[p] + my_off + b) = *reinterpret_cast<const unsigned*>(in + b);
+        else *reinterpret_cast<unsigned short*>(ctx.stage_peer[p] + my_off + b) = *reinterpret_cast<const unsigned short*>(in + b);
+      }
+    }
+  } else {
+    for (size_t b = threadIdx.x * esz; b < bytes; b += blockDim.x * esz) {
+      for (int p = 0; p < ctx.nranks; p++) {
+        if (esz == 4) *reinterpret_cast<unsigned*>(ctx.stage_peer[p] + my_off + b) = *reinterpret_cast<const unsigned*>(in + b);
+        else *reinterpret_cast<unsigned short*>(ctx.stage_peer[p] + my_off + b) = *reinterpret_cast<const unsigned short*>(in + b);
+      }
+    }
+  }
+  if (!ChannelBarrier(ctx, channel, 3, epoch, s_failed)) return;
+
+  // ---- reduce the n local copies ----
+  char* mine = ctx.stage_peer[ctx.rank];
+  char* out = static_cast<char*>(job.out) + c0 * esz;
+  if (MODE == MODE_QUANT) {
+    // One warp per block: exponent over all ranks' copies, then quantise, add, dequantise.
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+    const size_t B = ctx.block_numel;
+    const size_t nblocks = (len + B - 1) / B;
+    for (size_t b = warp; b < nblocks; b += nwarps) {
+      size_t base = b * B;
+      size_t n = len - base < B ? len - base : B;
+      float m = 0.f;
+      int e = quant::kZeroExponent;
+      for (int s = 0; s < ctx.nranks; s++) {
+        const char* src = mine + buf_off(s);
+        m = 0.f;
+        for (size_t i = lane; i < n; i += 32) {
+          float v = fabsf(LoadAsFloat<ELEM>(src, base + i));
+          if (v > m) m = v;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          float t = __shfl_xor_sync(0xffffffffu, m, o);
+          if (t > m) m = t;
+        }
+        int le = quant::LocalExponent(m);
+        if (le > e) e = le;
+      }
+      float sf = quant::ScaleFactor(e, ctx.nranks);
+      for (size_t i = lane; i < n; i += 32) {
+        unsigned acc = 0;
+        for (int s = 0; s < ctx.nranks; s++)
+          acc += static_cast<unsigned>(quant::Quantize(LoadAsFloat<ELEM>(mine + buf_off(s), base + i), sf));
+        float y = quant::Dequantize(static_cast<int>(acc), sf);
+        if (job.post_scale != 1.0f) y *= job.post_scale;
+        if (ELEM == ELEM_BF16) reinterpret_cast<unsigned short*>(out)[base + i] = FloatToBf16(y);
+        else reinterpret_cast<float*>(out)[base + i] = y;
+      }
+    }
+  } else {
+    for (size_t i = threadIdx.x; i < len; i += blockDim.x) {
+      if (ELEM == ELEM_I32) {
+        unsigned acc = 0;
+        for (int s = 0; s < ctx.nranks; s++) acc += reinterpret_cast<const unsigned*>(mine + buf_off(s))[i];
+        reinterpret_cast<unsigned*>(out)[i] = acc;
+      } else {
+        float acc = 0.f;
+        for (int s = 0; s < ctx.nranks; s++) acc += LoadAsFloat<ELEM>(mine + buf_off(s), i);
+        if (job.post_scale != 1.0f) acc *= job.post_scale;
+        if (ELEM == ELEM_BF16) reinterpret_cast<unsigned short*>(out)[i] = FloatToBf16(acc);
+        else reinterpret_cast<float*>(out)[i] = acc;
+      }
+    }
+  }
+  if (threadIdx.x == 0) atomicAdd(ctx.counters, 1ull);
+}
+
+// ------------------------------------------------------------------------------------
+template <int ELEM>
+__device__ void RunZeroCopy(const RankCtx& ctx, const JobArgs& job, int channel,
+                            unsigned long long elems_per_channel, int* s_failed) {
+  const int esz = ELEM == ELEM_BF16 ? 2 : 4;
+  const size_t vec_elems = 16 / esz;
+  const unsigned long long epoch = job.epoch_base + 1;
+  // Everybody's input must be complete before anybody reads it.
+  if (!ChannelBarrier(ctx, channel, 0, epoch, s_failed)) return;
+
+  unsigned long long c0 = static_cast<unsigned long long>(channel) * elems_per_channel;
+  unsigned long long c1 = c0 + elems_per_channel;
+  if (c1 > job.numel) c1 = job.numel;
+  if (c0 < job.numel) {
+    const size_t len = static_cast<size_t>(c1 - c0);
+    size_t sb, se;
+    ShardRange(len, ctx.nranks, ctx.rank, 128, &sb, &se);
+    // Whole vectors of my shard; the ragged end of the range (fewer than one vector, only
+    // in the last channel) is done element-wise by the rank that owns the last shard.
+    size_t full_end = se / vec_elems * vec_elems;
+    if (se < len) full_end = se;  // interior shard boundaries are multiples of 128 elements
+    const bool inplace = job.in_offset == job.out_offset;
+    size_t in_base = job.in_offset + (c0 + sb) * esz;
+    size_t out_base = job.out_offset + (c0 + sb) * esz;
+    size_t nvec = (full_end - sb) / vec_elems;
+    char* const* peers = job.user_peer;
+    size_t v = threadIdx.x;
+    for (; v + (kUnroll - 1) * blockDim.x < nvec; v += kUnroll * blockDim.x) {
+      uint4 r[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; u++)
+        r[u] = ReduceVec<ELEM>(ctx, peers, job.user_mc, in_base + (v + u * blockDim.x) * 16, job.post_scale);
+#pragma unroll
+      for (int u = 0; u < kUnroll; u++)
+        BroadcastVec(ctx, peers, job.user_mc, out_base + (v + u * blockDim.x) * 16, r[u]);
+    }
+    for (; v < nvec; v += blockDim.x) {
+      uint4 r = ReduceVec<ELEM>(ctx, peers, job.user_mc, in_base + v * 16, job.post_scale);
+      BroadcastVec(ctx, peers, job.user_mc, out_base + v * 16, r);
+    }
+    (void)inplace;
+    // Ragged end: plain peer loads and stores, element by element.
+    for (size_t i = full_end + threadIdx.x; i < se; i += blockDim.x) {
+      size_t io = job.in_offset + (c0 + i) * esz, oo = job.out_offset + (c0 + i) * esz;
+      if (ELEM == ELEM_I32) {
+        unsigned acc = 0;
+        for (int p = 0; p < ctx.nranks; p++) acc += __ldcg(reinterpret_cast<const unsigned*>(peers[p] + io));
+        for (int p = 0; p < ctx.nranks; p++) *reinterpret_cast<unsigned*>(peers[p] + oo) = acc;
+      } else if (ELEM == ELEM_F32) {
+        float acc = 0.f;
+        for (int p = 0; p < ctx.nranks; p++) acc += __ldcg(reinterpret_cast<const float*>(peers[p] + io));
+        acc *= job.post_scale;
+        for (int p = 0; p < ctx.nranks; p++) *reinterpret_cast<float*>(peers[p] + oo) = acc;
+      } else {
+        float acc = 0.f;
+        for (int p = 0; p < ctx.nranks; p++) acc += Bf16ToFloat(__ldcg(reinterpret_cast<const unsigned short*>(peers[p] + io)));
+        acc *= job.post_scale;
+        unsigned short h = FloatToBf16(acc);
+        for (int p = 0; p < ctx.nranks; p++) *reinterpret_cast<unsigned short*>(peers[p] + oo) = h;
+      }
+    }
+    if (threadIdx.x == 0) atomicAdd(ctx.counters, 1ull);
+  }
+  // Nobody may return (and let its stream touch the output) before all shards landed.
+  ChannelBarrier(ctx, channel, 1, epoch, s_failed);
+}
+
+// ------------------------------------------------------------------------------------
+template <int ELEM, int MODE, int ALGO>
+__device__ __forceinline__ void RunJob(const RankCtx& ctx, const JobArgs& job, int channel,
+                                       unsigned long long epc, int* s_failed, float* s_sf) {
+  if (ALGO == ALGO_STAGED) RunStaged<ELEM, MODE>(ctx, job, channel, epc, s_failed, s_sf);
+  else if (ALGO == ALGO_ONESHOT) RunOneShot<ELEM, MODE>(ctx, job, channel, epc, s_failed);
+  else RunZeroCopy<ELEM>(ctx, job, channel, epc, s_failed);
+}
+
+template <int ELEM, int MODE, int ALGO>
+__global__ void __launch_bounds__(kThreads)
+AllReduceKernel(const RankCtx ctx, const JobArgs job, unsigned long long epc) {
+  __shared__ int s_failed;
+  __shared__ float s_sf[(MODE == MODE_QUANT && ALGO == ALGO_STAGED) ? kMaxBlocksPerSlot : 1];
+  if (threadIdx.x == 0) s_failed = 0;
+  __syncthreads();
+  RunJob<ELEM, MODE, ALGO>(ctx, job, blockIdx.x, epc, &s_failed, s_sf);
+}
+
+// All ranks in one grid: blockIdx.y selects the rank whose role this CTA plays.
+template <int ELEM, int MODE, int ALGO>
+__global__ void __launch_bounds__(kThreads)
+AllReduceEmuKernel(const RankCtx* ctxs, const JobArgs* jobs, unsigned long long epc) {
+  __shared__ int s_failed;
+  __shared__ float s_sf[(MODE == MODE_QUANT && ALGO == ALGO_STAGED) ? kMaxBlocksPerSlot : 1];
+  __shared__ RankCtx s_ctx;
+  __shared__ JobArgs s_job;
+  if (threadIdx.x == 0) {
+    s_failed = 0;
+    s_ctx = ctxs[blockIdx.y];
+    s_job = jobs[blockIdx.y];
+  }
+  __syncthreads();
+  RunJob<ELEM, MODE, ALGO>(s_ctx, s_job, blockIdx.x, epc, &s_failed, s_sf);
+}
+
+__global__ void WaitProbeKernel(const RankCtx ctx) {
+  __shared__ int s_failed;
+  if (threadIdx.x == 0) s_failed = 0;
+  __syncthreads();
+  // Waits, without signalling, for an epoch that no job ever reaches.
+  ChannelBarrier(ctx, kMaxChannels - 1, kNumPhases - 1, ~0ull, &s_failed, false);
+}
+
+template <int ELEM, int MODE, int ALGO>
+cudaError_t LaunchOne(const RankCtx& ctx, const JobArgs& job, const LaunchPlan& plan,
+                      cudaStream_t stream) {
+  AllReduceKernel<ELEM, MODE, ALGO><<<plan.channels, kThreads, 0, stream>>>(ctx, job, plan.elems_per_channel);
+  return cudaGetLastError();
+}
+
+template <int ELEM, int MODE, int ALGO>
+cudaError_t LaunchOneEmu(const RankCtx* ctxs, const JobArgs* jobs, int nranks,
+                         const LaunchPlan& plan, cudaStream_t stream) {
+  unsigned long long epc = plan.elems_per_channel;
+  void* args[] = {&ctxs, &jobs, &epc};
+  dim3 grid(plan.channels, nranks);
+  // Cooperative launch: the runtime refuses the launch unless all CTAs can be resident
+  // together, which the cross-"rank" barriers need.
+  return cudaLaunchCooperativeKernel(reinterpret_cast<void*>(AllReduceEmuKernel<ELEM, MODE, ALGO>),
+                                     grid, dim3(kThreads), args, 0, stream);
+}
+
+#define SML_DISPATCH(FN, elem, mode, algo, ...)                                             \
+  do {                                                                                      \
+    if ((algo) == ALGO_ZEROCOPY) {                                                          \
+      if ((mode) != MODE_SUM) return cudaErrorInvalidValue;                                 \
+      if ((elem) == ELEM_F32) return FN<ELEM_F32, MODE_SUM, ALGO_ZEROCOPY>(__VA_ARGS__);    \
+      if ((elem) == ELEM_I32) return FN<ELEM_I32, MODE_SUM, ALGO_ZEROCOPY>(__VA_ARGS__);    \
+      return FN<ELEM_BF16, MODE_SUM, ALGO_ZEROCOPY>(__VA_ARGS__);                           \
+    }                                                                                       \
+    if ((elem) == ELEM_I32) {                                                               \
+      if ((algo) == ALGO_STAGED) return FN<ELEM_I32, MODE_SUM, ALGO_STAGED>(__VA_ARGS__);   \
+      return FN<ELEM_I32, MODE_SUM, ALGO_ONESHOT>(__VA_ARGS__);                             \
+    }                                                                                       \
+    if ((elem) == ELEM_F32) {                                                               \
+      if ((mode) == MODE_QUANT) {                                                           \
+        if ((algo) == ALGO_STAGED) return FN<ELEM_F32, MODE_QUANT, ALGO_STAGED>(__VA_ARGS__); \
+        return FN<ELEM_F32, MODE_QUANT, ALGO_ONESHOT>(__VA_ARGS__);                         \
+      }                                                                                     \
+      if ((algo) == ALGO_STAGED) return FN<ELEM_F32, MODE_SUM, ALGO_STAGED>(__VA_ARGS__);   \
+      return FN<ELEM_F32, MODE_SUM, ALGO_ONESHOT>(__VA_ARGS__);                             \
+    }                                                                                       \
+    if ((mode) == MODE_QUANT) {                                                             \
+      if ((algo) == ALGO_STAGED) return FN<ELEM_BF16, MODE_QUANT, ALGO_STAGED>(__VA_ARGS__); \
+      return FN<ELEM_BF16, MODE_QUANT, ALGO_ONESHOT>(__VA_ARGS__);                          \
+    }                                                                                       \
+    if ((algo) == ALGO_STAGED) return FN<ELEM_BF16, MODE_SUM, ALGO_STAGED>(__VA_ARGS__);    \
+    return FN<ELEM_BF16, MODE_SUM, ALGO_ONESHOT>(__VA_ARGS__);                              \
+  } while (0)
+
+}  // namespace
+
+size_t SlotElems(const RankCtx& ctx, int elem_type, int mode) {
+  int st_esz = mode == MODE_QUANT ? 4 : (elem_type == ELEM_BF16 ? 2 : 4);
+  return ctx.slot_bytes / st_esz;
+}
+
+size_t StagingBytes(size_t slot_bytes, int slots_per_channel, int block_numel, int max_channels,
+                    size_t oneshot_bytes, int nranks, size_t* data_offset, size_t* exp_offset,
+                    size_t* oneshot_offset) {
+  auto align = [](size_t x) { return (x + 4095) / 4096 * 4096; };
+  size_t flags = size_t(kMaxChannels) * kFlagWordsPerChannel * 8;
+  size_t off = align(flags);
+  *exp_offset = off;
+  size_t blocks_per_slot = slot_bytes / 4 / block_numel;
+  off = align(off + size_t(max_channels) * slots_per_channel * blocks_per_slot * 4);
+  *oneshot_offset = off;
+  off = align(off + 2 * size_t(nranks) * oneshot_bytes);
+  *data_offset = off;
+  off = align(off + size_t(max_channels) * slots_per_channel * slot_bytes);
+  return off;
+}
+
+LaunchPlan PlanLaunch(const RankCtx& ctx, const JobArgs& job, int requested_channels,
+                      int max_channels) {
+  LaunchPlan p;
+  const unsigned long long numel = job.numel ? job.numel : 1;
+  if (max_channels > kMaxChannels) max_channels = kMaxChannels;
+  if (job.algo == ALGO_STAGED) {
+    size_t slot_elems = SlotElems(ctx, job.elem_type, job.mode);
+    unsigned long long tiles = (numel + slot_elems - 1) / slot_elems;
+    int ch = requested_channels > 0 ? requested_channels : max_channels;
+    if (ch > max_channels) ch = max_channels;
+    if (static_cast<unsigned long long>(ch) > tiles) ch = static_cast<int>(tiles);
+    unsigned long long tiles_per_channel = (tiles + ch - 1) / ch;
+    p.elems_per_channel = tiles_per_channel * slot_elems;
+    p.channels = static_cast<int>((numel + p.elems_per_channel - 1) / p.elems_per_channel);
+    p.epochs = static_cast<unsigned>(tiles_per_channel);
+    p.tiles = tiles;
+  } else if (job.algo == ALGO_ONESHOT) {
+    // Whole quantisation blocks per channel; a few CTAs are enough for small messages.
+    unsigned long long unit = ctx.block_numel > 128 ? ctx.block_numel : 128;
+    unsigned long long units = (numel + unit - 1) / unit;
+    int ch = requested_channels > 0 ? requested_channels : 8;
+    if (ch > max_channels) ch = max_channels;
+    unsigned long long per = (units + ch - 1) / ch;
+    if (per < 8) per = 8;  // at least 8 units (>= 4 KiB of f32) per CTA
+    p.elems_per_channel = per * unit;
+    p.channels = static_cast<int>((numel + p.elems_per_channel - 1) / p.elems_per_channel);
+    p.epochs = 1;
+    p.tiles = p.channels;
+  } else {
+    // Ranges are multiples of nranks*128 elements so that interior shard boundaries stay
+    // vector aligned.
+    unsigned long long unit = 128ull * ctx.nranks;
+    unsigned long long units = (numel + unit - 1) / unit;
+    int ch = requested_channels > 0 ? requested_channels : max_channels;
+    if (ch > max_channels) ch = max_channels;
+    unsigned long long per = (units + ch - 1) / ch;
+    unsigned long long min_per = (64 * 1024) / (128 * 4);  // >= 64 KiB per shard-range
+    if (per < min_per) per = min_per;
+    p.elems_per_channel = per * unit;
+    p.channels = static_cast<int>((numel + p.elems_per_channel - 1) / p.elems_per_channel);
+    p.epochs = 1;
+    p.tiles = p.channels;
+  }
+  if (p.channels < 1) p.channels = 1;
+  return p;
+}
+
+cudaError_t LaunchAllReduce(const RankCtx& ctx, const JobArgs& job, const LaunchPlan& plan,
+                            cudaStream_t stream) {
+  if (ctx.nranks < 1 || ctx.nranks > kMaxRanks || plan.channels > kMaxChannels)
+    return cudaErrorInvalidValue;
+  SML_DISPATCH(LaunchOne, job.elem_type, job.mode, job.algo, ctx, job, plan, stream);
+}
+
+cudaError_t LaunchAllReduceEmulated(const RankCtx* ctxs_dev, const JobArgs* jobs_dev,
+                                    const JobArgs& job0, int nranks, const LaunchPlan& plan,
+                                    cudaStream_t stream) {
+  if (nranks < 1 || nranks > kMaxRanks || plan.channels > kMaxChannels) return cudaErrorInvalidValue;
+  SML_DISPATCH(LaunchOneEmu, job0.elem_type, job0.mode, job0.algo, ctxs_dev, jobs_dev, nranks, plan, stream);
+}
+
+cudaError_t LaunchWaitProbe(const RankCtx& ctx, cudaStream_t stream) {
+  WaitProbeKernel<<<1, 32, 0, stream>>>(ctx);
+  return cudaGetLastError();
+}
+
+}  // namespace kernels
+}  // namespace switchml

@@ -1,0 +1,110 @@
+// Host-side interface of the aggregation kernels (sm_100a).
+//
+// One launch = one allreduce job on one rank. All ranks launch the same kernel with the
+// same geometry; the kernels meet through flags in symmetric memory (device_sync.cuh).
+// The kernels stand in for the reference's worker hot loops + prepostprocessor + switch
+// pipeline: quantise (cpu_exponent_quantizer_ppp.cc:88-156), exponent max
+// (p4/exponents.p4:48-54), integer add (p4/processor.p4:48-54), multicast of the result
+// (p4/next_step_selector.p4:118-129), dequantise (cpu_exponent_quantizer_ppp.cc:200-260),
+// streamed through a ring of staging slots like the switch's slot pool.
+#ifndef SWITCHML_ALLREDUCE_KERNELS_H_
+#define SWITCHML_ALLREDUCE_KERNELS_H_
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace switchml {
+namespace kernels {
+
+static const int kMaxRanks = 8;
+static const int kMaxChannels = 512;
+static const int kNumPhases = 4;
+static const int kThreads = 512;            // threads per CTA of every aggregation kernel
+static const int kFlagWordsPerChannel = kNumPhases * kMaxRanks;
+// Layout of a rank's symmetric staging region (byte offsets from its base).
+static const size_t kFlagBytes = size_t(kMaxChannels) * kFlagWordsPerChannel * 8;  // 128 KiB of 64-bit epochs
+
+enum ElemType : int { ELEM_F32 = 0, ELEM_I32 = 1, ELEM_BF16 = 2 };
+enum ReduceMode : int {
+  MODE_SUM = 0,    // float add in f32 (bf16 inputs accumulate in f32) / wrapping int add
+  MODE_QUANT = 1,  // per-block exponent fixed point: exact, order-independent integer sum
+};
+enum Algo : int {
+  ALGO_STAGED = 0,    // copy-in, shard reduce, copy-out through the slot ring (any pointers)
+  ALGO_ONESHOT = 1,   // push inputs to every rank, one barrier, reduce locally (small messages)
+  ALGO_ZEROCOPY = 2,  // tensors live in symmetric memory: reduce in place, no staging (SUM only)
+};
+enum Status : int {
+  STATUS_OK = 0,
+  STATUS_TIMEOUT = 1,  // a bounded wait ran out; bits 8.. hold the channel, 4..7 the phase
+  STATUS_BAD_ARGS = 2,
+};
+
+// What a rank's kernel needs to reach its peers. Passed by value.
+struct RankCtx {
+  int rank;
+  int nranks;
+  int use_multimem;              // 1: reduce/broadcast through the multicast mapping
+  char* stage_peer[kMaxRanks];   // every rank's staging region as mapped here ([rank] = own)
+  char* stage_mc;                // multicast mapping of the staging regions (or nullptr)
+  size_t data_offset;            // start of the data slots inside the region
+  size_t exp_offset;             // start of the exponent slots
+  size_t oneshot_offset;         // start of the one-shot buffers
+  size_t slot_bytes;             // bytes of one data slot
+  int slots_per_channel;
+  int block_numel;               // quantisation block (= packet_numel)
+  size_t oneshot_bytes;          // capacity of one rank's one-shot buffer (per parity)
+  unsigned long long timeout_ns; // budget of every wait
+  int* status;                   // device-visible status word (0 = ok)
+  unsigned long long* counters;  // [0] tiles processed, [1] wait iterations, [2] timeouts
+};
+
+struct JobArgs {
+  const void* in;
+  void* out;
+  unsigned long long numel;
+  int elem_type;     // ElemType
+  int mode;          // ReduceMode
+  int algo;          // Algo
+  float post_scale;  // multiplied into the result (1/num_workers for averaging)
+  unsigned long long epoch_base;  // flags written by this job are epoch_base+1 .. epoch_base+epochs
+  int oneshot_parity;
+  // ALGO_ZEROCOPY: offsets of in/out inside the symmetric user region and its mappings
+  char* user_peer[kMaxRanks];
+  char* user_mc;
+  size_t in_offset, out_offset;
+};
+
+// Geometry chosen on the host; identical on every rank for the same job.
+struct LaunchPlan {
+  int channels;            // CTAs
+  unsigned epochs;         // how far the job advances the epoch counter
+  unsigned long long elems_per_channel;  // contiguous range of each channel (last may be short)
+  unsigned long long tiles;              // staged tiles summed over channels (stats)
+};
+
+// Number of elements of a slot for this element type / mode.
+size_t SlotElems(const RankCtx& ctx, int elem_type, int mode);
+// Bytes a staging region must have for `channels` channels.
+size_t StagingBytes(size_t slot_bytes, int slots_per_channel, int block_numel, int max_channels,
+                    size_t oneshot_bytes, int nranks, size_t* data_offset, size_t* exp_offset,
+                    size_t* oneshot_offset);
+LaunchPlan PlanLaunch(const RankCtx& ctx, const JobArgs& job, int requested_channels,
+                      int max_channels);
+// Enqueue the job on `stream`. Returns cudaSuccess or the launch error.
+cudaError_t LaunchAllReduce(const RankCtx& ctx, const JobArgs& job, const LaunchPlan& plan,
+                            cudaStream_t stream);
+// Single-GPU emulation of `nranks` ranks: one cooperative launch whose blockIdx.y is the
+// rank, every "peer" region living on the same device. `ctxs`/`jobs` are device arrays
+// of length nranks. Exercises the peer-memory code path bit for bit.
+// `job0` is the host copy of jobs_dev[0] (selects the instantiation).
+cudaError_t LaunchAllReduceEmulated(const RankCtx* ctxs_dev, const JobArgs* jobs_dev,
+                                    const JobArgs& job0, int nranks, const LaunchPlan& plan,
+                                    cudaStream_t stream);
+// A kernel whose only job is to wait for a flag nobody sets: checks that a bounded wait
+// gives up, reports STATUS_TIMEOUT and leaves the context usable.
+cudaError_t LaunchWaitProbe(const RankCtx& ctx, cudaStream_t stream);
+
+}  // namespace kernels
+}  // namespace switchml
+#endif  // SWITCHML_ALLREDUCE_KERNELS_H_

@@ -1,0 +1,455 @@
+// See control.h.
+#include "rendezvous/control.h"
+
+#include <arpa/inet.h>
+#include <errno.h>
+#include <netinet/in.h>
+#include <netinet/tcp.h>
+#include <poll.h>
+#include <sys/socket.h>
+#include <unistd.h>
+
+#include <chrono>
+#include <cstring>
+#include <sstream>
+
+#include "switchml/log.h"
+
+namespace switchml {
+
+std::string HexEncode(const std::string& raw) {
+  static const char* d = "0123456789abcdef";
+  std::string o;
+  o.reserve(raw.size() * 2 + 1);
+  for (unsigned char c : raw) {
+    o.push_back(d[c >> 4]);
+    o.push_back(d[c & 15]);
+  }
+  if (o.empty()) o = "-";
+  return o;
+}
+
+std::string HexDecode(const std::string& hex) {
+  std::string o;
+  if (hex == "-") return o;
+  auto v = [](char c) { return c <= '9' ? c - '0' : c - 'a' + 10; };
+  for (size_t i = 0; i + 1 < hex.size(); i += 2) o.push_back(static_cast<char>(v(hex[i]) << 4 | v(hex[i + 1])));
+  return o;
+}
+
+namespace {
+
+bool WriteAll(int fd, const std::string& s) {
+  size_t off = 0;
+  while (off < s.size()) {
+    ssize_t n = send(fd, s.data() + off, s.size() - off, MSG_NOSIGNAL);
+    if (n <= 0) {
+      if (n < 0 && errno == EINTR) continue;
+      return false;
+    }
+    off += static_cast<size_t>(n);
+  }
+  return true;
+}
+
+// Reads up to and excluding '\n'. `buf` keeps bytes beyond the line for the next call.
+bool ReadLine(int fd, std::string* buf, std::string* line, const std::atomic<bool>* stop) {
+  for (;;) {
+    size_t nl = buf->find('\n');
+    if (nl != std::string::npos) {
+      *line = buf->substr(0, nl);
+      buf->erase(0, nl + 1);
+      return true;
+    }
+    struct pollfd p = {fd, POLLIN, 0};
+    int r = poll(&p, 1, 200);
+    if (stop && stop->load()) return false;
+    if (r < 0 && errno != EINTR) return false;
+    if (r <= 0) continue;
+    char tmp[4096];
+    ssize_t n = recv(fd, tmp, sizeof(tmp), 0);
+    if (n == 0) return false;
+    if (n < 0) {
+      if (errno == EINTR || errno == EAGAIN) continue;
+      return false;
+    }
+    buf->append(tmp, static_cast<size_t>(n));
+  }
+}
+
+}  // namespace
+
+ControlServer::ControlServer() { memset(learned_, 0, sizeof(learned_)); }
+ControlServer::~ControlServer() { Stop(); }
+
+bool ControlServer::Start(const std::string& ip, uint16_t port, uint16_t udp_port) {
+  listen_fd_ = socket(AF_INET, SOCK_STREAM, 0);
+  if (listen_fd_ < 0) return false;
+  int one = 1;
+  setsockopt(listen_fd_, SOL_SOCKET, SO_REUSEADDR, &one, sizeof(one));
+  sockaddr_in a;
+  memset(&a, 0, sizeof(a));
+  a.sin_family = AF_INET;
+  a.sin_port = htons(port);
+  if (inet_pton(AF_INET, ip.c_str(), &a.sin_addr) != 1) a.sin_addr.s_addr = htonl(INADDR_ANY);
+  if (bind(listen_fd_, reinterpret_cast<sockaddr*>(&a), sizeof(a)) != 0 ||
+      listen(listen_fd_, 64) != 0) {
+    SML_LOG(ERROR) << "control server: cannot listen on " << ip << ":" << port << ": "
+                   << strerror(errno);
+    close(listen_fd_);
+    listen_fd_ = -1;
+    return false;
+  }
+  socklen_t al = sizeof(a);
+  getsockname(listen_fd_, reinterpret_cast<sockaddr*>(&a), &al);
+  port_ = ntohs(a.sin_port);
+
+  if (udp_port) {
+    udp_fd_ = socket(AF_INET, SOCK_DGRAM, 0);
+    sockaddr_in u;
+    memset(&u, 0, sizeof(u));
+    u.sin_family = AF_INET;
+    u.sin_port = htons(udp_port);
+    if (inet_pton(AF_INET, ip.c_str(), &u.sin_addr) != 1) u.sin_addr.s_addr = htonl(INADDR_ANY);
+    int big = 8 << 20;
+    setsockopt(udp_fd_, SOL_SOCKET, SO_RCVBUF, &big, sizeof(big));
+    setsockopt(udp_fd_, SOL_SOCKET, SO_SNDBUF, &big, sizeof(big));
+    if (udp_fd_ < 0 || bind(udp_fd_, reinterpret_cast<sockaddr*>(&u), sizeof(u)) != 0) {
+      SML_LOG(ERROR) << "software switch: cannot bind UDP port " << udp_port << ": "
+                     << strerror(errno);
+      if (udp_fd_ >= 0) close(udp_fd_);
+      udp_fd_ = -1;
+      close(listen_fd_);
+      listen_fd_ = -1;
+      return false;
+    }
+    al = sizeof(u);
+    getsockname(udp_fd_, reinterpret_cast<sockaddr*>(&u), &al);
+    udp_port_ = ntohs(u.sin_port);
+    data_thread_ = std::thread(&ControlServer::DataPlaneLoop, this);
+  }
+  stopping_ = false;
+  accept_thread_ = std::thread(&ControlServer::AcceptLoop, this);
+  SML_VLOG(1) << "control server listening on " << ip << ":" << port_
+              << (udp_port_ ? " (software switch on UDP " + std::to_string(udp_port_) + ")" : "");
+  return true;
+}
+
+void ControlServer::Stop() {
+  if (listen_fd_ < 0 && udp_fd_ < 0) return;
+  stopping_ = true;
+  {
+    // Release anybody blocked in a collective.
+    std::lock_guard<std::mutex> lk(coll_mu_);
+    for (auto& kv : collectives_) {
+      std::lock_guard<std::mutex> cl(kv.second->mu);
+      kv.second->cv.notify_all();
+    }
+  }
+  if (accept_thread_.joinable()) accept_thread_.join();
+  if (data_thread_.joinable()) data_thread_.join();
+  std::vector<std::thread> threads;
+  {
+    std::lock_guard<std::mutex> lk(conn_mu_);
+    for (int fd : conn_fds_) shutdown(fd, SHUT_RDWR);
+    threads.swap(conn_threads_);
+  }
+  for (auto& t : threads) t.join();
+  if (listen_fd_ >= 0) close(listen_fd_);
+  if (udp_fd_ >= 0) close(udp_fd_);
+  listen_fd_ = udp_fd_ = -1;
+}
+
+void ControlServer::AcceptLoop() {
+  while (!stopping_) {
+    struct pollfd p = {listen_fd_, POLLIN, 0};
+    int r = poll(&p, 1, 200);
+    if (r <= 0) continue;
+    int fd = accept(listen_fd_, nullptr, nullptr);
+    if (fd < 0) continue;
+    int one = 1;
+    setsockopt(fd, IPPROTO_TCP, TCP_NODELAY, &one, sizeof(one));
+    std::lock_guard<std::mutex> lk(conn_mu_);
+    conn_fds_.push_back(fd);
+    conn_threads_.emplace_back(&ControlServer::Serve, this, fd);
+  }
+}
+
+void ControlServer::Serve(int fd) {
+  std::string buf, line;
+  while (!stopping_ && ReadLine(fd, &buf, &line, &stopping_)) {
+    std::string reply;
+    try {
+      reply = Handle(line);
+    } catch (const std::exception& e) {
+      reply = std::string("ERR ") + e.what();
+    }
+    if (!WriteAll(fd, reply + "\n")) break;
+  }
+  close(fd);
+  std::lock_guard<std::mutex> lk(conn_mu_);
+  for (int& f : conn_fds_) {
+    if (f == fd) f = -1;
+  }
+}
+
+bool ControlServer::Collect(const std::string& name, int n, int rank, const std::string& token,
+                            std::vector<std::string>* all) {
+  Collective* c;
+  {
+    std::lock_guard<std::mutex> lk(coll_mu_);
+    auto& slot = collectives_[name + "/" + std::to_string(n)];
+    if (!slot) slot.reset(new Collective());
+    c = slot.get();
+  }
+  std::unique_lock<std::mutex> lk(c->mu);
+  if (c->tokens.size() != static_cast<size_t>(n)) c->tokens.assign(n, "");
+  if (rank < 0 || rank >= n) return false;
+  c->tokens[rank] = token;
+  uint64_t gen = c->generation;
+  if (++c->arrived == n) {
+    c->arrived = 0;
+    c->last_tokens = c->tokens;
+    c->tokens.assign(n, "");
+    c->generation++;
+    c->cv.notify_all();
+  } else {
+    c->cv.wait(lk, [&] { return c->generation != gen || stopping_.load(); });
+    if (c->generation == gen) return false;
+  }
+  *all = c->last_tokens;
+  return true;
+}
+
+std::string ControlServer::Handle(const std::string& line) {
+  std::istringstream in(line);
+  std::string cmd;
+  in >> cmd;
+  if (cmd == "BARRIER") {
+    int n = 0;
+    in >> n;
+    static std::atomic<int> anon{0};
+    (void)anon;
+    // Barrier callers are anonymous: give each arrival a distinct pseudo-rank.
+    Collective* c;
+    {
+      std::lock_guard<std::mutex> lk(coll_mu_);
+      auto& slot = collectives_["barrier/" + std::to_string(n)];
+      if (!slot) slot.reset(new Collective());
+      c = slot.get();
+    }
+    std::unique_lock<std::mutex> lk(c->mu);
+    uint64_t gen = c->generation;
+    if (++c->arrived >= n) {
+      c->arrived = 0;
+      c->generation++;
+      c->cv.notify_all();
+    } else {
+      c->cv.wait(lk, [&] { return c->generation != gen || stopping_.load(); });
+      if (c->generation == gen) return "ERR server stopping";
+    }
+    return "OK";
+  }
+  if (cmd == "BCAST") {
+    int n = 0, rank = 0, root = 0;
+    uint64_t v = 0;
+    in >> n >> rank >> root >> v;
+    std::vector<std::string> all;
+    if (root < 0 || root >= n || !Collect("bcast", n, rank, std::to_string(v), &all))
+      return "ERR broadcast failed";
+    return "OK " + all[root];
+  }
+  if (cmd == "GATHER") {
+    int n = 0, rank = 0;
+    std::string tok;
+    in >> n >> rank >> tok;
+    std::vector<std::string> all;
+    if (!Collect("gather", n, rank, tok, &all)) return "ERR gather failed";
+    std::string r = "OK";
+    for (auto& t : all) r += " " + t;
+    return r;
+  }
+  if (cmd == "UDPSESSION") {
+    uint64_t session = 0;
+    int rank = 0, n = 0, packet_numel = 0, nthreads = 0;
+    std::string ip;
+    unsigned port0 = 0;
+    in >> session >> rank >> n >> packet_numel >> ip >> port0 >> nthreads;
+    if (udp_fd_ < 0) return "ERR no software switch in this server";
+    if (n < 1 || n > kMaxWorkers || rank < 0 || rank >= n) return "ERR bad rank or num_workers";
+    if (packet_numel < 1 || packet_numel > kMaxPacketNumel) return "ERR bad packet_numel";
+    // Rank 0 opens the session and wipes the switch; the others join afterwards (the
+    // caller orders this with barriers, like the reference dpdk_backend.cc:95-128).
+    if (rank == 0) switch_.Reset(session, n, packet_numel);
+    if (switch_.session_id() != session) return "ERR unknown session";
+    if (!switch_.AddWorker(rank)) return "ERR cannot add worker";
+    (void)ip; (void)port0; (void)nthreads;  // return addresses are learned from the data packets
+    return "OK " + std::to_string(udp_port_);
+  }
+  if (cmd == "SHOW") {
+    std::string what;
+    in >> what;
+    std::string text;
+    if (what == "workers") text = switch_.DescribeWorkers();
+    else if (what == "statistics") text = switch_.DescribeStatistics();
+    else if (what == "drop") {
+      double i, e;
+      switch_.GetDropProbabilities(&i, &e);
+      text = "ingress " + std::to_string(i) + " egress " + std::to_string(e) + "\n";
+    } else if (what == "bitmap") {
+      uint32_t slot = 0;
+      in >> slot;
+      text = "slot " + std::to_string(slot) + " set0 " + std::to_string(switch_.Bitmap(slot, 0)) +
+             " set1 " + std::to_string(switch_.Bitmap(slot, 1)) + "\n";
+    } else return "ERR unknown table";
+    return "OK " + HexEncode(text);
+  }
+  if (cmd == "SET") {
+    std::string what;
+    in >> what;
+    if (what != "drop") return "ERR unknown setting";
+    double i = 0, e = 0;
+    uint64_t seed = 0;
+    in >> i >> e >> seed;
+    switch_.SetDropProbabilities(i, e, seed);
+    return "OK";
+  }
+  if (cmd == "RESET") {
+    switch_.Reset(0, 0, 0);
+    return "OK";
+  }
+  if (cmd == "PING") return "OK";
+  return "ERR unknown command '" + cmd + "'";
+}
+
+void ControlServer::DataPlaneLoop() {
+  std::vector<uint8_t> buf(kWireMaxBytes + 64);
+  std::vector<SwitchOutput> out;
+  while (!stopping_) {
+    struct pollfd p = {udp_fd_, POLLIN, 0};
+    int r = poll(&p, 1, 100);
+    if (r <= 0) continue;
+    for (int burst = 0; burst < 64; burst++) {
+      sockaddr_in src;
+      socklen_t sl = sizeof(src);
+      ssize_t n = recvfrom(udp_fd_, buf.data(), buf.size(), MSG_DONTWAIT,
+                           reinterpret_cast<sockaddr*>(&src), &sl);
+      if (n <= 0) break;
+      if (static_cast<size_t>(n) >= sizeof(WireHeader)) {
+        // Learn where this worker thread listens, like a switch learns a port.
+        WireHeader h;
+        memcpy(&h, buf.data(), sizeof(h));
+        int w = ntohs(h.worker_id);
+        if (ntohl(h.magic) == kWireMagic && w < kMaxWorkers && h.thread_id < kMaxThreads) {
+          learned_[w][h.thread_id] = src;
+        }
+      }
+      out.clear();
+      switch_.Process(buf.data(), static_cast<size_t>(n), &out);
+      for (const SwitchOutput& o : out) {
+        const sockaddr_in& d = learned_[o.dest_worker][o.dest_thread];
+        if (d.sin_port == 0) continue;
+        sendto(udp_fd_, o.bytes.data(), o.bytes.size(), 0,
+               reinterpret_cast<const sockaddr*>(&d), sizeof(d));
+      }
+    }
+  }
+}
+
+// ----------------------------------------------------------------------------------------
+
+ControlClient::ControlClient() {}
+ControlClient::~ControlClient() { Close(); }
+
+bool ControlClient::Connect(const std::string& ip, uint16_t port, int timeout_ms) {
+  auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms);
+  for (;;) {
+    int fd = socket(AF_INET, SOCK_STREAM, 0);
+    sockaddr_in a;
+    memset(&a, 0, sizeof(a));
+    a.sin_family = AF_INET;
+    a.sin_port = htons(port);
+    inet_pton(AF_INET, ip.c_str(), &a.sin_addr);
+    if (fd >= 0 && connect(fd, reinterpret_cast<sockaddr*>(&a), sizeof(a)) == 0) {
+      int one = 1;
+      setsockopt(fd, IPPROTO_TCP, TCP_NODELAY, &one, sizeof(one));
+      fd_ = fd;
+      return true;
+    }
+    if (fd >= 0) close(fd);
+    if (std::chrono::steady_clock::now() > deadline) {
+      SML_LOG(ERROR) << "cannot reach the controller at " << ip << ":" << port;
+      return false;
+    }
+    usleep(50 * 1000);
+  }
+}
+
+void ControlClient::Close() {
+  if (fd_ >= 0) close(fd_);
+  fd_ = -1;
+}
+
+bool ControlClient::RoundTrip(const std::string& line, std::string* reply) {
+  std::lock_guard<std::mutex> lk(mu_);
+  if (fd_ < 0) return false;
+  if (!WriteAll(fd_, line + "\n")) return false;
+  std::string r;
+  if (!ReadLine(fd_, &rbuf_, &r, nullptr)) return false;
+  if (r.compare(0, 2, "OK") != 0) {
+    SML_LOG(ERROR) << "controller replied: " << r << " (to '" << line.substr(0, 60) << "')";
+    return false;
+  }
+  *reply = r.size() > 3 ? r.substr(3) : "";
+  return true;
+}
+
+bool ControlClient::Barrier(int n) {
+  std::string r;
+  return RoundTrip("BARRIER " + std::to_string(n), &r);
+}
+
+bool ControlClient::Broadcast(int n, int rank, int root, uint64_t* value) {
+  std::string r;
+  if (!RoundTrip("BCAST " + std::to_string(n) + " " + std::to_string(rank) + " " +
+                     std::to_string(root) + " " + std::to_string(*value), &r))
+    return false;
+  *value = strtoull(r.c_str(), nullptr, 10);
+  return true;
+}
+
+bool ControlClient::AllGather(int n, int rank, const std::string& token,
+                              std::vector<std::string>* all) {
+  std::string r;
+  if (!RoundTrip("GATHER " + std::to_string(n) + " " + std::to_string(rank) + " " + token, &r))
+    return false;
+  std::istringstream in(r);
+  all->clear();
+  std::string t;
+  while (in >> t) all->push_back(t);
+  return all->size() == static_cast<size_t>(n);
+}
+
+bool ControlClient::CreateUdpSession(uint64_t session_id, int rank, int num_workers,
+                                     int packet_numel, const std::string& my_ip, uint16_t port0,
+                                     int nthreads, std::string* switch_ip,
+                                     uint16_t* switch_udp_port) {
+  std::ostringstream o;
+  o << "UDPSESSION " << session_id << " " << rank << " " << num_workers << " " << packet_numel
+    << " " << my_ip << " " << port0 << " " << nthreads;
+  std::string r;
+  if (!RoundTrip(o.str(), &r)) return false;
+  (void)switch_ip;
+  *switch_udp_port = static_cast<uint16_t>(atoi(r.c_str()));
+  return true;
+}
+
+bool ControlClient::Command(const std::string& line, std::string* reply) {
+  std::string r;
+  if (!RoundTrip(line, &r)) return false;
+  if (line.compare(0, 4, "SHOW") == 0) r = HexDecode(r);
+  *reply = r;
+  return true;
+}
+
+}  // namespace switchml

@@ -1,0 +1,340 @@
+// Native unit tests of the host-side building blocks. Prints one line per test and exits
+// non-zero on the first failure; run by tests/test_native_core.py.
+#include <arpa/inet.h>
+
+#include <atomic>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <thread>
+#include <vector>
+
+#include "backends/softswitch/soft_switch.h"
+#include "backends/timeout_queue.h"
+#include "ppp/cpu_exponent_quantizer_ppp.h"
+#include "rendezvous/control.h"
+#include "switchml/context.h"
+#include "switchml/log.h"
+#include "switchml/quant_math.h"
+#include "switchml/scheduler.h"
+#include "switchml/utils.h"
+
+using namespace switchml;
+
+static int g_failures = 0;
+#define EXPECT(cond)                                                         \
+  do {                                                                       \
+    if (!(cond)) {                                                           \
+      printf("  FAILED %s:%d: %s\n", __FILE__, __LINE__, #cond);             \
+      g_failures++;                                                          \
+    }                                                                        \
+  } while (0)
+
+static void TestStaticSlice() {
+  // 10 elements over 4 threads: 3,3,2,2 at offsets 0,3,6,8 (remainder to the first threads)
+  Numel off, len;
+  Numel want_off[] = {0, 3, 6, 8}, want_len[] = {3, 3, 2, 2};
+  for (int i = 0; i < 4; i++) {
+    StaticSlice(10, 4, i, &off, &len);
+    EXPECT(off == want_off[i] && len == want_len[i]);
+  }
+  Numel total = 0;
+  for (int i = 0; i < 7; i++) {
+    StaticSlice(1000003, 7, i, &off, &len);
+    EXPECT(off == total);
+    total += len;
+  }
+  EXPECT(total == 1000003);
+  StaticSlice(2, 4, 3, &off, &len);
+  EXPECT(len == 0);
+}
+
+static void TestBarrier() {
+  const int n = 4, rounds = 50;
+  Barrier b(n);
+  std::atomic<int> counter{0};
+  std::atomic<int> errors{0};
+  std::vector<std::thread> th;
+  for (int t = 0; t < n; t++) {
+    th.emplace_back([&] {
+      for (int r = 0; r < rounds; r++) {
+        counter++;
+        if (!b.Wait()) errors++;
+        if (counter.load() < (r + 1) * n) errors++;
+        if (!b.Wait()) errors++;
+      }
+    });
+  }
+  for (auto& t : th) t.join();
+  EXPECT(errors == 0);
+  // Destroy releases waiters and poisons the barrier.
+  Barrier d(2);
+  std::thread w([&] { EXPECT(!d.Wait()); });
+  std::this_thread::sleep_for(std::chrono::milliseconds(20));
+  d.Destroy();
+  w.join();
+  EXPECT(!d.Wait());
+}
+
+static void TestJobFsm() {
+  Tensor t;
+  ExtraJobInfo x;
+  x.allreduce_operation = SUM;
+  Job j(t, ALLREDUCE, x);
+  Job j2(t, ALLREDUCE, x);
+  EXPECT(j2.id_ == j.id_ + 1);
+  EXPECT(j.GetJobStatus() == INIT);
+  j.SetJobStatus(QUEUED);
+  j.SetJobStatus(RUNNING);
+  bool threw = false;
+  try { j.SetJobStatus(QUEUED); } catch (const FatalError&) { threw = true; }
+  EXPECT(threw);
+  EXPECT(!j.WaitToCompleteFor(5));
+  std::thread fin([&] { j.SetJobStatus(FINISHED); });
+  j.WaitToComplete();
+  fin.join();
+  threw = false;
+  try { j.SetJobStatus(FAILED); } catch (const FatalError&) { threw = true; }
+  EXPECT(threw);
+}
+
+static void TestTimeoutQueue() {
+  typedef TimeoutQueue::TimePoint TP;
+  TP t0 = std::chrono::steady_clock::now();
+  auto at = [&](int ms) { return t0 + std::chrono::milliseconds(ms); };
+  TimeoutQueue q(4, 10.0, 2, 2);
+  EXPECT(q.Check(at(100)) == -1);
+  q.Push(0, at(0));
+  q.Push(1, at(1));
+  q.Push(2, at(2));
+  EXPECT(q.Check(at(5)) == -1);
+  EXPECT(q.Check(at(10)) == 0);      // oldest first
+  q.Push(0, at(10));                  // retransmitted: becomes the youngest
+  EXPECT(q.Check(at(11)) == 1);      // second timeout: threshold reached, timeout doubles
+  EXPECT(std::fabs(q.timeout_ms() - 20.0) < 1e-9);
+  q.Remove(1);
+  EXPECT(q.Check(at(12)) == -1);     // entry 2 is 10 ms old, budget is now 20
+  EXPECT(q.Check(at(22)) == 2);
+  q.Remove(2);
+  q.Remove(0);
+  EXPECT(q.Empty());
+  EXPECT(q.timeouts() == 3);
+}
+
+static std::vector<uint8_t> MakePacket(int worker, uint16_t pool_index, uint32_t pkt_id, int8_t exp,
+                                       const std::vector<int32_t>& v, uint64_t session) {
+  std::vector<uint8_t> b(sizeof(WireHeader) + v.size() * 4);
+  WireHeader h;
+  h.magic = htonl(kWireMagic);
+  h.type = WIRE_DATA;
+  h.job_tag = 7;
+  h.worker_id = htons(static_cast<uint16_t>(worker));
+  h.pkt_id = htonl(pkt_id);
+  h.pool_index = htons(pool_index);
+  h.numel = htons(static_cast<uint16_t>(v.size()));
+  h.exponent = exp;
+  h.thread_id = 0;
+  h.session_lo = htons(static_cast<uint16_t>(session));
+  memcpy(b.data(), &h, sizeof(h));
+  for (size_t i = 0; i < v.size(); i++) {
+    uint32_t be = htonl(static_cast<uint32_t>(v[i]));
+    memcpy(b.data() + sizeof(h) + 4 * i, &be, 4);
+  }
+  return b;
+}
+
+static int32_t PayloadAt(const SwitchOutput& o, int i) {
+  uint32_t be;
+  memcpy(&be, o.bytes.data() + sizeof(WireHeader) + 4 * i, 4);
+  return static_cast<int32_t>(ntohl(be));
+}
+
+static void TestSoftSwitch() {
+  SoftSwitch sw(64);
+  sw.Reset(42, 3, 4);
+  for (int w = 0; w < 3; w++) EXPECT(sw.AddWorker(w));
+  EXPECT(!sw.AddWorker(3));
+  std::vector<SwitchOutput> out;
+  auto send = [&](int w, uint16_t idx, uint32_t id, int8_t e, std::vector<int32_t> v) {
+    auto p = MakePacket(w, idx, id, e, v, 42);
+    sw.Process(p.data(), p.size(), &out);
+  };
+  // Two of three workers: nothing comes out yet.
+  send(0, 5, 100, -3, {1, 2, 3, 4});
+  send(1, 5, 100, 2, {10, 20, 30, 2147483647});
+  EXPECT(out.empty());
+  EXPECT(sw.Bitmap(5, 0) == 0x3);
+  // A duplicate of worker 0 while the slot is still open is ignored.
+  send(0, 5, 100, -3, {1, 2, 3, 4});
+  EXPECT(out.empty());
+  // Third worker completes the slot: multicast to all three, exponent = max, wrapping add.
+  send(2, 5, 100, 0, {100, 200, 300, 1});
+  EXPECT(out.size() == 3);
+  if (out.size() == 3) {
+    WireHeader h;
+    memcpy(&h, out[1].bytes.data(), sizeof(h));
+    EXPECT(h.type == WIRE_RESULT && h.exponent == 2 && ntohl(h.pkt_id) == 100 && h.job_tag == 7);
+    EXPECT(out[1].dest_worker == 1);
+    EXPECT(PayloadAt(out[0], 0) == 111 && PayloadAt(out[0], 2) == 333);
+    EXPECT(PayloadAt(out[0], 3) == static_cast<int32_t>(2147483647u + 4u + 1u));  // wrapped
+  }
+  // A retransmission to the finished slot is answered to that worker only.
+  out.clear();
+  send(1, 5, 100, 2, {10, 20, 30, 40});
+  EXPECT(out.size() == 1 && out[0].dest_worker == 1);
+  if (!out.empty()) {
+    WireHeader h;
+    memcpy(&h, out[0].bytes.data(), sizeof(h));
+    EXPECT(h.type == WIRE_RESULT_RETX);
+    EXPECT(PayloadAt(out[0], 0) == 111);
+  }
+  // Using the other set acknowledges this one (bits cleared one worker at a time).
+  out.clear();
+  send(0, 5 | kSetBit, 164, 0, {1, 1, 1, 1});
+  EXPECT(sw.Bitmap(5, 0) == 0x6 && sw.Bitmap(5, 1) == 0x1);
+  send(1, 5 | kSetBit, 164, 0, {1, 1, 1, 1});
+  send(2, 5 | kSetBit, 164, 0, {1, 1, 1, 1});
+  EXPECT(out.size() == 3 && sw.Bitmap(5, 0) == 0);
+  // Set 0 is free again: a new first packet overwrites instead of adding.
+  out.clear();
+  send(2, 5, 228, 1, {7, 7, 7, 7});
+  send(0, 5, 228, 1, {1, 1, 1, 1});
+  send(1, 5, 228, 1, {1, 1, 1, 1});
+  EXPECT(out.size() == 3 && PayloadAt(out[0], 0) == 9);
+  // Wrong session, unknown worker, short packet: counted as malformed, no output.
+  out.clear();
+  auto bad = MakePacket(0, 5, 1, 0, {1}, 43);
+  sw.Process(bad.data(), bad.size(), &out);
+  bad = MakePacket(9, 5, 1, 0, {1}, 42);
+  sw.Process(bad.data(), bad.size(), &out);
+  sw.Process(bad.data(), 3, &out);
+  EXPECT(out.empty() && sw.counters().malformed == 3);
+  // Drop simulator: everything dropped on ingress.
+  sw.SetDropProbabilities(1.0, 0.0, 1);
+  send(0, 9, 1, 0, {1, 1, 1, 1});
+  EXPECT(sw.counters().ingress_dropped == 1 && sw.Bitmap(9, 0) == 0);
+  sw.SetDropProbabilities(0.0, 1.0, 1);
+  send(0, 9, 1, 0, {1, 1, 1, 1});
+  send(1, 9, 1, 0, {1, 1, 1, 1});
+  send(2, 9, 1, 0, {1, 1, 1, 1});
+  EXPECT(out.empty() && sw.counters().egress_dropped == 3);
+  // Single worker: every packet completes its slot at once.
+  sw.SetDropProbabilities(0, 0);
+  sw.Reset(1, 1, 4);
+  sw.AddWorker(0);
+  out.clear();
+  auto p1 = MakePacket(0, 0, 0, 0, {5, 6, 7, 8}, 1);
+  sw.Process(p1.data(), p1.size(), &out);
+  EXPECT(out.size() == 1 && PayloadAt(out[0], 3) == 8);
+}
+
+static void TestQuantMath() {
+  using namespace quant;
+  EXPECT(LocalExponent(0.0f) == -126);
+  EXPECT(LocalExponent(1.0f) == 1);      // 2^1 > 1
+  EXPECT(LocalExponent(0.75f) == 0);     // 2^0 > 0.75
+  EXPECT(LocalExponent(3.0f) == 2);
+  EXPECT(LocalExponent(INFINITY) == 127);
+  EXPECT(ScaleFactor(1, 2) == 536870912.0f);  // (2^31-1)/(2*2) rounds to 2^29 in float
+  EXPECT(std::isfinite(ScaleFactor(-126, 8)));
+  EXPECT(Quantize(0.5f, 4.0f) == 2 && Quantize(0.625f, 4.0f) == 2 && Quantize(0.875f, 4.0f) == 4);
+  EXPECT(Quantize(NAN, 1.0f) == 0 && Quantize(1e30f, 1e30f) == INT32_MAX);
+  // Oracle: exact for values that are representable at the block scale.
+  std::vector<float> a = {1.0f, -2.0f, 0.5f, 0.0f}, b = {0.25f, 4.0f, -0.5f, 0.0f}, out(4);
+  const float* in[2] = {a.data(), b.data()};
+  OracleQuantAllReduce(in, 2, 4, 4, out.data());
+  EXPECT(out[0] == 1.25f && out[1] == 2.0f && out[2] == 0.0f && out[3] == 0.0f);
+  // All-zero block stays zero (no NaN from an infinite scale).
+  std::vector<float> z(8, 0.0f);
+  const float* zin[2] = {z.data(), z.data()};
+  std::vector<float> zo(8, 1.0f);
+  OracleQuantAllReduce(zin, 2, 8, 4, zo.data());
+  for (float v : zo) EXPECT(v == 0.0f);
+}
+
+static void TestControlPlane() {
+  ControlServer s;
+  EXPECT(s.Start("127.0.0.1", 0, 0));
+  const int n = 3;
+  std::vector<std::thread> th;
+  std::atomic<int> errors{0};
+  for (int r = 0; r < n; r++) {
+    th.emplace_back([&, r] {
+      ControlClient c;
+      if (!c.Connect("127.0.0.1", s.port(), 2000)) { errors++; return; }
+      for (int round = 0; round < 3; round++) {
+        uint64_t v = r == 1 ? 1000 + round : 0;
+        if (!c.Broadcast(n, r, 1, &v) || v != static_cast<uint64_t>(1000 + round)) errors++;
+        std::vector<std::string> all;
+        if (!c.AllGather(n, r, "tok" + std::to_string(r * 10 + round), &all)) errors++;
+        for (int k = 0; k < n && all.size() == static_cast<size_t>(n); k++)
+          if (all[k] != "tok" + std::to_string(k * 10 + round)) errors++;
+        if (!c.Barrier(n)) errors++;
+      }
+    });
+  }
+  for (auto& t : th) t.join();
+  EXPECT(errors == 0);
+  ControlClient cli;
+  EXPECT(cli.Connect("127.0.0.1", s.port(), 2000));
+  std::string reply;
+  EXPECT(cli.Command("SET drop 0.25 0.5 7", &reply));
+  EXPECT(cli.Command("SHOW drop", &reply) && reply.find("0.25") != std::string::npos);
+  EXPECT(!cli.Command("BOGUS", &reply));
+  s.Stop();
+}
+
+static void TestContextDummy() {
+  Config cfg;
+  EXPECT(cfg.LoadFromString("[general]\nbackend = dummy\nnum_workers = 3\nnum_worker_threads = 3\n"
+                            "max_outstanding_packets = 10\npacket_numel = 64\n"
+                            "[backend.dummy]\nbandwidth = 0\n"));
+  Context& ctx = Context::GetInstance();
+  EXPECT(ctx.Start(&cfg));
+  EXPECT(ctx.GetConfig().general_.max_outstanding_packets == 9);  // rounded to a multiple of 3
+  const int numel = 100003;
+  std::vector<float> in(numel), out(numel);
+  for (int i = 0; i < numel; i++) in[i] = std::sin(i * 0.37f) * (i % 97);
+  std::vector<std::shared_ptr<Job>> jobs;
+  for (int k = 0; k < 4; k++) jobs.push_back(ctx.AllReduceAsync(in.data(), out.data(), numel, FLOAT32, SUM));
+  ctx.WaitForAllJobs();
+  for (auto& j : jobs) EXPECT(j->GetJobStatus() == FINISHED);
+  double worst = 0;
+  for (int i = 0; i < numel; i++) worst = std::max(worst, std::fabs(out[i] - 3.0 * in[i]));
+  EXPECT(worst < 1e-4);
+  std::vector<int32_t> iin(1000), iout(1000);
+  for (int i = 0; i < 1000; i++) iin[i] = i - 500;
+  auto j = ctx.AllReduce(iin.data(), iout.data(), 1000, INT32, SUM);
+  EXPECT(j->GetJobStatus() == FINISHED && iout[0] == -1500 && iout[999] == 1497);
+  EXPECT(ctx.GetStats().jobs_finished_num() == 5);
+  ctx.Stop();
+  EXPECT(ctx.GetContextState() == Context::STOPPED);
+  bool threw = false;
+  try { ctx.AllReduce(iin.data(), iout.data(), 10, INT32, SUM); } catch (const FatalError&) { threw = true; }
+  EXPECT(threw);
+  // Restart with instant completion: plumbing only, data untouched.
+  Config c2;
+  c2.LoadFromString("[general]\nbackend = dummy\ninstant_job_completion = true\n");
+  EXPECT(ctx.Start(&c2));
+  iout.assign(1000, -7);
+  ctx.AllReduce(iin.data(), iout.data(), 1000, INT32, SUM);
+  EXPECT(iout[10] == -7);
+  ctx.Stop();
+}
+
+int main() {
+  SetVerbosity(0);
+  struct { const char* name; void (*fn)(); } tests[] = {
+      {"static_slice", TestStaticSlice}, {"barrier", TestBarrier}, {"job_fsm", TestJobFsm},
+      {"timeout_queue", TestTimeoutQueue}, {"soft_switch", TestSoftSwitch},
+      {"quant_math", TestQuantMath}, {"control_plane", TestControlPlane},
+      {"context_dummy", TestContextDummy},
+  };
+  for (auto& t : tests) {
+    int before = g_failures;
+    t.fn();
+    printf("%s %s\n", g_failures == before ? "ok  " : "FAIL", t.name);
+    fflush(stdout);
+  }
+  return g_failures ? 1 : 0;
+}

@@ -1,0 +1,115 @@
+"""Operator console for the controller / software switch.
+
+The reference ships a ``cmd``-based shell inside its Python controller
+(controller/cli.py:136-660) to inspect and poke the Tofino: show_ports, show_bitmap,
+show_statistics, set_drop_probabilities, reset_workers ... This is the same kind of
+shell for the controller that rank 0 hosts in-process (or ``bin/switchml_switchd``):
+
+    python -m switchml_b200.utils.cli --ip 127.0.0.1 --port 50099
+    (switchml) show_workers
+    (switchml) set_drop_probabilities 0.01 0.01
+    (switchml) show_statistics
+
+Commands that only make sense for front-panel ports of a hardware switch (show_ports,
+forwarding table, ARP/ICMP responder) have no counterpart: an NVSwitch box has no
+Ethernet data plane to configure.
+"""
+import argparse
+import cmd
+import ctypes
+
+
+def controller_command(ip, port, line):
+    """One request/reply with a controller; raises on error."""
+    from .._native import lib, last_error, NativeError
+    buf = ctypes.create_string_buffer(1 << 16)
+    n = lib().sml_controller_command(ip.encode(), int(port), line.encode(), buf, len(buf))
+    if n < 0:
+        raise NativeError(last_error())
+    return buf.value.decode(errors="replace")
+
+
+class Cli(cmd.Cmd):
+    intro = "SwitchML controller console. Type help or ? to list commands."
+    prompt = "(switchml) "
+
+    def __init__(self, ip, port, stdout=None):
+        super().__init__(stdout=stdout)
+        self.ip, self.port = ip, port
+        self._history = []
+
+    def _send(self, line):
+        try:
+            out = controller_command(self.ip, self.port, line)
+            if out:
+                self.stdout.write(out if out.endswith("\n") else out + "\n")
+        except Exception as e:  # keep the shell alive
+            self.stdout.write("error: %s\n" % e)
+
+    def precmd(self, line):
+        if line.strip():
+            self._history.append(line)
+        return line
+
+    def do_show_workers(self, arg):
+        "Workers of the current session with their packet and byte counters."
+        self._send("SHOW workers")
+
+    do_show_udp_workers = do_show_workers
+
+    def do_show_statistics(self, arg):
+        "Broadcast / retransmit / consumed / dropped packet counters of the switch."
+        self._send("SHOW statistics")
+
+    def do_show_bitmap(self, arg):
+        "show_bitmap <slot>: the worker bitmaps of both sets of a slot."
+        self._send("SHOW bitmap %s" % (arg.strip() or "0"))
+
+    def do_show_drop_probabilities(self, arg):
+        "Current ingress and egress drop probabilities."
+        self._send("SHOW drop")
+
+    def do_set_drop_probabilities(self, arg):
+        "set_drop_probabilities <ingress> <egress> [seed]: lose packets on purpose (0..1)."
+        parts = arg.split()
+        if len(parts) < 2:
+            self.stdout.write("usage: set_drop_probabilities <ingress> <egress> [seed]\n")
+            return
+        self._send("SET drop " + " ".join(parts[:3]))
+
+    def do_reset_workers(self, arg):
+        "Forget every worker and clear all switch state."
+        self._send("RESET")
+
+    def do_ping(self, arg):
+        "Check that the controller answers."
+        self._send("PING")
+
+    def do_history(self, arg):
+        "Commands entered so far."
+        for i, h in enumerate(self._history):
+            self.stdout.write("%3d  %s\n" % (i, h))
+
+    def do_exit(self, arg):
+        "Leave the console."
+        return True
+
+    do_EOF = do_exit
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description="SwitchML controller console")
+    ap.add_argument("--ip", default="127.0.0.1")
+    ap.add_argument("--port", type=int, default=50099)
+    ap.add_argument("-c", "--command", action="append", help="run one command and exit (repeatable)")
+    a = ap.parse_args(argv)
+    cli = Cli(a.ip, a.port)
+    if a.command:
+        for c in a.command:
+            cli.onecmd(c)
+        return
+    cli.cmdloop()
+
+
+if __name__ == "__main__":
+    main()
