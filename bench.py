@@ -1,0 +1,361 @@
+#!/usr/bin/env python
+"""Headline benchmark: allreduce rate in aggregated tensor elements per second (ATE/s).
+
+    python bench.py --gpus 1 --steps 20 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29500 bench.py --gpus 8 --steps 20 --warmup 5
+    python bench.py --impl reference ...        # the reference's own NCCL path
+
+One step = one SUM allreduce of a float32 tensor of 2^28 elements (the default of the
+reference's benchmark tools, benchmarks/allreduce_benchmark/main.cc:101) through the
+public Context API. ATE/s = numel / time per step; bus GB/s = 4*numel/time * 2(n-1)/n.
+The timed region is bracketed by a barrier and a device synchronisation, timed with CUDA
+events on the launching stream, and the slowest rank counts. Rank 0 prints one JSON line.
+
+The end-to-end figure ("e2e") times the same allreduce for a caller whose data lives in
+pinned host memory: every step copies the input host→device, reduces it and reads the
+result back device→host, through Context.all_reduce_host.
+
+Other workloads (same JSON shape): --workload resnet50 | vgg19 | bert (synthetic DDP
+training, images/s or tokens/s).
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+PUBLISHED_ATE = 2.82e9  # SwitchML-RDMA, 8 workers, read off the reference's benchmark figure
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index=0):
+        self.gpu = gpu_index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax.append(float(f[2]))
+                power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", str(rank)))
+    addr = os.environ.get("MASTER_ADDR", "127.0.0.1")
+    port = int(os.environ.get("MASTER_PORT", "29500"))
+    return rank, world, local, addr, port
+
+
+def max_over_ranks(value, world):
+    import torch
+    import torch.distributed as dist
+    if world == 1:
+        return value
+    t = torch.tensor([value], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def barrier(world):
+    import torch
+    import torch.distributed as dist
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def start_context(args, rank, world, local, addr, port, heap_mb=0):
+    import switchml_b200 as sml
+    ctx = sml.Context.get_instance()
+    opts = dict(packet_numel=args.packet_numel, device=local, controller_ip=addr,
+                controller_port=port + 101, mode=args.mode, transport=args.transport, launch="inline",
+                symm_heap_mb=heap_mb, slot_bytes=args.slot_bytes, wait_timeout_ms=30000)
+    if args.channels:
+        opts["channels"] = args.channels
+    if not ctx.start(sml.make_config("cuda", rank=rank, num_workers=world, **opts)):
+        raise RuntimeError("Context.start failed")
+    return ctx
+
+
+# ------------------------------------------------------------------------------------------
+def bench_allreduce(args):
+    import torch
+    import torch.distributed as dist
+    rank, world, local, addr, port = dist_env()
+    if world != args.gpus:
+        raise SystemExit("--gpus %d but WORLD_SIZE is %d (launch with torch.distributed.run)" % (args.gpus, world))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local))
+    numel = args.numel
+    dtype = {"float32": torch.float32, "int32": torch.int32, "bfloat16": torch.bfloat16}[args.dtype]
+    esz = torch.empty((), dtype=dtype).element_size()
+    heap_mb = 0
+    if args.symmetric:
+        heap_mb = (2 * numel * esz >> 20) + 64
+    ctx = start_context(args, rank, world, local, addr, port, heap_mb)
+
+    g = torch.Generator(device="cuda").manual_seed(1234 + rank)
+    if args.symmetric:
+        x = ctx.symmetric_empty(numel, dtype)
+        y = ctx.symmetric_empty(numel, dtype)
+    else:
+        x = torch.empty(numel, dtype=dtype, device="cuda")
+        y = torch.empty(numel, dtype=dtype, device="cuda")
+    if dtype == torch.int32:
+        x.copy_(torch.randint(-2 ** 20, 2 ** 20, (numel,), generator=g, device="cuda", dtype=torch.int32))
+    else:
+        x.copy_((torch.rand(numel, generator=g, device="cuda") * 2 - 1).to(dtype))
+
+    def step():
+        job = ctx.all_reduce_async(x, y)  # enqueued on the current stream (inline launch)
+        return job
+
+    jobs = [step() for _ in range(args.warmup)]
+    barrier(world)
+    for j in jobs:
+        assert j.wait() == 3, j.error()
+        j.release()
+
+    # correctness spot check against NCCL / the plain sum on a slice
+    check = None
+    if world > 1 and dtype != torch.int32:
+        ref = x.clone().float()
+        dist.all_reduce(ref)
+        err = (y.float() - ref).abs().max().item()
+        scale = ref.abs().max().item()
+        check = {"max_abs_err_vs_nccl": err, "max_abs": scale}
+        assert err <= 1e-3 * max(scale, 1.0), "allreduce result is wrong: err %g" % err
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    barrier(world)
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    jobs = [step() for _ in range(args.steps)]
+    stop.record()
+    torch.cuda.synchronize()
+    barrier(world)
+    clocks = sampler.stop() if rank == 0 else None
+    ms = max_over_ranks(start.elapsed_time(stop), world) / args.steps
+    for j in jobs:
+        assert j.wait() == 3, j.error()
+        j.release()
+
+    # ---- end to end: pinned host -> device -> allreduce -> pinned host ----
+    hx = torch.empty(numel, dtype=dtype, pin_memory=True)
+    hy = torch.empty(numel, dtype=dtype, pin_memory=True)
+    hx.copy_(x)
+    from switchml_b200.parallel.host_pipeline import HostAllReduce
+    pipe = HostAllReduce(ctx, numel, dtype, chunk_numel=args.e2e_chunk)
+    for _ in range(max(1, min(args.warmup, 3))):
+        pipe.run(hx, hy)
+    torch.cuda.synchronize()
+    barrier(world)
+    t0 = time.perf_counter()
+    for _ in range(args.e2e_steps):
+        pipe.run(hx, hy)  # returns when the result is in host memory
+    torch.cuda.synchronize()
+    e2e_s = (time.perf_counter() - t0) / args.e2e_steps
+    e2e_ms = max_over_ranks(e2e_s * 1e3, world)
+    e2e_launches = pipe.launches_per_run
+    pipe.close()
+
+    stats = ctx.get_stats()
+    multimem = ctx.uses_multimem()
+    ctx.stop()
+    if world > 1:
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    ate = numel / (ms * 1e-3)
+    bus = esz * numel / (ms * 1e-3) * (2.0 * (world - 1) / world) / 1e9
+    out = {
+        "metric": "allreduce_ate_per_s", "value": ate, "unit": "elements/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": ate / PUBLISHED_ATE, "dtype": "fp32" if args.dtype == "float32" else args.dtype,
+        "data": "synthetic U(-1,1) seeded per rank",
+        "impl": "switchml_b200",
+        "config": {"model": "allreduce_microbenchmark", "numel": numel, "tensor_bytes": numel * esz,
+                   "global_batch": None, "seq_len": None, "parallelism": "dp%d" % world,
+                   "op": "SUM", "mode": args.mode, "transport": "nvls" if multimem else ("p2p" if world > 1 else "local"),
+                   "symmetric_buffers": bool(args.symmetric), "packet_numel": args.packet_numel,
+                   "l2": "input and output tensors (%d MiB each) are larger than the 126 MB L2" % (numel * esz >> 20)},
+        "bus_gbs": bus, "alg_gbs": esz * numel / (ms * 1e-3) / 1e9,
+        "e2e": {"value": numel / (e2e_ms * 1e-3), "unit": "elements/s", "ms_per_step": e2e_ms,
+                "h2d_bytes_per_step": numel * esz, "d2h_bytes_per_step": numel * esz,
+                "steps": args.e2e_steps, "gpu_launches_per_step": e2e_launches},
+        "gpu_launches": args.steps,
+        "clocks": clocks, "check": check,
+        "stats": {"jobs_finished": stats["jobs_finished"], "jobs_failed": stats["jobs_failed"],
+                  "tiles": stats["backend"]["tiles"]},
+    }
+    print(json.dumps(out), flush=True)
+
+
+# ------------------------------------------------------------------------------------------
+def bench_reference(args):
+    """Run the reference's own benchmark script, unmodified, on its NCCL backend.
+
+    The script times with the host clock around ``work.wait()``, which for NCCL does not
+    wait for the GPU, so the device time is taken here with CUDA events recorded around
+    the script's own ``dist.all_reduce`` calls (the calls themselves are untouched)."""
+    rank, world, local, addr, port = dist_env()
+    script = os.path.join(ROOT, "baseline", "_ref", "benchmarks", "allreduce_pytorch_benchmark",
+                          "allreduce_pytorch_benchmark.py")
+    if not os.path.exists(script):
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable":
+                              "baseline/_ref has no copy of the reference benchmark script (pip cannot install the "
+                              "reference: it has no setup.py/pyproject.toml at its root)"}))
+        return
+    import runpy
+    import torch
+    import torch.distributed as dist
+    if not torch.cuda.is_available():
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": "no GPU"}))
+        return
+    torch.cuda.set_device(local)
+    events = []
+    real_all_reduce = dist.all_reduce
+
+    def traced(*a, **kw):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        r = real_all_reduce(*a, **kw)
+        if hasattr(r, "wait"):
+            r.wait()  # stream-orders the collective before the end event (no host block)
+        e1.record()
+        events.append((e0, e1))
+        return r
+
+    dist.all_reduce = traced
+    tt = "float" if args.dtype == "float32" else "int32"
+    argv = [script, "-n", str(world), "-r", str(rank), "-ip", addr, "-bk", "nccl", "-tn", str(args.numel),
+            "-tt", tt, "-d", "gpu", "-nj", str(args.steps), "-nw", str(args.warmup), "--random", "--seed",
+            str(1234 + rank)]
+    old_argv, old_stdout = sys.argv, sys.stdout
+    sys.argv = argv
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    log = open(os.devnull, "w")
+    sys.stdout = log
+    try:
+        runpy.run_path(script, run_name="__main__")
+    finally:
+        sys.stdout = old_stdout
+        sys.argv = old_argv
+        dist.all_reduce = real_all_reduce
+    torch.cuda.synchronize()
+    clocks = sampler.stop() if rank == 0 else None
+    timed = events[args.warmup:]
+    total_ms = timed[0][0].elapsed_time(timed[-1][1])
+    ms = total_ms / len(timed)
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+        real_all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        dist.destroy_process_group()
+    if rank != 0:
+        return
+    numel = args.numel
+    ate = numel / (ms * 1e-3)
+    print(json.dumps({
+        "impl": "reference", "metric": "allreduce_ate_per_s", "value": ate, "unit": "elements/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": ate / PUBLISHED_ATE,
+        "dtype": "fp32" if args.dtype == "float32" else args.dtype, "data": "synthetic (script's --random)",
+        "config": {"model": "allreduce_microbenchmark", "numel": numel, "parallelism": "dp%d" % world,
+                   "backend": "nccl via dev_root/benchmarks/allreduce_pytorch_benchmark (unmodified)",
+                   "timing": "CUDA events around the script's dist.all_reduce calls"},
+        "bus_gbs": 4 * numel / (ms * 1e-3) * (2.0 * (world - 1) / world) / 1e9,
+        "clocks": clocks,
+    }), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="allreduce", choices=["allreduce", "resnet50", "vgg19", "bert"])
+    ap.add_argument("--numel", type=int, default=1 << 28)
+    ap.add_argument("--dtype", default="float32", choices=["float32", "int32", "bfloat16"])
+    ap.add_argument("--mode", default=os.environ.get("SWITCHML_MODE", "float_sum"),
+                    choices=["int32_quant", "float_sum"])
+    ap.add_argument("--transport", default="auto", choices=["auto", "nvls", "p2p"])
+    ap.add_argument("--symmetric", type=int, default=0, help="1: tensors live in the symmetric heap (zero-copy)")
+    ap.add_argument("--packet-numel", type=int, default=256)
+    ap.add_argument("--slot-bytes", type=int, default=131072)
+    ap.add_argument("--channels", type=int, default=0)
+    ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--e2e-chunk", type=int, default=1 << 24)
+    ap.add_argument("--batch", type=int, default=0, help="per-GPU batch for the training workloads")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        return bench_reference(args)
+    if args.workload == "allreduce":
+        return bench_allreduce(args)
+    from switchml_b200.benchmarks.ddp_train import bench_training
+    return bench_training(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -50,3 +50,76 @@ def udp_worker(rank, n, ctl_port, udp_port, numel, dtype, threads, packet_numel,
         q.put((rank, "ok", outs, stats, switch_stats))
     except Exception:
         q.put((rank, "error", traceback.format_exc(), None, None))
+
+
+def cuda_worker(rank, n, ctl_port, transport, mode, q, heap_mb=64, launch="inline"):
+    """One rank of the cuda backend on GPU `rank`; runs a fixed list of cases and checks
+    every result locally against the CPU oracle / a float64 sum."""
+    try:
+        import numpy as np
+        import torch
+        import switchml_b200 as sml
+        from switchml_b200.ops.oracle import quant_allreduce_oracle, int_allreduce_oracle
+        torch.cuda.set_device(rank)
+        ctx = sml.Context.get_instance()
+        cfg = sml.make_config("cuda", rank=rank, num_workers=n, packet_numel=256, device=rank,
+                              controller_port=ctl_port, transport=transport, mode=mode,
+                              symm_heap_mb=heap_mb, launch=launch, wait_timeout_ms=20000,
+                              slot_bytes=65536)
+        assert ctx.start(cfg), "start failed"
+        report = {"multimem": ctx.uses_multimem(), "cases": 0}
+        sizes = [1, 255, 4097, 65536, 70001, (1 << 20) + 3, 5 * (1 << 20)]
+        for numel in sizes:
+            xs = [rank_data(r, numel, "float32", seed=numel % 97) for r in range(n)]
+            x = torch.from_numpy(xs[rank]).cuda()
+            y = torch.empty_like(x)
+            job = ctx.all_reduce_async(x, y)
+            assert job.wait(60000) == sml.JobStatus.FINISHED, job.error()
+            got = y.cpu().numpy()
+            if mode == "int32_quant":
+                want = quant_allreduce_oracle(xs, 256)
+                assert np.array_equal(got, want), "quant mismatch at numel %d" % numel
+            else:
+                exact = sum(a.astype(np.float64) for a in xs)
+                assert np.max(np.abs(got - exact)) < 1e-4, "float sum mismatch at numel %d" % numel
+            report["cases"] += 1
+            # int32
+            xi = [rank_data(r, numel, "int32", seed=1) for r in range(n)]
+            t = torch.from_numpy(xi[rank]).cuda()
+            ctx.all_reduce(t)
+            assert np.array_equal(t.cpu().numpy(), int_allreduce_oracle(xi)), "int mismatch at %d" % numel
+            report["cases"] += 1
+            # bf16 in place
+            xb = [torch.from_numpy(a).bfloat16() for a in xs]
+            tb = xb[rank].cuda()
+            ctx.all_reduce(tb)
+            if mode == "int32_quant":
+                want = torch.from_numpy(quant_allreduce_oracle([a.float().numpy() for a in xb], 256)).bfloat16()
+                assert torch.equal(tb.cpu(), want), "bf16 quant mismatch at %d" % numel
+            else:
+                exact = sum(a.double() for a in xb)
+                assert torch.allclose(tb.cpu().double(), exact, rtol=2e-2, atol=2e-2), "bf16 sum mismatch"
+            report["cases"] += 1
+        # zero-copy path: tensors in the symmetric heap, reduced in place and out of place
+        if mode == "float_sum":
+            for numel in (1000, 300007, 4 * (1 << 20)):
+                xs = [rank_data(r, numel, "float32", seed=5) for r in range(n)]
+                a = ctx.symmetric_empty(numel, torch.float32)
+                b = ctx.symmetric_empty(numel, torch.float32)
+                guard = ctx.symmetric_empty(64, torch.float32)
+                guard.fill_(123.0)
+                a.copy_(torch.from_numpy(xs[rank]))
+                ctx.all_reduce(a, b)
+                exact = sum(v.astype(np.float64) for v in xs)
+                assert np.max(np.abs(b.cpu().numpy() - exact)) < 1e-4, "zero-copy mismatch at %d" % numel
+                assert np.array_equal(a.cpu().numpy(), xs[rank]), "zero-copy touched its input"
+                ctx.all_reduce(a)
+                assert np.max(np.abs(a.cpu().numpy() - exact)) < 1e-4, "in-place zero-copy mismatch"
+                assert float(guard.min()) == 123.0 and float(guard.max()) == 123.0, "wrote past the tensor"
+                report["cases"] += 2
+            ctx.symmetric_reset()
+        report["stats"] = ctx.get_stats()
+        ctx.stop()
+        q.put((rank, "ok", report))
+    except Exception:
+        q.put((rank, "error", traceback.format_exc()))

@@ -1,0 +1,118 @@
+"""The aggregation kernels on one GPU, all ranks emulated inside one cooperative launch
+(peer-memory code path), checked against the CPU oracle (bit-exact in quantised mode)
+and a float64 sum. Sizes follow the plan: 1, 63, 64, 65, 255, 2^20+1, zero blocks,
+extreme exponents, denormals."""
+import numpy as np
+import pytest
+import torch
+
+from switchml_b200.ops.emulation import emulated_allreduce
+from switchml_b200.ops.oracle import quant_allreduce_oracle, int_allreduce_oracle
+
+pytestmark = pytest.mark.gpu
+
+SIZES = [1, 63, 64, 65, 255, 4096, 40000, (1 << 20) + 1]
+
+
+def _inputs(n, numel, dtype=torch.float32, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    xs = []
+    for r in range(n):
+        if dtype == torch.int32:
+            x = torch.randint(-2 ** 30, 2 ** 30, (numel,), generator=g, dtype=torch.int32)
+        else:
+            x = (torch.rand(numel, generator=g) * 2 - 1) * (10.0 ** (r - 1))
+            x = x.to(dtype)
+        xs.append(x)
+    return xs
+
+
+@pytest.mark.parametrize("algo", ["staged", "oneshot"])
+@pytest.mark.parametrize("n", [1, 2, 4, 8])
+@pytest.mark.parametrize("numel", SIZES)
+def test_quant_bit_exact(n, numel, algo):
+    if algo == "oneshot" and numel > (1 << 16):
+        pytest.skip("one-shot is for small messages")
+    xs = _inputs(n, numel)
+    outs = emulated_allreduce([x.cuda() for x in xs], mode="quant", algo=algo, block_numel=64,
+                              slot_bytes=32768)
+    want = quant_allreduce_oracle([x.numpy() for x in xs], 64)
+    for o in outs:
+        assert np.array_equal(o.cpu().numpy(), want)
+    exact = sum(x.double() for x in xs).numpy()
+    scale = max(float(x.abs().max()) for x in xs)
+    assert np.max(np.abs(want - exact)) <= n * n * 2.0 ** -30 * scale
+
+
+@pytest.mark.parametrize("block", [32, 256, 1024])
+def test_quant_block_sizes_and_reuse(block):
+    # Several jobs back to back over the same staging (epochs and slot reuse).
+    xs = _inputs(4, 300001, seed=3)
+    outs = emulated_allreduce([x.cuda() for x in xs], mode="quant", block_numel=block,
+                              slot_bytes=16 * 4 * block, repeats=3, channels=3)
+    want = quant_allreduce_oracle([x.numpy() for x in xs], block)
+    for o in outs:
+        assert np.array_equal(o.cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("algo", ["staged", "oneshot"])
+@pytest.mark.parametrize("n", [2, 8])
+def test_int32_wrapping_sum(n, algo):
+    numel = 50001 if algo == "oneshot" else 777777
+    xs = _inputs(n, numel, torch.int32)
+    outs = emulated_allreduce([x.cuda() for x in xs], mode="sum", algo=algo)
+    want = int_allreduce_oracle([x.numpy() for x in xs])
+    for o in outs:
+        assert np.array_equal(o.cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("algo", ["staged", "oneshot"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_float_sum(dtype, algo):
+    n, numel = 4, 65537 if algo == "oneshot" else 999999
+    xs = _inputs(n, numel, dtype)
+    outs = emulated_allreduce([x.cuda() for x in xs], mode="sum", algo=algo, post_scale=0.25)
+    exact = sum(x.double() for x in xs) * 0.25
+    tol = 1e-6 if dtype == torch.float32 else 1e-2
+    for o in outs:
+        assert torch.allclose(o.cpu().double(), exact, rtol=tol, atol=tol * 10)
+    for o in outs[1:]:
+        assert torch.equal(o, outs[0]), "all ranks must hold identical bits"
+
+
+def test_quant_bf16_matches_oracle_after_rounding():
+    n, numel = 4, 100000
+    xs = _inputs(n, numel, torch.bfloat16)
+    outs = emulated_allreduce([x.cuda() for x in xs], mode="quant", block_numel=256)
+    want = quant_allreduce_oracle([x.float().numpy() for x in xs], 256)
+    want_bf16 = torch.from_numpy(want).to(torch.bfloat16)
+    for o in outs:
+        assert torch.equal(o.cpu(), want_bf16)
+
+
+def test_special_blocks():
+    numel = 64 * 8
+    a = torch.zeros(numel)
+    a[64:128] = 1e-30
+    a[128:192] = 3e37
+    a[192:256] = 1e-45       # denormal
+    a[256] = -1.5
+    a[320:384] = 2.0 ** -100
+    b = a.clone()
+    b[384:448] = 7.0         # only one rank is non-zero here
+    outs = emulated_allreduce([a.cuda(), b.cuda()], mode="quant", block_numel=64, slot_bytes=8192)
+    want = quant_allreduce_oracle([a.numpy(), b.numpy()], 64)
+    got = outs[0].cpu().numpy()
+    assert np.all(np.isfinite(got)) and np.array_equal(got, want)
+    assert np.all(got[:64] == 0) and got[256] == -3.0 and np.all(got[384:448] == 7.0)
+
+
+def test_unaligned_views_and_out_of_place():
+    n, numel = 2, 10007
+    bases = [torch.randn(numel + 3).cuda() for _ in range(n)]
+    xs = [b[1:1 + numel] for b in bases]            # 4-byte aligned only
+    keep = [x.clone() for x in xs]
+    outs = emulated_allreduce(xs, mode="sum")
+    for x, k in zip(xs, keep):
+        assert torch.equal(x, k), "inputs must stay untouched"
+    assert torch.allclose(outs[0], keep[0] + keep[1])
