@@ -49,7 +49,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits", "-lms", "25",
                  "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -58,9 +58,11 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.time(), line.strip()))
 
-    def stop(self):
+    def stop(self, window=None):
+        """Summary of the samples taken inside `window` = (t0, t1) wall-clock seconds; when
+        the window is shorter than the sampling period, of the samples closest to it."""
         if not self.proc:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
@@ -70,7 +72,15 @@ class ClockSampler:
             self.proc.kill()
         sm, smax, reasons, power = [], [], set(), []
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
+        time.sleep(0.05)
+        lines = self.lines
+        if window and lines:
+            inside = [l for l in lines if window[0] <= l[0] <= window[1] + 0.06]
+            if len(inside) < 3:
+                mid = 0.5 * (window[0] + window[1])
+                inside = sorted(lines, key=lambda l: abs(l[0] - mid))[:5]
+            lines = inside
+        for _, line in lines:
             f = [x.strip() for x in line.split(",")]
             if len(f) < 9:
                 continue
@@ -162,6 +172,9 @@ def bench_allreduce(args):
         job = ctx.all_reduce_async(x, y)  # enqueued on the current stream (inline launch)
         return job
 
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()  # nvidia-smi needs a moment to start: launch it before the warm-up
     jobs = [step() for _ in range(args.warmup)]
     barrier(world)
     for j in jobs:
@@ -178,17 +191,16 @@ def bench_allreduce(args):
         check = {"max_abs_err_vs_nccl": err, "max_abs": scale}
         assert err <= 1e-3 * max(scale, 1.0), "allreduce result is wrong: err %g" % err
 
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
     barrier(world)
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    w0 = time.time()
     start.record()
     jobs = [step() for _ in range(args.steps)]
     stop.record()
     torch.cuda.synchronize()
+    w1 = time.time()
     barrier(world)
-    clocks = sampler.stop() if rank == 0 else None
+    clocks = sampler.stop((w0, w1)) if rank == 0 else None
     ms = max_over_ranks(start.elapsed_time(stop), world) / args.steps
     for j in jobs:
         assert j.wait() == 3, j.error()

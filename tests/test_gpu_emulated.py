@@ -41,7 +41,8 @@ def test_quant_bit_exact(n, numel, algo):
         assert np.array_equal(o.cpu().numpy(), want)
     exact = sum(x.double() for x in xs).numpy()
     scale = max(float(x.abs().max()) for x in xs)
-    assert np.max(np.abs(want - exact)) <= n * n * 2.0 ** -30 * scale
+    # n rounded addends of half a quantum each, plus the final rounding to float32
+    assert np.max(np.abs(want - exact)) <= n * n * 2.0 ** -30 * scale + 2.0 ** -23 * n * scale
 
 
 @pytest.mark.parametrize("block", [32, 256, 1024])
