@@ -299,6 +299,9 @@ def bench_reference(args):
     argv = [script, "-n", str(world), "-r", str(rank), "-ip", addr, "-bk", "nccl", "-tn", str(args.numel),
             "-tt", tt, "-d", "gpu", "-nj", str(args.steps), "-nw", str(args.warmup), "--random", "--seed",
             str(1234 + rank)]
+    # torchrun tells c10d to reuse the launcher's store; the script brings its own
+    # tcp://<ip>:23456 store, whose server rank 0 only starts when that variable is unset.
+    os.environ.pop("TORCHELASTIC_USE_AGENT_STORE", None)
     old_argv, old_stdout = sys.argv, sys.stdout
     sys.argv = argv
     sampler = ClockSampler(local)
@@ -358,7 +361,12 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--e2e-chunk", type=int, default=1 << 24)
     ap.add_argument("--batch", type=int, default=0, help="per-GPU batch for the training workloads")
+    ap.add_argument("--watchdog", type=float, default=float(os.environ.get("SWITCHML_BENCH_WATCHDOG", "0")),
+                    help="dump all Python stacks and exit if the run takes longer than this many seconds")
     args = ap.parse_args()
+    if args.watchdog > 0:
+        import faulthandler
+        faulthandler.dump_traceback_later(args.watchdog, exit=True)
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":

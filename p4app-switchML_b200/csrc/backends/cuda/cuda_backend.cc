@@ -204,7 +204,9 @@ void CudaBackend::SetupWorker() {
   size_t bytes = kernels::StagingBytes(ctx_.slot_bytes, ctx_.slots_per_channel, ctx_.block_numel,
                                        max_channels_, ctx_.oneshot_bytes, n_, &ctx_.data_offset,
                                        &ctx_.exp_offset, &ctx_.oneshot_offset);
-  bool want_mc = c.transport != "p2p";
+  // Two GPUs exchange less data with plain peer loads/stores (N bytes each way) than
+  // through the switch (1.5 N); from three GPUs on the in-switch reduction wins.
+  bool want_mc = c.transport == "nvls" || (c.transport == "auto" && n_ > 2);
   std::string err;
   SML_CHECK(allocator_->Create(bytes, want_mc, &staging_, &err))
       << "cannot create the symmetric staging region (" << (bytes >> 20) << " MiB): " << err;
@@ -266,6 +268,8 @@ void CudaBackend::CleanupWorker() {
   cudaSetDevice(device_);
   cudaDeviceSynchronize();
   bool peers_alive = !failed_.load();
+  if (server_) server_->StopAccepting();
+  if (n_ > 1 && peers_alive && !client_.Barrier(n_, 10000)) peers_alive = false;
   if (heap_.local) allocator_->Destroy(&heap_, peers_alive);
   if (staging_.local) allocator_->Destroy(&staging_, peers_alive);
   if (comm_stream_) cudaStreamDestroy(comm_stream_);
@@ -339,6 +343,7 @@ void CudaBackend::LaunchJob(const std::shared_ptr<Job>& job, cudaStream_t stream
     a.algo = kernels::ALGO_STAGED;
   }
   kernels::LaunchPlan plan = kernels::PlanLaunch(ctx_, a, c.channels, max_channels_);
+  a.tile_elems = plan.tile_elems;
   epoch_base_ += plan.epochs;
   f->tiles = plan.tiles;
   f->status_slot = static_cast<int>(launched_jobs_++ % kStatusSlots);
@@ -593,6 +598,7 @@ int EmulatedAllReduce(int nranks, void* const* in_ptrs, void* const* out_ptrs,
       j.oneshot_parity = it & 1;
     }
     plan = PlanLaunch(ctxs[0], jobs[0], channels, max_channels);
+    for (int r = 0; r < nranks; r++) jobs[r].tile_elems = plan.tile_elems;
     epoch += plan.epochs;
     cudaMemcpy(d_ctx, ctxs.data(), nranks * sizeof(RankCtx), cudaMemcpyHostToDevice);
     cudaMemcpy(d_job, jobs.data(), nranks * sizeof(JobArgs), cudaMemcpyHostToDevice);

@@ -258,21 +258,21 @@ void SymmetricAllocator::Destroy(SymmetricRegion* r, bool peers_alive) {
   CUdevice dev;
   api->DeviceGet(&dev, device_);
   // Nobody may still be reducing through the multicast object when a rank leaves it.
-  if (peers_alive && n_ > 1) control_->Barrier(n_);
+  if (peers_alive && n_ > 1 && !control_->Barrier(n_, 10000)) peers_alive = false;
   if (r->multicast) UnmapVa(api, r->multicast, r->mapped_bytes);
   r->multicast = nullptr;
   if (r->mc_bound) api->MulticastUnbind(r->mc_handle, dev, 0, r->mapped_bytes);
   r->mc_bound = false;
   if (r->mc_handle) api->MemRelease(r->mc_handle);
   r->mc_handle = 0;
-  if (peers_alive && n_ > 1) control_->Barrier(n_);
+  if (peers_alive && n_ > 1 && !control_->Barrier(n_, 10000)) peers_alive = false;
   for (int p = 0; p < static_cast<int>(r->peers.size()); p++) {
     if (p == rank_ || !r->peers[p]) continue;
     UnmapVa(api, r->peers[p], r->mapped_bytes);
     if (r->peer_handles[p]) api->MemRelease(r->peer_handles[p]);
     r->peers[p] = nullptr;
   }
-  if (peers_alive && n_ > 1) control_->Barrier(n_);
+  if (peers_alive && n_ > 1) control_->Barrier(n_, 10000);
   UnmapVa(api, r->local, r->mapped_bytes);
   api->MemRelease(r->handle);
   r->local = nullptr;

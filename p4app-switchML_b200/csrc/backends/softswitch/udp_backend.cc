@@ -207,6 +207,8 @@ void UdpBackend::CleanupWorker() {
     if (t.joinable()) t.join();
   }
   threads_.clear();
+  if (server_) server_->StopAccepting();
+  if (client_.connected()) client_.Barrier(config_.general_.num_workers, 5000);
   for (int fd : fds_) close(fd);
   fds_.clear();
   client_.Close();

@@ -219,9 +219,10 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
   char* my_stage = ctx.stage_peer[ctx.rank];
   const size_t blocks_per_slot = slot_elems / ctx.block_numel;
   unsigned long long k = 0;
-  for (unsigned long long pos = c0; pos < c1; pos += slot_elems, ++k) {
+  const size_t tile_elems = job.tile_elems;  // <= slot_elems; small jobs use small tiles
+  for (unsigned long long pos = c0; pos < c1; pos += tile_elems, ++k) {
     const unsigned long long epoch = job.epoch_base + k + 1;
-    const size_t len = static_cast<size_t>(c1 - pos < slot_elems ? c1 - pos : slot_elems);
+    const size_t len = static_cast<size_t>(c1 - pos < tile_elems ? c1 - pos : tile_elems);
     const int slot = static_cast<int>(k % ctx.slots_per_channel);
     const size_t slot_index = static_cast<size_t>(channel) * ctx.slots_per_channel + slot;
     const size_t slot_off = ctx.data_offset + slot_index * ctx.slot_bytes;  // same on all ranks
@@ -633,14 +634,24 @@ LaunchPlan PlanLaunch(const RankCtx& ctx, const JobArgs& job, int requested_chan
   LaunchPlan p;
   const unsigned long long numel = job.numel ? job.numel : 1;
   if (max_channels > kMaxChannels) max_channels = kMaxChannels;
+  p.tile_elems = 0;
   if (job.algo == ALGO_STAGED) {
     size_t slot_elems = SlotElems(ctx, job.elem_type, job.mode);
-    unsigned long long tiles = (numel + slot_elems - 1) / slot_elems;
     int ch = requested_channels > 0 ? requested_channels : max_channels;
     if (ch > max_channels) ch = max_channels;
+    // Tile: a slot for big jobs; for smaller ones shrink it so that the job still spreads
+    // over all channels, but not below 16 Ki elements (barrier cost would dominate).
+    unsigned long long unit = static_cast<unsigned long long>(ctx.nranks) *
+                              (ctx.block_numel > 128 ? ctx.block_numel : 128);
+    unsigned long long tile = (numel + ch - 1) / ch;
+    if (tile < 16384) tile = 16384;
+    tile = (tile + unit - 1) / unit * unit;
+    if (tile > slot_elems) tile = slot_elems;
+    p.tile_elems = tile;
+    unsigned long long tiles = (numel + tile - 1) / tile;
     if (static_cast<unsigned long long>(ch) > tiles) ch = static_cast<int>(tiles);
     unsigned long long tiles_per_channel = (tiles + ch - 1) / ch;
-    p.elems_per_channel = tiles_per_channel * slot_elems;
+    p.elems_per_channel = tiles_per_channel * tile;
     p.channels = static_cast<int>((numel + p.elems_per_channel - 1) / p.elems_per_channel);
     p.epochs = static_cast<unsigned>(tiles_per_channel);
     p.tiles = tiles;

@@ -69,6 +69,7 @@ struct JobArgs {
   float post_scale;  // multiplied into the result (1/num_workers for averaging)
   unsigned long long epoch_base;  // flags written by this job are epoch_base+1 .. epoch_base+epochs
   int oneshot_parity;
+  unsigned long long tile_elems;  // ALGO_STAGED: elements per tile (<= elements of a slot)
   // ALGO_ZEROCOPY: offsets of in/out inside the symmetric user region and its mappings
   char* user_peer[kMaxRanks];
   char* user_mc;
@@ -81,6 +82,7 @@ struct LaunchPlan {
   unsigned epochs;         // how far the job advances the epoch counter
   unsigned long long elems_per_channel;  // contiguous range of each channel (last may be short)
   unsigned long long tiles;              // staged tiles summed over channels (stats)
+  unsigned long long tile_elems;         // ALGO_STAGED: copy into JobArgs::tile_elems
 };
 
 // Number of elements of a slot for this element type / mode.

@@ -53,8 +53,11 @@ bool WriteAll(int fd, const std::string& s) {
 }
 
 // Reads up to and excluding '\n'. `buf` keeps bytes beyond the line for the next call.
-bool ReadLine(int fd, std::string* buf, std::string* line, const std::atomic<bool>* stop) {
+bool ReadLine(int fd, std::string* buf, std::string* line, const std::atomic<bool>* stop,
+              int timeout_ms = -1) {
+  auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms);
   for (;;) {
+    if (timeout_ms >= 0 && std::chrono::steady_clock::now() > deadline) return false;
     size_t nl = buf->find('\n');
     if (nl != std::string::npos) {
       *line = buf->substr(0, nl);
@@ -129,14 +132,22 @@ bool ControlServer::Start(const std::string& ip, uint16_t port, uint16_t udp_por
     data_thread_ = std::thread(&ControlServer::DataPlaneLoop, this);
   }
   stopping_ = false;
+  accepting_ = true;
   accept_thread_ = std::thread(&ControlServer::AcceptLoop, this);
   SML_VLOG(1) << "control server listening on " << ip << ":" << port_
               << (udp_port_ ? " (software switch on UDP " + std::to_string(udp_port_) + ")" : "");
   return true;
 }
 
+void ControlServer::StopAccepting() {
+  accepting_ = false;
+  if (accept_thread_.joinable()) accept_thread_.join();
+  if (listen_fd_ >= 0) close(listen_fd_);
+  listen_fd_ = -1;
+}
+
 void ControlServer::Stop() {
-  if (listen_fd_ < 0 && udp_fd_ < 0) return;
+  if (listen_fd_ < 0 && udp_fd_ < 0 && !accept_thread_.joinable() && conn_threads_.empty()) return;
   stopping_ = true;
   {
     // Release anybody blocked in a collective.
@@ -161,7 +172,7 @@ void ControlServer::Stop() {
 }
 
 void ControlServer::AcceptLoop() {
-  while (!stopping_) {
+  while (!stopping_ && accepting_) {
     struct pollfd p = {listen_fd_, POLLIN, 0};
     int r = poll(&p, 1, 200);
     if (r <= 0) continue;
@@ -390,12 +401,18 @@ void ControlClient::Close() {
   fd_ = -1;
 }
 
-bool ControlClient::RoundTrip(const std::string& line, std::string* reply) {
+bool ControlClient::RoundTrip(const std::string& line, std::string* reply, int timeout_ms) {
   std::lock_guard<std::mutex> lk(mu_);
   if (fd_ < 0) return false;
   if (!WriteAll(fd_, line + "\n")) return false;
   std::string r;
-  if (!ReadLine(fd_, &rbuf_, &r, nullptr)) return false;
+  if (!ReadLine(fd_, &rbuf_, &r, nullptr, timeout_ms)) {
+    // The reply may still arrive later and would be taken for the answer to the next
+    // request: this connection is no longer usable.
+    close(fd_);
+    fd_ = -1;
+    return false;
+  }
   if (r.compare(0, 2, "OK") != 0) {
     SML_LOG(ERROR) << "controller replied: " << r << " (to '" << line.substr(0, 60) << "')";
     return false;
@@ -404,9 +421,9 @@ bool ControlClient::RoundTrip(const std::string& line, std::string* reply) {
   return true;
 }
 
-bool ControlClient::Barrier(int n) {
+bool ControlClient::Barrier(int n, int timeout_ms) {
   std::string r;
-  return RoundTrip("BARRIER " + std::to_string(n), &r);
+  return RoundTrip("BARRIER " + std::to_string(n), &r, timeout_ms);
 }
 
 bool ControlClient::Broadcast(int n, int rank, int root, uint64_t* value) {

@@ -45,6 +45,10 @@ class ControlServer {
   // switch data plane on that UDP port. Returns false if a socket cannot be bound.
   bool Start(const std::string& ip, uint16_t port, uint16_t udp_port = 0);
   void Stop();
+  // Close the listening socket but keep serving the connections that exist. A rank that
+  // restarts right after the final barrier of a shutdown then cannot reach the old server
+  // by accident; it retries until the next one listens.
+  void StopAccepting();
   uint16_t port() const { return port_; }
   uint16_t udp_port() const { return udp_port_; }
   SoftSwitch& soft_switch() { return switch_; }
@@ -71,6 +75,7 @@ class ControlServer {
   uint16_t port_ = 0;
   uint16_t udp_port_ = 0;
   std::atomic<bool> stopping_{false};
+  std::atomic<bool> accepting_{false};
   std::thread accept_thread_;
   std::thread data_thread_;
   std::mutex conn_mu_;
@@ -94,7 +99,9 @@ class ControlClient {
   void Close();
   bool connected() const { return fd_ >= 0; }
 
-  bool Barrier(int num_workers);
+  // Collective calls give up after `timeout_ms` (a peer that never arrives); the
+  // connection is closed then, because a late reply would be misread.
+  bool Barrier(int num_workers, int timeout_ms = 120000);
   bool Broadcast(int num_workers, int rank, int root, uint64_t* value);
   // `token` must not contain whitespace.
   bool AllGather(int num_workers, int rank, const std::string& token, std::vector<std::string>* all);
@@ -105,7 +112,7 @@ class ControlClient {
   bool Command(const std::string& line, std::string* reply);
 
  private:
-  bool RoundTrip(const std::string& line, std::string* reply);
+  bool RoundTrip(const std::string& line, std::string* reply, int timeout_ms = 120000);
   int fd_ = -1;
   std::string rbuf_;
   std::mutex mu_;

@@ -48,8 +48,14 @@ def test_peer_memory_transport(mode):
 
 
 @pytest.mark.parametrize("mode", ["int32_quant", "float_sum"])
-def test_auto_transport_prefers_multimem(mode):
-    reps = _run("auto", mode, launch="worker")
+def test_multimem_transport(mode):
+    reps = _run("nvls", mode, launch="worker")
+    assert all(r["multimem"] for r in reps.values())
+    assert all(r["stats"]["jobs_failed"] == 0 for r in reps.values())
+
+
+def test_auto_transport_agrees_on_all_ranks():
+    reps = _run("auto", "float_sum")
     # Whatever the fabric offers, all ranks must agree and every case must pass.
     assert len({r["multimem"] for r in reps.values()}) == 1
     assert all(r["stats"]["jobs_failed"] == 0 for r in reps.values())
