@@ -195,8 +195,6 @@ void CudaBackend::SetupWorker() {
   ctx_.rank = rank_;
   ctx_.nranks = n_;
   ctx_.slot_bytes = c.slot_bytes;
-  SML_CHECK(c.slot_bytes / 4 / g.packet_numel <= 8192)
-      << "backend.cuda.slot_bytes / packet_numel is too large (at most 8192 blocks per slot)";
   ctx_.slots_per_channel = c.slots_per_channel;
   ctx_.block_numel = static_cast<int>(g.packet_numel);
   ctx_.oneshot_bytes = (c.oneshot_max_bytes + 255) / 256 * 256;
@@ -526,6 +524,8 @@ int EmulatedAllReduce(int nranks, void* const* in_ptrs, void* const* out_ptrs,
   };
   if (nranks < 1 || nranks > kMaxRanks) return fail("nranks out of range", -1);
   if (algo == ALGO_ZEROCOPY) return fail("zero-copy needs real symmetric memory", -1);
+  if (slot_bytes / 4 / block_numel * slots_per_channel > 8192)
+    return fail("slots_per_channel * slot_bytes / (4 * block_numel) exceeds 8192", -1);
   int dev = 0;
   cudaGetDevice(&dev);
   cudaDeviceProp prop;

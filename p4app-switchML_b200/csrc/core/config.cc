@@ -268,8 +268,9 @@ void Config::Validate() {
                        << rounded << " (multiple of num_workers*max(packet_numel,128)*4)";
       c.slot_bytes = rounded;
     }
-    SML_CHECK(c.slot_bytes / 4 / g.packet_numel <= 8192)
-        << "backend.cuda.slot_bytes may hold at most 8192 quantisation blocks";
+    SML_CHECK(c.slot_bytes / 4 / g.packet_numel * c.slots_per_channel <= 8192)
+        << "backend.cuda: slots_per_channel * slot_bytes / (4 * packet_numel) may be at most 8192 "
+           "(scale factors of a channel's slots live in shared memory)";
     SML_CHECK(c.wait_timeout_ms > 0) << "backend.cuda.wait_timeout_ms must be positive";
     SML_CHECK(g.num_workers <= 8) << "the cuda backend serves at most 8 GPUs (one NVSwitch domain)";
   }

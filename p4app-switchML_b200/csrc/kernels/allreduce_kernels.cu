@@ -35,8 +35,9 @@ namespace kernels {
 
 namespace {
 
-static const int kMaxBlocksPerSlot = 8192;  // scale factors kept in shared memory
+static const int kMaxBlocksPerSlot = 8192;  // scale factors of all slots of a channel (shared memory)
 static const int kUnroll = 4;
+static const int kUnrollInt = 8;
 
 __device__ __forceinline__ bool Aligned16(const void* p) {
   return (reinterpret_cast<uintptr_t>(p) & 15) == 0;
@@ -60,42 +61,6 @@ __device__ __forceinline__ float Bf16ToFloat(unsigned short u) {
 __device__ __forceinline__ unsigned short FloatToBf16(float f) {
   __nv_bfloat16 h = __float2bfloat16_rn(f);
   return *reinterpret_cast<unsigned short*>(&h);
-}
-
-// Plain byte-wise identical copy of `bytes` bytes (multiple of the element size `esz`).
-__device__ __forceinline__ void CopyBytes(void* dst, const void* src, size_t bytes, int esz) {
-  if (Aligned16(dst) && Aligned16(src)) {
-    size_t nvec = bytes / 16;
-    const uint4* s = reinterpret_cast<const uint4*>(src);
-    uint4* d = reinterpret_cast<uint4*>(dst);
-    size_t i = threadIdx.x;
-    for (; i + (kUnroll - 1) * blockDim.x < nvec; i += kUnroll * blockDim.x) {
-      uint4 v[kUnroll];
-#pragma unroll
-      for (int u = 0; u < kUnroll; u++) v[u] = s[i + u * blockDim.x];
-#pragma unroll
-      for (int u = 0; u < kUnroll; u++) d[i + u * blockDim.x] = v[u];
-    }
-    for (; i < nvec; i += blockDim.x) d[i] = s[i];
-    size_t done = nvec * 16;
-    if (esz == 4) {
-      for (size_t b = done + threadIdx.x * 4; b < bytes; b += blockDim.x * 4)
-        *reinterpret_cast<unsigned*>(static_cast<char*>(dst) + b) =
-            *reinterpret_cast<const unsigned*>(static_cast<const char*>(src) + b);
-    } else {
-      for (size_t b = done + threadIdx.x * 2; b < bytes; b += blockDim.x * 2)
-        *reinterpret_cast<unsigned short*>(static_cast<char*>(dst) + b) =
-            *reinterpret_cast<const unsigned short*>(static_cast<const char*>(src) + b);
-    }
-  } else if (esz == 4) {
-    const unsigned* s = reinterpret_cast<const unsigned*>(src);
-    unsigned* d = reinterpret_cast<unsigned*>(dst);
-    for (size_t i = threadIdx.x; i < bytes / 4; i += blockDim.x) d[i] = s[i];
-  } else {
-    const unsigned short* s = reinterpret_cast<const unsigned short*>(src);
-    unsigned short* d = reinterpret_cast<unsigned short*>(dst);
-    for (size_t i = threadIdx.x; i < bytes / 2; i += blockDim.x) d[i] = s[i];
-  }
 }
 
 // Element `i` of the input as float (QUANT mode reads f32 or bf16).
@@ -185,12 +150,6 @@ __device__ __forceinline__ void BroadcastVec(const RankCtx& ctx, char* const* pe
   }
 }
 
-// Integer-sum one vector of quantised values over all ranks.
-__device__ __forceinline__ uint4 ReduceQuantVec(const RankCtx& ctx, char* const* peers, char* mc,
-                                                size_t off) {
-  return ReduceVec<ELEM_I32>(ctx, peers, mc, off, 1.0f);
-}
-
 // Shard [begin,end) (elements) of a tile that has `len` elements; units of `unit`.
 __device__ __forceinline__ void ShardRange(size_t len, int nranks, int rank, size_t unit,
                                            size_t* begin, size_t* end) {
@@ -202,148 +161,315 @@ __device__ __forceinline__ void ShardRange(size_t len, int nranks, int rank, siz
 }
 
 // ------------------------------------------------------------------------------------
+// Warp-specialised streaming pipeline. The 16 warps of a channel split into three roles
+// that walk the channel's tiles independently, so that for different tiles the local
+// HBM copies and the NVLink phase run at the same time:
+//   loader  (warps 0-5)   copy-in (SUM) / exponents + quantise (QUANT)  -> signals phase 1
+//   reducer (warps 6-11)  waits phase 1, reduces + broadcasts its shard  -> signals phase 2
+//   storer  (warps 12-15) waits phase 2, copies the finished tile out    -> frees the slot
+// A role synchronises internally with its own named barrier; the loader may run ahead of
+// the storer by the number of slots of the channel.
+static const int kLoadWarps = 6, kReduceWarps = 6, kStoreWarps = 4;
+
+struct StagedShared {
+  int failed;
+  volatile unsigned long long stored;  // tiles copied out so far
+};
+
+struct Role {
+  int tid;       // thread index inside the role
+  int nthreads;  // threads of the role
+  int bar_id;    // named barrier of the role
+  __device__ __forceinline__ void Sync() const {
+    asm volatile("bar.sync %0, %1;" ::"r"(bar_id), "r"(nthreads) : "memory");
+  }
+};
+
+// All threads of the role call this after writing data the peers will read.
+__device__ __forceinline__ void RoleSignal(const RankCtx& ctx, const Role& role, int channel,
+                                           int phase, Epoch epoch) {
+  role.Sync();
+  if (role.tid < ctx.nranks) {
+    __threadfence_system();
+    StoreReleaseSys(FlagPtr(ctx.stage_peer[role.tid], channel, phase, ctx.rank), epoch);
+  }
+}
+
+// All threads of the role call this before reading data the peers wrote. False = timed
+// out or another role failed.
+__device__ __forceinline__ bool RoleWait(const RankCtx& ctx, const Role& role, int channel,
+                                         int phase, Epoch epoch, StagedShared* sh) {
+  if (role.tid < ctx.nranks) {
+    const Epoch* mine = FlagPtr(ctx.stage_peer[ctx.rank], channel, phase, role.tid);
+    unsigned long long start = GlobalTimerNs();
+    unsigned long long spins = 0;
+    while (LoadAcquireSys(mine) < epoch) {
+      ++spins;
+      if ((spins & 63) == 0) {
+        if (*reinterpret_cast<volatile int*>(&sh->failed)) break;
+        if (GlobalTimerNs() - start > ctx.timeout_ns) {
+          atomicCAS(ctx.status, STATUS_OK, STATUS_TIMEOUT | (phase << 4) | (channel << 8));
+          atomicAdd(ctx.counters + 2, 1ull);
+          *reinterpret_cast<volatile int*>(&sh->failed) = 1;
+          break;
+        }
+      }
+      __nanosleep(20);
+    }
+    if (spins) atomicAdd(ctx.counters + 1, spins);
+  }
+  role.Sync();
+  return *reinterpret_cast<volatile int*>(&sh->failed) == 0;
+}
+
+// Byte-wise identical copy by the threads of one role.
+__device__ __forceinline__ void RoleCopy(const Role& role, void* dst, const void* src, size_t bytes,
+                                         int esz) {
+  const int t = role.tid, n = role.nthreads;
+  if (Aligned16(dst) && Aligned16(src)) {
+    size_t nvec = bytes / 16;
+    const uint4* s = reinterpret_cast<const uint4*>(src);
+    uint4* d = reinterpret_cast<uint4*>(dst);
+    size_t i = t;
+    for (; i + (kUnroll - 1) * n < nvec; i += kUnroll * n) {
+      uint4 v[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; u++) v[u] = s[i + u * n];
+#pragma unroll
+      for (int u = 0; u < kUnroll; u++) d[i + u * n] = v[u];
+    }
+    for (; i < nvec; i += n) d[i] = s[i];
+    for (size_t b = nvec * 16 + static_cast<size_t>(t) * esz; b < bytes; b += static_cast<size_t>(n) * esz) {
+      if (esz == 4) *reinterpret_cast<unsigned*>(static_cast<char*>(dst) + b) = *reinterpret_cast<const unsigned*>(static_cast<const char*>(src) + b);
+      else *reinterpret_cast<unsigned short*>(static_cast<char*>(dst) + b) = *reinterpret_cast<const unsigned short*>(static_cast<const char*>(src) + b);
+    }
+  } else if (esz == 4) {
+    const unsigned* s = reinterpret_cast<const unsigned*>(src);
+    unsigned* d = reinterpret_cast<unsigned*>(dst);
+    for (size_t i = t; i < bytes / 4; i += n) d[i] = s[i];
+  } else {
+    const unsigned short* s = reinterpret_cast<const unsigned short*>(src);
+    unsigned short* d = reinterpret_cast<unsigned short*>(dst);
+    for (size_t i = t; i < bytes / 2; i += n) d[i] = s[i];
+  }
+}
+
 template <int ELEM, int MODE>
 __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
-                          unsigned long long elems_per_channel, int* s_failed, float* s_sf) {
+                          unsigned long long elems_per_channel, StagedShared* sh, float* s_sf) {
   const int in_esz = ELEM == ELEM_BF16 ? 2 : 4;
   const int st_esz = MODE == MODE_QUANT ? 4 : in_esz;
   const size_t slot_elems = ctx.slot_bytes / st_esz;
   const size_t vec_elems = 16 / st_esz;
   const size_t unit = MODE == MODE_QUANT ? static_cast<size_t>(ctx.block_numel) : 128;
+  const int S = ctx.slots_per_channel;
 
   unsigned long long c0 = static_cast<unsigned long long>(channel) * elems_per_channel;
   if (c0 >= job.numel) return;
   unsigned long long c1 = c0 + elems_per_channel;
   if (c1 > job.numel) c1 = job.numel;
-
+  const size_t tile_elems = job.tile_elems;  // <= slot_elems; small jobs use small tiles
+  const unsigned long long ntiles = (c1 - c0 + tile_elems - 1) / tile_elems;
   char* my_stage = ctx.stage_peer[ctx.rank];
   const size_t blocks_per_slot = slot_elems / ctx.block_numel;
-  unsigned long long k = 0;
-  const size_t tile_elems = job.tile_elems;  // <= slot_elems; small jobs use small tiles
-  for (unsigned long long pos = c0; pos < c1; pos += tile_elems, ++k) {
-    const unsigned long long epoch = job.epoch_base + k + 1;
-    const size_t len = static_cast<size_t>(c1 - pos < tile_elems ? c1 - pos : tile_elems);
-    const int slot = static_cast<int>(k % ctx.slots_per_channel);
-    const size_t slot_index = static_cast<size_t>(channel) * ctx.slots_per_channel + slot;
-    const size_t slot_off = ctx.data_offset + slot_index * ctx.slot_bytes;  // same on all ranks
-    const char* in = static_cast<const char*>(job.in) + pos * in_esz;
-    char* out = static_cast<char*>(job.out) + pos * in_esz;
+  const int shift = 31 - __clz(ctx.block_numel);  // block_numel is a power of two
 
-    if (MODE == MODE_QUANT) {
-      // ---- A: exponents of my blocks ----
-      const size_t nblocks = (len + ctx.block_numel - 1) / ctx.block_numel;
-      const size_t exp_off = ctx.exp_offset + slot_index * blocks_per_slot * 4;
-      int* my_exp = reinterpret_cast<int*>(my_stage + exp_off);
-      const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-      for (size_t b = warp; b < nblocks; b += nwarps) {
-        size_t base = b * ctx.block_numel;
-        size_t n = len - base < static_cast<size_t>(ctx.block_numel) ? len - base : ctx.block_numel;
-        float m = 0.f;
-        for (size_t i = lane; i < n; i += 32) {
-          float v = fabsf(LoadAsFloat<ELEM>(in, base + i));
-          if (v > m) m = v;
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-          float t = __shfl_xor_sync(0xffffffffu, m, o);
-          if (t > m) m = t;
-        }
-        if (lane == 0) my_exp[b] = quant::LocalExponent(m);
-      }
-      if (!ChannelBarrier(ctx, channel, 0, epoch, s_failed)) return;
-      // ---- global exponents -> scale factors ----
-      for (size_t b = threadIdx.x; b < nblocks; b += blockDim.x) {
-        int e;
-        if (ctx.use_multimem) {
-          e = MultimemLdReduceMaxS32(ctx.stage_mc + exp_off + b * 4);
-        } else {
-          e = quant::kZeroExponent;
-          for (int p = 0; p < ctx.nranks; p++) {
-            int t = __ldcg(reinterpret_cast<const int*>(ctx.stage_peer[p] + exp_off) + b);
-            if (t > e) e = t;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  Role role;
+  int which;
+  if (warp < kLoadWarps) {
+    which = 0; role.tid = threadIdx.x; role.nthreads = kLoadWarps * 32; role.bar_id = 1;
+  } else if (warp < kLoadWarps + kReduceWarps) {
+    which = 1; role.tid = threadIdx.x - kLoadWarps * 32; role.nthreads = kReduceWarps * 32; role.bar_id = 2;
+  } else {
+    which = 2; role.tid = threadIdx.x - (kLoadWarps + kReduceWarps) * 32; role.nthreads = kStoreWarps * 32; role.bar_id = 3;
+  }
+  volatile int* failed = reinterpret_cast<volatile int*>(&sh->failed);
+
+  for (unsigned long long k = 0; k < ntiles; ++k) {
+    const unsigned long long pos = c0 + k * tile_elems;
+    const Epoch epoch = job.epoch_base + k + 1;
+    const size_t len = static_cast<size_t>(c1 - pos < tile_elems ? c1 - pos : tile_elems);
+    const int slot = static_cast<int>(k % S);
+    const size_t slot_index = static_cast<size_t>(channel) * S + slot;
+    const size_t slot_off = ctx.data_offset + slot_index * ctx.slot_bytes;  // same on all ranks
+    const size_t exp_off = ctx.exp_offset + slot_index * blocks_per_slot * 4;
+    float* sf = s_sf + static_cast<size_t>(slot) * blocks_per_slot;
+
+    if (which == 0) {
+      // ------------------------------ loader ------------------------------
+      // The slot is free once the tile that used it last has been copied out here; by
+      // then every peer has finished reading it as well (their phase-2 signals came
+      // before that copy-out).
+      if (k >= static_cast<unsigned long long>(S)) {
+        if (role.tid == 0) {
+          unsigned long long start = GlobalTimerNs(), spins = 0;
+          while (sh->stored + S < k + 1) {
+            if ((++spins & 63) == 0 && (*failed || GlobalTimerNs() - start > ctx.timeout_ns)) {
+              if (!*failed) atomicCAS(ctx.status, STATUS_OK, STATUS_TIMEOUT | (3 << 4) | (channel << 8));
+              *failed = 1;
+              break;
+            }
+            __nanosleep(20);
           }
         }
-        s_sf[b] = quant::ScaleFactor(e, ctx.nranks);
+        role.Sync();
+        if (*failed) return;
       }
-      __syncthreads();
-      // ---- quantise my tile into the slot ----
-      int* q = reinterpret_cast<int*>(my_stage + slot_off);
-      const int shift = 31 - __clz(ctx.block_numel);  // block_numel is a power of two
-      if (ELEM == ELEM_F32 && Aligned16(in)) {
-        const float4* in4 = reinterpret_cast<const float4*>(in);
-        size_t nvec = len / 4;
-        for (size_t i = threadIdx.x; i < nvec; i += blockDim.x) {
-          float4 x = in4[i];
-          float sf = s_sf[(i * 4) >> shift];  // a vector never straddles a block (>= 32)
-          int4 r;
-          r.x = quant::Quantize(x.x, sf);
-          r.y = quant::Quantize(x.y, sf);
-          r.z = quant::Quantize(x.z, sf);
-          r.w = quant::Quantize(x.w, sf);
-          reinterpret_cast<int4*>(q)[i] = r;
+      const char* in = static_cast<const char*>(job.in) + pos * in_esz;
+      if (MODE == MODE_QUANT) {
+        const size_t nblocks = (len + ctx.block_numel - 1) / ctx.block_numel;
+        int* my_exp = reinterpret_cast<int*>(my_stage + exp_off);
+        const int nwarps = kLoadWarps;
+        for (size_t b = warp; b < nblocks; b += nwarps) {
+          size_t base = b * ctx.block_numel;
+          size_t n = len - base < static_cast<size_t>(ctx.block_numel) ? len - base : ctx.block_numel;
+          float m = 0.f;
+          for (size_t i = lane; i < n; i += 32) {
+            float v = fabsf(LoadAsFloat<ELEM>(in, base + i));
+            if (v > m) m = v;
+          }
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) {
+            float t = __shfl_xor_sync(0xffffffffu, m, o);
+            if (t > m) m = t;
+          }
+          if (lane == 0) my_exp[b] = quant::LocalExponent(m);
         }
-        for (size_t i = nvec * 4 + threadIdx.x; i < len; i += blockDim.x)
-          q[i] = quant::Quantize(reinterpret_cast<const float*>(in)[i], s_sf[i >> shift]);
+        RoleSignal(ctx, role, channel, 0, epoch);
+        if (!RoleWait(ctx, role, channel, 0, epoch, sh)) return;
+        for (size_t b = role.tid; b < nblocks; b += role.nthreads) {
+          int e;
+          if (ctx.use_multimem) {
+            e = MultimemLdReduceMaxS32(ctx.stage_mc + exp_off + b * 4);
+          } else {
+            e = quant::kZeroExponent;
+            for (int p = 0; p < ctx.nranks; p++) {
+              int t = __ldcg(reinterpret_cast<const int*>(ctx.stage_peer[p] + exp_off) + b);
+              if (t > e) e = t;
+            }
+          }
+          sf[b] = quant::ScaleFactor(e, ctx.nranks);
+        }
+        role.Sync();
+        int* q = reinterpret_cast<int*>(my_stage + slot_off);
+        if (ELEM == ELEM_F32 && Aligned16(in)) {
+          const float4* in4 = reinterpret_cast<const float4*>(in);
+          size_t nvec = len / 4;
+          for (size_t i = role.tid; i < nvec; i += role.nthreads) {
+            float4 x = in4[i];
+            float f = sf[(i * 4) >> shift];  // a vector never straddles a block (>= 32)
+            int4 r;
+            r.x = quant::Quantize(x.x, f);
+            r.y = quant::Quantize(x.y, f);
+            r.z = quant::Quantize(x.z, f);
+            r.w = quant::Quantize(x.w, f);
+            reinterpret_cast<int4*>(q)[i] = r;
+          }
+          for (size_t i = nvec * 4 + role.tid; i < len; i += role.nthreads)
+            q[i] = quant::Quantize(reinterpret_cast<const float*>(in)[i], sf[i >> shift]);
+        } else {
+          for (size_t i = role.tid; i < len; i += role.nthreads)
+            q[i] = quant::Quantize(LoadAsFloat<ELEM>(in, i), sf[i >> shift]);
+        }
       } else {
-        for (size_t i = threadIdx.x; i < len; i += blockDim.x)
-          q[i] = quant::Quantize(LoadAsFloat<ELEM>(in, i), s_sf[i >> shift]);
+        RoleCopy(role, my_stage + slot_off, in, len * in_esz, in_esz);
       }
-    } else {
-      CopyBytes(my_stage + slot_off, in, len * in_esz, in_esz);
-    }
-    if (!ChannelBarrier(ctx, channel, 1, epoch, s_failed)) return;
-
-    // ---- B: reduce and broadcast my shard ----
-    {
+      RoleSignal(ctx, role, channel, 1, epoch);
+    } else if (which == 1) {
+      // ------------------------------ reducer ------------------------------
+      if (!RoleWait(ctx, role, channel, 1, epoch, sh)) return;
       size_t sb, se;
       ShardRange(len, ctx.nranks, ctx.rank, unit, &sb, &se);
-      size_t v0 = sb / vec_elems, v1 = (se + vec_elems - 1) / vec_elems;
-      if (MODE == MODE_QUANT) {
-        const int shift = 31 - __clz(ctx.block_numel);
-        for (size_t v = v0 + threadIdx.x; v < v1; v += blockDim.x) {
-          size_t off = slot_off + v * 16;
-          uint4 s = ReduceQuantVec(ctx, ctx.stage_peer, ctx.stage_mc, off);
-          float sf = s_sf[(v * 4) >> shift];
-          float4 y;
-          y.x = quant::Dequantize(static_cast<int>(s.x), sf);
-          y.y = quant::Dequantize(static_cast<int>(s.y), sf);
-          y.z = quant::Dequantize(static_cast<int>(s.z), sf);
-          y.w = quant::Dequantize(static_cast<int>(s.w), sf);
-          if (job.post_scale != 1.0f) { y.x *= job.post_scale; y.y *= job.post_scale; y.z *= job.post_scale; y.w *= job.post_scale; }
-          BroadcastVec(ctx, ctx.stage_peer, ctx.stage_mc, off,
-                       make_uint4(__float_as_uint(y.x), __float_as_uint(y.y), __float_as_uint(y.z), __float_as_uint(y.w)));
+      const int t = role.tid, n = role.nthreads;
+      // An empty shard (short last tile) must not touch anything: rounding its bounds to
+      // whole vectors would make it overlap the last vector of the previous rank's shard.
+      if (sb >= se) {
+      } else if (MODE == MODE_QUANT || ELEM == ELEM_I32) {
+        if (ctx.use_multimem) {
+          // Integer in-switch adds are one 32-bit lane per instruction: let consecutive
+          // lanes take consecutive words so that a warp moves one full 128-byte line.
+          char* mc = ctx.stage_mc + slot_off;
+          size_t i = sb + t;
+          for (; i + (kUnrollInt - 1) * n < se; i += kUnrollInt * n) {
+            int v[kUnrollInt];
+#pragma unroll
+            for (int u = 0; u < kUnrollInt; u++) v[u] = MultimemLdReduceAddS32(mc + (i + u * n) * 4);
+#pragma unroll
+            for (int u = 0; u < kUnrollInt; u++) {
+              unsigned bits = static_cast<unsigned>(v[u]);
+              if (MODE == MODE_QUANT) {
+                float y = quant::Dequantize(v[u], sf[(i + u * n) >> shift]);
+                if (job.post_scale != 1.0f) y *= job.post_scale;
+                bits = __float_as_uint(y);
+              }
+              MultimemStore4(mc + (i + u * n) * 4, bits);
+            }
+          }
+          for (; i < se; i += n) {
+            int v = MultimemLdReduceAddS32(mc + i * 4);
+            unsigned bits = static_cast<unsigned>(v);
+            if (MODE == MODE_QUANT) {
+              float y = quant::Dequantize(v, sf[i >> shift]);
+              if (job.post_scale != 1.0f) y *= job.post_scale;
+              bits = __float_as_uint(y);
+            }
+            MultimemStore4(mc + i * 4, bits);
+          }
+        } else {
+          size_t v0 = sb / 4, v1 = (se + 3) / 4;
+          for (size_t v = v0 + t; v < v1; v += n) {
+            size_t off = slot_off + v * 16;
+            uint4 s = ReduceVec<ELEM_I32>(ctx, ctx.stage_peer, ctx.stage_mc, off, 1.0f);
+            if (MODE == MODE_QUANT) {
+              float f = sf[(v * 4) >> shift];
+              float4 y;
+              y.x = quant::Dequantize(static_cast<int>(s.x), f);
+              y.y = quant::Dequantize(static_cast<int>(s.y), f);
+              y.z = quant::Dequantize(static_cast<int>(s.z), f);
+              y.w = quant::Dequantize(static_cast<int>(s.w), f);
+              if (job.post_scale != 1.0f) { y.x *= job.post_scale; y.y *= job.post_scale; y.z *= job.post_scale; y.w *= job.post_scale; }
+              s = make_uint4(__float_as_uint(y.x), __float_as_uint(y.y), __float_as_uint(y.z), __float_as_uint(y.w));
+            }
+            BroadcastVec(ctx, ctx.stage_peer, ctx.stage_mc, off, s);
+          }
         }
       } else {
-        size_t v = v0 + threadIdx.x;
-        for (; v + (kUnroll - 1) * blockDim.x < v1; v += kUnroll * blockDim.x) {
+        size_t v0 = sb / vec_elems, v1 = (se + vec_elems - 1) / vec_elems;
+        size_t v = v0 + t;
+        for (; v + (kUnroll - 1) * n < v1; v += kUnroll * n) {
           uint4 r[kUnroll];
 #pragma unroll
           for (int u = 0; u < kUnroll; u++)
-            r[u] = ReduceVec<ELEM>(ctx, ctx.stage_peer, ctx.stage_mc, slot_off + (v + u * blockDim.x) * 16, job.post_scale);
+            r[u] = ReduceVec<ELEM>(ctx, ctx.stage_peer, ctx.stage_mc, slot_off + (v + u * n) * 16, job.post_scale);
 #pragma unroll
           for (int u = 0; u < kUnroll; u++)
-            BroadcastVec(ctx, ctx.stage_peer, ctx.stage_mc, slot_off + (v + u * blockDim.x) * 16, r[u]);
+            BroadcastVec(ctx, ctx.stage_peer, ctx.stage_mc, slot_off + (v + u * n) * 16, r[u]);
         }
-        for (; v < v1; v += blockDim.x) {
+        for (; v < v1; v += n) {
           uint4 r = ReduceVec<ELEM>(ctx, ctx.stage_peer, ctx.stage_mc, slot_off + v * 16, job.post_scale);
           BroadcastVec(ctx, ctx.stage_peer, ctx.stage_mc, slot_off + v * 16, r);
         }
       }
-    }
-    if (!ChannelBarrier(ctx, channel, 2, epoch, s_failed)) return;
-
-    // ---- C: copy the finished tile out ----
-    if (MODE == MODE_QUANT && ELEM == ELEM_BF16) {
-      const float* y = reinterpret_cast<const float*>(my_stage + slot_off);
-      unsigned short* o = reinterpret_cast<unsigned short*>(out);
-      for (size_t i = threadIdx.x; i < len; i += blockDim.x) o[i] = FloatToBf16(y[i]);
+      RoleSignal(ctx, role, channel, 2, epoch);
     } else {
-      CopyBytes(out, my_stage + slot_off, len * in_esz, in_esz);
+      // ------------------------------ storer ------------------------------
+      if (!RoleWait(ctx, role, channel, 2, epoch, sh)) return;
+      char* out = static_cast<char*>(job.out) + pos * in_esz;
+      if (MODE == MODE_QUANT && ELEM == ELEM_BF16) {
+        const float* y = reinterpret_cast<const float*>(my_stage + slot_off);
+        unsigned short* o = reinterpret_cast<unsigned short*>(out);
+        for (size_t i = role.tid; i < len; i += role.nthreads) o[i] = FloatToBf16(y[i]);
+      } else {
+        RoleCopy(role, out, my_stage + slot_off, len * in_esz, in_esz);
+      }
+      role.Sync();
+      if (role.tid == 0) {
+        __threadfence_block();
+        sh->stored = k + 1;
+        atomicAdd(ctx.counters, 1ull);
+      }
     }
-    if (threadIdx.x == 0) atomicAdd(ctx.counters, 1ull);
-    // The next use of this slot (tile k + slots_per_channel) writes it only after this
-    // copy-out, because the same threads do both, separated by the barrier's syncs.
-    __syncthreads();
   }
 }
 
@@ -465,10 +591,12 @@ __device__ void RunZeroCopy(const RankCtx& ctx, const JobArgs& job, int channel,
     const size_t len = static_cast<size_t>(c1 - c0);
     size_t sb, se;
     ShardRange(len, ctx.nranks, ctx.rank, 128, &sb, &se);
+    if (sb >= se) sb = se = 0;  // empty shard: nothing to do, and no unsigned wrap below
     // Whole vectors of my shard; the ragged end of the range (fewer than one vector, only
     // in the last channel) is done element-wise by the rank that owns the last shard.
     size_t full_end = se / vec_elems * vec_elems;
     if (se < len) full_end = se;  // interior shard boundaries are multiples of 128 elements
+    if (full_end < sb) full_end = sb;
     const bool inplace = job.in_offset == job.out_offset;
     size_t in_base = job.in_offset + (c0 + sb) * esz;
     size_t out_base = job.out_offset + (c0 + sb) * esz;
@@ -519,7 +647,7 @@ __device__ void RunZeroCopy(const RankCtx& ctx, const JobArgs& job, int channel,
 template <int ELEM, int MODE, int ALGO>
 __device__ __forceinline__ void RunJob(const RankCtx& ctx, const JobArgs& job, int channel,
                                        unsigned long long epc, int* s_failed, float* s_sf) {
-  if (ALGO == ALGO_STAGED) RunStaged<ELEM, MODE>(ctx, job, channel, epc, s_failed, s_sf);
+  if (ALGO == ALGO_STAGED) RunStaged<ELEM, MODE>(ctx, job, channel, epc, reinterpret_cast<StagedShared*>(s_failed), s_sf);
   else if (ALGO == ALGO_ONESHOT) RunOneShot<ELEM, MODE>(ctx, job, channel, epc, s_failed);
   else RunZeroCopy<ELEM>(ctx, job, channel, epc, s_failed);
 }
@@ -527,28 +655,29 @@ __device__ __forceinline__ void RunJob(const RankCtx& ctx, const JobArgs& job, i
 template <int ELEM, int MODE, int ALGO>
 __global__ void __launch_bounds__(kThreads)
 AllReduceKernel(const RankCtx ctx, const JobArgs job, unsigned long long epc) {
-  __shared__ int s_failed;
+  __shared__ StagedShared s_state;
   __shared__ float s_sf[(MODE == MODE_QUANT && ALGO == ALGO_STAGED) ? kMaxBlocksPerSlot : 1];
-  if (threadIdx.x == 0) s_failed = 0;
+  if (threadIdx.x == 0) { s_state.failed = 0; s_state.stored = 0; }
   __syncthreads();
-  RunJob<ELEM, MODE, ALGO>(ctx, job, blockIdx.x, epc, &s_failed, s_sf);
+  RunJob<ELEM, MODE, ALGO>(ctx, job, blockIdx.x, epc, &s_state.failed, s_sf);
 }
 
 // All ranks in one grid: blockIdx.y selects the rank whose role this CTA plays.
 template <int ELEM, int MODE, int ALGO>
 __global__ void __launch_bounds__(kThreads)
 AllReduceEmuKernel(const RankCtx* ctxs, const JobArgs* jobs, unsigned long long epc) {
-  __shared__ int s_failed;
+  __shared__ StagedShared s_state;
   __shared__ float s_sf[(MODE == MODE_QUANT && ALGO == ALGO_STAGED) ? kMaxBlocksPerSlot : 1];
   __shared__ RankCtx s_ctx;
   __shared__ JobArgs s_job;
   if (threadIdx.x == 0) {
-    s_failed = 0;
+    s_state.failed = 0;
+    s_state.stored = 0;
     s_ctx = ctxs[blockIdx.y];
     s_job = jobs[blockIdx.y];
   }
   __syncthreads();
-  RunJob<ELEM, MODE, ALGO>(s_ctx, s_job, blockIdx.x, epc, &s_failed, s_sf);
+  RunJob<ELEM, MODE, ALGO>(s_ctx, s_job, blockIdx.x, epc, &s_state.failed, s_sf);
 }
 
 __global__ void WaitProbeKernel(const RankCtx ctx) {

@@ -44,6 +44,10 @@ __device__ __forceinline__ void MultimemStore16(void* mc, uint4 v) {
                  "f"(__uint_as_float(v.z)), "f"(__uint_as_float(v.w)) : "memory");
 }
 
+__device__ __forceinline__ void MultimemStore4(void* mc, unsigned v) {
+  asm volatile("multimem.st.relaxed.sys.global.b32 [%0], %1;" ::"l"(mc), "r"(v) : "memory");
+}
+
 }  // namespace kernels
 }  // namespace switchml
 #endif  // SWITCHML_MULTIMEM_CUH_
