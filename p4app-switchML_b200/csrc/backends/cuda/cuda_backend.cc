@@ -227,12 +227,13 @@ void CudaBackend::SetupWorker() {
   int lo = 0, hi = 0;
   cudaDeviceGetStreamPriorityRange(&lo, &hi);
   SML_CUDA_CHECK(cudaStreamCreateWithPriority(&comm_stream_, cudaStreamNonBlocking, hi));
-  SML_CUDA_CHECK(cudaMalloc(&dev_status_, sizeof(int)));
-  SML_CUDA_CHECK(cudaMalloc(&dev_counters_, 8 * sizeof(unsigned long long)));
-  SML_CUDA_CHECK(cudaMemset(dev_status_, 0, sizeof(int)));
-  SML_CUDA_CHECK(cudaMemset(dev_counters_, 0, 8 * sizeof(unsigned long long)));
-  SML_CUDA_CHECK(cudaHostAlloc(&host_status_, kStatusSlots * sizeof(int), cudaHostAllocDefault));
+  SML_CUDA_CHECK(cudaMalloc(&dev_counters_, 16 * sizeof(unsigned long long)));
+  SML_CUDA_CHECK(cudaMemset(dev_counters_, 0, 16 * sizeof(unsigned long long)));
+  // Status words live in pinned host memory that the device can write: a kernel stores
+  // its error code there directly, so a job costs no extra copy or memset on the stream.
+  SML_CUDA_CHECK(cudaHostAlloc(&host_status_, kStatusSlots * sizeof(int), cudaHostAllocMapped));
   memset(host_status_, 0, kStatusSlots * sizeof(int));
+  SML_CUDA_CHECK(cudaHostGetDevicePointer(reinterpret_cast<void**>(&dev_status_), host_status_, 0));
   ctx_.status = dev_status_;
   ctx_.counters = dev_counters_;
   epoch_base_ = 0;
@@ -272,7 +273,6 @@ void CudaBackend::CleanupWorker() {
   if (staging_.local) allocator_->Destroy(&staging_, peers_alive);
   if (comm_stream_) cudaStreamDestroy(comm_stream_);
   comm_stream_ = nullptr;
-  if (dev_status_) cudaFree(dev_status_);
   if (dev_counters_) cudaFree(dev_counters_);
   if (host_status_) cudaFreeHost(host_status_);
   dev_status_ = nullptr;
@@ -348,13 +348,10 @@ void CudaBackend::LaunchJob(const std::shared_ptr<Job>& job, cudaStream_t stream
   f->done = GetEvent();
 
   cudaError_t e = cudaSuccess;
-  if (t.numel > 0) e = kernels::LaunchAllReduce(ctx_, a, plan, stream);
-  if (e == cudaSuccess) {
-    // Bring the status word home and clear it for the next job, in stream order.
-    e = cudaMemcpyAsync(host_status_ + f->status_slot, dev_status_, sizeof(int),
-                        cudaMemcpyDeviceToHost, stream);
-  }
-  if (e == cudaSuccess) e = cudaMemsetAsync(dev_status_, 0, sizeof(int), stream);
+  host_status_[f->status_slot] = kernels::STATUS_OK;  // the ring is far longer than the queue
+  kernels::RankCtx job_ctx = ctx_;
+  job_ctx.status = dev_status_ + f->status_slot;
+  if (t.numel > 0) e = kernels::LaunchAllReduce(job_ctx, a, plan, stream);
   if (e == cudaSuccess) e = cudaEventRecord(f->done, stream);
   if (e != cudaSuccess) {
     f->launch_error = std::string("kernel launch failed: ") + cudaGetErrorString(e);
@@ -448,7 +445,7 @@ void CudaBackend::CompletionLoop() {
         why = std::string("device error: ") + cudaGetErrorString(e);
         failed_ = true;
       } else {
-        int st = host_status_[f.status_slot];
+        int st = *reinterpret_cast<volatile int*>(host_status_ + f.status_slot);
         if (st != kernels::STATUS_OK) {
           ok = false;
           std::ostringstream o;
@@ -478,7 +475,7 @@ void CudaBackend::CompletionLoop() {
 }
 
 std::string CudaBackend::ExtraStatsJson() {
-  unsigned long long c[8] = {0};
+  unsigned long long c[16] = {0};
   if (dev_counters_) {
     cudaSetDevice(device_);
     cudaMemcpy(c, dev_counters_, sizeof(c), cudaMemcpyDeviceToHost);
@@ -486,7 +483,10 @@ std::string CudaBackend::ExtraStatsJson() {
   std::ostringstream o;
   o << "{\"device\":" << device_ << ",\"multimem\":" << (ctx_.use_multimem ? "true" : "false")
     << ",\"tiles\":" << c[0] << ",\"wait_spins\":" << c[1] << ",\"device_timeouts\":" << c[2]
-    << ",\"jobs_launched\":" << launched_jobs_ << ",\"epoch\":" << epoch_base_ << "}";
+    << ",\"jobs_launched\":" << launched_jobs_ << ",\"epoch\":" << epoch_base_
+    << ",\"channel0_ns\":{\"loader_wait\":" << c[3] << ",\"loader_work\":" << c[4]
+    << ",\"reducer_wait\":" << c[5] << ",\"reducer_work\":" << c[6] << ",\"storer_wait\":" << c[7]
+    << ",\"storer_work\":" << c[8] << "}}";
   return o.str();
 }
 
@@ -497,11 +497,12 @@ int CudaBackend::RunWaitProbe(double budget_ms) {
   probe.timeout_ns = static_cast<unsigned long long>(budget_ms * 1e6);
   cudaStream_t s = comm_stream_;
   int st = -1;
+  int slot = static_cast<int>(launched_jobs_++ % kStatusSlots);
+  host_status_[slot] = kernels::STATUS_OK;
+  probe.status = dev_status_ + slot;
   cudaError_t e = kernels::LaunchWaitProbe(probe, s);
-  if (e == cudaSuccess) e = cudaMemcpyAsync(host_status_ + kStatusSlots - 1, dev_status_, sizeof(int), cudaMemcpyDeviceToHost, s);
-  if (e == cudaSuccess) e = cudaMemsetAsync(dev_status_, 0, sizeof(int), s);
   if (e == cudaSuccess) e = cudaStreamSynchronize(s);
-  if (e == cudaSuccess) st = host_status_[kStatusSlots - 1];
+  if (e == cudaSuccess) st = *reinterpret_cast<volatile int*>(host_status_ + slot);
   return e == cudaSuccess ? st : -static_cast<int>(e);
 }
 
@@ -567,8 +568,8 @@ int EmulatedAllReduce(int nranks, void* const* in_ptrs, void* const* out_ptrs,
   }
   if (e == cudaSuccess) e = cudaMalloc(&status, nranks * sizeof(int));
   if (e == cudaSuccess) e = cudaMemset(status, 0, nranks * sizeof(int));
-  if (e == cudaSuccess) e = cudaMalloc(&counters, nranks * 8 * sizeof(unsigned long long));
-  if (e == cudaSuccess) e = cudaMemset(counters, 0, nranks * 8 * sizeof(unsigned long long));
+  if (e == cudaSuccess) e = cudaMalloc(&counters, nranks * 16 * sizeof(unsigned long long));
+  if (e == cudaSuccess) e = cudaMemset(counters, 0, nranks * 16 * sizeof(unsigned long long));
   if (e == cudaSuccess) e = cudaMalloc(&d_ctx, nranks * sizeof(RankCtx));
   if (e == cudaSuccess) e = cudaMalloc(&d_job, nranks * sizeof(JobArgs));
   if (e != cudaSuccess) {
@@ -584,7 +585,7 @@ int EmulatedAllReduce(int nranks, void* const* in_ptrs, void* const* out_ptrs,
       ctxs[r].rank = r;
       for (int p = 0; p < nranks; p++) ctxs[r].stage_peer[p] = stage[p];
       ctxs[r].status = status + r;
-      ctxs[r].counters = counters + r * 8;
+      ctxs[r].counters = counters + r * 16;
       JobArgs& j = jobs[r];
       memset(&j, 0, sizeof(j));
       j.in = in_ptrs[r];

@@ -268,9 +268,15 @@ void Config::Validate() {
                        << rounded << " (multiple of num_workers*max(packet_numel,128)*4)";
       c.slot_bytes = rounded;
     }
-    SML_CHECK(c.slot_bytes / 4 / g.packet_numel * c.slots_per_channel <= 8192)
-        << "backend.cuda: slots_per_channel * slot_bytes / (4 * packet_numel) may be at most 8192 "
-           "(scale factors of a channel's slots live in shared memory)";
+    // The scale factors of all slots of a channel live in shared memory (8192 floats).
+    uint64_t max_slot = 8192ull / c.slots_per_channel * g.packet_numel * 4 / quantum * quantum;
+    SML_CHECK(max_slot >= quantum) << "backend.cuda: packet_numel too small for " << c.slots_per_channel
+                                   << " slots per channel";
+    if (c.slot_bytes > max_slot) {
+      SML_VLOG(1) << "backend.cuda.slot_bytes lowered from " << c.slot_bytes << " to " << max_slot
+                  << " (at most 8192 quantisation blocks over a channel's slots)";
+      c.slot_bytes = max_slot;
+    }
     SML_CHECK(c.wait_timeout_ms > 0) << "backend.cuda.wait_timeout_ms must be positive";
     SML_CHECK(g.num_workers <= 8) << "the cuda backend serves at most 8 GPUs (one NVSwitch domain)";
   }

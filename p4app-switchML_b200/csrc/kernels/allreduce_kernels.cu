@@ -36,7 +36,8 @@ namespace kernels {
 namespace {
 
 static const int kMaxBlocksPerSlot = 8192;  // scale factors of all slots of a channel (shared memory)
-static const int kUnroll = 4;
+static const int kUnroll = 4;        // 16-byte vectors in flight per thread, local copies
+static const int kUnrollLink = 4;    // ... for loads that cross NVLink (more in flight measured slower)
 static const int kUnrollInt = 8;
 
 __device__ __forceinline__ bool Aligned16(const void* p) {
@@ -208,7 +209,7 @@ __device__ __forceinline__ bool RoleWait(const RankCtx& ctx, const Role& role, i
       if ((spins & 63) == 0) {
         if (*reinterpret_cast<volatile int*>(&sh->failed)) break;
         if (GlobalTimerNs() - start > ctx.timeout_ns) {
-          atomicCAS(ctx.status, STATUS_OK, STATUS_TIMEOUT | (phase << 4) | (channel << 8));
+          ReportStatus(ctx, STATUS_TIMEOUT | (phase << 4) | (channel << 8));
           atomicAdd(ctx.counters + 2, 1ull);
           *reinterpret_cast<volatile int*>(&sh->failed) = 1;
           break;
@@ -285,6 +286,17 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
     which = 2; role.tid = threadIdx.x - (kLoadWarps + kReduceWarps) * 32; role.nthreads = kStoreWarps * 32; role.bar_id = 3;
   }
   volatile int* failed = reinterpret_cast<volatile int*>(&sh->failed);
+  // Channel 0 keeps a coarse time budget of its roles (ns waiting for others / ns doing
+  // its own work) in counters[3 + 2*role], [4 + 2*role]: a built-in pipeline profile.
+  const bool timed = channel == 0 && role.tid == 0;
+  unsigned long long t_mark = timed ? GlobalTimerNs() : 0;
+  auto lap = [&](int idx) {
+    if (timed) {
+      unsigned long long now = GlobalTimerNs();
+      atomicAdd(ctx.counters + idx, now - t_mark);
+      t_mark = now;
+    }
+  };
 
   for (unsigned long long k = 0; k < ntiles; ++k) {
     const unsigned long long pos = c0 + k * tile_elems;
@@ -306,7 +318,7 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
           unsigned long long start = GlobalTimerNs(), spins = 0;
           while (sh->stored + S < k + 1) {
             if ((++spins & 63) == 0 && (*failed || GlobalTimerNs() - start > ctx.timeout_ns)) {
-              if (!*failed) atomicCAS(ctx.status, STATUS_OK, STATUS_TIMEOUT | (3 << 4) | (channel << 8));
+              if (!*failed) ReportStatus(ctx, STATUS_TIMEOUT | (3 << 4) | (channel << 8));
               *failed = 1;
               break;
             }
@@ -316,6 +328,7 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
         role.Sync();
         if (*failed) return;
       }
+      lap(3);
       const char* in = static_cast<const char*>(job.in) + pos * in_esz;
       if (MODE == MODE_QUANT) {
         const size_t nblocks = (len + ctx.block_numel - 1) / ctx.block_numel;
@@ -376,9 +389,11 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
         RoleCopy(role, my_stage + slot_off, in, len * in_esz, in_esz);
       }
       RoleSignal(ctx, role, channel, 1, epoch);
+      lap(4);
     } else if (which == 1) {
       // ------------------------------ reducer ------------------------------
       if (!RoleWait(ctx, role, channel, 1, epoch, sh)) return;
+      lap(5);
       size_t sb, se;
       ShardRange(len, ctx.nranks, ctx.rank, unit, &sb, &se);
       const int t = role.tid, n = role.nthreads;
@@ -437,13 +452,13 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
       } else {
         size_t v0 = sb / vec_elems, v1 = (se + vec_elems - 1) / vec_elems;
         size_t v = v0 + t;
-        for (; v + (kUnroll - 1) * n < v1; v += kUnroll * n) {
-          uint4 r[kUnroll];
+        for (; v + (kUnrollLink - 1) * n < v1; v += kUnrollLink * n) {
+          uint4 r[kUnrollLink];
 #pragma unroll
-          for (int u = 0; u < kUnroll; u++)
+          for (int u = 0; u < kUnrollLink; u++)
             r[u] = ReduceVec<ELEM>(ctx, ctx.stage_peer, ctx.stage_mc, slot_off + (v + u * n) * 16, job.post_scale);
 #pragma unroll
-          for (int u = 0; u < kUnroll; u++)
+          for (int u = 0; u < kUnrollLink; u++)
             BroadcastVec(ctx, ctx.stage_peer, ctx.stage_mc, slot_off + (v + u * n) * 16, r[u]);
         }
         for (; v < v1; v += n) {
@@ -452,9 +467,11 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
         }
       }
       RoleSignal(ctx, role, channel, 2, epoch);
+      lap(6);
     } else {
       // ------------------------------ storer ------------------------------
       if (!RoleWait(ctx, role, channel, 2, epoch, sh)) return;
+      lap(7);
       char* out = static_cast<char*>(job.out) + pos * in_esz;
       if (MODE == MODE_QUANT && ELEM == ELEM_BF16) {
         const float* y = reinterpret_cast<const float*>(my_stage + slot_off);
@@ -469,6 +486,7 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
         sh->stored = k + 1;
         atomicAdd(ctx.counters, 1ull);
       }
+      lap(8);
     }
   }
 }
@@ -491,9 +509,47 @@ __device__ void RunOneShot(const RankCtx& ctx, const JobArgs& job, int channel,
            (static_cast<size_t>(job.oneshot_parity) * ctx.nranks + s) * ctx.oneshot_bytes + c0 * esz;
   };
   const char* in = static_cast<const char*>(job.in) + c0 * esz;
-  const size_t my_off = buf_off(ctx.rank);
   const size_t bytes = len * esz;
 
+  if (MODE == MODE_SUM && ctx.use_multimem) {
+    // Pull variant: every rank parks its input at the same offset of its own buffer, and
+    // after one barrier each rank lets the switch reduce the whole range straight into its
+    // output. No broadcast, no second barrier; costs n times the outbound traffic, which
+    // small messages do not notice.
+    const size_t off = buf_off(0);
+    char* mine = ctx.stage_peer[ctx.rank] + off;
+    Role all = {static_cast<int>(threadIdx.x), static_cast<int>(blockDim.x), 0};
+    RoleCopy(all, mine, in, bytes, esz);
+    if (!ChannelBarrier(ctx, channel, 3, epoch, s_failed)) return;
+    char* mc = ctx.stage_mc + off;
+    char* out = static_cast<char*>(job.out) + c0 * esz;
+    if (ELEM == ELEM_I32) {
+      for (size_t i = threadIdx.x; i < len; i += blockDim.x)
+        reinterpret_cast<int*>(out)[i] = MultimemLdReduceAddS32(mc + i * 4);
+    } else {
+      const size_t vec_elems = 16 / esz;
+      const size_t nfull = len / vec_elems;
+      const bool aligned = Aligned16(out);
+      for (size_t v = threadIdx.x; v * vec_elems < len; v += blockDim.x) {
+        uint4 r = ReduceVec<ELEM>(ctx, ctx.stage_peer, ctx.stage_mc, off + v * 16, job.post_scale);
+        if (aligned && v < nfull) {
+          reinterpret_cast<uint4*>(out)[v] = r;
+        } else {
+          // unaligned output or the ragged last vector: element by element
+          const unsigned w[4] = {r.x, r.y, r.z, r.w};
+          for (size_t j = 0; j < vec_elems && v * vec_elems + j < len; j++) {
+            if (esz == 4) reinterpret_cast<unsigned*>(out)[v * vec_elems + j] = w[j];
+            else reinterpret_cast<unsigned short*>(out)[v * vec_elems + j] =
+                     static_cast<unsigned short>(w[j >> 1] >> ((j & 1) * 16));
+          }
+        }
+      }
+    }
+    if (threadIdx.x == 0) atomicAdd(ctx.counters, 1ull);
+    return;
+  }
+
+  const size_t my_off = buf_off(ctx.rank);
   // ---- push my range to everybody ----
   if (Aligned16(in)) {
     size_t nvec = bytes / 16;
@@ -603,13 +659,13 @@ __device__ void RunZeroCopy(const RankCtx& ctx, const JobArgs& job, int channel,
     size_t nvec = (full_end - sb) / vec_elems;
     char* const* peers = job.user_peer;
     size_t v = threadIdx.x;
-    for (; v + (kUnroll - 1) * blockDim.x < nvec; v += kUnroll * blockDim.x) {
-      uint4 r[kUnroll];
+    for (; v + (kUnrollLink - 1) * blockDim.x < nvec; v += kUnrollLink * blockDim.x) {
+      uint4 r[kUnrollLink];
 #pragma unroll
-      for (int u = 0; u < kUnroll; u++)
+      for (int u = 0; u < kUnrollLink; u++)
         r[u] = ReduceVec<ELEM>(ctx, peers, job.user_mc, in_base + (v + u * blockDim.x) * 16, job.post_scale);
 #pragma unroll
-      for (int u = 0; u < kUnroll; u++)
+      for (int u = 0; u < kUnrollLink; u++)
         BroadcastVec(ctx, peers, job.user_mc, out_base + (v + u * blockDim.x) * 16, r[u]);
     }
     for (; v < nvec; v += blockDim.x) {
@@ -788,10 +844,11 @@ LaunchPlan PlanLaunch(const RankCtx& ctx, const JobArgs& job, int requested_chan
     // Whole quantisation blocks per channel; a few CTAs are enough for small messages.
     unsigned long long unit = ctx.block_numel > 128 ? ctx.block_numel : 128;
     unsigned long long units = (numel + unit - 1) / unit;
-    int ch = requested_channels > 0 ? requested_channels : 8;
+    int ch = requested_channels > 0 ? requested_channels : 64;
     if (ch > max_channels) ch = max_channels;
     unsigned long long per = (units + ch - 1) / ch;
-    if (per < 8) per = 8;  // at least 8 units (>= 4 KiB of f32) per CTA
+    unsigned long long min_per = (4096 + unit - 1) / unit;  // at least 4 Ki elements per CTA
+    if (per < min_per) per = min_per;
     p.elems_per_channel = per * unit;
     p.channels = static_cast<int>((numel + p.elems_per_channel - 1) / p.elems_per_channel);
     p.epochs = 1;

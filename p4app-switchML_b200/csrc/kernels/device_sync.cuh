@@ -44,6 +44,13 @@ __device__ __forceinline__ Epoch* FlagPtr(char* region, int channel, int phase, 
          (static_cast<size_t>(channel) * kNumPhases + phase) * kMaxRanks + src;
 }
 
+// The status word may live in host memory mapped into the device (no atomics there): a
+// plain store; when several waits fail at once any of their codes will do.
+__device__ __forceinline__ void ReportStatus(const RankCtx& ctx, int code) {
+  *reinterpret_cast<volatile int*>(ctx.status) = code;
+  __threadfence_system();
+}
+
 // Barrier over all ranks for one channel. Must be called by every thread of the CTA.
 // Returns false when the wait timed out (the whole CTA gets the same answer). With
 // `signal` false the caller only waits (used to exercise the timeout path).
@@ -60,7 +67,7 @@ __device__ __forceinline__ bool ChannelBarrier(const RankCtx& ctx, int channel, 
     while (LoadAcquireSys(mine) < epoch) {
       ++spins;
       if ((spins & 63) == 0 && GlobalTimerNs() - start > ctx.timeout_ns) {
-        atomicCAS(ctx.status, STATUS_OK, STATUS_TIMEOUT | (phase << 4) | (channel << 8));
+        ReportStatus(ctx, STATUS_TIMEOUT | (phase << 4) | (channel << 8));
         atomicAdd(ctx.counters + 2, 1ull);
         *s_failed = 1;
         break;
