@@ -893,3 +893,108 @@ cudaError_t LaunchWaitProbe(const RankCtx& ctx, cudaStream_t stream) {
 
 }  // namespace kernels
 }  // namespace switchml
+
+// ---------------------------------------------------------------------------------------
+// Allocation-free single-worker entry point; see kernels/local_noalloc.h for the contract.
+#include <mutex>
+
+#include "kernels/local_noalloc.h"
+
+namespace {
+
+// Geometry small enough for a static array: 8 channels x 2 slots x 32 KiB.
+const int kNoAllocChannels = 8;
+const int kNoAllocSlots = 2;
+const size_t kNoAllocSlotBytes = 32768;
+const size_t kNoAllocAuxOffset = 768u << 10;  // counters and status word behind the staging
+
+// Scratch of the allocation-free entry point. In host code this name is only a handle for
+// cudaGetSymbolAddress, never a device address.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[SWITCHML_NOALLOC_SCRATCH_BYTES];
+
+std::mutex g_noalloc_mu;
+void* g_noalloc_ptr[64] = {nullptr};  // per device: device address of g_noalloc_scratch
+
+}  // namespace
+
+extern "C" const char* switchml_noalloc_strerror(int code) {
+  switch (code) {
+    case SWITCHML_NOALLOC_OK: return "ok";
+    case SWITCHML_NOALLOC_BAD_ARGUMENT:
+      return "bad argument: null pointer, unknown elem_type/mode, int32 with quantised mode, or "
+             "block_numel not a power of two in [32,1024]";
+    case SWITCHML_NOALLOC_TOO_LARGE:
+      return "numel exceeds SWITCHML_NOALLOC_MAX_NUMEL (2^26 elements)";
+    case SWITCHML_NOALLOC_CUDA_ERROR: return "a CUDA call failed (see cudaGetLastError)";
+  }
+  return "unknown code";
+}
+
+extern "C" int switchml_local_allreduce_noalloc(const void* in, void* out,
+                                                unsigned long long numel, int elem_type, int mode,
+                                                int block_numel, void* stream_ptr) {
+  using namespace switchml::kernels;
+  if (!in || !out) return SWITCHML_NOALLOC_BAD_ARGUMENT;
+  if (elem_type < ELEM_F32 || elem_type > ELEM_BF16) return SWITCHML_NOALLOC_BAD_ARGUMENT;
+  if (mode != MODE_SUM && mode != MODE_QUANT) return SWITCHML_NOALLOC_BAD_ARGUMENT;
+  if (elem_type == ELEM_I32 && mode == MODE_QUANT) return SWITCHML_NOALLOC_BAD_ARGUMENT;
+  if (block_numel < 32 || block_numel > 1024 || (block_numel & (block_numel - 1)))
+    return SWITCHML_NOALLOC_BAD_ARGUMENT;
+  if (numel > SWITCHML_NOALLOC_MAX_NUMEL) return SWITCHML_NOALLOC_TOO_LARGE;
+  if (numel == 0) return SWITCHML_NOALLOC_OK;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return SWITCHML_NOALLOC_CUDA_ERROR;
+  char* scratch = nullptr;
+  {
+    // Once per device, with that device current: ask the runtime where the array lives.
+    std::lock_guard<std::mutex> lk(g_noalloc_mu);
+    if (!g_noalloc_ptr[dev]) {
+      void* p = nullptr;
+      if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || !p)
+        return SWITCHML_NOALLOC_CUDA_ERROR;
+      g_noalloc_ptr[dev] = p;
+    }
+    scratch = static_cast<char*>(g_noalloc_ptr[dev]);
+  }
+
+  RankCtx ctx;
+  memset(&ctx, 0, sizeof(ctx));
+  ctx.rank = 0;
+  ctx.nranks = 1;
+  ctx.use_multimem = 0;
+  ctx.stage_peer[0] = scratch;
+  ctx.slot_bytes = kNoAllocSlotBytes;
+  ctx.slots_per_channel = kNoAllocSlots;
+  ctx.block_numel = block_numel;
+  ctx.oneshot_bytes = 256;
+  ctx.timeout_ns = 1000000000ull;
+  size_t staging = StagingBytes(ctx.slot_bytes, ctx.slots_per_channel, ctx.block_numel,
+                                kNoAllocChannels, ctx.oneshot_bytes, 1, &ctx.data_offset,
+                                &ctx.exp_offset, &ctx.oneshot_offset);
+  if (staging > kNoAllocAuxOffset) return SWITCHML_NOALLOC_BAD_ARGUMENT;  // cannot happen for the limits above
+  ctx.counters = reinterpret_cast<unsigned long long*>(scratch + kNoAllocAuxOffset);
+  ctx.status = reinterpret_cast<int*>(scratch + kNoAllocAuxOffset + 256);
+
+  JobArgs job;
+  memset(&job, 0, sizeof(job));
+  job.in = in;
+  job.out = out;
+  job.numel = numel;
+  job.elem_type = elem_type;
+  job.mode = mode;
+  job.algo = ALGO_STAGED;
+  job.post_scale = 1.0f;
+  job.epoch_base = 0;
+  LaunchPlan plan = PlanLaunch(ctx, job, 0, kNoAllocChannels);
+  job.tile_elems = plan.tile_elems;
+
+  // The array keeps the previous call's flags (epochs) and counters; this call counts its
+  // epochs from zero again, so both have to be cleared first, in stream order.
+  if (cudaMemsetAsync(scratch, 0, kFlagBytes, stream) != cudaSuccess) return SWITCHML_NOALLOC_CUDA_ERROR;
+  if (cudaMemsetAsync(scratch + kNoAllocAuxOffset, 0, 512, stream) != cudaSuccess)
+    return SWITCHML_NOALLOC_CUDA_ERROR;
+  if (LaunchAllReduce(ctx, job, plan, stream) != cudaSuccess) return SWITCHML_NOALLOC_CUDA_ERROR;
+  return SWITCHML_NOALLOC_OK;
+}
