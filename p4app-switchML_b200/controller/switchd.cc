@@ -1,0 +1,44 @@
+// switchml_switchd: the controller and the software aggregation switch as a stand-alone
+// process, for setups where no worker should host them (backend.udp.spawn_switch = false).
+//
+//   switchml_switchd --ip 0.0.0.0 --port 50099 --udp-port 48864 [--drop-ingress p --drop-egress p]
+//
+// It plays the part of the reference's controller process (controller/switchml.py:579-664:
+// connect to the switch, serve the workers' session and synchronisation requests, offer a
+// console) for the switch that lives in this very process. Talk to it with
+// `python -m switchml_b200.utils.cli --port 50099`.
+#include <signal.h>
+#include <unistd.h>
+
+#include <atomic>
+#include <iostream>
+
+#include "rendezvous/control.h"
+#include "switchml/cli_flags.h"
+#include "switchml/log.h"
+
+static std::atomic<bool> g_run{true};
+static void OnSignal(int) { g_run = false; }
+
+int main(int argc, char** argv) {
+  switchml::CliFlags f;
+  f.Add("ip", "0.0.0.0", "Address to listen on (TCP control and UDP data).")
+      .Add("port", "50099", "TCP port of the control plane.")
+      .Add("udp-port", "48864", "UDP port of the aggregation data plane (0xBEE0).")
+      .Add("drop-ingress", "0", "Probability of dropping a packet on arrival.")
+      .Add("drop-egress", "0", "Probability of dropping each result copy.")
+      .Add("log-level", "1", "Verbosity 0..4.");
+  if (!f.Parse(argc, argv, "SwitchML controller + software switch")) return 1;
+  switchml::SetVerbosity(static_cast<int>(f.U64("log-level")));
+  switchml::ControlServer server;
+  if (!server.Start(f.Str("ip"), static_cast<uint16_t>(f.U64("port")), static_cast<uint16_t>(f.U64("udp-port")))) return 1;
+  server.soft_switch().SetDropProbabilities(f.F64("drop-ingress"), f.F64("drop-egress"));
+  signal(SIGINT, OnSignal);
+  signal(SIGTERM, OnSignal);
+  std::cout << "switchml_switchd: control on " << f.Str("ip") << ":" << server.port() << ", data on UDP "
+            << server.udp_port() << std::endl;
+  while (g_run) usleep(200 * 1000);
+  std::cout << server.soft_switch().DescribeStatistics();
+  server.Stop();
+  return 0;
+}

@@ -1,0 +1,51 @@
+/* Weight-gradient GEMM on tcgen05 tensor cores, optionally fused with the cross-GPU
+ * reduction of the result.
+ *
+ *   dW[M,N] (fp32, row-major) = dY[K,M]^T * X[K,N]      dY, X bf16 row-major
+ *
+ * Plain call (fused == NULL or nranks <= 1): dW may be any 16-byte aligned device buffer.
+ *
+ * Fused call: every rank calls with the same shapes. `dw` must be this rank's address of
+ * a buffer that lives at the same offset of a symmetric, multicast-bound region on every
+ * rank, `out_mc` the multicast address of the same buffer. As soon as a 128x256 tile has
+ * been stored by all ranks, its owner (tile index mod nranks) lets the NVSwitch sum the
+ * ranks' copies (multimem.ld_reduce.add.f32) and broadcasts the sum into every rank's
+ * buffer (multimem.st) while the tensor cores continue with later tiles; the kernel returns
+ * after a closing barrier, with the reduced (and scaled) gradient in every rank's dW.
+ * This is the role the reference gives to "aggregate the gradient right where it is
+ * produced"; the reference itself has no GPU code (its integrations copy gradients to host
+ * memory first, frameworks_integration/pytorch_plugin/ProcessGroupSML.cpp:117-163).
+ *
+ * `flags_peer[r]` is rank r's copy of a flag array of switchml_wgrad_flag_words(M, N)
+ * 64-bit words in symmetric memory, zero-initialised once; `epoch` must grow with every
+ * fused call that uses the same flag array. Waits give up after `timeout_ns` and set
+ * *error_flag (device or mapped host memory) to 1.
+ *
+ * M and N must be multiples of 8 and all base addresses 16-byte aligned (TMA).
+ * Returns 0, or < 0: -1 bad argument, -2 alignment, -3 tensor map, -4 launch.
+ */
+#ifndef SWITCHML_WGRAD_GEMM_H_
+#define SWITCHML_WGRAD_GEMM_H_
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct WgradFusedArgs {
+  int rank;
+  int nranks;
+  unsigned long long* flags_peer[8];
+  char* out_mc;
+  unsigned long long epoch;
+  unsigned long long timeout_ns;
+  float scale; /* multiplied into the reduced gradient (1/nranks for the mean) */
+} WgradFusedArgs;
+
+int switchml_wgrad_gemm(const void* dy, const void* x, float* dw, int M, int N, int K,
+                        const WgradFusedArgs* fused, int* error_flag, void* stream);
+int switchml_wgrad_flag_words(int M, int N);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SWITCHML_WGRAD_GEMM_H_ */
