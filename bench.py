@@ -361,6 +361,9 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--e2e-chunk", type=int, default=1 << 24)
     ap.add_argument("--batch", type=int, default=0, help="per-GPU batch for the training workloads")
+    ap.add_argument("--ddp", default="sml", choices=["sml", "torch"], help="training workloads: this library or PyTorch DDP/NCCL")
+    ap.add_argument("--fused-wgrad", type=int, default=0, help="training workloads: tcgen05 wgrad GEMM with fused reduce")
+    ap.add_argument("--model", default="resnet50")
     ap.add_argument("--watchdog", type=float, default=float(os.environ.get("SWITCHML_BENCH_WATCHDOG", "0")),
                     help="dump all Python stacks and exit if the run takes longer than this many seconds")
     args = ap.parse_args()

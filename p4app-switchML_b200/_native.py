@@ -47,6 +47,7 @@ def _declare(l):
         "sml_symm_reset": (None, []),
         "sml_uses_multimem": (i32, []),
         "sml_device": (i32, []),
+        "sml_symm_info": (i32, [c.POINTER(vp), c.POINTER(vp), c.POINTER(vp), c.POINTER(c.c_size_t)]),
         "sml_wait_probe": (i32, [c.c_double]),
         "sml_oracle_quant_allreduce": (None, [c.POINTER(vp), i32, u64, u64, vp]),
         "sml_oracle_int_allreduce": (None, [c.POINTER(vp), i32, u64, vp]),

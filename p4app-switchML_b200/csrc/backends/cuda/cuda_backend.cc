@@ -98,6 +98,14 @@ class CudaBackend : public CudaBackendInterface {
   void* SymmetricAlloc(size_t bytes) override;
   void SymmetricReset() override;
   bool UsesMultimem() const override { return ctx_.use_multimem != 0; }
+  bool SymmetricHeapInfo(void** local, void** peers, void** multicast, size_t* bytes) override {
+    if (!heap_.local) return false;
+    *local = heap_.local;
+    for (int p = 0; p < n_; p++) peers[p] = heap_.peers[p];
+    *multicast = heap_.multicast;
+    *bytes = heap_.bytes;
+    return true;
+  }
   int Device() const override { return device_; }
   int RunWaitProbe(double budget_ms) override;
 

@@ -35,6 +35,9 @@ class CudaBackendInterface : public Backend {
   // Release everything allocated from the heap (again on every rank alike).
   virtual void SymmetricReset() = 0;
   virtual bool UsesMultimem() const = 0;
+  // Mappings of the symmetric heap: this rank's base, every rank's base as mapped here
+  // (`peers` has room for 8 entries), the multicast base (nullptr without NVLS), its size.
+  virtual bool SymmetricHeapInfo(void** local, void** peers, void** multicast, size_t* bytes) = 0;
   virtual int Device() const = 0;
   // Enqueue a kernel that waits for a signal nobody sends and report how the wait ended
   // (kernels::Status). Used to check that bounded waits give up cleanly.

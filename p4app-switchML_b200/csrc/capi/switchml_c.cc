@@ -204,6 +204,12 @@ int sml_uses_multimem(void) {
   return b && b->UsesMultimem() ? 1 : 0;
 }
 
+int sml_symm_info(void** local, void** peers, void** multicast, size_t* bytes) {
+  CudaBackendInterface* b = Cuda();
+  if (!b || !b->SymmetricHeapInfo(local, peers, multicast, bytes)) return Fail("no symmetric heap");
+  return 0;
+}
+
 int sml_device(void) {
   CudaBackendInterface* b = Cuda();
   return b ? b->Device() : -1;

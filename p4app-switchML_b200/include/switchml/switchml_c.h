@@ -53,6 +53,8 @@ void sml_stats_reset(void);
 void* sml_symm_alloc(size_t bytes);
 void sml_symm_reset(void);
 int sml_uses_multimem(void);
+/* Bases of the symmetric heap: local, peers[0..num_workers) (room for 8), multicast. */
+int sml_symm_info(void** local, void** peers, void** multicast, size_t* bytes);
 int sml_device(void);
 int sml_wait_probe(double budget_ms);
 

@@ -66,3 +66,98 @@ def wgrad_gemm(dy, x, out=None, error_flag=None):
 
 def flag_words(M, N):
     return _lib().switchml_wgrad_flag_words(M, N)
+
+
+class FusedWgrad:
+    """Weight-gradient GEMM whose result is summed over all workers inside the kernel.
+
+    One instance per weight matrix [M, N]. The gradient buffer and the tile flags live in
+    the context's symmetric heap (every rank must create its instances in the same order).
+    ``run(dy, x)`` leaves the reduced (scaled) gradient in ``self.grad`` on every rank; the
+    kernel is enqueued on the current stream and needs no separate allreduce.
+    """
+
+    def __init__(self, ctx, M, N, scale=1.0, timeout_ms=20000.0):
+        self.ctx, self.M, self.N, self.scale = ctx, M, N, scale
+        self.grad = ctx.symmetric_empty(M * N, torch.float32).view(M, N)
+        words = flag_words(M, N)
+        self.flags = ctx.symmetric_empty(words * 2, torch.int32)   # 64-bit words
+        self.flags.zero_()
+        self.error = torch.zeros(1, dtype=torch.int32, device=self.grad.device)
+        local, peers, mc, _ = ctx.symmetric_info()
+        stats = ctx.get_stats()
+        self.nranks = sum(1 for p in peers if p)
+        self.rank = peers.index(local)
+        self.args = _FusedArgs()
+        self.args.rank, self.args.nranks = self.rank, self.nranks
+        flag_off = self.flags.data_ptr() - local
+        for r in range(self.nranks):
+            self.args.flags_peer[r] = peers[r] + flag_off
+        self.args.out_mc = (mc + (self.grad.data_ptr() - local)) if mc else None
+        self.args.epoch = 0
+        self.args.timeout_ns = int(timeout_ms * 1e6)
+        self.args.scale = scale
+        self.fused = self.nranks > 1 and bool(mc)
+        torch.cuda.synchronize()
+
+    def run(self, dy, x):
+        assert dy.dtype == torch.bfloat16 and x.dtype == torch.bfloat16
+        dy, x = dy.contiguous(), x.contiguous()
+        K = dy.shape[0]
+        self.args.epoch += 1
+        stream = torch.cuda.current_stream(dy.device).cuda_stream
+        rc = _lib().switchml_wgrad_gemm(dy.data_ptr(), x.data_ptr(), self.grad.data_ptr(), self.M, self.N, K,
+                                        ctypes.byref(self.args) if self.fused else None,
+                                        self.error.data_ptr(), ctypes.c_void_p(stream))
+        if rc != 0:
+            raise NativeError("wgrad_gemm: " + _ERRORS.get(rc, str(rc)))
+        if not self.fused and self.nranks > 1:
+            # No multicast mapping: reduce the finished gradient with the zero-copy kernel.
+            job = self.ctx.all_reduce_async(self.grad.view(-1))
+            job.stream_wait()
+            job.release()
+        return self.grad
+
+
+class _FusedLinearFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, layer):
+        ctx.layer = layer
+        ctx.save_for_backward(x, weight)
+        return torch.nn.functional.linear(x, weight, bias)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight = ctx.saved_tensors
+        layer = ctx.layer
+        x2 = x.reshape(-1, x.shape[-1])
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        dx = (dy2 @ weight.to(dy2.dtype)).reshape(x.shape) if ctx.needs_input_grad[0] else None
+        # dW on the tcgen05 tensor cores, summed over the workers in the same kernel,
+        # written straight into the parameter's gradient.
+        layer.wgrad.run(dy2.to(torch.bfloat16), x2.to(torch.bfloat16))
+        dbias = dy2.sum(0).to(layer.bias.dtype) if layer.bias is not None else None
+        return dx, None, dbias, None
+
+
+class FusedWgradLinear(torch.nn.Linear):
+    """``nn.Linear`` whose weight gradient is computed by ``FusedWgrad`` (fp32 weights,
+    bf16 activations). Call ``attach(ctx)`` once after the context has started; the weight's
+    ``.grad`` then aliases the symmetric gradient buffer and arrives already reduced."""
+
+    wgrad = None
+
+    def attach(self, ctx, scale=1.0):
+        self.wgrad = FusedWgrad(ctx, self.out_features, self.in_features, scale)
+        self.weight.grad = self.wgrad.grad
+        self.weight._sml_reduced_in_backward = True
+        return self
+
+    def forward(self, x):
+        if self.wgrad is None or not torch.is_grad_enabled():
+            return super().forward(x)
+        w = self.weight
+        if torch.is_autocast_enabled():
+            dt = torch.get_autocast_dtype("cuda")
+            return _FusedLinearFn.apply(x.to(dt), w.to(dt), self.bias.to(dt) if self.bias is not None else None, self)
+        return _FusedLinearFn.apply(x, w, self.bias, self)

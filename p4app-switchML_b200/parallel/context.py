@@ -191,6 +191,16 @@ class Context:
         dev = torch.device("cuda", self.device() if device is None else device)
         return _tensor_from_ptr(ptr, numel, dtype, dev)
 
+    def symmetric_info(self):
+        """(local base, [peer bases], multicast base or None, bytes) of the symmetric heap."""
+        local = ctypes.c_void_p()
+        peers = (ctypes.c_void_p * 8)()
+        mc = ctypes.c_void_p()
+        nbytes = ctypes.c_size_t()
+        if lib().sml_symm_info(ctypes.byref(local), peers, ctypes.byref(mc), ctypes.byref(nbytes)) != 0:
+            raise NativeError(last_error())
+        return local.value, [p for p in peers], mc.value, nbytes.value
+
     def symmetric_reset(self):
         lib().sml_symm_reset()
 

@@ -22,7 +22,8 @@ class GradientBuckets:
 
     def __init__(self, params, ctx, bucket_mb=25, symmetric="auto"):
         self.ctx = ctx
-        params = [p for p in params if p.requires_grad]
+        # Gradients that a fused kernel already reduces during backward stay out of the buckets.
+        params = [p for p in params if p.requires_grad and not getattr(p, "_sml_reduced_in_backward", False)]
         self.params = list(reversed(params))
         cap = int(bucket_mb * (1 << 20))
         groups, cur, cur_bytes, cur_dtype = [], [], 0, None
@@ -111,6 +112,7 @@ class DistributedDataParallel(torch.nn.Module):
             self._comm_stream = torch.cuda.Stream(device=dev, priority=-1)
         for p in self.buckets.params:
             p.register_post_accumulate_grad_hook(self._on_grad)
+        self._callback_queued = False
 
     def forward(self, *args, **kwargs):
         if torch.is_grad_enabled():

@@ -118,8 +118,65 @@ def cuda_worker(rank, n, ctl_port, transport, mode, q, heap_mb=64, launch="inlin
                 assert float(guard.min()) == 123.0 and float(guard.max()) == 123.0, "wrote past the tensor"
                 report["cases"] += 2
             ctx.symmetric_reset()
+        # tcgen05 weight-gradient GEMM with the cross-GPU reduce fused into the kernel
+        if mode == "float_sum":
+            from switchml_b200.ops.wgrad import FusedWgrad
+            for (K, M, N) in ((256, 384, 520), (64, 1024, 2048), (1024, 128, 256)):
+                fw = FusedWgrad(ctx, M, N, scale=1.0 / n)
+                report["fused_in_kernel"] = fw.fused
+                for it in range(3):
+                    g = torch.Generator(device="cuda").manual_seed(1000 * rank + it)
+                    dy = torch.randn(K, M, device="cuda", generator=g).bfloat16()
+                    x = torch.randn(K, N, device="cuda", generator=g).bfloat16()
+                    got = fw.run(dy, x).clone()
+                    ref = (dy.float().t() @ x.float()).contiguous()
+                    ctx.all_reduce(ref.view(-1))
+                    ref /= n
+                    torch.cuda.synchronize()
+                    assert int(fw.error.item()) == 0, "fused wgrad: a wait gave up"
+                    err = float((got - ref).abs().max())
+                    assert err < 2e-2 * (K ** 0.5), "fused wgrad mismatch %g at %s it %d" % (err, (K, M, N), it)
+                    report["cases"] += 1
+            ctx.symmetric_reset()
         report["stats"] = ctx.get_stats()
         ctx.stop()
         q.put((rank, "ok", report))
+    except Exception:
+        q.put((rank, "error", traceback.format_exc()))
+
+
+def pg_worker(rank, n, port, q):
+    """torch.distributed with backend "sml" on CPU (udp transport): plain all_reduce and a
+    DistributedDataParallel step, compared with the sum computed locally."""
+    try:
+        import torch
+        import torch.distributed as dist
+        os.environ["MASTER_ADDR"] = "127.0.0.1"
+        os.environ["MASTER_PORT"] = str(port)
+        import switchml_b200.parallel.process_group  # noqa: F401
+        dist.init_process_group("sml", rank=rank, world_size=n, init_method="tcp://127.0.0.1:%d" % port)
+        t = torch.arange(10000, dtype=torch.float32) * (rank + 1)
+        dist.all_reduce(t)
+        want = torch.arange(10000, dtype=torch.float32) * sum(r + 1 for r in range(n))
+        assert torch.allclose(t, want, rtol=1e-6), "float allreduce"
+        ti = torch.full((1000,), rank + 1, dtype=torch.int32)
+        work = dist.all_reduce(ti, async_op=True)
+        work.wait()
+        assert int(ti[0]) == sum(r + 1 for r in range(n)), "int allreduce"
+        d = torch.ones(4, dtype=torch.float64) * rank          # unsupported dtype: Gloo fallback
+        dist.all_reduce(d)
+        assert float(d[0]) == sum(range(n)), "fallback"
+        torch.manual_seed(0)
+        model = torch.nn.Linear(32, 8)
+        ddp = torch.nn.parallel.DistributedDataParallel(model)
+        x = torch.randn(16, 32, generator=torch.Generator().manual_seed(rank))
+        ddp(x).square().mean().backward()
+        g = model.weight.grad.clone()
+        gl = [torch.zeros_like(g) for _ in range(n)]
+        dist.all_gather(gl, g)
+        assert all(torch.allclose(gl[0], o, atol=1e-6) for o in gl), "DDP gradients differ across ranks"
+        dist.barrier()
+        dist.destroy_process_group()
+        q.put((rank, "ok", None))
     except Exception:
         q.put((rank, "error", traceback.format_exc()))
