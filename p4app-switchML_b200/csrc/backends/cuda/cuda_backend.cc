@@ -359,7 +359,10 @@ void CudaBackend::LaunchJob(const std::shared_ptr<Job>& job, cudaStream_t stream
   host_status_[f->status_slot] = kernels::STATUS_OK;  // the ring is far longer than the queue
   kernels::RankCtx job_ctx = ctx_;
   job_ctx.status = dev_status_ + f->status_slot;
-  if (t.numel > 0) e = kernels::LaunchAllReduce(job_ctx, a, plan, stream);
+  // A single worker reducing in place has nothing to do (float_sum: the sum of one term;
+  // quantised mode still runs, because quantise/dequantise rounds the values).
+  bool nothing_to_do = n_ == 1 && t.in_ptr == t.out_ptr && a.mode == kernels::MODE_SUM && a.post_scale == 1.0f;
+  if (t.numel > 0 && !nothing_to_do) e = kernels::LaunchAllReduce(job_ctx, a, plan, stream);
   if (e == cudaSuccess) e = cudaEventRecord(f->done, stream);
   if (e != cudaSuccess) {
     f->launch_error = std::string("kernel launch failed: ") + cudaGetErrorString(e);

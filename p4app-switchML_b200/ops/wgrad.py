@@ -116,6 +116,8 @@ class FusedWgrad:
             job = self.ctx.all_reduce_async(self.grad.view(-1))
             job.stream_wait()
             job.release()
+            if self.scale != 1.0:
+                self.grad.mul_(self.scale)
         return self.grad
 
 

@@ -138,6 +138,27 @@ def cuda_worker(rank, n, ctl_port, transport, mode, q, heap_mb=64, launch="inlin
                     assert err < 2e-2 * (K ** 0.5), "fused wgrad mismatch %g at %s it %d" % (err, (K, M, N), it)
                     report["cases"] += 1
             ctx.symmetric_reset()
+        # DDP wrapper: overlapped, bucketed reduction must equal the mean of the local gradients
+        if mode == "float_sum":
+            from switchml_b200.parallel.ddp import DistributedDataParallel
+            torch.manual_seed(0)
+            model = torch.nn.Sequential(torch.nn.Linear(256, 512), torch.nn.ReLU(), torch.nn.Linear(512, 512),
+                                        torch.nn.ReLU(), torch.nn.Linear(512, 16)).cuda()
+            ref_model = torch.nn.Sequential(torch.nn.Linear(256, 512), torch.nn.ReLU(), torch.nn.Linear(512, 512),
+                                            torch.nn.ReLU(), torch.nn.Linear(512, 16)).cuda()
+            ref_model.load_state_dict(model.state_dict())
+            ddp = DistributedDataParallel(model, ctx, bucket_mb=0.5, overlap=True)
+            for it in range(3):
+                ddp.zero_grad()
+                xs_all = [torch.randn(32, 256, generator=torch.Generator().manual_seed(10 * r + it)) for r in range(n)]
+                ddp(xs_all[rank].cuda()).square().mean().backward()
+                torch.cuda.synchronize()
+                ref_model.zero_grad()
+                for r in range(n):
+                    (ref_model(xs_all[r].cuda()).square().mean()).backward()
+                for p, rp in zip(model.parameters(), ref_model.parameters()):
+                    assert torch.allclose(p.grad, rp.grad, rtol=1e-4, atol=1e-6), "DDP gradient != sum of local gradients"
+                report["cases"] += 1
         report["stats"] = ctx.get_stats()
         ctx.stop()
         q.put((rank, "ok", report))
