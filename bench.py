@@ -232,10 +232,14 @@ def bench_allreduce(args):
         dist.destroy_process_group()
     if rank != 0:
         return
-    ate = numel / (ms * 1e-3)
+    ate = numel / (ms * 1e-3)  # per worker, the reference's definition
     bus = esz * numel / (ms * 1e-3) * (2.0 * (world - 1) / world) / 1e9
     out = {
-        "metric": "allreduce_ate_per_s", "value": ate, "unit": "elements/s", "n_gpus": world,
+        "metric": "allreduce_ate_per_s", "value": ate * world, "unit": "elements/s", "n_gpus": world,
+        "value_definition": "whole-job aggregate: n_gpus x numel / time per allreduce; ate_per_worker = numel / time "
+                            "is the reference's per-worker ATE/s, and vs_baseline = ate_per_worker / 2.82e9 "
+                            "(SwitchML-RDMA, 8 workers, published figure)",
+        "ate_per_worker": ate,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": ate / PUBLISHED_ATE, "dtype": "fp32" if args.dtype == "float32" else args.dtype,
         "data": "synthetic U(-1,1) seeded per rank",
@@ -246,7 +250,8 @@ def bench_allreduce(args):
                    "symmetric_buffers": bool(args.symmetric), "packet_numel": args.packet_numel,
                    "l2": "input and output tensors (%d MiB each) are larger than the 126 MB L2" % (numel * esz >> 20)},
         "bus_gbs": bus, "alg_gbs": esz * numel / (ms * 1e-3) / 1e9,
-        "e2e": {"value": numel / (e2e_ms * 1e-3), "unit": "elements/s", "ms_per_step": e2e_ms,
+        "e2e": {"value": world * numel / (e2e_ms * 1e-3), "unit": "elements/s", "ms_per_step": e2e_ms,
+                "ate_per_worker": numel / (e2e_ms * 1e-3),
                 "h2d_bytes_per_step": numel * esz, "d2h_bytes_per_step": numel * esz,
                 "steps": args.e2e_steps, "gpu_launches_per_step": e2e_launches},
         "gpu_launches": args.steps,
@@ -330,7 +335,8 @@ def bench_reference(args):
     numel = args.numel
     ate = numel / (ms * 1e-3)
     print(json.dumps({
-        "impl": "reference", "metric": "allreduce_ate_per_s", "value": ate, "unit": "elements/s",
+        "impl": "reference", "metric": "allreduce_ate_per_s", "value": ate * world, "unit": "elements/s",
+        "ate_per_worker": ate,
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": ate / PUBLISHED_ATE,
         "dtype": "fp32" if args.dtype == "float32" else args.dtype, "data": "synthetic (script's --random)",
