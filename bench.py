@@ -130,7 +130,9 @@ def start_context(args, rank, world, local, addr, port, heap_mb=0):
     ctx = sml.Context.get_instance()
     opts = dict(packet_numel=args.packet_numel, device=local, controller_ip=addr,
                 controller_port=port + 101, mode=args.mode, transport=args.transport, launch="inline",
-                symm_heap_mb=heap_mb, slot_bytes=args.slot_bytes, wait_timeout_ms=30000)
+                symm_heap_mb=heap_mb, wait_timeout_ms=30000)
+    if args.slot_bytes:
+        opts["slot_bytes"] = args.slot_bytes
     if args.channels:
         opts["channels"] = args.channels
     if not ctx.start(sml.make_config("cuda", rank=rank, num_workers=world, **opts)):
@@ -362,7 +364,7 @@ def main():
     ap.add_argument("--transport", default="auto", choices=["auto", "nvls", "p2p"])
     ap.add_argument("--symmetric", type=int, default=0, help="1: tensors live in the symmetric heap (zero-copy)")
     ap.add_argument("--packet-numel", type=int, default=256)
-    ap.add_argument("--slot-bytes", type=int, default=131072)
+    ap.add_argument("--slot-bytes", type=int, default=0, help="0 = library default")
     ap.add_argument("--channels", type=int, default=0)
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--e2e-chunk", type=int, default=1 << 24)

@@ -57,7 +57,7 @@ def main():
     ap.add_argument("--impls", default="nccl,sml-float,sml-float-symm,sml-quant,sml-int32")
     ap.add_argument("--transport", default="auto")
     ap.add_argument("--channels", type=int, default=0)
-    ap.add_argument("--slot-bytes", type=int, default=131072)
+    ap.add_argument("--slot-bytes", type=int, default=0, help="0 = library default")
     ap.add_argument("--out", default="")
     a = ap.parse_args()
 
@@ -81,7 +81,9 @@ def main():
             heap = (2 * max_bytes >> 20) + 64 if impl == "sml-float-symm" else 0
             opts = dict(packet_numel=256, device=local, controller_ip=addr, controller_port=port + 201,
                         mode=mode, transport=a.transport, launch="inline", symm_heap_mb=heap,
-                        slot_bytes=a.slot_bytes, wait_timeout_ms=30000)
+                        wait_timeout_ms=30000)
+            if a.slot_bytes:
+                opts["slot_bytes"] = a.slot_bytes
             if a.channels:
                 opts["channels"] = a.channels
             assert ctx.start(sml.make_config("cuda", rank=rank, num_workers=world, **opts))

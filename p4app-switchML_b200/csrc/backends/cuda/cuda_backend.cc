@@ -322,6 +322,7 @@ void CudaBackend::LaunchJob(const std::shared_ptr<Job>& job, cudaStream_t stream
   a.mode = (t.data_type != INT32 && c.mode == "int32_quant") ? kernels::MODE_QUANT : kernels::MODE_SUM;
   a.post_scale = c.average && t.data_type != INT32 ? 1.0f / static_cast<float>(n_) : 1.0f;
   a.epoch_base = epoch_base_;
+  a.tune = static_cast<int>(c.tune);
   size_t esz = DataTypeSize(t.data_type);
   size_t bytes = t.numel * esz;
 

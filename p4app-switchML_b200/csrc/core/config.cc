@@ -114,6 +114,7 @@ bool Config::LoadFromString(const std::string& text, const std::string& origin) 
   opts["backend.cuda.average"] = SML_OPT_BOOL(backend_.cuda.average);
   opts["backend.cuda.launch"] = SML_OPT_STRING(backend_.cuda.launch);
   opts["backend.cuda.rendezvous_dir"] = SML_OPT_STRING(backend_.cuda.rendezvous_dir);
+  opts["backend.cuda.tune"] = SML_OPT_UNSIGNED(backend_.cuda.tune);
   opts["backend.cuda.wait_timeout_ms"] = [this](const std::string& v) {
     return ParseDouble(v, &backend_.cuda.wait_timeout_ms);
   };

@@ -37,7 +37,8 @@ namespace {
 
 static const int kMaxBlocksPerSlot = 8192;  // scale factors of all slots of a channel (shared memory)
 static const int kUnroll = 4;        // 16-byte vectors in flight per thread, local copies
-static const int kUnrollLink = 4;    // ... for loads that cross NVLink (more in flight measured slower)
+static const int kDefaultUnrollLink = 4;  // ... for staged loads that cross NVLink (8 measured slower)
+static const int kZeroCopyUnrollLink = 2;  // the in-place kernel has all 512 threads on the link
 static const int kUnrollInt = 8;
 
 __device__ __forceinline__ bool Aligned16(const void* p) {
@@ -165,12 +166,13 @@ __device__ __forceinline__ void ShardRange(size_t len, int nranks, int rank, siz
 // Warp-specialised streaming pipeline. The 16 warps of a channel split into three roles
 // that walk the channel's tiles independently, so that for different tiles the local
 // HBM copies and the NVLink phase run at the same time:
-//   loader  (warps 0-5)   copy-in (SUM) / exponents + quantise (QUANT)  -> signals phase 1
-//   reducer (warps 6-11)  waits phase 1, reduces + broadcasts its shard  -> signals phase 2
+//   loader  (warps 0-3)   copy-in (SUM) / exponents + quantise (QUANT)  -> signals phase 1
+//   reducer (warps 4-11)  waits phase 1, reduces + broadcasts its shard  -> signals phase 2
 //   storer  (warps 12-15) waits phase 2, copies the finished tile out    -> frees the slot
 // A role synchronises internally with its own named barrier; the loader may run ahead of
 // the storer by the number of slots of the channel.
-static const int kLoadWarps = 6, kReduceWarps = 6, kStoreWarps = 4;
+// Measured on 8 GPUs (1 GiB float32): 4/8/4 warps 2.51 ms, 6/6/4 2.62 ms, 3/10/3 2.76 ms.
+static const int kDefaultLoadWarps = 4, kDefaultReduceWarps = 8;  // the rest of the 16 warps store
 
 struct StagedShared {
   int failed;
@@ -255,9 +257,11 @@ __device__ __forceinline__ void RoleCopy(const Role& role, void* dst, const void
   }
 }
 
-template <int ELEM, int MODE>
+template <int ELEM, int MODE, int kLoadWarps = kDefaultLoadWarps, int kReduceWarps = kDefaultReduceWarps,
+          int kUnrollLink = kDefaultUnrollLink>
 __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
                           unsigned long long elems_per_channel, StagedShared* sh, float* s_sf) {
+  constexpr int kStoreWarps = kThreads / 32 - kLoadWarps - kReduceWarps;
   const int in_esz = ELEM == ELEM_BF16 ? 2 : 4;
   const int st_esz = MODE == MODE_QUANT ? 4 : in_esz;
   const size_t slot_elems = ctx.slot_bytes / st_esz;
@@ -631,7 +635,7 @@ __device__ void RunOneShot(const RankCtx& ctx, const JobArgs& job, int channel,
 }
 
 // ------------------------------------------------------------------------------------
-template <int ELEM>
+template <int ELEM, int kUnrollLink = kZeroCopyUnrollLink>
 __device__ void RunZeroCopy(const RankCtx& ctx, const JobArgs& job, int channel,
                             unsigned long long elems_per_channel, int* s_failed) {
   const int esz = ELEM == ELEM_BF16 ? 2 : 4;
@@ -734,6 +738,19 @@ AllReduceEmuKernel(const RankCtx* ctxs, const JobArgs* jobs, unsigned long long 
   }
   __syncthreads();
   RunJob<ELEM, MODE, ALGO>(s_ctx, s_job, blockIdx.x, epc, &s_state.failed, s_sf);
+}
+
+// Float32 SUM with explicit pipeline parameters (role split, loads in flight): used to
+// pick the defaults by measurement ([backend.cuda] tune).
+template <int ALGO, int LW, int RW, int UL>
+__global__ void __launch_bounds__(kThreads)
+TunedF32SumKernel(const RankCtx ctx, const JobArgs job, unsigned long long epc) {
+  __shared__ StagedShared s_state;
+  __shared__ float s_sf[1];
+  if (threadIdx.x == 0) { s_state.failed = 0; s_state.stored = 0; }
+  __syncthreads();
+  if (ALGO == ALGO_STAGED) RunStaged<ELEM_F32, MODE_SUM, LW, RW, UL>(ctx, job, blockIdx.x, epc, &s_state, s_sf);
+  else RunZeroCopy<ELEM_F32, UL>(ctx, job, blockIdx.x, epc, &s_state.failed);
 }
 
 __global__ void WaitProbeKernel(const RankCtx ctx) {
@@ -876,6 +893,29 @@ cudaError_t LaunchAllReduce(const RankCtx& ctx, const JobArgs& job, const Launch
                             cudaStream_t stream) {
   if (ctx.nranks < 1 || ctx.nranks > kMaxRanks || plan.channels > kMaxChannels)
     return cudaErrorInvalidValue;
+  if (job.tune > 0 && job.elem_type == ELEM_F32 && job.mode == MODE_SUM && job.algo != ALGO_ONESHOT) {
+    const unsigned long long epc = plan.elems_per_channel;
+#define SML_TUNED(ALGO, LW, RW, UL) TunedF32SumKernel<ALGO, LW, RW, UL><<<plan.channels, kThreads, 0, stream>>>(ctx, job, epc)
+    if (job.algo == ALGO_STAGED) {
+      switch (job.tune) {
+        case 1: SML_TUNED(ALGO_STAGED, 6, 6, 4); break;
+        case 2: SML_TUNED(ALGO_STAGED, 6, 6, 8); break;
+        case 3: SML_TUNED(ALGO_STAGED, 4, 8, 8); break;
+        case 4: SML_TUNED(ALGO_STAGED, 3, 10, 4); break;
+        case 5: SML_TUNED(ALGO_STAGED, 4, 8, 2); break;
+        default: SML_TUNED(ALGO_STAGED, 4, 8, 4); break;
+      }
+    } else {
+      switch (job.tune) {
+        case 1: SML_TUNED(ALGO_ZEROCOPY, 6, 6, 8); break;
+        case 2: SML_TUNED(ALGO_ZEROCOPY, 6, 6, 4); break;
+        case 3: SML_TUNED(ALGO_ZEROCOPY, 6, 6, 16); break;
+        default: SML_TUNED(ALGO_ZEROCOPY, 6, 6, 2); break;
+      }
+    }
+#undef SML_TUNED
+    return cudaGetLastError();
+  }
   SML_DISPATCH(LaunchOne, job.elem_type, job.mode, job.algo, ctx, job, plan, stream);
 }
 

@@ -69,6 +69,7 @@ struct JobArgs {
   float post_scale;  // multiplied into the result (1/num_workers for averaging)
   unsigned long long epoch_base;  // flags written by this job are epoch_base+1 .. epoch_base+epochs
   int oneshot_parity;
+  int tune;          // > 0: float32 SUM variant with other pipeline parameters (see LaunchAllReduce)
   unsigned long long tile_elems;  // ALGO_STAGED: elements per tile (<= elements of a slot)
   // ALGO_ZEROCOPY: offsets of in/out inside the symmetric user region and its mappings
   char* user_peer[kMaxRanks];
