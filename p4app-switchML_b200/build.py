@@ -12,7 +12,9 @@ Products (all inside this directory, never installed elsewhere):
 
 The role of the reference's Makefiles (dev_root/Makefile, client_lib/Makefile,
 benchmarks/Makefile, examples/Makefile) with their DEBUG/DUMMY/... switches: DEBUG=1 in
-the environment builds with -O0 -g, SWITCHML_CHECKED=1 adds bounds checks in kernels.
+the environment builds with -O0 -g. `python build.py --sanitize thread` (or address)
+builds the host-only parts and the native unit tests under that sanitizer as
+build-<sanitizer>/core_tests (the reference has no sanitizer configuration at all).
 """
 import argparse
 import concurrent.futures as cf
@@ -31,6 +33,9 @@ ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 DEBUG = os.environ.get("DEBUG", "0") == "1"
 OPT = ["-O0", "-g"] if DEBUG else ["-O3"]
 DEFS = ["-DSWITCHML_CHECKED"] if os.environ.get("SWITCHML_CHECKED", "0") == "1" else []
+# SANITIZE=thread|address builds the host code (and bin/core_tests) under that sanitizer into
+# build-<name>/; used by the CPU race/memory checks, never for the GPU library in lib/.
+SANITIZE = os.environ.get("SANITIZE", "")
 INCLUDES = ["-I" + os.path.join(ROOT, "include"), "-I" + os.path.join(ROOT, "csrc"),
             "-I" + os.path.join(CUDA_HOME, "include")]
 
@@ -141,6 +146,31 @@ def build(jobs=None, verbose=False, programs=True):
     return main_lib
 
 
+HOST_ONLY = [s for s in LIB_SOURCES if s.endswith(".cc") and "/cuda/" not in s and "capi" not in s and
+             s != "csrc/core/backend.cc"]
+
+
+def build_sanitized(kind, verbose=False):
+    """Host-only build of the core + CPU backends + native tests with -fsanitize=<kind>.
+    The cuda backend is replaced by a stub factory, so no CUDA library is involved."""
+    out = os.path.join(ROOT, "build-" + kind)
+    os.makedirs(out, exist_ok=True)
+    stub = os.path.join(out, "cuda_stub.cc")
+    with open(stub, "w") as f:
+        f.write('#include "backends/cuda/cuda_backend.h"\n#include "switchml/log.h"\nnamespace switchml {\n'
+                'Backend* CreateCudaBackend(Context&, Config&) { SML_LOG(FATAL) << "no cuda in this build"; return nullptr; }\n}\n')
+    srcs = [os.path.join(ROOT, s) for s in HOST_ONLY + ["csrc/core/backend.cc", "csrc/tests/core_tests.cc"]] + [stub]
+    exe = os.path.join(out, "core_tests")
+    cmd = ["g++", "-std=c++17", "-O1", "-g", "-fno-omit-frame-pointer", "-fsanitize=" + kind, "-pthread"] + \
+          INCLUDES + srcs + ["-o", exe]
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("sanitized build failed:\n" + r.stdout + r.stderr)
+    return exe
+
+
 def clean():
     for d in (os.path.join(ROOT, "build"), LIB, BIN):
         shutil.rmtree(d, ignore_errors=True)
@@ -151,9 +181,13 @@ if __name__ == "__main__":
     ap.add_argument("--clean", action="store_true")
     ap.add_argument("--jobs", type=int, default=None)
     ap.add_argument("-v", "--verbose", action="store_true")
+    ap.add_argument("--sanitize", choices=["thread", "address", "undefined"], default=SANITIZE or None)
     a = ap.parse_args()
     if a.clean:
         clean()
+    if a.sanitize:
+        print(build_sanitized(a.sanitize, a.verbose))
+        sys.exit(0)
     try:
         print(build(a.jobs, a.verbose))
     except RuntimeError as e:

@@ -2,10 +2,19 @@
 #include "backends/cuda/cuda_backend.h"
 
 #include <cuda_runtime.h>
+#if __has_include(<nvtx3/nvToolsExt.h>)
+#include <nvtx3/nvToolsExt.h>
+#define SML_NVTX_PUSH(name) nvtxRangePushA(name)
+#define SML_NVTX_POP() nvtxRangePop()
+#else
+#define SML_NVTX_PUSH(name) ((void)0)
+#define SML_NVTX_POP() ((void)0)
+#endif
 
 #include <atomic>
 #include <chrono>
 #include <condition_variable>
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <deque>
@@ -363,7 +372,13 @@ void CudaBackend::LaunchJob(const std::shared_ptr<Job>& job, cudaStream_t stream
   // A single worker reducing in place has nothing to do (float_sum: the sum of one term;
   // quantised mode still runs, because quantise/dequantise rounds the values).
   bool nothing_to_do = n_ == 1 && t.in_ptr == t.out_ptr && a.mode == kernels::MODE_SUM && a.post_scale == 1.0f;
+  // One NVTX range per job: shows up in timeline tools, costs nothing without one.
+  char range[96];
+  snprintf(range, sizeof(range), "switchml job %llu: %llu x %s", static_cast<unsigned long long>(job->id_),
+           static_cast<unsigned long long>(t.numel), DataTypeName(t.data_type));
+  SML_NVTX_PUSH(range);
   if (t.numel > 0 && !nothing_to_do) e = kernels::LaunchAllReduce(job_ctx, a, plan, stream);
+  SML_NVTX_POP();
   if (e == cudaSuccess) e = cudaEventRecord(f->done, stream);
   if (e != cudaSuccess) {
     f->launch_error = std::string("kernel launch failed: ") + cudaGetErrorString(e);

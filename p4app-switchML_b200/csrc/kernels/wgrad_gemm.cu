@@ -41,7 +41,7 @@ constexpr int kTileM = 128;
 constexpr int kTileN = 256;
 constexpr int kTileK = 64;    // rows of K per pipeline stage
 constexpr int kMmaK = 16;     // K of one tcgen05.mma for 16-bit operands
-constexpr int kStages = 3;
+constexpr int kStages = 4;
 constexpr int kAtomMN = 64;   // bf16 elements in one 128-byte swizzle row
 constexpr int kABytes = kTileK * kTileM * 2;  // 16 KiB
 constexpr int kBBytes = kTileK * kTileN * 2;  // 32 KiB
@@ -347,9 +347,12 @@ WgradGemmKernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   } else if (kFused && warp >= 8) {
     // ------------------------------ cross-GPU reducer ------------------------------
     // Tile t is reduced by rank t mod nranks, by the CTA that runs (t / nranks) mod grid.
+    // Only the first `reduce_ctas` CTAs reduce; the others leave as soon as their GEMM tiles
+    // are stored, which returns their SMs to whatever runs next on other streams.
     const int rtid = threadIdx.x - 256;  // 0..127
+    const int reduce_ctas = min(static_cast<int>(gridDim.x), fused.reduce_ctas);
     bool ok = true;
-    for (int j = blockIdx.x; ok; j += gridDim.x) {
+    for (int j = blockIdx.x; ok && static_cast<int>(blockIdx.x) < reduce_ctas; j += reduce_ctas) {
       const long long tile = static_cast<long long>(j) * fused.nranks + fused.rank;
       if (tile >= num_tiles) break;
       ok = WaitFlags(fused.flags_peer[fused.rank] + static_cast<size_t>(tile) * 8, fused.nranks, fused.epoch,
@@ -381,9 +384,10 @@ WgradGemmKernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         }
       }
     }
-    // Nobody leaves before every rank has finished reducing its tiles.
+    // No reducing CTA leaves before every rank's matching CTA has finished its tiles, so
+    // when the kernel has ended on all ranks every tile holds the global sum.
     NamedBarrier(3, 128);
-    if (rtid < 32) {
+    if (rtid < 32 && static_cast<int>(blockIdx.x) < reduce_ctas) {
       if (lane < fused.nranks) {
         __threadfence_system();
         StoreReleaseSys(fused.flags_peer[lane] + static_cast<size_t>(num_tiles + blockIdx.x) * 8 + fused.rank,
@@ -467,7 +471,7 @@ extern "C" int switchml_wgrad_gemm(const void* dy, const void* x, float* dw, int
   memset(&none, 0, sizeof(none));
   cudaError_t e;
   if (fused && fused->nranks > 1) {
-    if (fused->nranks > 8 || !fused->out_mc) return -1;
+    if (fused->nranks > 8 || !fused->out_mc || fused->reduce_ctas < 1) return -1;
     // All CTAs take part in the closing cross-GPU barrier, so the grid must be the same on
     // every rank and fully resident: one CTA per SM at most.
     static bool attr_f = false;

@@ -39,6 +39,7 @@ typedef struct WgradFusedArgs {
   unsigned long long epoch;
   unsigned long long timeout_ns;
   float scale; /* multiplied into the reduced gradient (1/nranks for the mean) */
+  int reduce_ctas; /* CTAs that take part in the cross-GPU reduction (>= 1; 32 is plenty) */
 } WgradFusedArgs;
 
 int switchml_wgrad_gemm(const void* dy, const void* x, float* dw, int M, int N, int K,

@@ -15,6 +15,7 @@
 #ifndef SWITCHML_CONTEXT_H_
 #define SWITCHML_CONTEXT_H_
 
+#include <atomic>
 #include <condition_variable>
 #include <memory>
 #include <mutex>
@@ -67,7 +68,7 @@ class Context {
   ~Context();
   void FinishJob(const std::shared_ptr<Job>& job, bool ok, const std::string& why);
 
-  ContextState context_state_;
+  std::atomic<ContextState> context_state_;  // read by worker threads while Start/Stop write it
   Config config_;
   Stats stats_;
   std::unique_ptr<Backend> backend_;

@@ -20,7 +20,7 @@ class _FusedArgs(ctypes.Structure):
     _fields_ = [("rank", ctypes.c_int), ("nranks", ctypes.c_int),
                 ("flags_peer", ctypes.c_void_p * 8), ("out_mc", ctypes.c_void_p),
                 ("epoch", ctypes.c_ulonglong), ("timeout_ns", ctypes.c_ulonglong),
-                ("scale", ctypes.c_float)]
+                ("scale", ctypes.c_float), ("reduce_ctas", ctypes.c_int)]
 
 
 def _lib():
@@ -77,7 +77,7 @@ class FusedWgrad:
     kernel is enqueued on the current stream and needs no separate allreduce.
     """
 
-    def __init__(self, ctx, M, N, scale=1.0, timeout_ms=20000.0):
+    def __init__(self, ctx, M, N, scale=1.0, timeout_ms=20000.0, reduce_ctas=32):
         self.ctx, self.M, self.N, self.scale = ctx, M, N, scale
         self.grad = ctx.symmetric_empty(M * N, torch.float32).view(M, N)
         words = flag_words(M, N)
@@ -97,12 +97,26 @@ class FusedWgrad:
         self.args.epoch = 0
         self.args.timeout_ns = int(timeout_ms * 1e6)
         self.args.scale = scale
+        self.args.reduce_ctas = reduce_ctas
         self.fused = self.nranks > 1 and bool(mc)
         torch.cuda.synchronize()
 
-    def run(self, dy, x):
+    def run(self, dy, x, side_stream=None):
+        """Compute (and reduce) the gradient. With `side_stream` the kernel runs there,
+        ordered after the current stream; call ``wait_pending()`` before using the result.
+        Nothing later in backward needs dW, so this keeps the reduction off the critical path."""
         assert dy.dtype == torch.bfloat16 and x.dtype == torch.bfloat16
         dy, x = dy.contiguous(), x.contiguous()
+        if side_stream is not None:
+            side_stream.wait_stream(torch.cuda.current_stream(dy.device))
+            dy.record_stream(side_stream)
+            x.record_stream(side_stream)
+            with torch.cuda.stream(side_stream):
+                out = self.run(dy, x)
+                ev = torch.cuda.Event()
+                ev.record(side_stream)
+            _PENDING.append(ev)
+            return out
         K = dy.shape[0]
         self.args.epoch += 1
         stream = torch.cuda.current_stream(dy.device).cuda_stream
@@ -121,6 +135,24 @@ class FusedWgrad:
         return self.grad
 
 
+_PENDING = []
+_SIDE_STREAMS = {}
+
+
+def wait_pending(stream=None):
+    """Order `stream` (default: current) after every weight-gradient kernel that was sent to
+    a side stream since the last call."""
+    s = stream or torch.cuda.current_stream()
+    while _PENDING:
+        s.wait_event(_PENDING.pop())
+
+
+def _side_stream(device):
+    if device not in _SIDE_STREAMS:
+        _SIDE_STREAMS[device] = torch.cuda.Stream(device=device, priority=-1)
+    return _SIDE_STREAMS[device]
+
+
 class _FusedLinearFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias, layer):
@@ -137,7 +169,8 @@ class _FusedLinearFn(torch.autograd.Function):
         dx = (dy2 @ weight.to(dy2.dtype)).reshape(x.shape) if ctx.needs_input_grad[0] else None
         # dW on the tcgen05 tensor cores, summed over the workers in the same kernel,
         # written straight into the parameter's gradient.
-        layer.wgrad.run(dy2.to(torch.bfloat16), x2.to(torch.bfloat16))
+        layer.wgrad.run(dy2.to(torch.bfloat16), x2.to(torch.bfloat16),
+                        side_stream=_side_stream(dy2.device) if layer.overlap else None)
         dbias = dy2.sum(0).to(layer.bias.dtype) if layer.bias is not None else None
         return dx, None, dbias, None
 
@@ -148,6 +181,7 @@ class FusedWgradLinear(torch.nn.Linear):
     ``.grad`` then aliases the symmetric gradient buffer and arrives already reduced."""
 
     wgrad = None
+    overlap = True  # run the weight-gradient kernel on a side stream
 
     def attach(self, ctx, scale=1.0):
         self.wgrad = FusedWgrad(ctx, self.out_features, self.in_features, scale)

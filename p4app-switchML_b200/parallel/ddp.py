@@ -150,6 +150,8 @@ class DistributedDataParallel(torch.nn.Module):
                 # that all ranks submit the same jobs in the same order.
                 self._launch(bi)
         self.buckets.wait()
+        from ..ops import wgrad as _wgrad
+        _wgrad.wait_pending()  # fused weight-gradient kernels running on their side stream
 
     def zero_grad(self, set_to_none=False):
         self.buckets.zero_()

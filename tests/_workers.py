@@ -201,3 +201,83 @@ def pg_worker(rank, n, port, q):
         q.put((rank, "ok", None))
     except Exception:
         q.put((rank, "error", traceback.format_exc()))
+
+
+def ddp_hook_worker(rank, n, ctl_port, dist_port, q):
+    """PyTorch DDP (NCCL process group for its own bookkeeping) with the SwitchML
+    communication hook doing the gradient reduction; compared with gradients computed
+    from all ranks' data on one device."""
+    try:
+        import torch
+        import torch.distributed as dist
+        import switchml_b200 as sml
+        from switchml_b200.parallel.ddp_hook import SwitchMLHookState, switchml_allreduce_hook
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=n, init_method="tcp://127.0.0.1:%d" % dist_port,
+                                device_id=torch.device("cuda", rank))
+        ctx = sml.Context.get_instance()
+        assert ctx.start(sml.make_config("cuda", rank=rank, num_workers=n, packet_numel=256, device=rank,
+                                         controller_port=ctl_port, mode="float_sum", launch="inline",
+                                         average=True, wait_timeout_ms=20000))
+        torch.manual_seed(0)
+        def make():
+            return torch.nn.Sequential(torch.nn.Linear(128, 1024), torch.nn.ReLU(), torch.nn.Linear(1024, 1024),
+                                       torch.nn.ReLU(), torch.nn.Linear(1024, 8)).cuda()
+        model, ref = make(), make()
+        ref.load_state_dict(model.state_dict())
+        ddp = torch.nn.parallel.DistributedDataParallel(model, device_ids=[rank], bucket_cap_mb=1)
+        ddp.register_comm_hook(SwitchMLHookState(ctx), switchml_allreduce_hook)
+        for it in range(3):
+            xs = [torch.randn(16, 128, generator=torch.Generator().manual_seed(7 * r + it)) for r in range(n)]
+            ddp.zero_grad()
+            ddp(xs[rank].cuda()).square().mean().backward()
+            torch.cuda.synchronize()
+            ref.zero_grad()
+            for r in range(n):
+                (ref(xs[r].cuda()).square().mean() / n).backward()
+            for p, rp in zip(model.parameters(), ref.parameters()):
+                assert torch.allclose(p.grad, rp.grad, rtol=1e-4, atol=1e-6), "hook gradient != mean of local gradients"
+        ctx.stop()
+        dist.destroy_process_group()
+        q.put((rank, "ok", None))
+    except Exception:
+        q.put((rank, "error", traceback.format_exc()))
+
+
+def absent_peer_worker(rank, n, ctl_port, q):
+    """Failure detection without any GPU fault: after one common job, the last rank
+    simply stops submitting. The others' next job runs into the bounded device wait, fails
+    with a timeout status, and their context remains usable for reading statistics and for
+    an orderly stop. Peer memory only (no multicast objects are bound while a rank is
+    'gone')."""
+    try:
+        import time
+        import torch
+        import switchml_b200 as sml
+        torch.cuda.set_device(rank)
+        ctx = sml.Context.get_instance()
+        assert ctx.start(sml.make_config("cuda", rank=rank, num_workers=n, packet_numel=256, device=rank,
+                                         controller_port=ctl_port, transport="p2p", mode="float_sum",
+                                         launch="worker", wait_timeout_ms=400))
+        x = torch.ones(1 << 20, device="cuda")
+        ctx.all_reduce(x)                       # everybody takes part: works
+        assert float(x[0]) == float(n)
+        info = {}
+        if rank == n - 1:
+            time.sleep(3.0)                     # "absent": submits nothing while the others wait
+        else:
+            t0 = time.time()
+            job = ctx.all_reduce_async(x)
+            st = job.wait(timeout_ms=20000)
+            info["status"] = st.name
+            info["error"] = job.error()
+            info["seconds"] = time.time() - t0
+            stats = ctx.get_stats()
+            info["jobs_failed"] = stats["jobs_failed"]
+            info["device_timeouts"] = stats["backend"]["device_timeouts"]
+            torch.cuda.synchronize()            # the device still answers
+            info["alive"] = float((x * 0 + 1).sum()) == float(x.numel())
+        ctx.stop()
+        q.put((rank, "ok", info))
+    except Exception:
+        q.put((rank, "error", traceback.format_exc()))

@@ -59,3 +59,39 @@ def test_auto_transport_agrees_on_all_ranks():
     # Whatever the fabric offers, all ranks must agree and every case must pass.
     assert len({r["multimem"] for r in reps.values()}) == 1
     assert all(r["stats"]["jobs_failed"] == 0 for r in reps.values())
+
+
+def _spawn(target, n, extra_ports=1):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    ports = [free_port() for _ in range(extra_ports)]
+    procs = [ctx.Process(target=target, args=(r, n, *ports, q)) for r in range(n)]
+    for p in procs:
+        p.start()
+    out = {}
+    try:
+        for _ in range(n):
+            rank, status, info = q.get(timeout=300)
+            assert status == "ok", "rank %d:\n%s" % (rank, info)
+            out[rank] = info
+    finally:
+        for p in procs:
+            p.join(timeout=60)
+            if p.is_alive():
+                p.kill()
+    return out
+
+
+def test_torch_ddp_with_switchml_comm_hook():
+    from _workers import ddp_hook_worker
+    _spawn(ddp_hook_worker, min(_world(), 4), extra_ports=2)
+
+
+def test_absent_peer_is_detected_by_bounded_wait():
+    from _workers import absent_peer_worker
+    n = 2
+    infos = _spawn(absent_peer_worker, n)
+    waiting = infos[0]
+    assert waiting["status"] == "FAILED" and "did not arrive" in waiting["error"]
+    assert waiting["jobs_failed"] == 1 and waiting["device_timeouts"] >= 1
+    assert waiting["seconds"] < 10 and waiting["alive"]
