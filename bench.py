@@ -14,7 +14,7 @@ events on the launching stream, and the slowest rank counts. Rank 0 prints one J
 
 The end-to-end figure ("e2e") times the same allreduce for a caller whose data lives in
 pinned host memory: every step copies the input host→device, reduces it and reads the
-result back device→host, through Context.all_reduce_host.
+result back device→host, through switchml_b200.parallel.host_pipeline.HostAllReduce.
 
 Other workloads (same JSON shape): --workload resnet50 | vgg19 | bert (synthetic DDP
 training, images/s or tokens/s).
@@ -34,68 +34,7 @@ if ROOT not in sys.path:
 PUBLISHED_ATE = 2.82e9  # SwitchML-RDMA, 8 workers, read off the reference's benchmark figure
 
 
-class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
-
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
-
-    def __init__(self, gpu_index=0):
-        self.gpu = gpu_index
-        self.proc = None
-        self.lines = []
-
-    def start(self):
-        try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits", "-lms", "25",
-                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
-            self.thread.start()
-        except OSError:
-            self.proc = None
-
-    def _read(self):
-        for line in self.proc.stdout:
-            self.lines.append((time.time(), line.strip()))
-
-    def stop(self, window=None):
-        """Summary of the samples taken inside `window` = (t0, t1) wall-clock seconds; when
-        the window is shorter than the sampling period, of the samples closest to it."""
-        if not self.proc:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-        sm, smax, reasons, power = [], [], set(), []
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        time.sleep(0.05)
-        lines = self.lines
-        if window and lines:
-            inside = [l for l in lines if window[0] <= l[0] <= window[1] + 0.06]
-            if len(inside) < 3:
-                mid = 0.5 * (window[0] + window[1])
-                inside = sorted(lines, key=lambda l: abs(l[0] - mid))[:5]
-            lines = inside
-        for _, line in lines:
-            f = [x.strip() for x in line.split(",")]
-            if len(f) < 9:
-                continue
-            try:
-                sm.append(float(f[1]))
-                smax.append(float(f[2]))
-                power.append(float(f[3]))
-            except ValueError:
-                continue
-            for name, val in zip(names, f[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        sm.sort()
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(smax) if smax else None,
-                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+from switchml_b200.utils.clocks import ClockSampler  # noqa: E402
 
 
 def dist_env():

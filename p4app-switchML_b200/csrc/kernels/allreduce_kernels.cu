@@ -39,7 +39,7 @@ static const int kMaxBlocksPerSlot = 8192;  // scale factors of all slots of a c
 static const int kUnroll = 4;        // 16-byte vectors in flight per thread, local copies
 static const int kDefaultUnrollLink = 4;  // ... for staged loads that cross NVLink (8 measured slower)
 static const int kZeroCopyUnrollLink = 2;  // the in-place kernel has all 512 threads on the link
-static const int kUnrollInt = 8;
+
 
 __device__ __forceinline__ bool Aligned16(const void* p) {
   return (reinterpret_cast<uintptr_t>(p) & 15) == 0;
@@ -262,6 +262,7 @@ template <int ELEM, int MODE, int kLoadWarps = kDefaultLoadWarps, int kReduceWar
 __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
                           unsigned long long elems_per_channel, StagedShared* sh, float* s_sf) {
   constexpr int kStoreWarps = kThreads / 32 - kLoadWarps - kReduceWarps;
+  constexpr int kUnrollInt = 2 * kUnrollLink;  // 4-byte integer lanes in flight per thread
   const int in_esz = ELEM == ELEM_BF16 ? 2 : 4;
   const int st_esz = MODE == MODE_QUANT ? 4 : in_esz;
   const size_t slot_elems = ctx.slot_bytes / st_esz;
@@ -740,16 +741,16 @@ AllReduceEmuKernel(const RankCtx* ctxs, const JobArgs* jobs, unsigned long long 
   RunJob<ELEM, MODE, ALGO>(s_ctx, s_job, blockIdx.x, epc, &s_state.failed, s_sf);
 }
 
-// Float32 SUM with explicit pipeline parameters (role split, loads in flight): used to
+// Float32 kernels with explicit pipeline parameters (role split, loads in flight): used to
 // pick the defaults by measurement ([backend.cuda] tune).
-template <int ALGO, int LW, int RW, int UL>
+template <int MODE, int ALGO, int LW, int RW, int UL>
 __global__ void __launch_bounds__(kThreads)
-TunedF32SumKernel(const RankCtx ctx, const JobArgs job, unsigned long long epc) {
+TunedF32Kernel(const RankCtx ctx, const JobArgs job, unsigned long long epc) {
   __shared__ StagedShared s_state;
-  __shared__ float s_sf[1];
+  __shared__ float s_sf[MODE == MODE_QUANT ? kMaxBlocksPerSlot : 1];
   if (threadIdx.x == 0) { s_state.failed = 0; s_state.stored = 0; }
   __syncthreads();
-  if (ALGO == ALGO_STAGED) RunStaged<ELEM_F32, MODE_SUM, LW, RW, UL>(ctx, job, blockIdx.x, epc, &s_state, s_sf);
+  if (ALGO == ALGO_STAGED) RunStaged<ELEM_F32, MODE, LW, RW, UL>(ctx, job, blockIdx.x, epc, &s_state, s_sf);
   else RunZeroCopy<ELEM_F32, UL>(ctx, job, blockIdx.x, epc, &s_state.failed);
 }
 
@@ -893,24 +894,34 @@ cudaError_t LaunchAllReduce(const RankCtx& ctx, const JobArgs& job, const Launch
                             cudaStream_t stream) {
   if (ctx.nranks < 1 || ctx.nranks > kMaxRanks || plan.channels > kMaxChannels)
     return cudaErrorInvalidValue;
-  if (job.tune > 0 && job.elem_type == ELEM_F32 && job.mode == MODE_SUM && job.algo != ALGO_ONESHOT) {
+  if (job.tune > 0 && job.elem_type == ELEM_F32 && job.algo != ALGO_ONESHOT) {
     const unsigned long long epc = plan.elems_per_channel;
-#define SML_TUNED(ALGO, LW, RW, UL) TunedF32SumKernel<ALGO, LW, RW, UL><<<plan.channels, kThreads, 0, stream>>>(ctx, job, epc)
-    if (job.algo == ALGO_STAGED) {
+#define SML_TUNED(MODE, ALGO, LW, RW, UL) TunedF32Kernel<MODE, ALGO, LW, RW, UL><<<plan.channels, kThreads, 0, stream>>>(ctx, job, epc)
+    if (job.algo == ALGO_STAGED && job.mode == MODE_QUANT) {
       switch (job.tune) {
-        case 1: SML_TUNED(ALGO_STAGED, 6, 6, 4); break;
-        case 2: SML_TUNED(ALGO_STAGED, 6, 6, 8); break;
-        case 3: SML_TUNED(ALGO_STAGED, 4, 8, 8); break;
-        case 4: SML_TUNED(ALGO_STAGED, 3, 10, 4); break;
-        case 5: SML_TUNED(ALGO_STAGED, 4, 8, 2); break;
-        default: SML_TUNED(ALGO_STAGED, 4, 8, 4); break;
+        case 1: SML_TUNED(MODE_QUANT, ALGO_STAGED, 6, 8, 4); break;
+        case 2: SML_TUNED(MODE_QUANT, ALGO_STAGED, 8, 6, 4); break;
+        case 3: SML_TUNED(MODE_QUANT, ALGO_STAGED, 6, 6, 4); break;
+        case 4: SML_TUNED(MODE_QUANT, ALGO_STAGED, 6, 8, 8); break;
+        case 5: SML_TUNED(MODE_QUANT, ALGO_STAGED, 4, 8, 8); break;
+        case 6: SML_TUNED(MODE_QUANT, ALGO_STAGED, 7, 7, 4); break;
+        default: SML_TUNED(MODE_QUANT, ALGO_STAGED, 4, 8, 4); break;
+      }
+    } else if (job.algo == ALGO_STAGED) {
+      switch (job.tune) {
+        case 1: SML_TUNED(MODE_SUM, ALGO_STAGED, 6, 6, 4); break;
+        case 2: SML_TUNED(MODE_SUM, ALGO_STAGED, 6, 6, 8); break;
+        case 3: SML_TUNED(MODE_SUM, ALGO_STAGED, 4, 8, 8); break;
+        case 4: SML_TUNED(MODE_SUM, ALGO_STAGED, 3, 10, 4); break;
+        case 5: SML_TUNED(MODE_SUM, ALGO_STAGED, 4, 8, 2); break;
+        default: SML_TUNED(MODE_SUM, ALGO_STAGED, 4, 8, 4); break;
       }
     } else {
       switch (job.tune) {
-        case 1: SML_TUNED(ALGO_ZEROCOPY, 6, 6, 8); break;
-        case 2: SML_TUNED(ALGO_ZEROCOPY, 6, 6, 4); break;
-        case 3: SML_TUNED(ALGO_ZEROCOPY, 6, 6, 16); break;
-        default: SML_TUNED(ALGO_ZEROCOPY, 6, 6, 2); break;
+        case 1: SML_TUNED(MODE_SUM, ALGO_ZEROCOPY, 6, 6, 8); break;
+        case 2: SML_TUNED(MODE_SUM, ALGO_ZEROCOPY, 6, 6, 4); break;
+        case 3: SML_TUNED(MODE_SUM, ALGO_ZEROCOPY, 6, 6, 16); break;
+        default: SML_TUNED(MODE_SUM, ALGO_ZEROCOPY, 6, 6, 2); break;
       }
     }
 #undef SML_TUNED

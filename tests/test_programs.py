@@ -1,0 +1,118 @@
+"""The C++ programs on the dummy backend (hello_world, allreduce_benchmark, dnn_benchmark;
+reference examples/hello_world, benchmarks/allreduce_benchmark, benchmarks/dnn_benchmark),
+the shipped configuration templates, and workers using a stand-alone switchml_switchd."""
+import glob
+import multiprocessing as mp
+import os
+import signal
+import subprocess
+import time
+
+import numpy as np
+import pytest
+
+from conftest import free_port
+from switchml_b200.utils.config import check_config
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+PKG = os.path.join(ROOT, "p4app-switchML_b200")
+BIN = os.path.join(PKG, "bin")
+
+
+@pytest.fixture(scope="module")
+def built():
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("_switchml_build", os.path.join(PKG, "build.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    mod.build()
+
+
+@pytest.fixture
+def cfg_dir(tmp_path):
+    text = open(os.path.join(PKG, "configs", "switchml-dummy.cfg")).read()
+    text = text.replace("num_workers = 1", "num_workers = 3").replace("bandwidth = 100000.0", "bandwidth = 0")
+    (tmp_path / "switchml.cfg").write_text(text)
+    return tmp_path
+
+
+def test_shipped_templates_validate():
+    files = sorted(glob.glob(os.path.join(PKG, "configs", "switchml-*.cfg")))
+    assert len(files) == 3
+    for f in files:
+        dump = check_config(open(f).read())
+        assert "backend = " + os.path.basename(f)[len("switchml-"):-len(".cfg")] in dump
+
+
+def test_hello_world(built, cfg_dir):
+    r = subprocess.run([os.path.join(BIN, "hello_world")], cwd=cfg_dir, capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "Data verified successfully" in r.stdout
+
+
+@pytest.mark.parametrize("extra", [["--tensor-type", "float", "--inplace", "false"], ["--tensor-type", "int32"],
+                                   ["--tensor-type", "float", "--random", "true", "--seed", "5", "--sync-every", "0"]])
+def test_allreduce_benchmark_verifies(built, cfg_dir, extra):
+    cmd = [os.path.join(BIN, "allreduce_benchmark"), "--tensor-numel", "200001", "--num-jobs", "4",
+           "--num-warmup-jobs", "2", "--verify", "true", "--dump-stats", "true"] + extra
+    r = subprocess.run(cmd, cwd=cfg_dir, capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "Results verified successfully." in r.stdout
+    assert "Goodput min: #" in r.stdout and "Aggregated tensor elements per second: #" in r.stdout
+    assert "Submitted jobs: #" in r.stdout
+
+
+def test_dnn_benchmark(built, cfg_dir):
+    cmd = [os.path.join(BIN, "dnn_benchmark"), "--model", os.path.join(PKG, "benchmarks", "models", "example.csv"),
+           "--num-iters", "3", "--num-warmup-iters", "1", "--verify", "true"]
+    r = subprocess.run(cmd, cwd=cfg_dir, capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "Results verified successfully." in r.stdout and "Iterations/s min: #" in r.stdout
+
+
+def test_benchmark_stops_on_sigint(built, cfg_dir):
+    text = (cfg_dir / "switchml.cfg").read_text().replace("bandwidth = 0", "bandwidth = 50.0")
+    (cfg_dir / "switchml.cfg").write_text(text)
+    p = subprocess.Popen([os.path.join(BIN, "allreduce_benchmark"), "--tensor-numel", "4000000", "--num-jobs", "50"],
+                         cwd=cfg_dir, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    time.sleep(1.5)
+    p.send_signal(signal.SIGINT)
+    out, _ = p.communicate(timeout=30)
+    assert p.returncode == 0 and "stopping the context" in out
+
+
+def _switchd_worker(rank, n, ctl_port, udp_port, q):
+    try:
+        import switchml_b200 as sml
+        ctx = sml.Context.get_instance()
+        assert ctx.start(sml.make_config("udp", rank=rank, num_workers=n, packet_numel=64, num_worker_threads=2,
+                                         max_outstanding_packets=64, controller_port=ctl_port, switch_port=udp_port,
+                                         worker_port=0, spawn_switch=False))
+        x = np.full(5000, rank + 1.0, dtype=np.float32)
+        ctx.all_reduce(x)
+        ctx.stop()
+        q.put((rank, float(x[0]), float(x[-1])))
+    except Exception as e:  # pragma: no cover
+        q.put((rank, repr(e), None))
+
+
+def test_workers_with_standalone_switchd(built):
+    ctl, udp = free_port(), free_port()
+    d = subprocess.Popen([os.path.join(BIN, "switchml_switchd"), "--ip", "127.0.0.1", "--port", str(ctl),
+                          "--udp-port", str(udp), "--log-level", "0"], stdout=subprocess.PIPE, text=True)
+    try:
+        time.sleep(0.5)
+        ctx = mp.get_context("spawn")
+        q = ctx.Queue()
+        procs = [ctx.Process(target=_switchd_worker, args=(r, 2, ctl, udp, q)) for r in range(2)]
+        for p in procs:
+            p.start()
+        got = [q.get(timeout=120) for _ in range(2)]
+        for p in procs:
+            p.join(timeout=30)
+        for rank, first, last in got:
+            assert first == 3.0 and last == 3.0, (rank, first, last)
+    finally:
+        d.send_signal(signal.SIGTERM)
+        out, _ = d.communicate(timeout=10)
+    assert "broadcast" in out
