@@ -377,7 +377,9 @@ void CudaBackend::LaunchJob(const std::shared_ptr<Job>& job, cudaStream_t stream
   snprintf(range, sizeof(range), "switchml job %llu: %llu x %s", static_cast<unsigned long long>(job->id_),
            static_cast<unsigned long long>(t.numel), DataTypeName(t.data_type));
   SML_NVTX_PUSH(range);
-  if (t.numel > 0 && !nothing_to_do) e = kernels::LaunchAllReduce(job_ctx, a, plan, stream);
+  bool plain_copy = n_ == 1 && a.mode == kernels::MODE_SUM && a.post_scale == 1.0f && !nothing_to_do;
+  if (t.numel > 0 && plain_copy) e = kernels::LaunchLocalCopy(t.in_ptr, t.out_ptr, bytes, stream);
+  else if (t.numel > 0 && !nothing_to_do) e = kernels::LaunchAllReduce(job_ctx, a, plan, stream);
   SML_NVTX_POP();
   if (e == cudaSuccess) e = cudaEventRecord(f->done, stream);
   if (e != cudaSuccess) {

@@ -17,6 +17,7 @@
 #include "switchml/context.h"
 #include "switchml/log.h"
 #include "switchml/prepostprocessor.h"
+#include "switchml/utils.h"
 
 namespace switchml {
 
@@ -223,6 +224,13 @@ void UdpBackend::WorkerLoop(WorkerTid tid, int fd) {
   int window = static_cast<int>(g.max_outstanding_packets / g.num_worker_threads);
   int packet_numel = static_cast<int>(g.packet_numel);
   auto ppp = PrePostProcessor::CreateInstance(config_, tid, g.packet_numel * 4, window);
+  if (!config_.backend_.udp.cores.empty()) {
+    int ids[256], count = 0;
+    std::string err;
+    if (ParseCoreList(config_.backend_.udp.cores, &err, ids, 256, &count) && tid < count && !BindToCore(ids[tid])) {
+      SML_LOG(WARNING) << "worker thread " << tid << ": cannot bind to core " << ids[tid];
+    }
+  }
   UdpTransport transport(config_, tid, fd, session_id_, window);
   std::vector<int32_t> pool;
   Stats& stats = context_.GetStats();

@@ -13,6 +13,7 @@
 #include <vector>
 
 #include "switchml/log.h"
+#include "switchml/utils.h"
 
 namespace switchml {
 
@@ -100,6 +101,7 @@ bool Config::LoadFromString(const std::string& text, const std::string& origin) 
   opts["backend.udp.worker_port"] = SML_OPT_UNSIGNED(backend_.udp.worker_port);
   opts["backend.udp.spawn_switch"] = SML_OPT_BOOL(backend_.udp.spawn_switch);
   opts["backend.udp.pool_size"] = SML_OPT_UNSIGNED(backend_.udp.pool_size);
+  opts["backend.udp.cores"] = SML_OPT_STRING(backend_.udp.cores);
 
   opts["backend.cuda.device"] = [this](const std::string& v) {
     return ParseInt(v, &backend_.cuda.device);
@@ -243,6 +245,16 @@ void Config::Validate() {
         << "the udp backend supports packet_numel 64 or 256, got " << g.packet_numel;
     SML_CHECK(g.max_outstanding_packets / g.num_worker_threads <= backend_.udp.pool_size)
         << "window per worker thread exceeds backend.udp.pool_size";
+    SML_CHECK(g.max_outstanding_packets <= 16384) << "the software switch has 16384 slots";
+    if (!backend_.udp.cores.empty()) {
+      int ids[256], count = 0;
+      std::string err;
+      SML_CHECK(ParseCoreList(backend_.udp.cores, &err, ids, 256, &count))
+          << "backend.udp.cores: " << err;
+      SML_CHECK(count >= g.num_worker_threads)
+          << "backend.udp.cores names " << count << " core(s) for " << g.num_worker_threads
+          << " worker threads";
+    }
   }
   if (g.backend == "cuda") {
     CudaBackendConfig& c = backend_.cuda;
@@ -319,7 +331,8 @@ std::string Config::ToString() const {
       << "    worker_ip = " << u.worker_ip_str << "\n"
       << "    worker_port = " << u.worker_port << "\n"
       << "    spawn_switch = " << (u.spawn_switch ? "true" : "false") << "\n"
-      << "    pool_size = " << u.pool_size << "\n";
+      << "    pool_size = " << u.pool_size << "\n"
+      << "    cores = " << u.cores << "\n";
   } else if (g.backend == "cuda") {
     const CudaBackendConfig& c = backend_.cuda;
     o << "[backend.cuda]\n"

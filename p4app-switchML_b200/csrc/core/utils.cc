@@ -1,6 +1,9 @@
 // Barrier and process helpers. Parity: reference client_lib/src/utils.cc:29-72.
 #include "switchml/utils.h"
 
+#include <pthread.h>
+#include <sched.h>
+
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -65,6 +68,23 @@ bool ParseCoreList(const std::string& spec, std::string* error, int* out, int ma
     }
   }
   return true;
+}
+
+bool BindToCore(int core) {
+  cpu_set_t set;
+  CPU_ZERO(&set);
+  CPU_SET(core, &set);
+  return pthread_setaffinity_np(pthread_self(), sizeof(set), &set) == 0;
+}
+
+int GetDeviceNuma(const std::string& pci_bus_id) {
+  std::string path = "/sys/bus/pci/devices/" + pci_bus_id + "/numa_node";
+  FILE* f = fopen(path.c_str(), "r");
+  if (!f) return -1;
+  int node = -1;
+  if (fscanf(f, "%d", &node) != 1) node = -1;
+  fclose(f);
+  return node;
 }
 
 }  // namespace switchml

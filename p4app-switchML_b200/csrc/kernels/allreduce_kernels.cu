@@ -754,6 +754,29 @@ TunedF32Kernel(const RankCtx ctx, const JobArgs job, unsigned long long epc) {
   else RunZeroCopy<ELEM_F32, UL>(ctx, job, blockIdx.x, epc, &s_state.failed);
 }
 
+// The sum over a single worker, out of place: one pass over the data, no staging.
+__global__ void __launch_bounds__(kThreads) LocalCopyKernel(const char* in, char* out, size_t bytes) {
+  const size_t tid = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const size_t nthreads = static_cast<size_t>(gridDim.x) * blockDim.x;
+  if (Aligned16(in) && Aligned16(out)) {
+    const size_t nvec = bytes / 16;
+    const uint4* s = reinterpret_cast<const uint4*>(in);
+    uint4* d = reinterpret_cast<uint4*>(out);
+    size_t i = tid;
+    for (; i + (kUnroll - 1) * nthreads < nvec; i += kUnroll * nthreads) {
+      uint4 v[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; u++) v[u] = s[i + u * nthreads];
+#pragma unroll
+      for (int u = 0; u < kUnroll; u++) d[i + u * nthreads] = v[u];
+    }
+    for (; i < nvec; i += nthreads) d[i] = s[i];
+    for (size_t b = nvec * 16 + tid; b < bytes; b += nthreads) out[b] = in[b];
+  } else {
+    for (size_t b = tid; b < bytes; b += nthreads) out[b] = in[b];
+  }
+}
+
 __global__ void WaitProbeKernel(const RankCtx ctx) {
   __shared__ int s_failed;
   if (threadIdx.x == 0) s_failed = 0;
@@ -935,6 +958,13 @@ cudaError_t LaunchAllReduceEmulated(const RankCtx* ctxs_dev, const JobArgs* jobs
                                     cudaStream_t stream) {
   if (nranks < 1 || nranks > kMaxRanks || plan.channels > kMaxChannels) return cudaErrorInvalidValue;
   SML_DISPATCH(LaunchOneEmu, job0.elem_type, job0.mode, job0.algo, ctxs_dev, jobs_dev, nranks, plan, stream);
+}
+
+cudaError_t LaunchLocalCopy(const void* in, void* out, size_t bytes, cudaStream_t stream) {
+  if (bytes == 0 || in == out) return cudaSuccess;
+  int blocks = 148 * 4;
+  LocalCopyKernel<<<blocks, kThreads, 0, stream>>>(static_cast<const char*>(in), static_cast<char*>(out), bytes);
+  return cudaGetLastError();
 }
 
 cudaError_t LaunchWaitProbe(const RankCtx& ctx, cudaStream_t stream) {

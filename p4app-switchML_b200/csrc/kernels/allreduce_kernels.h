@@ -104,6 +104,8 @@ cudaError_t LaunchAllReduce(const RankCtx& ctx, const JobArgs& job, const Launch
 cudaError_t LaunchAllReduceEmulated(const RankCtx* ctxs_dev, const JobArgs* jobs_dev,
                                     const JobArgs& job0, int nranks, const LaunchPlan& plan,
                                     cudaStream_t stream);
+// Single worker, plain sum, out of place: copy `bytes` bytes with one kernel.
+cudaError_t LaunchLocalCopy(const void* in, void* out, size_t bytes, cudaStream_t stream);
 // A kernel whose only job is to wait for a flag nobody sets: checks that a bounded wait
 // gives up, reports STATUS_TIMEOUT and leaves the context usable.
 cudaError_t LaunchWaitProbe(const RankCtx& ctx, cudaStream_t stream);

@@ -36,5 +36,12 @@ std::string Execute(const char* cmd);
 // Parse "a-b,c" style core lists ("0-3", "0,2,4-6") into ids; empty on syntax error.
 bool ParseCoreList(const std::string& spec, std::string* error, int* out, int max_out, int* count);
 
+// Pin the calling thread to one CPU core; false if the kernel refuses.
+// (The reference pins its RDMA worker threads to cores on the NIC's NUMA node,
+// backends/rdma/rdma_utils.h:135-204.)
+bool BindToCore(int core);
+// NUMA node of a PCI device given its sysfs bus id ("0000:1b:00.0"), -1 if unknown.
+int GetDeviceNuma(const std::string& pci_bus_id);
+
 }  // namespace switchml
 #endif  // SWITCHML_UTILS_H_

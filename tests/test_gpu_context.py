@@ -37,7 +37,10 @@ def test_single_rank_roundtrip(ctx, launch, mode):
     ctx.all_reduce(xi)
     assert torch.equal(xi, torch.arange(100000, dtype=torch.int32, device="cuda"))
     st = ctx.get_stats()
-    assert st["jobs_finished"] == 5 and st["backend"]["tiles"] > 0
+    assert st["jobs_finished"] == 5 and st["jobs_failed"] == 0
+    if mode == "int32_quant":
+        assert st["backend"]["tiles"] > 0   # a single worker still goes through the slot pipeline
+    # (float_sum with one worker is a plain copy kernel, or nothing at all in place)
 
 
 def test_stream_ordering_without_host_sync(ctx):
