@@ -29,6 +29,7 @@
 #include "rendezvous/control.h"
 #include "switchml/context.h"
 #include "switchml/log.h"
+#include "switchml/quant_math.h"
 
 namespace switchml {
 
@@ -214,6 +215,7 @@ void CudaBackend::SetupWorker() {
   ctx_.slot_bytes = c.slot_bytes;
   ctx_.slots_per_channel = c.slots_per_channel;
   ctx_.block_numel = static_cast<int>(g.packet_numel);
+  ctx_.quant_base = quant::QuantBase(n_);
   ctx_.oneshot_bytes = (c.oneshot_max_bytes + 255) / 256 * 256;
   ctx_.timeout_ns = static_cast<unsigned long long>(c.wait_timeout_ms * 1e6);
   size_t bytes = kernels::StagingBytes(ctx_.slot_bytes, ctx_.slots_per_channel, ctx_.block_numel,
@@ -572,6 +574,7 @@ int EmulatedAllReduce(int nranks, void* const* in_ptrs, void* const* out_ptrs,
   proto.slot_bytes = slot_bytes;
   proto.slots_per_channel = slots_per_channel;
   proto.block_numel = block_numel;
+  proto.quant_base = quant::QuantBase(nranks);
   proto.oneshot_bytes = oneshot_bytes;
   proto.timeout_ns = 2000000000ull;  // 2 s: generous for one GPU, still bounded
   size_t bytes = StagingBytes(slot_bytes, slots_per_channel, block_numel, max_channels,

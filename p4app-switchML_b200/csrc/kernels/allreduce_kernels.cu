@@ -339,20 +339,42 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
         const size_t nblocks = (len + ctx.block_numel - 1) / ctx.block_numel;
         int* my_exp = reinterpret_cast<int*>(my_stage + exp_off);
         const int nwarps = kLoadWarps;
-        for (size_t b = warp; b < nblocks; b += nwarps) {
-          size_t base = b * ctx.block_numel;
-          size_t n = len - base < static_cast<size_t>(ctx.block_numel) ? len - base : ctx.block_numel;
-          float m = 0.f;
-          for (size_t i = lane; i < n; i += 32) {
-            float v = fabsf(LoadAsFloat<ELEM>(in, base + i));
-            if (v > m) m = v;
+        const size_t B = ctx.block_numel;
+        const bool vec_ok = ELEM == ELEM_F32 && Aligned16(in) && (B % 128) == 0;
+        constexpr int kBlocksPerIter = 4;  // independent blocks per warp iteration: loads in flight
+        for (size_t b0 = static_cast<size_t>(warp) * kBlocksPerIter; b0 < nblocks;
+             b0 += static_cast<size_t>(nwarps) * kBlocksPerIter) {
+          float m[kBlocksPerIter];
+#pragma unroll
+          for (int u = 0; u < kBlocksPerIter; u++) {
+            m[u] = 0.f;
+            const size_t b = b0 + u;
+            if (b >= nblocks) continue;
+            const size_t base = b * B;
+            const size_t n = len - base < B ? len - base : B;
+            if (vec_ok && n == B) {
+              const float4* p4 = reinterpret_cast<const float4*>(in) + base / 4;
+              for (size_t j = lane; j < B / 4; j += 32) {
+                float4 x = p4[j];
+                m[u] = fmaxf(m[u], fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w))));
+              }
+            } else {
+              for (size_t i = lane; i < n; i += 32) {
+                float v = fabsf(LoadAsFloat<ELEM>(in, base + i));
+                if (v > m[u]) m[u] = v;
+              }
+            }
           }
 #pragma unroll
-          for (int o = 16; o > 0; o >>= 1) {
-            float t = __shfl_xor_sync(0xffffffffu, m, o);
-            if (t > m) m = t;
+          for (int u = 0; u < kBlocksPerIter; u++) {
+            float mm = m[u];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+              float t = __shfl_xor_sync(0xffffffffu, mm, o);
+              if (t > mm) mm = t;
+            }
+            if (lane == 0 && b0 + u < nblocks) my_exp[b0 + u] = quant::LocalExponent(mm);
           }
-          if (lane == 0) my_exp[b] = quant::LocalExponent(m);
         }
         RoleSignal(ctx, role, channel, 0, epoch);
         if (!RoleWait(ctx, role, channel, 0, epoch, sh)) return;
@@ -367,16 +389,33 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
               if (t > e) e = t;
             }
           }
-          sf[b] = quant::ScaleFactor(e, ctx.nranks);
+          sf[b] = quant::ScaleFactorFromBase(e, ctx.quant_base);
         }
         role.Sync();
         int* q = reinterpret_cast<int*>(my_stage + slot_off);
         if (ELEM == ELEM_F32 && Aligned16(in)) {
           const float4* in4 = reinterpret_cast<const float4*>(in);
           size_t nvec = len / 4;
-          for (size_t i = role.tid; i < nvec; i += role.nthreads) {
+          const size_t nt = role.nthreads;
+          size_t i = role.tid;
+          for (; i + (kUnroll - 1) * nt < nvec; i += kUnroll * nt) {
+            float4 x[kUnroll];
+#pragma unroll
+            for (int u = 0; u < kUnroll; u++) x[u] = in4[i + u * nt];
+#pragma unroll
+            for (int u = 0; u < kUnroll; u++) {
+              float f = sf[((i + u * nt) * 4) >> shift];  // a vector never straddles a block (>= 32)
+              int4 r;
+              r.x = quant::Quantize(x[u].x, f);
+              r.y = quant::Quantize(x[u].y, f);
+              r.z = quant::Quantize(x[u].z, f);
+              r.w = quant::Quantize(x[u].w, f);
+              reinterpret_cast<int4*>(q)[i + u * nt] = r;
+            }
+          }
+          for (; i < nvec; i += nt) {
             float4 x = in4[i];
-            float f = sf[(i * 4) >> shift];  // a vector never straddles a block (>= 32)
+            float f = sf[(i * 4) >> shift];
             int4 r;
             r.x = quant::Quantize(x.x, f);
             r.y = quant::Quantize(x.y, f);
@@ -606,7 +645,7 @@ __device__ void RunOneShot(const RankCtx& ctx, const JobArgs& job, int channel,
         int le = quant::LocalExponent(m);
         if (le > e) e = le;
       }
-      float sf = quant::ScaleFactor(e, ctx.nranks);
+      float sf = quant::ScaleFactorFromBase(e, ctx.quant_base);
       for (size_t i = lane; i < n; i += 32) {
         unsigned acc = 0;
         for (int s = 0; s < ctx.nranks; s++)
@@ -708,7 +747,13 @@ __device__ void RunZeroCopy(const RankCtx& ctx, const JobArgs& job, int channel,
 template <int ELEM, int MODE, int ALGO>
 __device__ __forceinline__ void RunJob(const RankCtx& ctx, const JobArgs& job, int channel,
                                        unsigned long long epc, int* s_failed, float* s_sf) {
-  if (ALGO == ALGO_STAGED) RunStaged<ELEM, MODE>(ctx, job, channel, epc, reinterpret_cast<StagedShared*>(s_failed), s_sf);
+  // The quantising loader reads its input twice and meets its peers once more per tile,
+  // so it gets more warps than the plain copy-in of the SUM modes (8-GPU measurements with
+  // 1 GiB: 4/8/4 3.72 ms, 6/8/2 3.30 ms, 8/6/2 3.07 ms before the loader was vectorised).
+  if (ALGO == ALGO_STAGED && MODE == MODE_QUANT)
+    RunStaged<ELEM, MODE, 6, 8>(ctx, job, channel, epc, reinterpret_cast<StagedShared*>(s_failed), s_sf);
+  else if (ALGO == ALGO_STAGED)
+    RunStaged<ELEM, MODE>(ctx, job, channel, epc, reinterpret_cast<StagedShared*>(s_failed), s_sf);
   else if (ALGO == ALGO_ONESHOT) RunOneShot<ELEM, MODE>(ctx, job, channel, epc, s_failed);
   else RunZeroCopy<ELEM>(ctx, job, channel, epc, s_failed);
 }
@@ -922,13 +967,13 @@ cudaError_t LaunchAllReduce(const RankCtx& ctx, const JobArgs& job, const Launch
 #define SML_TUNED(MODE, ALGO, LW, RW, UL) TunedF32Kernel<MODE, ALGO, LW, RW, UL><<<plan.channels, kThreads, 0, stream>>>(ctx, job, epc)
     if (job.algo == ALGO_STAGED && job.mode == MODE_QUANT) {
       switch (job.tune) {
-        case 1: SML_TUNED(MODE_QUANT, ALGO_STAGED, 6, 8, 4); break;
+        case 1: SML_TUNED(MODE_QUANT, ALGO_STAGED, 4, 8, 4); break;
         case 2: SML_TUNED(MODE_QUANT, ALGO_STAGED, 8, 6, 4); break;
         case 3: SML_TUNED(MODE_QUANT, ALGO_STAGED, 6, 6, 4); break;
         case 4: SML_TUNED(MODE_QUANT, ALGO_STAGED, 6, 8, 8); break;
         case 5: SML_TUNED(MODE_QUANT, ALGO_STAGED, 4, 8, 8); break;
         case 6: SML_TUNED(MODE_QUANT, ALGO_STAGED, 7, 7, 4); break;
-        default: SML_TUNED(MODE_QUANT, ALGO_STAGED, 4, 8, 4); break;
+        default: SML_TUNED(MODE_QUANT, ALGO_STAGED, 6, 8, 4); break;
       }
     } else if (job.algo == ALGO_STAGED) {
       switch (job.tune) {
@@ -1051,6 +1096,7 @@ extern "C" int switchml_local_allreduce_noalloc(const void* in, void* out,
   ctx.block_numel = block_numel;
   ctx.oneshot_bytes = 256;
   ctx.timeout_ns = 1000000000ull;
+  ctx.quant_base = switchml::quant::QuantBase(1);
   size_t staging = StagingBytes(ctx.slot_bytes, ctx.slots_per_channel, ctx.block_numel,
                                 kNoAllocChannels, ctx.oneshot_bytes, 1, &ctx.data_offset,
                                 &ctx.exp_offset, &ctx.oneshot_offset);

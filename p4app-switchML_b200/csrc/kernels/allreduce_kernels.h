@@ -53,6 +53,7 @@ struct RankCtx {
   size_t slot_bytes;             // bytes of one data slot
   int slots_per_channel;
   int block_numel;               // quantisation block (= packet_numel)
+  float quant_base;              // quant::QuantBase(nranks): scale factor at exponent 0
   size_t oneshot_bytes;          // capacity of one rank's one-shot buffer (per parity)
   unsigned long long timeout_ns; // budget of every wait
   int* status;                   // device-visible status word (0 = ok)

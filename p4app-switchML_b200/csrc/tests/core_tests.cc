@@ -239,6 +239,9 @@ static void TestQuantMath() {
   EXPECT(std::isfinite(ScaleFactor(-126, 8)));
   EXPECT(Quantize(0.5f, 4.0f) == 2 && Quantize(0.625f, 4.0f) == 2 && Quantize(0.875f, 4.0f) == 4);
   EXPECT(Quantize(NAN, 1.0f) == 0 && Quantize(1e30f, 1e30f) == INT32_MAX);
+  // The float-only scale factor used on the GPU equals the double-precision definition.
+  for (int n = 1; n <= 32; n++)
+    for (int e = -130; e <= 130; e++) EXPECT(ScaleFactorFromBase(e, QuantBase(n)) == ScaleFactor(e, n));
   // Oracle: exact for values that are representable at the block scale.
   std::vector<float> a = {1.0f, -2.0f, 0.5f, 0.0f}, b = {0.25f, 4.0f, -0.5f, 0.0f}, out(4);
   const float* in[2] = {a.data(), b.data()};

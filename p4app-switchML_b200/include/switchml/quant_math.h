@@ -69,6 +69,29 @@ SML_HD float ScaleFactor(int global_exponent, int num_workers) {
   return static_cast<float>(ldexp(k / static_cast<double>(num_workers), -e));
 }
 
+// The same scale factor without double precision in the hot path: `base` = QuantBase(n) is
+// computed once per context, the power of two is applied with exact float multiplications
+// (two steps, so that every intermediate stays a normal number). Bit-identical to
+// ScaleFactor(): scaling by a power of two commutes with the rounding to float.
+SML_HD float QuantBase(int num_workers) {
+  bool pow2 = (num_workers & (num_workers - 1)) == 0;
+  double k = pow2 ? 2147483647.0 : 2147483647.0 - 256.0;
+  return static_cast<float>(k / static_cast<double>(num_workers));
+}
+
+SML_HD float ScaleFactorFromBase(int global_exponent, float base) {
+  int e = ClampExponent(global_exponent);
+  int h = e / 2;
+#if defined(__CUDA_ARCH__)
+  float s1 = __int_as_float((127 - h) << 23);        // 2^-h
+  float s2 = __int_as_float((127 - (e - h)) << 23);  // 2^-(e-h)
+#else
+  float s1 = ldexpf(1.0f, -h);
+  float s2 = ldexpf(1.0f, -(e - h));
+#endif
+  return base * s1 * s2;
+}
+
 SML_HD int32_t Quantize(float x, float sf) {
 #if defined(__CUDA_ARCH__)
   return __float2int_rn(x * sf);  // cvt.rni.s32.f32: nearest-even, saturating, NaN -> 0
