@@ -98,54 +98,63 @@ def bench_allreduce(args):
     ctx = start_context(args, rank, world, local, addr, port, heap_mb)
 
     g = torch.Generator(device="cuda").manual_seed(1234 + rank)
-    if args.symmetric:
-        x = ctx.symmetric_empty(numel, dtype)
-        y = ctx.symmetric_empty(numel, dtype)
-    else:
-        x = torch.empty(numel, dtype=dtype, device="cuda")
-        y = torch.empty(numel, dtype=dtype, device="cuda")
-    if dtype == torch.int32:
-        x.copy_(torch.randint(-2 ** 20, 2 ** 20, (numel,), generator=g, device="cuda", dtype=torch.int32))
-    else:
-        x.copy_((torch.rand(numel, generator=g, device="cuda") * 2 - 1).to(dtype))
 
-    def step():
-        job = ctx.all_reduce_async(x, y)  # enqueued on the current stream (inline launch)
-        return job
+    def make_tensors(symmetric):
+        if symmetric:
+            a, b = ctx.symmetric_empty(numel, dtype), ctx.symmetric_empty(numel, dtype)
+        else:
+            a = torch.empty(numel, dtype=dtype, device="cuda")
+            b = torch.empty(numel, dtype=dtype, device="cuda")
+        if dtype == torch.int32:
+            a.copy_(torch.randint(-2 ** 20, 2 ** 20, (numel,), generator=g, device="cuda", dtype=torch.int32))
+        else:
+            a.copy_((torch.rand(numel, generator=g, device="cuda") * 2 - 1).to(dtype))
+        return a, b
 
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()  # nvidia-smi needs a moment to start: launch it before the warm-up
-    jobs = [step() for _ in range(args.warmup)]
-    barrier(world)
-    for j in jobs:
-        assert j.wait() == 3, j.error()
-        j.release()
 
-    # correctness spot check against NCCL / the plain sum on a slice
-    check = None
-    if world > 1 and dtype != torch.int32:
-        ref = x.clone().float()
-        dist.all_reduce(ref)
-        err = (y.float() - ref).abs().max().item()
-        scale = ref.abs().max().item()
-        check = {"max_abs_err_vs_nccl": err, "max_abs": scale}
-        assert err <= 1e-3 * max(scale, 1.0), "allreduce result is wrong: err %g" % err
+    def measure(x, y, steps, want_clocks):
+        """W warm-up jobs, a correctness check against NCCL, then `steps` timed jobs."""
+        jobs = [ctx.all_reduce_async(x, y) for _ in range(args.warmup)]  # enqueued on the current stream
+        barrier(world)
+        for j in jobs:
+            assert j.wait() == 3, j.error()
+            j.release()
+        check = None
+        if world > 1 and dtype != torch.int32:
+            ref = x.clone().float()
+            dist.all_reduce(ref)
+            err = (y.float() - ref).abs().max().item()
+            scale = ref.abs().max().item()
+            check = {"max_abs_err_vs_nccl": err, "max_abs": scale}
+            assert err <= 1e-3 * max(scale, 1.0), "allreduce result is wrong: err %g" % err
+            del ref
+        barrier(world)
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        w0 = time.time()
+        start.record()
+        jobs = [ctx.all_reduce_async(x, y) for _ in range(steps)]
+        stop.record()
+        torch.cuda.synchronize()
+        w1 = time.time()
+        barrier(world)
+        clocks = sampler.stop((w0, w1)) if (rank == 0 and want_clocks) else None
+        t = max_over_ranks(start.elapsed_time(stop), world) / steps
+        for j in jobs:
+            assert j.wait() == 3, j.error()
+            j.release()
+        return t, check, clocks
 
-    barrier(world)
-    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    w0 = time.time()
-    start.record()
-    jobs = [step() for _ in range(args.steps)]
-    stop.record()
-    torch.cuda.synchronize()
-    w1 = time.time()
-    barrier(world)
-    clocks = sampler.stop((w0, w1)) if rank == 0 else None
-    ms = max_over_ranks(start.elapsed_time(stop), world) / args.steps
-    for j in jobs:
-        assert j.wait() == 3, j.error()
-        j.release()
+    # Secondary measurement first: ordinary device tensors, which go through the staging ring.
+    plain_ms = None
+    if args.symmetric and args.mode == "float_sum":
+        px, py = make_tensors(False)
+        plain_ms, _, _ = measure(px, py, max(3, args.steps // 2), False)
+        del px, py
+    x, y = make_tensors(bool(args.symmetric) and args.mode == "float_sum")
+    ms, check, clocks = measure(x, y, args.steps, True)
 
     # ---- end to end: pinned host -> device -> allreduce -> pinned host ----
     hx = torch.empty(numel, dtype=dtype, pin_memory=True)
@@ -188,9 +197,12 @@ def bench_allreduce(args):
         "config": {"model": "allreduce_microbenchmark", "numel": numel, "tensor_bytes": numel * esz,
                    "global_batch": None, "seq_len": None, "parallelism": "dp%d" % world,
                    "op": "SUM", "mode": args.mode, "transport": "nvls" if multimem else ("p2p" if world > 1 else "local"),
-                   "symmetric_buffers": bool(args.symmetric), "packet_numel": args.packet_numel,
+                   "symmetric_buffers": bool(args.symmetric) and args.mode == "float_sum", "packet_numel": args.packet_numel,
                    "l2": "input and output tensors (%d MiB each) are larger than the 126 MB L2" % (numel * esz >> 20)},
         "bus_gbs": bus, "alg_gbs": esz * numel / (ms * 1e-3) / 1e9,
+        "plain_tensors": None if plain_ms is None else {
+            "note": "same allreduce on ordinary torch tensors (staged through the slot ring)",
+            "ms_per_step": plain_ms, "ate_per_worker": numel / (plain_ms * 1e-3)},
         "e2e": {"value": world * numel / (e2e_ms * 1e-3), "unit": "elements/s", "ms_per_step": e2e_ms,
                 "ate_per_worker": numel / (e2e_ms * 1e-3),
                 "h2d_bytes_per_step": numel * esz, "d2h_bytes_per_step": numel * esz,
@@ -301,7 +313,9 @@ def main():
     ap.add_argument("--mode", default=os.environ.get("SWITCHML_MODE", "float_sum"),
                     choices=["int32_quant", "float_sum"])
     ap.add_argument("--transport", default="auto", choices=["auto", "nvls", "p2p"])
-    ap.add_argument("--symmetric", type=int, default=0, help="1: tensors live in the symmetric heap (zero-copy)")
+    ap.add_argument("--symmetric", type=int, default=1,
+                    help="1: the tensors are allocated with Context.symmetric_empty (reduced in place over NVLink, "
+                         "float_sum mode); 0: ordinary torch tensors through the staging ring")
     ap.add_argument("--packet-numel", type=int, default=256)
     ap.add_argument("--slot-bytes", type=int, default=0, help="0 = library default")
     ap.add_argument("--channels", type=int, default=0)

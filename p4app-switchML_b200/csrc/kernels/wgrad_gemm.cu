@@ -20,7 +20,7 @@
 // The fused variant additionally reduces every finished tile across GPUs (see
 // wgrad_gemm.h): warps 8-11 wait until all ranks have stored tile t, let the NVSwitch add
 // the ranks' copies (multimem.ld_reduce) and broadcast the sum (multimem.st), while the
-// tensor cores already work on later tiles.
+// tensor cores already work on later tiles; warps whose GEMM role is over join in.
 //
 // Every wait is bounded: an mbarrier or flag wait that runs out of budget raises an abort
 // flag in shared memory, records an error code for the host, and all roles drain, free
@@ -204,6 +204,55 @@ __device__ __forceinline__ bool WaitFlags(const unsigned long long* flags, int n
   return __all_sync(0xffffffffu, ok);
 }
 
+// Cross-GPU reduction of the tiles this rank owns (tile index mod nranks == rank), shared
+// by all warps of all CTAs through one work counter: an item is a quarter tile (32 rows).
+// Called by whole warps. Items are handed out in tile order, the order in which the GEMM
+// produces them, so a warp rarely waits long for the flags of its item.
+__device__ __forceinline__ bool ReduceWork(const WgradFusedArgs& fused, int M, int N, int tiles_n,
+                                           int num_tiles, volatile int* abort) {
+  const int lane = threadIdx.x & 31;
+  const int owned = (num_tiles - fused.rank + fused.nranks - 1) / fused.nranks;
+  const int items = owned * 4;
+  char* mc = fused.out_mc;
+  for (;;) {
+    int item = 0;
+    if (lane == 0) item = atomicAdd(fused.work_counter, 1);
+    item = __shfl_sync(0xffffffffu, item, 0);
+    if (item >= items) return true;
+    const long long tile = static_cast<long long>(item >> 2) * fused.nranks + fused.rank;
+    if (!WaitFlags(fused.flags_peer[fused.rank] + static_cast<size_t>(tile) * 8, fused.nranks, fused.epoch,
+                   fused.timeout_ns, abort))
+      return false;
+    const int m0 = static_cast<int>(tile / tiles_n) * kTileM + (item & 3) * 32;
+    const int n0 = static_cast<int>(tile % tiles_n) * kTileN;
+    const int rows = min(32, M - m0), cols = min(kTileN, N - n0);
+    if (rows <= 0) continue;
+    const int vec_per_row = cols / 4;  // N is a multiple of 8: rows are whole float4s
+    const int total = rows * vec_per_row;
+    for (int idx = lane; idx < total; idx += 32 * 4) {
+      float4 v[4];
+      size_t off[4];
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        int id = idx + u * 32;
+        if (id < total) {
+          int r = id / vec_per_row, cv = id % vec_per_row;
+          off[u] = (static_cast<size_t>(m0 + r) * N + n0 + cv * 4) * 4;
+          v[u] = MultimemLdReduceAddF32x4(mc + off[u]);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; u++) {
+        int id = idx + u * 32;
+        if (id < total) {
+          if (fused.scale != 1.0f) { v[u].x *= fused.scale; v[u].y *= fused.scale; v[u].z *= fused.scale; v[u].w *= fused.scale; }
+          MultimemStoreF32x4(mc + off[u], v[u]);
+        }
+      }
+    }
+  }
+}
+
 template <bool kFused>
 __global__ void __launch_bounds__(kThreads, 1)
 WgradGemmKernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -344,60 +393,13 @@ WgradGemmKernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       }
     }
     if (epi_tid == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-  } else if (kFused && warp >= 8) {
-    // ------------------------------ cross-GPU reducer ------------------------------
-    // Tile t is reduced by rank t mod nranks, by the CTA that runs (t / nranks) mod grid.
-    // Only the first `reduce_ctas` CTAs reduce; the others leave as soon as their GEMM tiles
-    // are stored, which returns their SMs to whatever runs next on other streams.
-    const int rtid = threadIdx.x - 256;  // 0..127
-    const int reduce_ctas = min(static_cast<int>(gridDim.x), fused.reduce_ctas);
-    bool ok = true;
-    for (int j = blockIdx.x; ok && static_cast<int>(blockIdx.x) < reduce_ctas; j += reduce_ctas) {
-      const long long tile = static_cast<long long>(j) * fused.nranks + fused.rank;
-      if (tile >= num_tiles) break;
-      ok = WaitFlags(fused.flags_peer[fused.rank] + static_cast<size_t>(tile) * 8, fused.nranks, fused.epoch,
-                     fused.timeout_ns, &sh.abort);
-      if (!ok) break;
-      const int m0 = static_cast<int>(tile / tiles_n) * kTileM, n0 = static_cast<int>(tile % tiles_n) * kTileN;
-      const int rows = min(kTileM, M - m0), cols = min(kTileN, N - n0);
-      const int vec_per_row = cols / 4;  // N is a multiple of 8, so rows are whole float4s
-      char* mc = fused.out_mc;
-      for (int idx = rtid; idx < rows * vec_per_row; idx += 128 * 4) {
-        float4 v[4];
-        size_t off[4];
-#pragma unroll
-        for (int u = 0; u < 4; u++) {
-          int id = idx + u * 128;
-          if (id < rows * vec_per_row) {
-            int r = id / vec_per_row, cv = id % vec_per_row;
-            off[u] = (static_cast<size_t>(m0 + r) * N + n0 + cv * 4) * 4;
-            v[u] = MultimemLdReduceAddF32x4(mc + off[u]);
-          }
-        }
-#pragma unroll
-        for (int u = 0; u < 4; u++) {
-          int id = idx + u * 128;
-          if (id < rows * vec_per_row) {
-            if (fused.scale != 1.0f) { v[u].x *= fused.scale; v[u].y *= fused.scale; v[u].z *= fused.scale; v[u].w *= fused.scale; }
-            MultimemStoreF32x4(mc + off[u], v[u]);
-          }
-        }
-      }
-    }
-    // No reducing CTA leaves before every rank's matching CTA has finished its tiles, so
-    // when the kernel has ended on all ranks every tile holds the global sum.
-    NamedBarrier(3, 128);
-    if (rtid < 32 && static_cast<int>(blockIdx.x) < reduce_ctas) {
-      if (lane < fused.nranks) {
-        __threadfence_system();
-        StoreReleaseSys(fused.flags_peer[lane] + static_cast<size_t>(num_tiles + blockIdx.x) * 8 + fused.rank,
-                        fused.epoch);
-      }
-      __syncwarp();
-      if (!WaitFlags(fused.flags_peer[fused.rank] + static_cast<size_t>(num_tiles + blockIdx.x) * 8, fused.nranks,
-                     fused.epoch, fused.timeout_ns, &sh.abort))
-        ok = false;
-    }
+  }
+
+  if (kFused) {
+    // Every warp that has nothing (more) to do for the GEMM helps with the cross-GPU
+    // reduction: warps 8-11 and 3 from the start, the others when their role is finished.
+    __syncwarp();
+    ReduceWork(fused, M, N, tiles_n, num_tiles, &sh.abort);
   }
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -405,6 +407,18 @@ WgradGemmKernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   if (warp == 2) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+  if (kFused && warp == 0) {
+    // No CTA leaves before the matching CTA of every rank has finished reducing, so when
+    // the kernel has ended everywhere every tile holds the global sum on every rank.
+    unsigned long long* done = fused.flags_peer[fused.rank] + static_cast<size_t>(num_tiles + blockIdx.x) * 8;
+    if (lane < fused.nranks) {
+      __threadfence_system();
+      StoreReleaseSys(fused.flags_peer[lane] + static_cast<size_t>(num_tiles + blockIdx.x) * 8 + fused.rank,
+                      fused.epoch);
+    }
+    __syncwarp();
+    WaitFlags(done, fused.nranks, fused.epoch, fused.timeout_ns, &sh.abort);
   }
   if (threadIdx.x == 0 && sh.abort && error_flag) *reinterpret_cast<volatile int*>(error_flag) = 1;
 }
@@ -471,7 +485,7 @@ extern "C" int switchml_wgrad_gemm(const void* dy, const void* x, float* dw, int
   memset(&none, 0, sizeof(none));
   cudaError_t e;
   if (fused && fused->nranks > 1) {
-    if (fused->nranks > 8 || !fused->out_mc || fused->reduce_ctas < 1) return -1;
+    if (fused->nranks > 8 || !fused->out_mc || !fused->work_counter) return -1;
     // All CTAs take part in the closing cross-GPU barrier, so the grid must be the same on
     // every rank and fully resident: one CTA per SM at most.
     static bool attr_f = false;

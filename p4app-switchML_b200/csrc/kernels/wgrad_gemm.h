@@ -18,7 +18,8 @@
  *
  * `flags_peer[r]` is rank r's copy of a flag array of switchml_wgrad_flag_words(M, N)
  * 64-bit words in symmetric memory, zero-initialised once; `epoch` must grow with every
- * fused call that uses the same flag array. Waits give up after `timeout_ns` and set
+* fused call that uses the same flag array, and `work_counter` must be zero when the kernel
+ * starts. Waits give up after `timeout_ns` and set
  * *error_flag (device or mapped host memory) to 1.
  *
  * M and N must be multiples of 8 and all base addresses 16-byte aligned (TMA).
@@ -39,7 +40,7 @@ typedef struct WgradFusedArgs {
   unsigned long long epoch;
   unsigned long long timeout_ns;
   float scale; /* multiplied into the reduced gradient (1/nranks for the mean) */
-  int reduce_ctas; /* CTAs that take part in the cross-GPU reduction (>= 1; 32 is plenty) */
+  int* work_counter; /* one int in this rank's device memory, zeroed (in stream order) before every fused call */
 } WgradFusedArgs;
 
 int switchml_wgrad_gemm(const void* dy, const void* x, float* dw, int M, int N, int K,

@@ -20,7 +20,7 @@ class _FusedArgs(ctypes.Structure):
     _fields_ = [("rank", ctypes.c_int), ("nranks", ctypes.c_int),
                 ("flags_peer", ctypes.c_void_p * 8), ("out_mc", ctypes.c_void_p),
                 ("epoch", ctypes.c_ulonglong), ("timeout_ns", ctypes.c_ulonglong),
-                ("scale", ctypes.c_float), ("reduce_ctas", ctypes.c_int)]
+                ("scale", ctypes.c_float), ("work_counter", ctypes.c_void_p)]
 
 
 def _lib():
@@ -77,7 +77,7 @@ class FusedWgrad:
     kernel is enqueued on the current stream and needs no separate allreduce.
     """
 
-    def __init__(self, ctx, M, N, scale=1.0, timeout_ms=20000.0, reduce_ctas=32):
+    def __init__(self, ctx, M, N, scale=1.0, timeout_ms=20000.0):
         self.ctx, self.M, self.N, self.scale = ctx, M, N, scale
         self.grad = ctx.symmetric_empty(M * N, torch.float32).view(M, N)
         words = flag_words(M, N)
@@ -97,7 +97,8 @@ class FusedWgrad:
         self.args.epoch = 0
         self.args.timeout_ns = int(timeout_ms * 1e6)
         self.args.scale = scale
-        self.args.reduce_ctas = reduce_ctas
+        self.counter = torch.zeros(1, dtype=torch.int32, device=self.grad.device)
+        self.args.work_counter = self.counter.data_ptr()
         self.fused = self.nranks > 1 and bool(mc)
         torch.cuda.synchronize()
 
@@ -119,6 +120,8 @@ class FusedWgrad:
             return out
         K = dy.shape[0]
         self.args.epoch += 1
+        if self.fused:
+            self.counter.zero_()  # work queue of the in-kernel reduction starts at zero
         stream = torch.cuda.current_stream(dy.device).cuda_stream
         rc = _lib().switchml_wgrad_gemm(dy.data_ptr(), x.data_ptr(), self.grad.data_ptr(), self.M, self.N, K,
                                         ctypes.byref(self.args) if self.fused else None,
