@@ -145,6 +145,8 @@ _SIDE_STREAMS = {}
 def wait_pending(stream=None):
     """Order `stream` (default: current) after every weight-gradient kernel that was sent to
     a side stream since the last call."""
+    if not _PENDING:
+        return
     s = stream or torch.cuda.current_stream()
     while _PENDING:
         s.wait_event(_PENDING.pop())

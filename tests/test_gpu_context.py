@@ -86,3 +86,19 @@ def test_bfloat16_needs_cuda_backend():
         assert job.wait() == sml.JobStatus.FAILED and "cuda" in job.error()
     finally:
         c.stop()
+
+
+def test_host_pipeline_roundtrip(ctx):
+    """Pinned host -> device -> allreduce -> pinned host, chunked over three streams."""
+    from switchml_b200.parallel.host_pipeline import HostAllReduce
+    assert ctx.start(sml.make_config("cuda", packet_numel=256, mode="float_sum", launch="inline"))
+    n = (1 << 20) + 123
+    hx = torch.randn(n).pin_memory()
+    hy = torch.zeros(n).pin_memory()
+    pipe = HostAllReduce(ctx, n, torch.float32, chunk_numel=1 << 18)
+    assert pipe.launches_per_run == 5
+    for _ in range(2):
+        pipe.run(hx, hy)
+        assert torch.equal(hx, hy)
+        hy.zero_()
+    pipe.close()
