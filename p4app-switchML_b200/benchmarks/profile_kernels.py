@@ -7,7 +7,8 @@
 Kernels: allreduce_quant / allreduce_sum / allreduce_int (streamed aggregation, 4 ranks
 emulated in one cooperative launch over peer memory, 2^24 elements per rank: inputs and
 outputs of 512 MiB together exceed the 126 MB L2 while staying far below a few GB);
-wgrad (tcgen05 weight-gradient GEMM, BERT FFN shape 8192 x 4096 x 1024);
+wgrad / wgrad_2cta (tcgen05 weight-gradient GEMM, one CTA per 128x256 tile / two CTAs per
+256x256 tile, BERT FFN shape 8192 x 4096 x 1024);
 wgrad_fc6 (VGG fc6 shape, K = 32: output-bandwidth bound). Prints CUDA-event timings.
 """
 import argparse
@@ -60,7 +61,8 @@ def main():
         dy = torch.randn(K, M, device="cuda", dtype=torch.bfloat16)
         x = torch.randn(K, N, device="cuda", dtype=torch.bfloat16)
         out = torch.empty(M, N, device="cuda")
-        ms = timed(lambda: wgrad_gemm(dy, x, out=out), a.iters)
+        two = a.kernel == "wgrad_2cta"
+        ms = timed(lambda: wgrad_gemm(dy, x, out=out, two_cta=two), a.iters)
         print("%s: K=%d M=%d N=%d, %.3f ms, %.0f TFLOP/s, output %.0f GB/s" %
               (a.kernel, K, M, N, ms, 2.0 * K * M * N / ms / 1e9, M * N * 4 / ms / 1e6))
 

@@ -47,7 +47,7 @@ def main():
     shapes = [("vgg_fc6", 32, 4096, 25088), ("vgg_fc7", 32, 4096, 4096), ("bert_ffn", 8192, 4096, 1024)]
     for name, K, M, N in shapes:
         ctx.symmetric_reset()
-        fw = FusedWgrad(ctx, M, N, scale=1.0 / world)
+        fw = FusedWgrad(ctx, M, N, scale=1.0 / world, policy="fused")
         dy = torch.randn(K, M, device="cuda", dtype=torch.bfloat16)
         x = torch.randn(K, N, device="cuda", dtype=torch.bfloat16)
         plain = torch.empty(M, N, device="cuda")

@@ -423,6 +423,201 @@ WgradGemmKernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   if (threadIdx.x == 0 && sh.abort && error_flag) *reinterpret_cast<volatile int*>(error_flag) = 1;
 }
 
+// ---- 2-CTA variant ---------------------------------------------------------------------
+// Two CTAs of a cluster share one 256 x 256 tile: each loads its own 128 rows of A and its
+// own 128 columns of B, the leader issues tcgen05.mma.cta_group::2 (M256 N256 K16) which
+// reads B from both CTAs' shared memory, and each CTA ends up with its 128 x 256 half of
+// the accumulator in its own TMEM. Per SM this halves the shared-memory traffic for B, which
+// is what bounds the 1-CTA kernel on large shapes. Plain GEMM only (no fused reduce).
+constexpr int k2Stages = 6;
+constexpr int k2ABytes = kTileK * 128 * 2;  // 128 rows of A   : 16 KiB
+constexpr int k2BBytes = kTileK * 128 * 2;  // 128 columns of B: 16 KiB
+constexpr int k2StageBytes = k2ABytes + k2BBytes;
+constexpr int k2Threads = 256;
+constexpr uint32_t kPeerBitMask = 0xFEFFFFFFu;  // clears the CTA-rank bit of a shared::cluster address
+
+struct __align__(1024) SharedStorage2 {
+  uint8_t stage[k2Stages][k2StageBytes];
+  uint8_t epi[kEpiBufs][kEpiBytes];
+  uint64_t full[k2Stages];
+  uint64_t empty[k2Stages];
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
+  uint32_t tmem_base;
+  volatile int abort;
+};
+
+constexpr uint32_t kInstrDesc2 = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | (1u << 16) |
+                                 (static_cast<uint32_t>(256 >> 3) << 17) | (static_cast<uint32_t>(256 >> 4) << 24);
+
+__device__ __forceinline__ void ClusterSync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// TMA load issued by either CTA of the pair; the bytes are counted on the leader's barrier.
+__device__ __forceinline__ void TmaLoad2D_2Cta(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(SmemAddr(smem_dst)), "l"(map), "r"(x), "r"(y), "r"(SmemAddr(bar) & kPeerBitMask) : "memory");
+}
+
+__device__ __forceinline__ void Mma2(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(kInstrDesc2), "r"(accumulate) : "memory");
+}
+
+// Arrive, in both CTAs of the pair, on the barrier at this shared-memory offset once all
+// MMAs issued so far are done.
+__device__ __forceinline__ void MmaCommit2(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(SmemAddr(bar)), "h"(static_cast<uint16_t>(3)) : "memory");
+}
+
+__device__ __forceinline__ void MbarArriveOnLeader(uint64_t* bar) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(remote) : "r"(SmemAddr(bar)));
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(remote) : "memory");
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(k2Threads, 1)
+WgradGemm2CtaKernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    const __grid_constant__ CUtensorMap map_d, int M, int N, int K, int* error_flag) {
+  extern __shared__ uint8_t smem_raw[];
+  SharedStorage2& sh = *reinterpret_cast<SharedStorage2*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint32_t cta_rank;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(cta_rank));
+  const bool leader = cta_rank == 0;
+  const int tiles_m = (M + 255) / 256, tiles_n = (N + 255) / 256;
+  const int num_tiles = tiles_m * tiles_n;
+  const int k_blocks = (K + kTileK - 1) / kTileK;
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < k2Stages; s++) {
+      MbarInit(&sh.full[s], 1);
+      MbarInit(&sh.empty[s], 1);
+    }
+    for (int b = 0; b < 2; b++) {
+      MbarInit(&sh.acc_full[b], 1);
+      MbarInit(&sh.acc_empty[b], 256);  // the epilogue threads of both CTAs
+    }
+    sh.abort = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 2) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(SmemAddr(&sh.tmem_base)), "r"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  ClusterSync();  // both CTAs' barriers exist before anybody signals across the pair
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = sh.tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t it = 0;
+      for (int tile = pair; tile < num_tiles && !sh.abort; tile += num_pairs) {
+        const int m0 = (tile / tiles_n) * 256 + static_cast<int>(cta_rank) * 128;
+        const int n0 = (tile % tiles_n) * 256 + static_cast<int>(cta_rank) * 128;
+        for (int kb = 0; kb < k_blocks; kb++, it++) {
+          const int s = it % k2Stages;
+          const uint32_t phase = (it / k2Stages) & 1;
+          if (!MbarWait(&sh.empty[s], phase ^ 1, &sh.abort)) break;
+          if (leader) MbarExpectTx(&sh.full[s], 2 * k2StageBytes);  // both CTAs' loads
+          uint8_t* a = sh.stage[s];
+          uint8_t* b = sh.stage[s] + k2ABytes;
+          for (int j = 0; j < 2; j++) TmaLoad2D_2Cta(a + j * (kTileK * 128), &map_a, m0 + j * kAtomMN, kb * kTileK, &sh.full[s]);
+          for (int j = 0; j < 2; j++) TmaLoad2D_2Cta(b + j * (kTileK * 128), &map_b, n0 + j * kAtomMN, kb * kTileK, &sh.full[s]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && leader) {
+      uint32_t it = 0, local_tile = 0;
+      for (int tile = pair; tile < num_tiles && !sh.abort; tile += num_pairs, local_tile++) {
+        const int acc = local_tile & 1;
+        const uint32_t acc_phase = (local_tile >> 1) & 1;
+        if (!MbarWait(&sh.acc_empty[acc], acc_phase ^ 1, &sh.abort)) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t tmem_d = tmem_base + acc * kTileN;
+        bool ok = true;
+        for (int kb = 0; kb < k_blocks && ok; kb++, it++) {
+          const int s = it % k2Stages;
+          const uint32_t phase = (it / k2Stages) & 1;
+          ok = MbarWait(&sh.full[s], phase, &sh.abort);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t a_addr = SmemAddr(sh.stage[s]);
+          const uint32_t b_addr = a_addr + k2ABytes;
+#pragma unroll
+          for (int kk = 0; kk < kTileK / kMmaK; kk++) {
+            uint64_t da = OperandDesc(a_addr + kk * kMmaK * 128, kTileK * 128);
+            uint64_t db = OperandDesc(b_addr + kk * kMmaK * 128, kTileK * 128);
+            Mma2(tmem_d, da, db, (kb | kk) != 0);
+          }
+          MmaCommit2(&sh.empty[s]);
+        }
+        if (!ok) break;
+        MmaCommit2(&sh.acc_full[acc]);
+      }
+    }
+  } else if (warp >= 4) {
+    const int q = warp - 4;
+    const int row = q * 32 + lane;
+    const int epi_tid = threadIdx.x - 128;
+    uint32_t local_tile = 0, stores = 0;
+    for (int tile = pair; tile < num_tiles; tile += num_pairs, local_tile++) {
+      const int m0 = (tile / tiles_n) * 256 + static_cast<int>(cta_rank) * 128;
+      const int n0 = (tile % tiles_n) * 256;
+      const int acc = local_tile & 1;
+      const uint32_t acc_phase = (local_tile >> 1) & 1;
+      if (!MbarWait(&sh.acc_full[acc], acc_phase, &sh.abort)) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      for (int c = 0; c < kTileN / kEpiCols; c++, stores++) {
+        const int buf = stores % kEpiBufs;
+        if (epi_tid == 0 && stores >= kEpiBufs) asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kEpiBufs - 1) : "memory");
+        NamedBarrier(1, 128);
+        uint32_t v[32];
+        TmemLoad32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * kTileN + c * kEpiCols, v);
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        uint8_t* dst_row = sh.epi[buf] + row * 128;
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+          uint4 w = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          *reinterpret_cast<uint4*>(dst_row + ((j ^ (row & 7)) << 4)) = w;
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        NamedBarrier(2, 128);
+        if (epi_tid == 0) {
+          TmaStore2D(&map_d, sh.epi[buf], n0 + c * kEpiCols, m0);
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+      }
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      if (leader) MbarArrive(&sh.acc_empty[acc]);
+      else MbarArriveOnLeader(&sh.acc_empty[acc]);
+    }
+    if (epi_tid == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  ClusterSync();  // the peer may still be signalling into this CTA's shared memory
+  if (warp == 2) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+  if (threadIdx.x == 0 && sh.abort && error_flag) *reinterpret_cast<volatile int*>(error_flag) = 1;
+}
+
 // ---- host side ------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
@@ -505,6 +700,35 @@ extern "C" int switchml_wgrad_gemm(const void* dy, const void* x, float* dw, int
     e = cudaGetLastError();
   }
   return e == cudaSuccess ? 0 : -4;
+}
+
+extern "C" int switchml_wgrad_gemm_2cta(const void* dy, const void* x, float* dw, int M, int N, int K,
+                                        int* error_flag, void* stream_ptr) {
+  if (!dy || !x || !dw || M <= 0 || N <= 0 || K <= 0) return -1;
+  if ((M % 8) || (N % 8)) return -2;
+  if ((reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dw)) & 15)
+    return -2;
+  CUtensorMap map_a, map_b, map_d;
+  if (!MakeMap(&map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, dy, K, M, kTileK, kAtomMN) ||
+      !MakeMap(&map_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, K, N, kTileK, kAtomMN) ||
+      !MakeMap(&map_d, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dw, M, N, kTileM, kEpiCols))
+    return -3;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && g_sm_count[dev] == 0)
+    cudaDeviceGetAttribute(&g_sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
+  int sms = (dev >= 0 && dev < 64 && g_sm_count[dev] > 0) ? g_sm_count[dev] : 148;
+  int tiles = ((M + 255) / 256) * ((N + 255) / 256);
+  int pairs = tiles < sms / 2 ? tiles : sms / 2;
+  size_t smem = sizeof(SharedStorage2) + 1024;
+  static bool attr = false;
+  if (!attr) {
+    cudaFuncSetAttribute(WgradGemm2CtaKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    attr = true;
+  }
+  WgradGemm2CtaKernel<<<pairs * 2, k2Threads, smem, static_cast<cudaStream_t>(stream_ptr)>>>(
+      map_a, map_b, map_d, M, N, K, error_flag);
+  return cudaGetLastError() == cudaSuccess ? 0 : -4;
 }
 
 extern "C" int switchml_wgrad_flag_words(int M, int N) {

@@ -45,6 +45,9 @@ typedef struct WgradFusedArgs {
 
 int switchml_wgrad_gemm(const void* dy, const void* x, float* dw, int M, int N, int K,
                         const WgradFusedArgs* fused, int* error_flag, void* stream);
+/* Same GEMM (no fused reduce) with pairs of CTAs sharing 256x256 tiles (tcgen05 cta_group::2). */
+int switchml_wgrad_gemm_2cta(const void* dy, const void* x, float* dw, int M, int N, int K,
+                             int* error_flag, void* stream);
 int switchml_wgrad_flag_words(int M, int N);
 
 #ifdef __cplusplus

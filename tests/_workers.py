@@ -122,7 +122,7 @@ def cuda_worker(rank, n, ctl_port, transport, mode, q, heap_mb=64, launch="inlin
         if mode == "float_sum":
             from switchml_b200.ops.wgrad import FusedWgrad
             for (K, M, N) in ((256, 384, 520), (64, 1024, 2048), (1024, 128, 256)):
-                fw = FusedWgrad(ctx, M, N, scale=1.0 / n)
+                fw = FusedWgrad(ctx, M, N, scale=1.0 / n, policy="fused" if M != 128 else "split")
                 report["fused_in_kernel"] = fw.fused
                 for it in range(3):
                     g = torch.Generator(device="cuda").manual_seed(1000 * rank + it)

@@ -18,13 +18,14 @@ def _ref(dy, x):
     (4096, 1024, 512),     # long K: many pipeline wraps, both accumulators
     (257, 8, 8),
 ])
-def test_matches_fp32_reference(K, M, N):
+@pytest.mark.parametrize("two_cta", [False, True])
+def test_matches_fp32_reference(K, M, N, two_cta):
     from switchml_b200.ops.wgrad import wgrad_gemm
     torch.manual_seed(K + M + N)
     dy = torch.randn(K, M, device="cuda", dtype=torch.bfloat16)
     x = torch.randn(K, N, device="cuda", dtype=torch.bfloat16)
     err = torch.zeros(1, dtype=torch.int32, device="cuda")
-    out = wgrad_gemm(dy, x, error_flag=err)
+    out = wgrad_gemm(dy, x, error_flag=err, two_cta=two_cta)
     torch.cuda.synchronize()
     assert int(err.item()) == 0, "a bounded wait inside the kernel gave up"
     ref = _ref(dy, x)
@@ -33,10 +34,11 @@ def test_matches_fp32_reference(K, M, N):
     assert torch.allclose(out, ref, rtol=1e-3, atol=tol), float((out - ref).abs().max())
 
 
-def test_repeated_calls_and_structured_input():
+@pytest.mark.parametrize("two_cta", [False, True])
+def test_repeated_calls_and_structured_input(two_cta):
     from switchml_b200.ops.wgrad import wgrad_gemm
     # An operand with one non-zero per row/column makes any layout mistake visible.
-    K, M, N = 128, 256, 512
+    K, M, N = 128, 512, 768
     dy = torch.zeros(K, M, device="cuda", dtype=torch.bfloat16)
     x = torch.zeros(K, N, device="cuda", dtype=torch.bfloat16)
     for k in range(K):
@@ -44,7 +46,7 @@ def test_repeated_calls_and_structured_input():
         x[k, (k * 13) % N] = 2.0 + k % 5
     ref = _ref(dy, x)
     for _ in range(3):
-        out = wgrad_gemm(dy, x)
+        out = wgrad_gemm(dy, x, two_cta=two_cta)
         assert torch.equal(out, ref)
 
 
