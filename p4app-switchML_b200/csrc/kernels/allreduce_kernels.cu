@@ -342,7 +342,38 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
         const size_t B = ctx.block_numel;
         const bool vec_ok = ELEM == ELEM_F32 && Aligned16(in) && (B % 128) == 0;
         constexpr int kBlocksPerIter = 4;  // independent blocks per warp iteration: loads in flight
-        for (size_t b0 = static_cast<size_t>(warp) * kBlocksPerIter; b0 < nblocks;
+        size_t first_block = 0;
+        if (ELEM == ELEM_F32 && Aligned16(in) && B < 128) {
+          // Small blocks (32 or 64 elements): a warp reads rows of 128 elements with one
+          // float4 per lane; a block is B/4 neighbouring lanes, reduced with a butterfly.
+          const int g = static_cast<int>(B / 4);           // lanes per block: 8 or 16
+          const size_t per_row = 128 / B;                  // blocks per row: 4 or 2
+          const size_t nrows = len / 128;                  // whole rows; the rest goes the slow way
+          const float4* p4 = reinterpret_cast<const float4*>(in);
+          for (size_t r0 = static_cast<size_t>(warp) * kBlocksPerIter; r0 < nrows;
+               r0 += static_cast<size_t>(nwarps) * kBlocksPerIter) {
+            float m[kBlocksPerIter];
+#pragma unroll
+            for (int u = 0; u < kBlocksPerIter; u++) {
+              m[u] = 0.f;
+              if (r0 + u < nrows) {
+                float4 x = p4[(r0 + u) * 32 + lane];
+                m[u] = fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w)));
+              }
+            }
+#pragma unroll
+            for (int u = 0; u < kBlocksPerIter; u++) {
+              float mm = m[u];
+              for (int o = g >> 1; o > 0; o >>= 1) {
+                float t = __shfl_xor_sync(0xffffffffu, mm, o);
+                if (t > mm) mm = t;
+              }
+              if ((lane % g) == 0 && r0 + u < nrows) my_exp[(r0 + u) * per_row + lane / g] = quant::LocalExponent(mm);
+            }
+          }
+          first_block = nrows * per_row;
+        }
+        for (size_t b0 = first_block + static_cast<size_t>(warp) * kBlocksPerIter; b0 < nblocks;
              b0 += static_cast<size_t>(nwarps) * kBlocksPerIter) {
           float m[kBlocksPerIter];
 #pragma unroll
@@ -477,21 +508,30 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
           }
         } else {
           size_t v0 = sb / 4, v1 = (se + 3) / 4;
-          for (size_t v = v0 + t; v < v1; v += n) {
-            size_t off = slot_off + v * 16;
-            uint4 s = ReduceVec<ELEM_I32>(ctx, ctx.stage_peer, ctx.stage_mc, off, 1.0f);
+          auto finish = [&](size_t v, uint4 sum) {
             if (MODE == MODE_QUANT) {
               float f = sf[(v * 4) >> shift];
               float4 y;
-              y.x = quant::Dequantize(static_cast<int>(s.x), f);
-              y.y = quant::Dequantize(static_cast<int>(s.y), f);
-              y.z = quant::Dequantize(static_cast<int>(s.z), f);
-              y.w = quant::Dequantize(static_cast<int>(s.w), f);
+              y.x = quant::Dequantize(static_cast<int>(sum.x), f);
+              y.y = quant::Dequantize(static_cast<int>(sum.y), f);
+              y.z = quant::Dequantize(static_cast<int>(sum.z), f);
+              y.w = quant::Dequantize(static_cast<int>(sum.w), f);
               if (job.post_scale != 1.0f) { y.x *= job.post_scale; y.y *= job.post_scale; y.z *= job.post_scale; y.w *= job.post_scale; }
-              s = make_uint4(__float_as_uint(y.x), __float_as_uint(y.y), __float_as_uint(y.z), __float_as_uint(y.w));
+              sum = make_uint4(__float_as_uint(y.x), __float_as_uint(y.y), __float_as_uint(y.z), __float_as_uint(y.w));
             }
-            BroadcastVec(ctx, ctx.stage_peer, ctx.stage_mc, off, s);
+            BroadcastVec(ctx, ctx.stage_peer, ctx.stage_mc, slot_off + v * 16, sum);
+          };
+          size_t v = v0 + t;
+          for (; v + (kUnrollLink - 1) * n < v1; v += kUnrollLink * n) {
+            uint4 r[kUnrollLink];
+#pragma unroll
+            for (int u = 0; u < kUnrollLink; u++)
+              r[u] = ReduceVec<ELEM_I32>(ctx, ctx.stage_peer, ctx.stage_mc, slot_off + (v + u * n) * 16, 1.0f);
+#pragma unroll
+            for (int u = 0; u < kUnrollLink; u++) finish(v + u * n, r[u]);
           }
+          for (; v < v1; v += n)
+            finish(v, ReduceVec<ELEM_I32>(ctx, ctx.stage_peer, ctx.stage_mc, slot_off + v * 16, 1.0f));
         }
       } else {
         size_t v0 = sb / vec_elems, v1 = (se + vec_elems - 1) / vec_elems;
