@@ -1,6 +1,6 @@
 """The software stack on the dummy backend (reference backends/dummy): every process
 sees its own data multiplied by num_workers, packets complete out of order, float jobs go
-through the block-exponent quantiser. Includes the first BASELINE configuration: 2 workers,
+through the block-exponent quantiser. Includes the plumbing configuration of the benchmark plan: 2 workers,
 2^20 float32 ~N(0,1), packet_numel 64, 256 slots, checked against a float64 sum."""
 import numpy as np
 import pytest
