@@ -87,6 +87,8 @@ def bench_allreduce(args):
     if world != args.gpus:
         raise SystemExit("--gpus %d but WORLD_SIZE is %d (launch with torch.distributed.run)" % (args.gpus, world))
     torch.cuda.set_device(local)
+    from switchml_b200.utils.numa import bind_to_device_numa
+    numa_node = bind_to_device_numa(local)  # pinned host buffers end up next to the GPU
     if world > 1:
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local))
     numel = args.numel
@@ -206,7 +208,7 @@ def bench_allreduce(args):
         "e2e": {"value": world * numel / (e2e_ms * 1e-3), "unit": "elements/s", "ms_per_step": e2e_ms,
                 "ate_per_worker": numel / (e2e_ms * 1e-3),
                 "h2d_bytes_per_step": numel * esz, "d2h_bytes_per_step": numel * esz,
-                "steps": args.e2e_steps, "gpu_launches_per_step": e2e_launches},
+                "steps": args.e2e_steps, "gpu_launches_per_step": e2e_launches, "host_numa_node": numa_node},
         "gpu_launches": args.steps,
         "clocks": clocks, "check": check,
         "stats": {"jobs_finished": stats["jobs_finished"], "jobs_failed": stats["jobs_failed"],
