@@ -192,8 +192,8 @@ bool SymmetricAllocator::Create(size_t bytes, bool want_multicast, SymmetricRegi
         r = api->MemExportToShareableHandle(&fd, reg.mc_handle, CU_MEM_HANDLE_TYPE_POSIX_FILE_DESCRIPTOR, 0);
         if (r != CUDA_SUCCESS) { ok = false; why = "export multicast handle: " + api->ErrorString(r); }
         for (int p = 1; p < n_; p++) {
-          // Always send something so that nobody blocks; -1 cannot travel, so send the
-          // memory handle's fd of a pipe-less dummy when the export failed.
+          // If the export failed there is nothing to send; the peers' receive then times
+          // out and all ranks agree below to fall back to peer mappings.
           if (fd >= 0) fds_->SendTo(p, rank_, tag + 1, fd);
         }
         if (fd >= 0) close(fd);

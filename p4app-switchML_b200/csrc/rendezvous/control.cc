@@ -239,9 +239,7 @@ std::string ControlServer::Handle(const std::string& line) {
   if (cmd == "BARRIER") {
     int n = 0;
     in >> n;
-    static std::atomic<int> anon{0};
-    (void)anon;
-    // Barrier callers are anonymous: give each arrival a distinct pseudo-rank.
+    // Barrier callers are anonymous: only the number of arrivals counts.
     Collective* c;
     {
       std::lock_guard<std::mutex> lk(coll_mu_);

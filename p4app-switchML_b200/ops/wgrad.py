@@ -99,7 +99,6 @@ class FusedWgrad:
         self.flags.zero_()
         self.error = torch.zeros(1, dtype=torch.int32, device=self.grad.device)
         local, peers, mc, _ = ctx.symmetric_info()
-        stats = ctx.get_stats()
         self.nranks = sum(1 for p in peers if p)
         self.rank = peers.index(local)
         self.args = _FusedArgs()

@@ -35,7 +35,6 @@ def switchml_allreduce_hook(state, bucket):
         for j in state.jobs[:-32]:
             j.release()
         state.jobs = state.jobs[-32:]
-    world = state.ctx.get_stats  # noqa: F841  (keeps the context alive in the closure)
     state.stream.wait_stream(torch.cuda.current_stream(buf.device))
     fut = torch.futures.Future(devices=[buf.device])
     with torch.cuda.stream(state.stream):
