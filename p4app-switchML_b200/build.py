@@ -7,6 +7,7 @@
 Products (all inside this directory, never installed elsewhere):
     lib/libswitchml_b200.so        core + CPU backends + CUDA backend + C interface
     lib/libswitchml_gemm.so        tcgen05 weight-gradient GEMM (loaded on demand)
+    lib/torch_switchml.so          native c10d backend for PyTorch (python build.py --torch)
     bin/switchml_switchd           stand-alone controller / software switch
     bin/hello_world, bin/allreduce_benchmark, bin/dnn_benchmark, bin/core_tests
 
@@ -171,6 +172,37 @@ def build_sanitized(kind, verbose=False):
     return exe
 
 
+def build_torch_extension(verbose=False):
+    """lib/torch_switchml.so: the native c10d backend. Needs the headers and libraries of the
+    installed PyTorch; returns None (with a note) when they are not usable."""
+    try:
+        import torch
+        from torch.utils import cpp_extension as ce
+    except Exception as e:  # pragma: no cover
+        print("torch extension skipped: %s" % e)
+        return None
+    src = os.path.join(ROOT, "csrc", "torch", "process_group_sml.cc")
+    out = os.path.join(LIB, "torch_switchml.so")
+    if os.path.exists(out) and os.path.getmtime(out) > max(os.path.getmtime(src), _headers_mtime()):
+        return out
+    import sysconfig
+    tlib = ce.library_paths()[0]
+    have_cuda = os.path.exists(os.path.join(tlib, "libc10_cuda.so"))
+    cmd = ["g++", "-std=c++17", "-O2", "-fPIC", "-shared", "-pthread", "-Wno-deprecated-declarations",
+           "-D_GLIBCXX_USE_CXX11_ABI=%d" % int(torch._C._GLIBCXX_USE_CXX11_ABI),
+           "-DTORCH_EXTENSION_NAME=torch_switchml", "-DTORCH_API_INCLUDE_EXTENSION_H"] + \
+          (["-DSWITCHML_TORCH_CUDA"] if have_cuda else []) + \
+          ["-I" + p for p in ce.include_paths()] + ["-I" + sysconfig.get_paths()["include"]] + INCLUDES + \
+          [src, "-o", out, "-L" + LIB, "-lswitchml_b200", "-Wl,-rpath,$ORIGIN", "-L" + tlib, "-Wl,-rpath," + tlib,
+           "-ltorch", "-ltorch_cpu", "-lc10", "-ltorch_python"] + (["-lc10_cuda"] if have_cuda else [])
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("torch extension failed to build:\n" + r.stdout + r.stderr[-4000:])
+    return out
+
+
 def clean():
     for d in (os.path.join(ROOT, "build"), LIB, BIN):
         shutil.rmtree(d, ignore_errors=True)
@@ -182,6 +214,7 @@ if __name__ == "__main__":
     ap.add_argument("--jobs", type=int, default=None)
     ap.add_argument("-v", "--verbose", action="store_true")
     ap.add_argument("--sanitize", choices=["thread", "address", "undefined"], default=SANITIZE or None)
+    ap.add_argument("--torch", action="store_true", help="also build lib/torch_switchml.so (native c10d backend)")
     a = ap.parse_args()
     if a.clean:
         clean()
@@ -190,6 +223,8 @@ if __name__ == "__main__":
         sys.exit(0)
     try:
         print(build(a.jobs, a.verbose))
+        if a.torch:
+            print(build_torch_extension(a.verbose))
     except RuntimeError as e:
         print(e, file=sys.stderr)
         sys.exit(1)

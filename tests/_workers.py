@@ -281,3 +281,74 @@ def absent_peer_worker(rank, n, ctl_port, q):
         q.put((rank, "ok", info))
     except Exception:
         q.put((rank, "error", traceback.format_exc()))
+
+
+def native_pg_worker(rank, n, port, ctl_port, udp_port, cfg_dir, q):
+    """The native c10d backend "sml_native" (C++ extension) on CPU ranks over udp."""
+    try:
+        import torch
+        import torch.distributed as dist
+        import switchml_b200 as sml
+        path = os.path.join(cfg_dir, "switchml-rank%d.cfg" % rank)
+        with open(path, "w") as f:
+            f.write(sml.make_config("udp", rank=rank, num_workers=n, packet_numel=64, num_worker_threads=2,
+                                    max_outstanding_packets=64, controller_port=ctl_port, switch_port=udp_port,
+                                    worker_port=0))
+        os.environ["SWITCHML_CONFIG"] = path
+        import switchml_b200.parallel.native_process_group  # noqa: F401
+        dist.init_process_group("sml_native", rank=rank, world_size=n, init_method="tcp://127.0.0.1:%d" % port)
+        t = torch.arange(5000, dtype=torch.float32) * (rank + 1)
+        dist.all_reduce(t)
+        assert torch.allclose(t, torch.arange(5000, dtype=torch.float32) * sum(r + 1 for r in range(n)), rtol=1e-6)
+        ti = torch.full((333,), rank + 5, dtype=torch.int32)
+        w = dist.all_reduce(ti, async_op=True)
+        fut = w.get_future()
+        fut.wait()
+        assert int(ti[7]) == sum(r + 5 for r in range(n))
+        try:
+            dist.all_reduce(torch.ones(4, dtype=torch.float64))
+            raised = False
+        except RuntimeError:
+            raised = True
+        assert raised, "float64 must be refused"
+        try:
+            dist.broadcast(t, 0)
+            raised = False
+        except RuntimeError:
+            raised = True
+        assert raised, "the native backend implements allreduce only"
+        dist.destroy_process_group()
+        q.put((rank, "ok", None))
+    except Exception:
+        q.put((rank, "error", traceback.format_exc()))
+
+
+def native_pg_cuda_worker(rank, n, port, ctl_port, cfg_dir, q):
+    """The native c10d backend on GPUs: CUDA tensors are reduced in place on the device."""
+    try:
+        import torch
+        import torch.distributed as dist
+        import switchml_b200 as sml
+        torch.cuda.set_device(rank)
+        path = os.path.join(cfg_dir, "switchml-rank%d.cfg" % rank)
+        with open(path, "w") as f:
+            f.write(sml.make_config("cuda", rank=rank, num_workers=n, packet_numel=256, device=rank,
+                                    controller_port=ctl_port, mode="float_sum", launch="inline",
+                                    wait_timeout_ms=20000))
+        os.environ["SWITCHML_CONFIG"] = path
+        import switchml_b200.parallel.native_process_group  # noqa: F401
+        dist.init_process_group("sml_native", rank=rank, world_size=n, init_method="tcp://127.0.0.1:%d" % port)
+        for numel in (1000, 300001, 1 << 22):
+            t = torch.full((numel,), float(rank + 1), device="cuda")
+            dist.all_reduce(t)
+            torch.cuda.synchronize()
+            assert float(t.min()) == float(t.max()) == float(sum(r + 1 for r in range(n))), numel
+        tb = torch.ones(70000, device="cuda", dtype=torch.bfloat16)
+        work = dist.all_reduce(tb, async_op=True)
+        work.get_future().wait()
+        torch.cuda.synchronize()
+        assert float(tb.float().mean()) == float(n)
+        dist.destroy_process_group()
+        q.put((rank, "ok", None))
+    except Exception:
+        q.put((rank, "error", traceback.format_exc()))

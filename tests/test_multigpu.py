@@ -95,3 +95,27 @@ def test_absent_peer_is_detected_by_bounded_wait():
     assert waiting["status"] == "FAILED" and "did not arrive" in waiting["error"]
     assert waiting["jobs_failed"] == 1 and waiting["device_timeouts"] >= 1
     assert waiting["seconds"] < 10 and waiting["alive"]
+
+
+def test_native_c10d_backend_on_gpus(tmp_path):
+    import os
+    from _workers import native_pg_cuda_worker
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    if not os.path.exists(os.path.join(root, "p4app-switchML_b200", "lib", "torch_switchml.so")):
+        pytest.skip("torch_switchml.so not built")
+    n = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    ports = [free_port(), free_port()]
+    procs = [ctx.Process(target=native_pg_cuda_worker, args=(r, n, *ports, str(tmp_path), q)) for r in range(n)]
+    for p in procs:
+        p.start()
+    try:
+        for _ in range(n):
+            rank, status, info = q.get(timeout=300)
+            assert status == "ok", "rank %d:\n%s" % (rank, info)
+    finally:
+        for p in procs:
+            p.join(timeout=60)
+            if p.is_alive():
+                p.kill()
