@@ -200,7 +200,11 @@ def bench_allreduce(args):
                    "global_batch": None, "seq_len": None, "parallelism": "dp%d" % world,
                    "op": "SUM", "mode": args.mode, "transport": "nvls" if multimem else ("p2p" if world > 1 else "local"),
                    "symmetric_buffers": bool(args.symmetric) and args.mode == "float_sum", "packet_numel": args.packet_numel,
-                   "l2": "input and output tensors (%d MiB each) are larger than the 126 MB L2" % (numel * esz >> 20)},
+                   "l2": "input and output tensors (%d MiB each) are larger than the 126 MB L2" % (numel * esz >> 20),
+                   "placement": "out of place (input -> output), so repeated steps keep their values bounded",
+                   "single_gpu_note": None if world > 1 else
+                   "with one worker the sum is a copy: one pass over input and output at HBM speed; NCCL's "
+                   "in-place allreduce on a single rank returns without touching the data"},
         "bus_gbs": bus, "alg_gbs": esz * numel / (ms * 1e-3) / 1e9,
         "plain_tensors": None if plain_ms is None else {
             "note": "same allreduce on ordinary torch tensors (staged through the slot ring)",
