@@ -180,6 +180,20 @@ def bench_allreduce(args):
     stats = ctx.get_stats()
     multimem = ctx.uses_multimem()
     ctx.stop()
+    # Secondary measurement: the exact, order-independent integer mode (SwitchML's block
+    # fixed point), ordinary tensors, same size. It needs its own context (mode is a setting).
+    quant = None
+    if args.mode == "float_sum" and dtype == torch.float32 and args.quant_steps > 0:
+        del x, y
+        saved_mode, args.mode = args.mode, "int32_quant"
+        ctx = start_context(args, rank, world, local, addr, port, 0)
+        args.mode = saved_mode
+        qx, qy = make_tensors(False)
+        q_ms, _, _ = measure(qx, qy, args.quant_steps, False)
+        quant = {"note": "int32_quant mode (per-block exponent fixed point, exact integer sum), ordinary tensors",
+                 "ms_per_step": q_ms, "ate_per_worker": numel / (q_ms * 1e-3), "steps": args.quant_steps}
+        del qx, qy
+        ctx.stop()
     if world > 1:
         dist.destroy_process_group()
     if rank != 0:
@@ -206,6 +220,7 @@ def bench_allreduce(args):
                    "with one worker the sum is a copy: one pass over input and output at HBM speed; NCCL's "
                    "in-place allreduce on a single rank returns without touching the data"},
         "bus_gbs": bus, "alg_gbs": esz * numel / (ms * 1e-3) / 1e9,
+        "int32_quant": quant,
         "plain_tensors": None if plain_ms is None else {
             "note": "same allreduce on ordinary torch tensors (staged through the slot ring)",
             "ms_per_step": plain_ms, "ate_per_worker": numel / (plain_ms * 1e-3)},
@@ -326,6 +341,7 @@ def main():
     ap.add_argument("--slot-bytes", type=int, default=0, help="0 = library default")
     ap.add_argument("--channels", type=int, default=0)
     ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--quant-steps", type=int, default=5, help="steps of the secondary int32_quant measurement (0 = skip)")
     ap.add_argument("--e2e-chunk", type=int, default=1 << 24)
     ap.add_argument("--batch", type=int, default=0, help="per-GPU batch for the training workloads")
     ap.add_argument("--ddp", default="sml", choices=["sml", "torch"], help="training workloads: this library or PyTorch DDP/NCCL")
