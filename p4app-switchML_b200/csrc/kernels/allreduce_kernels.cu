@@ -38,7 +38,8 @@ namespace {
 static const int kMaxBlocksPerSlot = 8192;  // scale factors of all slots of a channel (shared memory)
 static const int kUnroll = 4;        // 16-byte vectors in flight per thread, local copies
 static const int kDefaultUnrollLink = 4;  // ... for staged loads that cross NVLink (8 measured slower)
-static const int kZeroCopyUnrollLink = 2;  // the in-place kernel has all 512 threads on the link
+static const int kZeroCopyUnrollLink = 2;  // in-switch reduction: few requests in flight are best (8 GPUs: 2.25 ms vs 2.38 ms with 8)
+static const int kZeroCopyUnrollPeer = 16;  // plain peer loads want many (2 GPUs: 1.75 ms vs 1.91 ms with 2)
 
 
 __device__ __forceinline__ bool Aligned16(const void* p) {
@@ -795,7 +796,8 @@ __device__ __forceinline__ void RunJob(const RankCtx& ctx, const JobArgs& job, i
   else if (ALGO == ALGO_STAGED)
     RunStaged<ELEM, MODE>(ctx, job, channel, epc, reinterpret_cast<StagedShared*>(s_failed), s_sf);
   else if (ALGO == ALGO_ONESHOT) RunOneShot<ELEM, MODE>(ctx, job, channel, epc, s_failed);
-  else RunZeroCopy<ELEM>(ctx, job, channel, epc, s_failed);
+  else if (ctx.use_multimem) RunZeroCopy<ELEM, kZeroCopyUnrollLink>(ctx, job, channel, epc, s_failed);
+  else RunZeroCopy<ELEM, kZeroCopyUnrollPeer>(ctx, job, channel, epc, s_failed);
 }
 
 template <int ELEM, int MODE, int ALGO>
