@@ -123,7 +123,9 @@ class CudaBackend : public CudaBackendInterface {
   void LauncherLoop();
   void CompletionLoop();
   // Enqueue the kernels of `job` on `stream`; fills `f`. Caller holds launch_mu_.
-  void LaunchJob(const std::shared_ptr<Job>& job, cudaStream_t stream, InFlight* f);
+  // `capturing`: the stream is being captured into a CUDA graph; nothing that belongs to
+  // this one submission (events, status slot, buffer parity) may end up in the launch.
+  void LaunchJob(const std::shared_ptr<Job>& job, cudaStream_t stream, InFlight* f, bool capturing = false);
   cudaEvent_t GetEvent() { return events_->Get(); }
   void PutEvent(cudaEvent_t e) { events_->Put(e); }
 
@@ -143,6 +145,7 @@ class CudaBackend : public CudaBackendInterface {
   cudaStream_t comm_stream_ = nullptr;
   int* dev_status_ = nullptr;
   unsigned long long* dev_counters_ = nullptr;
+  unsigned long long* dev_epochs_ = nullptr;  // per-channel epochs, advanced by the kernels themselves
   int* host_status_ = nullptr;  // pinned ring of status words
 
   std::mutex launch_mu_;  // serialises launches: one job order on every rank
@@ -248,6 +251,8 @@ void CudaBackend::SetupWorker() {
   SML_CUDA_CHECK(cudaStreamCreateWithPriority(&comm_stream_, cudaStreamNonBlocking, hi));
   SML_CUDA_CHECK(cudaMalloc(&dev_counters_, 16 * sizeof(unsigned long long)));
   SML_CUDA_CHECK(cudaMemset(dev_counters_, 0, 16 * sizeof(unsigned long long)));
+  SML_CUDA_CHECK(cudaMalloc(&dev_epochs_, kernels::kMaxChannels * sizeof(unsigned long long)));
+  SML_CUDA_CHECK(cudaMemset(dev_epochs_, 0, kernels::kMaxChannels * sizeof(unsigned long long)));
   // Status words live in pinned host memory that the device can write: a kernel stores
   // its error code there directly, so a job costs no extra copy or memset on the stream.
   SML_CUDA_CHECK(cudaHostAlloc(&host_status_, kStatusSlots * sizeof(int), cudaHostAllocMapped));
@@ -255,6 +260,7 @@ void CudaBackend::SetupWorker() {
   SML_CUDA_CHECK(cudaHostGetDevicePointer(reinterpret_cast<void**>(&dev_status_), host_status_, 0));
   ctx_.status = dev_status_;
   ctx_.counters = dev_counters_;
+  ctx_.epoch_words = dev_epochs_;
   epoch_base_ = 0;
   oneshot_parity_ = 0;
   launched_jobs_ = 0;
@@ -293,6 +299,8 @@ void CudaBackend::CleanupWorker() {
   if (comm_stream_) cudaStreamDestroy(comm_stream_);
   comm_stream_ = nullptr;
   if (dev_counters_) cudaFree(dev_counters_);
+  if (dev_epochs_) cudaFree(dev_epochs_);
+  dev_epochs_ = nullptr;
   if (host_status_) cudaFreeHost(host_status_);
   dev_status_ = nullptr;
   dev_counters_ = nullptr;
@@ -320,7 +328,7 @@ void CudaBackend::SymmetricReset() {
   heap_used_ = 0;
 }
 
-void CudaBackend::LaunchJob(const std::shared_ptr<Job>& job, cudaStream_t stream, InFlight* f) {
+void CudaBackend::LaunchJob(const std::shared_ptr<Job>& job, cudaStream_t stream, InFlight* f, bool capturing) {
   const CudaBackendConfig& c = config_.backend_.cuda;
   const Tensor& t = job->tensor_;
   kernels::JobArgs a;
@@ -332,7 +340,6 @@ void CudaBackend::LaunchJob(const std::shared_ptr<Job>& job, cudaStream_t stream
               : t.data_type == INT32 ? kernels::ELEM_I32 : kernels::ELEM_BF16;
   a.mode = (t.data_type != INT32 && c.mode == "int32_quant") ? kernels::MODE_QUANT : kernels::MODE_SUM;
   a.post_scale = c.average && t.data_type != INT32 ? 1.0f / static_cast<float>(n_) : 1.0f;
-  a.epoch_base = epoch_base_;
   a.tune = static_cast<int>(c.tune);
   size_t esz = DataTypeSize(t.data_type);
   size_t bytes = t.numel * esz;
@@ -356,16 +363,24 @@ void CudaBackend::LaunchJob(const std::shared_ptr<Job>& job, cudaStream_t stream
   } else if (bytes <= c.oneshot_max_bytes) {
     a.algo = kernels::ALGO_ONESHOT;
     a.oneshot_parity = oneshot_parity_;
-    oneshot_parity_ ^= 1;
+    if (!capturing) oneshot_parity_ ^= 1;
   } else {
     a.algo = kernels::ALGO_STAGED;
   }
   kernels::LaunchPlan plan = kernels::PlanLaunch(ctx_, a, c.channels, max_channels_);
   a.tile_elems = plan.tile_elems;
-  epoch_base_ += plan.epochs;
+  a.epochs = plan.epochs;
+  if (capturing && a.algo == kernels::ALGO_ONESHOT) {
+    a.trailing_barrier = 1;  // a replayed launch cannot alternate buffers: meet again instead,
+    a.oneshot_parity = 2;    // in a buffer set of its own, apart from the alternating pair
+    a.epochs = 2;
+  }
+  epoch_base_ += a.epochs;
   f->tiles = plan.tiles;
-  f->status_slot = static_cast<int>(launched_jobs_++ % kStatusSlots);
-  f->done = GetEvent();
+  // Replays of a captured launch share one status word that nobody waits on; a timeout in
+  // a replay still shows up in the device counters.
+  f->status_slot = capturing ? kStatusSlots - 2 : static_cast<int>(launched_jobs_++ % (kStatusSlots - 2));
+  f->done = capturing ? nullptr : GetEvent();
 
   cudaError_t e = cudaSuccess;
   host_status_[f->status_slot] = kernels::STATUS_OK;  // the ring is far longer than the queue
@@ -383,7 +398,7 @@ void CudaBackend::LaunchJob(const std::shared_ptr<Job>& job, cudaStream_t stream
   if (t.numel > 0 && plain_copy) e = kernels::LaunchLocalCopy(t.in_ptr, t.out_ptr, bytes, stream);
   else if (t.numel > 0 && !nothing_to_do) e = kernels::LaunchAllReduce(job_ctx, a, plan, stream);
   SML_NVTX_POP();
-  if (e == cudaSuccess) e = cudaEventRecord(f->done, stream);
+  if (e == cudaSuccess && f->done) e = cudaEventRecord(f->done, stream);
   if (e != cudaSuccess) {
     f->launch_error = std::string("kernel launch failed: ") + cudaGetErrorString(e);
     cudaGetLastError();
@@ -391,10 +406,14 @@ void CudaBackend::LaunchJob(const std::shared_ptr<Job>& job, cudaStream_t stream
   SML_VLOG(2) << "job " << job->id_ << ": " << t.numel << " x " << DataTypeName(t.data_type)
               << " algo " << a.algo << " mode " << a.mode << " channels " << plan.channels
               << " epochs " << plan.epochs;
-  auto st = std::make_shared<EventState>();
-  st->done = f->done;
-  st->pool = events_;
-  job->SetDeviceState(st);
+  if (f->done) {
+    auto st = std::make_shared<EventState>();
+    st->done = f->done;
+    st->pool = events_;
+    job->SetDeviceState(st);
+  } else {
+    job->SetDeviceState(nullptr);  // captured: the work is ordered by the graph itself
+  }
 }
 
 bool CudaBackend::OnSubmit(const std::shared_ptr<Job>& job) {
@@ -417,11 +436,24 @@ bool CudaBackend::OnSubmit(const std::shared_ptr<Job>& job) {
   }
   InFlight f;
   f.job = job;
+  cudaStream_t user_stream = static_cast<cudaStream_t>(job->producer_stream_);
+  cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(user_stream, &capture) != cudaSuccess) {
+    capture = cudaStreamCaptureStatusNone;
+    cudaGetLastError();
+  }
+  const bool capturing = capture == cudaStreamCaptureStatusActive;
   {
     std::lock_guard<std::mutex> lk(launch_mu_);
     job->SetJobStatus(QUEUED);
     job->SetJobStatus(RUNNING);
-    LaunchJob(job, static_cast<cudaStream_t>(job->producer_stream_), &f);
+    LaunchJob(job, user_stream, &f, capturing);
+  }
+  if (capturing) {
+    // The kernels now live in the graph under capture and run whenever it is replayed;
+    // as far as this submission goes the job is done.
+    context_.NotifyJobCompletion(job, f.launch_error.empty(), f.launch_error);
+    return true;
   }
   {
     std::lock_guard<std::mutex> lk(q_mu_);
@@ -528,7 +560,7 @@ int CudaBackend::RunWaitProbe(double budget_ms) {
   probe.timeout_ns = static_cast<unsigned long long>(budget_ms * 1e6);
   cudaStream_t s = comm_stream_;
   int st = -1;
-  int slot = static_cast<int>(launched_jobs_++ % kStatusSlots);
+  int slot = kStatusSlots - 1;
   host_status_[slot] = kernels::STATUS_OK;
   probe.status = dev_status_ + slot;
   cudaError_t e = kernels::LaunchWaitProbe(probe, s);
@@ -585,12 +617,14 @@ int EmulatedAllReduce(int nranks, void* const* in_ptrs, void* const* out_ptrs,
   unsigned long long* counters = nullptr;
   RankCtx* d_ctx = nullptr;
   JobArgs* d_job = nullptr;
+  unsigned long long* epochs = nullptr;
   int result = 0;
   cudaError_t e = cudaSuccess;
   auto cleanup = [&] {
     for (char* p : stage) if (p) cudaFree(p);
     if (status) cudaFree(status);
     if (counters) cudaFree(counters);
+    if (epochs) cudaFree(epochs);
     if (d_ctx) cudaFree(d_ctx);
     if (d_job) cudaFree(d_job);
   };
@@ -602,6 +636,8 @@ int EmulatedAllReduce(int nranks, void* const* in_ptrs, void* const* out_ptrs,
   if (e == cudaSuccess) e = cudaMemset(status, 0, nranks * sizeof(int));
   if (e == cudaSuccess) e = cudaMalloc(&counters, nranks * 16 * sizeof(unsigned long long));
   if (e == cudaSuccess) e = cudaMemset(counters, 0, nranks * 16 * sizeof(unsigned long long));
+  if (e == cudaSuccess) e = cudaMalloc(&epochs, nranks * kMaxChannels * sizeof(unsigned long long));
+  if (e == cudaSuccess) e = cudaMemset(epochs, 0, nranks * kMaxChannels * sizeof(unsigned long long));
   if (e == cudaSuccess) e = cudaMalloc(&d_ctx, nranks * sizeof(RankCtx));
   if (e == cudaSuccess) e = cudaMalloc(&d_job, nranks * sizeof(JobArgs));
   if (e != cudaSuccess) {
@@ -618,6 +654,7 @@ int EmulatedAllReduce(int nranks, void* const* in_ptrs, void* const* out_ptrs,
       for (int p = 0; p < nranks; p++) ctxs[r].stage_peer[p] = stage[p];
       ctxs[r].status = status + r;
       ctxs[r].counters = counters + r * 16;
+      ctxs[r].epoch_words = epochs + static_cast<size_t>(r) * kMaxChannels;
       JobArgs& j = jobs[r];
       memset(&j, 0, sizeof(j));
       j.in = in_ptrs[r];
@@ -627,11 +664,13 @@ int EmulatedAllReduce(int nranks, void* const* in_ptrs, void* const* out_ptrs,
       j.mode = mode;
       j.algo = algo;
       j.post_scale = post_scale;
-      j.epoch_base = epoch;
       j.oneshot_parity = it & 1;
     }
     plan = PlanLaunch(ctxs[0], jobs[0], channels, max_channels);
-    for (int r = 0; r < nranks; r++) jobs[r].tile_elems = plan.tile_elems;
+    for (int r = 0; r < nranks; r++) {
+      jobs[r].tile_elems = plan.tile_elems;
+      jobs[r].epochs = plan.epochs;
+    }
     epoch += plan.epochs;
     cudaMemcpy(d_ctx, ctxs.data(), nranks * sizeof(RankCtx), cudaMemcpyHostToDevice);
     cudaMemcpy(d_job, jobs.data(), nranks * sizeof(JobArgs), cudaMemcpyHostToDevice);

@@ -261,7 +261,7 @@ __device__ __forceinline__ void RoleCopy(const Role& role, void* dst, const void
 template <int ELEM, int MODE, int kLoadWarps = kDefaultLoadWarps, int kReduceWarps = kDefaultReduceWarps,
           int kUnrollLink = kDefaultUnrollLink>
 __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
-                          unsigned long long elems_per_channel, StagedShared* sh, float* s_sf) {
+                          unsigned long long elems_per_channel, Epoch base, StagedShared* sh, float* s_sf) {
   constexpr int kStoreWarps = kThreads / 32 - kLoadWarps - kReduceWarps;
   constexpr int kUnrollInt = 2 * kUnrollLink;  // 4-byte integer lanes in flight per thread
   const int in_esz = ELEM == ELEM_BF16 ? 2 : 4;
@@ -306,7 +306,7 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
 
   for (unsigned long long k = 0; k < ntiles; ++k) {
     const unsigned long long pos = c0 + k * tile_elems;
-    const Epoch epoch = job.epoch_base + k + 1;
+    const Epoch epoch = base + k + 1;
     const size_t len = static_cast<size_t>(c1 - pos < tile_elems ? c1 - pos : tile_elems);
     const int slot = static_cast<int>(k % S);
     const size_t slot_index = static_cast<size_t>(channel) * S + slot;
@@ -579,14 +579,14 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
 // ------------------------------------------------------------------------------------
 template <int ELEM, int MODE>
 __device__ void RunOneShot(const RankCtx& ctx, const JobArgs& job, int channel,
-                           unsigned long long elems_per_channel, int* s_failed) {
+                           unsigned long long elems_per_channel, Epoch base, int* s_failed) {
   const int esz = ELEM == ELEM_BF16 ? 2 : 4;
   unsigned long long c0 = static_cast<unsigned long long>(channel) * elems_per_channel;
   if (c0 >= job.numel) return;
   unsigned long long c1 = c0 + elems_per_channel;
   if (c1 > job.numel) c1 = job.numel;
   const size_t len = static_cast<size_t>(c1 - c0);
-  const unsigned long long epoch = job.epoch_base + 1;
+  const unsigned long long epoch = base + 1;
 
   // Buffer of source rank s (same offset on every rank).
   auto buf_off = [&](int s) {
@@ -631,6 +631,8 @@ __device__ void RunOneShot(const RankCtx& ctx, const JobArgs& job, int channel,
       }
     }
     if (threadIdx.x == 0) atomicAdd(ctx.counters, 1ull);
+    // Replayable launches reuse one buffer: nobody may refill it before all have read it.
+    if (job.trailing_barrier) ChannelBarrier(ctx, channel, 3, epoch + 1, s_failed);
     return;
   }
 
@@ -713,15 +715,16 @@ __device__ void RunOneShot(const RankCtx& ctx, const JobArgs& job, int channel,
     }
   }
   if (threadIdx.x == 0) atomicAdd(ctx.counters, 1ull);
+  if (job.trailing_barrier) ChannelBarrier(ctx, channel, 3, epoch + 1, s_failed);
 }
 
 // ------------------------------------------------------------------------------------
 template <int ELEM, int kUnrollLink = kZeroCopyUnrollLink>
 __device__ void RunZeroCopy(const RankCtx& ctx, const JobArgs& job, int channel,
-                            unsigned long long elems_per_channel, int* s_failed) {
+                            unsigned long long elems_per_channel, Epoch base, int* s_failed) {
   const int esz = ELEM == ELEM_BF16 ? 2 : 4;
   const size_t vec_elems = 16 / esz;
-  const unsigned long long epoch = job.epoch_base + 1;
+  const unsigned long long epoch = base + 1;
   // Everybody's input must be complete before anybody reads it.
   if (!ChannelBarrier(ctx, channel, 0, epoch, s_failed)) return;
 
@@ -787,27 +790,43 @@ __device__ void RunZeroCopy(const RankCtx& ctx, const JobArgs& job, int channel,
 // ------------------------------------------------------------------------------------
 template <int ELEM, int MODE, int ALGO>
 __device__ __forceinline__ void RunJob(const RankCtx& ctx, const JobArgs& job, int channel,
-                                       unsigned long long epc, int* s_failed, float* s_sf) {
+                                       unsigned long long epc, Epoch base, int* s_failed, float* s_sf) {
   // The quantising loader reads its input twice and meets its peers once more per tile,
   // so it gets more warps than the plain copy-in of the SUM modes (8-GPU measurements with
   // 1 GiB: 4/8/4 3.72 ms, 6/8/2 3.30 ms, 8/6/2 3.07 ms before the loader was vectorised).
   if (ALGO == ALGO_STAGED && MODE == MODE_QUANT)
-    RunStaged<ELEM, MODE, 6, 8>(ctx, job, channel, epc, reinterpret_cast<StagedShared*>(s_failed), s_sf);
+    RunStaged<ELEM, MODE, 6, 8>(ctx, job, channel, epc, base, reinterpret_cast<StagedShared*>(s_failed), s_sf);
   else if (ALGO == ALGO_STAGED)
-    RunStaged<ELEM, MODE>(ctx, job, channel, epc, reinterpret_cast<StagedShared*>(s_failed), s_sf);
-  else if (ALGO == ALGO_ONESHOT) RunOneShot<ELEM, MODE>(ctx, job, channel, epc, s_failed);
-  else if (ctx.use_multimem) RunZeroCopy<ELEM, kZeroCopyUnrollLink>(ctx, job, channel, epc, s_failed);
-  else RunZeroCopy<ELEM, kZeroCopyUnrollPeer>(ctx, job, channel, epc, s_failed);
+    RunStaged<ELEM, MODE>(ctx, job, channel, epc, base, reinterpret_cast<StagedShared*>(s_failed), s_sf);
+  else if (ALGO == ALGO_ONESHOT) RunOneShot<ELEM, MODE>(ctx, job, channel, epc, base, s_failed);
+  else if (ctx.use_multimem) RunZeroCopy<ELEM, kZeroCopyUnrollLink>(ctx, job, channel, epc, base, s_failed);
+  else RunZeroCopy<ELEM, kZeroCopyUnrollPeer>(ctx, job, channel, epc, base, s_failed);
 }
+
+// Every channel keeps the epoch it has reached in device memory: read it when the kernel
+// starts, advance it by the job's count when the kernel ends (on every path, also after a
+// timeout, so that the ranks stay in step). Nothing about epochs is baked into the launch,
+// which is what lets a captured launch be replayed.
+#define SML_EPOCH_PROLOGUE(CTX, CHANNEL)                                  \
+  __shared__ Epoch s_base;                                                \
+  if (threadIdx.x == 0) {                                                 \
+    s_state.failed = 0;                                                   \
+    s_state.stored = 0;                                                   \
+    s_base = (CTX).epoch_words[CHANNEL];                                  \
+  }                                                                       \
+  __syncthreads();
+#define SML_EPOCH_EPILOGUE(CTX, JOB, CHANNEL)                             \
+  __syncthreads();                                                        \
+  if (threadIdx.x == 0) (CTX).epoch_words[CHANNEL] = s_base + (JOB).epochs;
 
 template <int ELEM, int MODE, int ALGO>
 __global__ void __launch_bounds__(kThreads)
 AllReduceKernel(const RankCtx ctx, const JobArgs job, unsigned long long epc) {
   __shared__ StagedShared s_state;
   __shared__ float s_sf[(MODE == MODE_QUANT && ALGO == ALGO_STAGED) ? kMaxBlocksPerSlot : 1];
-  if (threadIdx.x == 0) { s_state.failed = 0; s_state.stored = 0; }
-  __syncthreads();
-  RunJob<ELEM, MODE, ALGO>(ctx, job, blockIdx.x, epc, &s_state.failed, s_sf);
+  SML_EPOCH_PROLOGUE(ctx, blockIdx.x)
+  RunJob<ELEM, MODE, ALGO>(ctx, job, blockIdx.x, epc, s_base, &s_state.failed, s_sf);
+  SML_EPOCH_EPILOGUE(ctx, job, blockIdx.x)
 }
 
 // All ranks in one grid: blockIdx.y selects the rank whose role this CTA plays.
@@ -819,13 +838,13 @@ AllReduceEmuKernel(const RankCtx* ctxs, const JobArgs* jobs, unsigned long long 
   __shared__ RankCtx s_ctx;
   __shared__ JobArgs s_job;
   if (threadIdx.x == 0) {
-    s_state.failed = 0;
-    s_state.stored = 0;
     s_ctx = ctxs[blockIdx.y];
     s_job = jobs[blockIdx.y];
   }
   __syncthreads();
-  RunJob<ELEM, MODE, ALGO>(s_ctx, s_job, blockIdx.x, epc, &s_state.failed, s_sf);
+  SML_EPOCH_PROLOGUE(s_ctx, blockIdx.x)
+  RunJob<ELEM, MODE, ALGO>(s_ctx, s_job, blockIdx.x, epc, s_base, &s_state.failed, s_sf);
+  SML_EPOCH_EPILOGUE(s_ctx, s_job, blockIdx.x)
 }
 
 // Float32 kernels with explicit pipeline parameters (role split, loads in flight): used to
@@ -835,10 +854,10 @@ __global__ void __launch_bounds__(kThreads)
 TunedF32Kernel(const RankCtx ctx, const JobArgs job, unsigned long long epc) {
   __shared__ StagedShared s_state;
   __shared__ float s_sf[MODE == MODE_QUANT ? kMaxBlocksPerSlot : 1];
-  if (threadIdx.x == 0) { s_state.failed = 0; s_state.stored = 0; }
-  __syncthreads();
-  if (ALGO == ALGO_STAGED) RunStaged<ELEM_F32, MODE, LW, RW, UL>(ctx, job, blockIdx.x, epc, &s_state, s_sf);
-  else RunZeroCopy<ELEM_F32, UL>(ctx, job, blockIdx.x, epc, &s_state.failed);
+  SML_EPOCH_PROLOGUE(ctx, blockIdx.x)
+  if (ALGO == ALGO_STAGED) RunStaged<ELEM_F32, MODE, LW, RW, UL>(ctx, job, blockIdx.x, epc, s_base, &s_state, s_sf);
+  else RunZeroCopy<ELEM_F32, UL>(ctx, job, blockIdx.x, epc, s_base, &s_state.failed);
+  SML_EPOCH_EPILOGUE(ctx, job, blockIdx.x)
 }
 
 // The sum over a single worker, out of place: one pass over the data, no staging.
@@ -936,7 +955,7 @@ size_t StagingBytes(size_t slot_bytes, int slots_per_channel, int block_numel, i
   size_t blocks_per_slot = slot_bytes / 4 / block_numel;
   off = align(off + size_t(max_channels) * slots_per_channel * blocks_per_slot * 4);
   *oneshot_offset = off;
-  off = align(off + 2 * size_t(nranks) * oneshot_bytes);
+  off = align(off + 3 * size_t(nranks) * oneshot_bytes);  // two alternating sets + one for captured launches
   *data_offset = off;
   off = align(off + size_t(max_channels) * slots_per_channel * slot_bytes);
   return off;
@@ -1145,6 +1164,7 @@ extern "C" int switchml_local_allreduce_noalloc(const void* in, void* out,
   if (staging > kNoAllocAuxOffset) return SWITCHML_NOALLOC_BAD_ARGUMENT;  // cannot happen for the limits above
   ctx.counters = reinterpret_cast<unsigned long long*>(scratch + kNoAllocAuxOffset);
   ctx.status = reinterpret_cast<int*>(scratch + kNoAllocAuxOffset + 256);
+  ctx.epoch_words = reinterpret_cast<unsigned long long*>(scratch + kNoAllocAuxOffset + 320);  // 8 channels
 
   JobArgs job;
   memset(&job, 0, sizeof(job));
@@ -1155,9 +1175,9 @@ extern "C" int switchml_local_allreduce_noalloc(const void* in, void* out,
   job.mode = mode;
   job.algo = ALGO_STAGED;
   job.post_scale = 1.0f;
-  job.epoch_base = 0;
   LaunchPlan plan = PlanLaunch(ctx, job, 0, kNoAllocChannels);
   job.tile_elems = plan.tile_elems;
+  job.epochs = plan.epochs;
 
   // The array keeps the previous call's flags (epochs) and counters; this call counts its
   // epochs from zero again, so both have to be cleared first, in stream order.

@@ -58,6 +58,8 @@ struct RankCtx {
   unsigned long long timeout_ns; // budget of every wait
   int* status;                   // device-visible status word (0 = ok)
   unsigned long long* counters;  // [0] tiles processed, [1] wait iterations, [2] timeouts
+  unsigned long long* epoch_words;  // [kMaxChannels] in this rank's device memory: the epoch each channel has
+                                 // reached. Kept on the device so that a captured launch can be replayed.
 };
 
 struct JobArgs {
@@ -68,7 +70,8 @@ struct JobArgs {
   int mode;          // ReduceMode
   int algo;          // Algo
   float post_scale;  // multiplied into the result (1/num_workers for averaging)
-  unsigned long long epoch_base;  // flags written by this job are epoch_base+1 .. epoch_base+epochs
+  unsigned epochs;      // how far the job advances the epoch counter of each channel it uses
+  int trailing_barrier; // ALGO_ONESHOT: meet once more after reading, so the buffer needs no parity (graph replays)
   int oneshot_parity;
   int tune;          // > 0: float32 SUM variant with other pipeline parameters (see LaunchAllReduce)
   unsigned long long tile_elems;  // ALGO_STAGED: elements per tile (<= elements of a slot)

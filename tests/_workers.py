@@ -138,6 +138,30 @@ def cuda_worker(rank, n, ctl_port, transport, mode, q, heap_mb=64, launch="inlin
                     assert err < 2e-2 * (K ** 0.5), "fused wgrad mismatch %g at %s it %d" % (err, (K, M, N), it)
                     report["cases"] += 1
             ctx.symmetric_reset()
+        # CUDA graph: capture a small (one-barrier) and a large (streamed) job, replay with new data
+        if launch == "inline":
+            gs = torch.full((20_000,), 0.0, device="cuda")
+            gl = torch.full((2_500_003,), 0.0, device="cuda")
+            os_, ol_ = torch.empty_like(gs), torch.empty_like(gl)
+            graph = torch.cuda.CUDAGraph()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.graph(graph, stream=side):
+                ctx.all_reduce_async(gs, os_)
+                ctx.all_reduce_async(gl, ol_)
+            for it in range(4):
+                gs.fill_(rank + 1.0 + it)
+                gl.fill_(0.5 * (rank + 1) + it)
+                graph.replay()
+                torch.cuda.synchronize()
+                want_s = sum(r + 1.0 + it for r in range(n))
+                want_l = sum(0.5 * (r + 1) + it for r in range(n))
+                assert abs(float(os_.min()) - want_s) < 1e-4 and abs(float(os_.max()) - want_s) < 1e-4, "graph small"
+                assert abs(float(ol_.min()) - want_l) < 1e-4 and abs(float(ol_.max()) - want_l) < 1e-4, "graph large"
+                report["cases"] += 1
+            t = torch.full((50_000,), float(rank), device="cuda")   # ordinary job after the replays
+            ctx.all_reduce(t)
+            assert float(t[0]) == float(sum(range(n))), "job after graph replays"
         # DDP wrapper: overlapped, bucketed reduction must equal the mean of the local gradients
         if mode == "float_sum":
             from switchml_b200.parallel.ddp import DistributedDataParallel

@@ -102,3 +102,36 @@ def test_host_pipeline_roundtrip(ctx):
         assert torch.equal(hx, hy)
         hy.zero_()
     pipe.close()
+
+
+def test_jobs_can_be_captured_in_a_cuda_graph_and_replayed(ctx):
+    """Epochs live on the device, so a captured launch carries nothing that goes stale:
+    replaying the graph runs the same jobs again on whatever the buffers hold then."""
+    assert ctx.start(sml.make_config("cuda", packet_numel=256, mode="int32_quant", launch="inline"))
+    small = torch.randn(10_000, device="cuda")          # one-barrier kernel
+    large = torch.randn(3_000_001, device="cuda")       # streamed through the slot ring
+    out_s, out_l = torch.empty_like(small), torch.empty_like(large)
+    warm = ctx.all_reduce_async(large, out_l)            # ordinary job first: epochs are not zero
+    assert warm.wait() == sml.JobStatus.FINISHED
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.graph(graph, stream=side):
+        j1 = ctx.all_reduce_async(small, out_s)
+        j2 = ctx.all_reduce_async(large, out_l)
+        j1.stream_wait()
+        j2.stream_wait()
+    assert j1.status() == sml.JobStatus.FINISHED and j2.status() == sml.JobStatus.FINISHED
+    for it in range(3):
+        small.normal_()
+        large.normal_()
+        out_s.zero_()
+        out_l.zero_()
+        graph.replay()
+        torch.cuda.synchronize()
+        assert np.array_equal(out_s.cpu().numpy(), quant_allreduce_oracle([small.cpu().numpy()], 256))
+        assert np.array_equal(out_l.cpu().numpy(), quant_allreduce_oracle([large.cpu().numpy()], 256))
+    # ordinary jobs keep working after replays
+    ctx.all_reduce(large, out_l)
+    assert np.array_equal(out_l.cpu().numpy(), quant_allreduce_oracle([large.cpu().numpy()], 256))
+    assert ctx.get_stats()["backend"]["device_timeouts"] == 0
