@@ -8,6 +8,7 @@ Products (all inside this directory, never installed elsewhere):
     lib/libswitchml_b200.so        core + CPU backends + CUDA backend + C interface
     lib/libswitchml_gemm.so        tcgen05 weight-gradient GEMM (loaded on demand)
     lib/torch_switchml.so          native c10d backend for PyTorch (python build.py --torch)
+    lib/libnccl-net-switchml.so    NCCL collective-network plugin (bin/collnet_harness drives it)
     bin/switchml_switchd           stand-alone controller / software switch
     bin/hello_world, bin/allreduce_benchmark, bin/dnn_benchmark, bin/core_tests
 
@@ -53,12 +54,14 @@ LIB_SOURCES = [
     "csrc/capi/switchml_c.cc",
 ]
 GEMM_SOURCES = ["csrc/kernels/wgrad_gemm.cu"]
+NCCL_PLUGIN_SOURCES = ["csrc/nccl/collnet_plugin.cc"]
 PROGRAMS = {
     "switchml_switchd": ["controller/switchd.cc"],
     "hello_world": ["examples/hello_world/main.cc"],
     "allreduce_benchmark": ["benchmarks/allreduce_benchmark.cc"],
     "dnn_benchmark": ["benchmarks/dnn_benchmark.cc"],
     "core_tests": ["csrc/tests/core_tests.cc"],
+    "collnet_harness": ["csrc/nccl/collnet_harness.cc"],
 }
 
 
@@ -115,7 +118,8 @@ def build(jobs=None, verbose=False, programs=True):
     gemm = [s for s in GEMM_SOURCES if os.path.exists(os.path.join(ROOT, s))]
     progs = {k: v for k, v in PROGRAMS.items()
              if programs and all(os.path.exists(os.path.join(ROOT, s)) for s in v)}
-    every = sources + gemm + [s for v in progs.values() for s in v]
+    plugin = [s for s in NCCL_PLUGIN_SOURCES if os.path.exists(os.path.join(ROOT, s))]
+    every = sources + gemm + plugin + [s for v in progs.values() for s in v]
     errors = []
     with cf.ThreadPoolExecutor(max_workers=jobs) as ex:
         for obj, err in ex.map(lambda s: _compile(s, hdr, verbose), every):
@@ -137,6 +141,13 @@ def build(jobs=None, verbose=False, programs=True):
         gobjs = [_obj_path(s) for s in gemm]
         if newer(gemm_lib, gobjs):
             _link([NVCC] + ARCH + ["-shared", "-o", gemm_lib] + gobjs + ["-lpthread", "-ldl", "-lrt"], verbose)
+    if plugin:
+        # NCCL looks for libnccl-net-<NCCL_NET_PLUGIN>.so on the library path.
+        plugin_lib = os.path.join(LIB, "libnccl-net-switchml.so")
+        pobjs = [_obj_path(s) for s in plugin]
+        if newer(plugin_lib, pobjs + [main_lib]):
+            _link(["g++", "-shared", "-o", plugin_lib] + pobjs +
+                  ["-L" + LIB, "-lswitchml_b200", "-Wl,-rpath,$ORIGIN", "-lpthread"], verbose)
     for name, srcs in progs.items():
         exe = os.path.join(BIN, name)
         pobjs = [_obj_path(s) for s in srcs]

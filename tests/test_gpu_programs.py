@@ -50,3 +50,14 @@ def test_dnn_benchmark_on_gpu(cuda_cfg):
                 os.path.join(PKG, "benchmarks", "models", "example.csv"), "--num-iters", "5",
                 "--num-warmup-iters", "2", "--verify", "true"], cuda_cfg)
     assert "Results verified successfully." in out and "Iterations/s" in out
+
+
+def test_nccl_collnet_plugin_on_gpu(cuda_cfg):
+    """The collective-network plugin with device pointers (NCCL_PTR_CUDA), driven by its harness."""
+    exe, plugin = os.path.join(BIN, "collnet_harness"), os.path.join(PKG, "lib", "libnccl-net-switchml.so")
+    if not (os.path.exists(exe) and os.path.exists(plugin)):
+        pytest.skip("plugin not built")
+    out = _run([exe, "--plugin", plugin, "--device", "gpu", "--numel", "300000", "--rounds", "2"], cuda_cfg)
+    assert "ptrSupport 0x3" in out and "collnet harness ok" in out and "on the gpu" in out
+    out = _run([exe, "--plugin", plugin, "--device", "cpu", "--numel", "5000", "--rounds", "1"], cuda_cfg)
+    assert "collnet harness ok" in out
