@@ -3,6 +3,7 @@
 
 #include <arpa/inet.h>
 
+#include <cstddef>
 #include <cstring>
 #include <sstream>
 
@@ -24,6 +25,8 @@ void SoftSwitch::Reset(uint64_t session_id, int num_workers, int packet_numel) {
   registered_ = 0;
   counters_ = SwitchCounters();
   for (WorkerCounters& w : worker_counters_) w = WorkerCounters();
+  for (auto& row : endpoint_counters_)
+    for (EndpointCounters& e : row) e = EndpointCounters();
 }
 
 bool SoftSwitch::AddWorker(int rank) {
@@ -55,7 +58,13 @@ void SoftSwitch::Emit(const SlotSet& s, uint16_t pool_index, int dest_worker, in
                       uint8_t type, std::vector<SwitchOutput>* out) {
   if (Roll(drop_egress_)) {
     counters_.egress_dropped++;
+    worker_counters_[dest_worker].egress_dropped++;
     return;
+  }
+  if (dest_thread < kMaxThreads) {
+    EndpointCounters& e = endpoint_counters_[dest_worker][dest_thread];
+    if (type == WIRE_RESULT_RETX) e.retransmitted_results++;
+    else e.results++;
   }
   SwitchOutput o;
   o.dest_worker = dest_worker;
@@ -91,6 +100,10 @@ void SoftSwitch::Process(const uint8_t* data, size_t len, std::vector<SwitchOutp
   uint16_t numel = ntohs(h.numel);
   int worker = ntohs(h.worker_id);
   uint16_t pool_index = ntohs(h.pool_index);
+  if (ntohl(h.magic) == kWireMagic && (h.type == WIRE_ECHO_REQUEST || h.type == WIRE_FORWARD)) {
+    ProcessOther(h, data, len, out);
+    return;
+  }
   if (ntohl(h.magic) != kWireMagic || h.type != WIRE_DATA || numel > kMaxPacketNumel ||
       len != sizeof(h) + numel * 4u || worker >= num_workers_ || worker >= kMaxWorkers ||
       !(registered_ & (1u << worker)) || ntohs(h.session_lo) != static_cast<uint16_t>(session_id_) ||
@@ -100,7 +113,13 @@ void SoftSwitch::Process(const uint8_t* data, size_t len, std::vector<SwitchOutp
   }
   worker_counters_[worker].rx_packets++;
   worker_counters_[worker].rx_bytes += len;
-  if (Roll(drop_ingress_)) { counters_.ingress_dropped++; return; }
+  if (Roll(drop_ingress_)) {
+    counters_.ingress_dropped++;
+    worker_counters_[worker].ingress_dropped++;
+    return;
+  }
+  EndpointCounters* ep = h.thread_id < kMaxThreads ? &endpoint_counters_[worker][h.thread_id] : nullptr;
+  if (ep) ep->rx_packets++;
 
   int k = (pool_index & kSetBit) ? 1 : 0;
   uint32_t slot = pool_index & ~kSetBit;
@@ -114,6 +133,7 @@ void SoftSwitch::Process(const uint8_t* data, size_t len, std::vector<SwitchOutp
   other.bitmap &= ~bit;
 
   if (seen) {
+    if (ep) ep->out_of_order++;
     // A retransmission. If the slot is finished the worker lost the result: send it again
     // from the retained copy, to that worker only. Otherwise the first copy was already
     // absorbed and the aggregate is still waiting for others: nothing to do.
@@ -162,6 +182,57 @@ void SoftSwitch::Process(const uint8_t* data, size_t len, std::vector<SwitchOutp
   }
 }
 
+void SoftSwitch::ProcessOther(const WireHeader& h, const uint8_t* data, size_t len,
+                              std::vector<SwitchOutput>* out) {
+  int worker = ntohs(h.worker_id);
+  if (worker >= kMaxWorkers || h.thread_id >= kMaxThreads || len > static_cast<size_t>(kWireMaxBytes)) {
+    counters_.malformed++;
+    return;
+  }
+  if (h.type == WIRE_ECHO_REQUEST) {
+    // Answered for anyone who asks, registered or not, like a ping to the switch's address.
+    SwitchOutput o;
+    o.dest_worker = worker;
+    o.dest_thread = h.thread_id;
+    o.bytes.assign(data, data + len);
+    o.bytes[offsetof(WireHeader, type)] = WIRE_ECHO_REPLY;
+    o.to_sender = true;
+    counters_.echo_replies++;
+    out->push_back(std::move(o));
+    return;
+  }
+  // WIRE_FORWARD: only between registered workers of the current session.
+  uint16_t dest = ntohs(h.pool_index);
+  int dest_worker = dest >> 8, dest_thread = dest & 0xff;
+  if (worker >= num_workers_ || !(registered_ & (1u << worker)) ||
+      ntohs(h.session_lo) != static_cast<uint16_t>(session_id_) || dest_thread >= kMaxThreads) {
+    counters_.malformed++;
+    return;
+  }
+  if (dest_worker == kFloodWorker) {
+    counters_.flooded++;
+    for (int w = 0; w < num_workers_; w++) {
+      if (w == worker || !(registered_ & (1u << w))) continue;
+      SwitchOutput o;
+      o.dest_worker = w;
+      o.dest_thread = dest_thread;
+      o.bytes.assign(data, data + len);
+      out->push_back(std::move(o));
+    }
+    return;
+  }
+  if (dest_worker >= num_workers_ || !(registered_ & (1u << dest_worker))) {
+    counters_.malformed++;
+    return;
+  }
+  counters_.forwarded++;
+  SwitchOutput o;
+  o.dest_worker = dest_worker;
+  o.dest_thread = dest_thread;
+  o.bytes.assign(data, data + len);
+  out->push_back(std::move(o));
+}
+
 SwitchCounters SoftSwitch::counters() const {
   std::lock_guard<std::mutex> lk(mu_);
   return counters_;
@@ -170,6 +241,12 @@ SwitchCounters SoftSwitch::counters() const {
 WorkerCounters SoftSwitch::worker_counters(int rank) const {
   std::lock_guard<std::mutex> lk(mu_);
   return worker_counters_[rank];
+}
+
+EndpointCounters SoftSwitch::endpoint_counters(int rank, int thread) const {
+  std::lock_guard<std::mutex> lk(mu_);
+  if (rank < 0 || rank >= kMaxWorkers || thread < 0 || thread >= kMaxThreads) return EndpointCounters();
+  return endpoint_counters_[rank][thread];
 }
 
 uint32_t SoftSwitch::Bitmap(uint32_t slot, int set) const {
@@ -196,7 +273,35 @@ std::string SoftSwitch::DescribeStatistics() const {
   o << "broadcast " << counters_.broadcast << "\nretransmit " << counters_.retransmit
     << "\nconsumed " << counters_.consumed << "\nignored " << counters_.ignored
     << "\ningress_dropped " << counters_.ingress_dropped << "\negress_dropped "
-    << counters_.egress_dropped << "\nmalformed " << counters_.malformed << "\n";
+    << counters_.egress_dropped << "\nmalformed " << counters_.malformed << "\necho_replies "
+    << counters_.echo_replies << "\nforwarded " << counters_.forwarded << "\nflooded "
+    << counters_.flooded << "\n";
+  return o.str();
+}
+
+std::string SoftSwitch::DescribeDropped() const {
+  std::lock_guard<std::mutex> lk(mu_);
+  std::ostringstream o;
+  o << " rank  ingress_dropped  egress_dropped\n";
+  for (int w = 0; w < num_workers_; w++)
+    o << " " << w << "  " << worker_counters_[w].ingress_dropped << "  " << worker_counters_[w].egress_dropped
+      << "\n";
+  o << " total  " << counters_.ingress_dropped << "  " << counters_.egress_dropped << "\n";
+  return o.str();
+}
+
+std::string SoftSwitch::DescribeEndpoints() const {
+  std::lock_guard<std::mutex> lk(mu_);
+  std::ostringstream o;
+  o << " rank  thread  rx_pkts  out_of_order  results  retransmitted_results\n";
+  for (int w = 0; w < num_workers_; w++) {
+    for (int t = 0; t < kMaxThreads; t++) {
+      const EndpointCounters& e = endpoint_counters_[w][t];
+      if (e.rx_packets == 0 && e.results == 0 && e.retransmitted_results == 0) continue;
+      o << " " << w << "  " << t << "  " << e.rx_packets << "  " << e.out_of_order << "  " << e.results << "  "
+        << e.retransmitted_results << "\n";
+    }
+  }
   return o.str();
 }
 

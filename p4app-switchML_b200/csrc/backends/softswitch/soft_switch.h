@@ -27,16 +27,29 @@ struct SwitchOutput {
   int dest_worker;
   int dest_thread;
   std::vector<uint8_t> bytes;  // WireHeader + payload
+  bool to_sender = false;      // send to the address the input came from (echo replies)
 };
 
 struct SwitchCounters {
   // per slot and set, like the counters behind the reference CLI's show_statistics
   uint64_t broadcast = 0, retransmit = 0, consumed = 0, ignored = 0;
   uint64_t ingress_dropped = 0, egress_dropped = 0, malformed = 0;
+  uint64_t echo_replies = 0, forwarded = 0, flooded = 0;
 };
 
 struct WorkerCounters {
   uint64_t rx_packets = 0, rx_bytes = 0, tx_packets = 0, tx_bytes = 0;
+  // packets of this worker lost to the drop simulator (reference: per-queue-pair dropped
+  // counter of p4/drop_simulator.p4, shown by the CLI's show_dropped_packets)
+  uint64_t ingress_dropped = 0, egress_dropped = 0;
+};
+
+// Per (worker, worker thread): the counterpart of the reference's per-queue-pair counters
+// (controller/rdma_receiver.py:199-286: packets, messages, sequence violations). A thread's
+// endpoint plays the role of a queue pair; a packet for a slot use that was already absorbed
+// or finished is what a sequence violation is there: a packet outside the expected order.
+struct EndpointCounters {
+  uint64_t rx_packets = 0, out_of_order = 0, results = 0, retransmitted_results = 0;
 };
 
 class SoftSwitch {
@@ -61,10 +74,13 @@ class SoftSwitch {
 
   SwitchCounters counters() const;
   WorkerCounters worker_counters(int rank) const;
+  EndpointCounters endpoint_counters(int rank, int thread) const;
   uint32_t Bitmap(uint32_t slot, int set) const;
   // Human-readable tables for the CLI.
   std::string DescribeWorkers() const;
   std::string DescribeStatistics() const;
+  std::string DescribeDropped() const;
+  std::string DescribeEndpoints() const;
 
  private:
   struct SlotSet {
@@ -81,6 +97,8 @@ class SoftSwitch {
   void Emit(const SlotSet& s, uint16_t pool_index, int dest_worker, int dest_thread, uint8_t type,
             std::vector<SwitchOutput>* out);
   bool Roll(double p);
+  // Echo and forwarding: everything that is not aggregation traffic.
+  void ProcessOther(const WireHeader& h, const uint8_t* data, size_t len, std::vector<SwitchOutput>* out);
 
   mutable std::mutex mu_;
   uint32_t num_slots_;
@@ -93,6 +111,7 @@ class SoftSwitch {
   std::mt19937_64 rng_;
   SwitchCounters counters_;
   WorkerCounters worker_counters_[kMaxWorkers];
+  EndpointCounters endpoint_counters_[kMaxWorkers][kMaxThreads];
 };
 
 }  // namespace switchml

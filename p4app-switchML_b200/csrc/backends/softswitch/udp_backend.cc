@@ -138,6 +138,35 @@ class UdpTransport : public SlotTransport {
 
 }  // namespace
 
+bool EchoSwitch(int fd, uint16_t worker, uint8_t thread, uint64_t session, int timeout_ms) {
+  uint8_t pkt[sizeof(WireHeader) + 8];
+  WireHeader h;
+  memset(&h, 0, sizeof(h));
+  h.magic = htonl(kWireMagic);
+  h.type = WIRE_ECHO_REQUEST;
+  h.worker_id = htons(worker);
+  h.thread_id = thread;
+  h.session_lo = htons(static_cast<uint16_t>(session));
+  const uint64_t cookie = session ^ (static_cast<uint64_t>(worker) << 48) ^ (static_cast<uint64_t>(thread) << 40);
+  h.pkt_id = htonl(static_cast<uint32_t>(cookie));
+  memcpy(pkt, &h, sizeof(h));
+  memcpy(pkt + sizeof(h), &cookie, 8);
+  auto deadline = std::chrono::steady_clock::now() + std::chrono::milliseconds(timeout_ms);
+  while (std::chrono::steady_clock::now() < deadline) {
+    if (send(fd, pkt, sizeof(pkt), 0) < 0 && errno != ECONNREFUSED) return false;
+    struct pollfd p = {fd, POLLIN, 0};
+    if (poll(&p, 1, 100) <= 0) continue;
+    uint8_t in[kWireMaxBytes];
+    ssize_t n = recv(fd, in, sizeof(in), MSG_DONTWAIT);
+    if (n != static_cast<ssize_t>(sizeof(pkt))) continue;  // ECONNREFUSED or something else: ask again
+    WireHeader r;
+    memcpy(&r, in, sizeof(r));
+    if (ntohl(r.magic) == kWireMagic && r.type == WIRE_ECHO_REPLY && memcmp(in + sizeof(r), &cookie, 8) == 0)
+      return true;
+  }
+  return false;
+}
+
 UdpBackend::UdpBackend(Context& context, Config& config) : Backend(context, config) {}
 UdpBackend::~UdpBackend() { CleanupWorker(); }
 
@@ -195,6 +224,14 @@ void UdpBackend::SetupWorker() {
   for (int fd : fds_) {
     SML_CHECK(connect(fd, reinterpret_cast<sockaddr*>(&sw), sizeof(sw)) == 0)
         << "connect to switch: " << strerror(errno);
+  }
+  // Make sure the data plane answers before any job depends on it: one echo request per
+  // socket (the switch answers these itself, like the reference switch answers ARP and
+  // ping for its own address, p4/arp_icmp_responder.p4:40-84). The drop simulator does not
+  // touch echo traffic, so a missing answer means a wrong address or a closed port.
+  for (int t = 0; t < g.num_worker_threads; t++) {
+    SML_CHECK(EchoSwitch(fds_[t], static_cast<uint16_t>(g.rank), static_cast<uint8_t>(t), session_id_, 2000))
+        << "the software switch does not answer on UDP " << u.switch_ip_str << ":" << switch_udp_port_;
   }
   SML_CHECK(client_.Barrier(g.num_workers)) << "barrier failed";
 

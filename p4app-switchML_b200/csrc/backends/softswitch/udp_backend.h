@@ -20,6 +20,10 @@
 
 namespace switchml {
 
+// Sends echo requests from the connected socket `fd` until the software switch sends one
+// back or `timeout_ms` passes. True if the data plane answered.
+bool EchoSwitch(int fd, uint16_t worker, uint8_t thread, uint64_t session, int timeout_ms);
+
 class UdpBackend : public Backend {
  public:
   UdpBackend(Context& context, Config& config);

@@ -16,11 +16,20 @@ static const uint32_t kWireMagic = 0x534d4c31;  // "SML1"
 static const uint16_t kSetBit = 0x8000;         // pool_index MSB selects the slot set
 static const int kMaxPacketNumel = 256;         // 1024-byte payload, the largest SwitchML packet
 static const int kMaxWorkers = 32;              // width of the per-slot worker bitmap
+static const int kMaxThreads = 64;              // worker threads (return ports) per worker
+static const uint8_t kFloodWorker = 0xff;       // WIRE_FORWARD destination: every other worker
 
 enum WireType : uint8_t {
   WIRE_DATA = 0,        // worker -> switch
   WIRE_RESULT = 1,      // switch -> every worker (multicast of a completed slot)
-  WIRE_RESULT_RETX = 2  // switch -> one worker (answer to a retransmission)
+  WIRE_RESULT_RETX = 2, // switch -> one worker (answer to a retransmission)
+  // Traffic that is not aggregation (the reference switch answers ARP and ICMP echo for its
+  // own address, p4/arp_icmp_responder.p4:40-84, and forwards everything else by destination
+  // or floods it, p4/forwarder.p4:31-64):
+  WIRE_ECHO_REQUEST = 3,  // anyone -> switch: "are you there"; payload comes back unchanged
+  WIRE_ECHO_REPLY = 4,    // switch -> the sender of the request
+  WIRE_FORWARD = 5        // worker -> worker through the switch; pool_index = dest worker << 8 |
+                          // dest thread, dest worker kFloodWorker = all other workers
 };
 
 #pragma pack(push, 1)

@@ -83,6 +83,32 @@ bool ReadLine(int fd, std::string* buf, std::string* line, const std::atomic<boo
 }  // namespace
 
 ControlServer::ControlServer() { memset(learned_, 0, sizeof(learned_)); }
+
+// A bound, non-connected UDP socket with large buffers, or -1 with the reason in *err.
+static int BindUdp(const std::string& ip, unsigned port, uint16_t* bound, std::string* err) {
+  int fd = socket(AF_INET, SOCK_DGRAM, 0);
+  if (fd < 0) {
+    *err = strerror(errno);
+    return -1;
+  }
+  sockaddr_in u;
+  memset(&u, 0, sizeof(u));
+  u.sin_family = AF_INET;
+  u.sin_port = htons(static_cast<uint16_t>(port));
+  if (inet_pton(AF_INET, ip.c_str(), &u.sin_addr) != 1) u.sin_addr.s_addr = htonl(INADDR_ANY);
+  int big = 8 << 20;
+  setsockopt(fd, SOL_SOCKET, SO_RCVBUF, &big, sizeof(big));
+  setsockopt(fd, SOL_SOCKET, SO_SNDBUF, &big, sizeof(big));
+  if (bind(fd, reinterpret_cast<sockaddr*>(&u), sizeof(u)) != 0) {
+    *err = strerror(errno);
+    close(fd);
+    return -1;
+  }
+  socklen_t al = sizeof(u);
+  getsockname(fd, reinterpret_cast<sockaddr*>(&u), &al);
+  *bound = ntohs(u.sin_port);
+  return fd;
+}
 ControlServer::~ControlServer() { Stop(); }
 
 bool ControlServer::Start(const std::string& ip, uint16_t port, uint16_t udp_port) {
@@ -107,28 +133,19 @@ bool ControlServer::Start(const std::string& ip, uint16_t port, uint16_t udp_por
   getsockname(listen_fd_, reinterpret_cast<sockaddr*>(&a), &al);
   port_ = ntohs(a.sin_port);
 
+  ip_ = ip;
   if (udp_port) {
-    udp_fd_ = socket(AF_INET, SOCK_DGRAM, 0);
-    sockaddr_in u;
-    memset(&u, 0, sizeof(u));
-    u.sin_family = AF_INET;
-    u.sin_port = htons(udp_port);
-    if (inet_pton(AF_INET, ip.c_str(), &u.sin_addr) != 1) u.sin_addr.s_addr = htonl(INADDR_ANY);
-    int big = 8 << 20;
-    setsockopt(udp_fd_, SOL_SOCKET, SO_RCVBUF, &big, sizeof(big));
-    setsockopt(udp_fd_, SOL_SOCKET, SO_SNDBUF, &big, sizeof(big));
-    if (udp_fd_ < 0 || bind(udp_fd_, reinterpret_cast<sockaddr*>(&u), sizeof(u)) != 0) {
-      SML_LOG(ERROR) << "software switch: cannot bind UDP port " << udp_port << ": "
-                     << strerror(errno);
-      if (udp_fd_ >= 0) close(udp_fd_);
-      udp_fd_ = -1;
+    uint16_t bound = 0;
+    std::string err;
+    int fd = BindUdp(ip, udp_port, &bound, &err);
+    if (fd < 0) {
+      SML_LOG(ERROR) << "software switch: cannot bind UDP port " << udp_port << ": " << err;
       close(listen_fd_);
       listen_fd_ = -1;
       return false;
     }
-    al = sizeof(u);
-    getsockname(udp_fd_, reinterpret_cast<sockaddr*>(&u), &al);
-    udp_port_ = ntohs(u.sin_port);
+    udp_fd_ = fd;
+    udp_port_ = bound;
     data_thread_ = std::thread(&ControlServer::DataPlaneLoop, this);
   }
   stopping_ = false;
@@ -168,7 +185,10 @@ void ControlServer::Stop() {
   for (auto& t : threads) t.join();
   if (listen_fd_ >= 0) close(listen_fd_);
   if (udp_fd_ >= 0) close(udp_fd_);
-  listen_fd_ = udp_fd_ = -1;
+  int pend = pending_udp_fd_.exchange(-1);
+  if (pend >= 0) close(pend);
+  listen_fd_ = -1;
+  udp_fd_ = -1;
 }
 
 void ControlServer::AcceptLoop() {
@@ -232,7 +252,71 @@ bool ControlServer::Collect(const std::string& name, int n, int rank, const std:
   return true;
 }
 
+std::string ControlServer::RebindDataPlane(const std::string& ip, unsigned port) {
+  if (udp_fd_ < 0) return "ERR no software switch in this server";
+  uint16_t bound = 0;
+  std::string err;
+  int fd = BindUdp(ip, port, &bound, &err);
+  if (fd < 0) return "ERR cannot bind " + ip + ":" + std::to_string(port) + ": " + err;
+  int previous = pending_udp_fd_.exchange(fd);
+  if (previous >= 0) close(previous);
+  // The data-plane thread adopts the socket between two bursts (it polls with 100 ms).
+  for (int i = 0; i < 200 && pending_udp_fd_.load() == fd && !stopping_; i++) usleep(5 * 1000);
+  if (pending_udp_fd_.load() == fd) return "ERR the data plane did not pick up the new socket";
+  {
+    std::lock_guard<std::mutex> lk(learned_mu_);
+    ip_ = ip;
+  }
+  udp_port_ = bound;
+  return "OK " + std::to_string(bound);
+}
+
+static std::string AddrText(const sockaddr_in& a) {
+  char ip[INET_ADDRSTRLEN] = "?";
+  inet_ntop(AF_INET, &a.sin_addr, ip, sizeof(ip));
+  return std::string(ip) + ":" + std::to_string(ntohs(a.sin_port));
+}
+
+std::string ControlServer::DescribePorts() {
+  // The "front panel" of the software switch: its control socket, its data-plane socket and
+  // one virtual port per worker (the set of that worker's learned return addresses).
+  std::ostringstream o;
+  std::string ip;
+  {
+    std::lock_guard<std::mutex> lk(learned_mu_);
+    ip = ip_;
+  }
+  o << " port  address  state  rx_pkts  rx_bytes  tx_pkts  tx_bytes\n";
+  o << " control  " << ip << ":" << port_ << "/tcp  " << (listen_fd_ >= 0 ? "up" : "closed") << "  "
+    << ctl_requests_.load() << "  -  -  -\n";
+  o << " data  " << ip << ":" << udp_port_.load() << "/udp  " << (udp_fd_ >= 0 ? "up" : "absent") << "  "
+    << udp_rx_packets_.load() << "  " << udp_rx_bytes_.load() << "  " << udp_tx_packets_.load() << "  "
+    << udp_tx_bytes_.load() << "\n";
+  for (int w = 0; w < switch_.num_workers(); w++) {
+    int endpoints = 0;
+    {
+      std::lock_guard<std::mutex> lk(learned_mu_);
+      for (int t = 0; t < kMaxThreads; t++) endpoints += learned_[w][t].sin_port != 0;
+    }
+    WorkerCounters c = switch_.worker_counters(w);
+    o << " worker" << w << "  " << endpoints << " endpoint(s)  " << (endpoints ? "up" : "down") << "  "
+      << c.rx_packets << "  " << c.rx_bytes << "  " << c.tx_packets << "  " << c.tx_bytes << "\n";
+  }
+  return o.str();
+}
+
+std::string ControlServer::DescribeForwarding() {
+  std::ostringstream o;
+  o << " rank  thread  address\n";
+  std::lock_guard<std::mutex> lk(learned_mu_);
+  for (int w = 0; w < kMaxWorkers; w++)
+    for (int t = 0; t < kMaxThreads; t++)
+      if (learned_[w][t].sin_port != 0) o << " " << w << "  " << t << "  " << AddrText(learned_[w][t]) << "\n";
+  return o.str();
+}
+
 std::string ControlServer::Handle(const std::string& line) {
+  ctl_requests_++;
   std::istringstream in(line);
   std::string cmd;
   in >> cmd;
@@ -310,12 +394,31 @@ std::string ControlServer::Handle(const std::string& line) {
       in >> slot;
       text = "slot " + std::to_string(slot) + " set0 " + std::to_string(switch_.Bitmap(slot, 0)) +
              " set1 " + std::to_string(switch_.Bitmap(slot, 1)) + "\n";
+    } else if (what == "dropped") text = switch_.DescribeDropped();
+    else if (what == "qp") text = switch_.DescribeEndpoints();
+    else if (what == "ports") text = DescribePorts();
+    else if (what == "forwarding") text = DescribeForwarding();
+    else if (what == "address") {
+      std::string ip;
+      {
+        std::lock_guard<std::mutex> lk(learned_mu_);
+        ip = ip_;
+      }
+      text = "ip " + ip + " control_port " + std::to_string(port_) + " udp_port " +
+             std::to_string(udp_port_.load()) + "\n";
     } else return "ERR unknown table";
     return "OK " + HexEncode(text);
   }
   if (cmd == "SET") {
     std::string what;
     in >> what;
+    if (what == "address") {
+      std::string ip;
+      unsigned port = 0;
+      in >> ip >> port;
+      if (ip.empty() || port > 65535) return "ERR usage: SET address <ip> <udp port>";
+      return RebindDataPlane(ip, port);
+    }
     if (what != "drop") return "ERR unknown setting";
     double i = 0, e = 0;
     uint64_t seed = 0;
@@ -325,6 +428,8 @@ std::string ControlServer::Handle(const std::string& line) {
   }
   if (cmd == "RESET") {
     switch_.Reset(0, 0, 0);
+    std::lock_guard<std::mutex> lk(learned_mu_);
+    memset(learned_, 0, sizeof(learned_));
     return "OK";
   }
   if (cmd == "PING") return "OK";
@@ -335,31 +440,49 @@ void ControlServer::DataPlaneLoop() {
   std::vector<uint8_t> buf(kWireMaxBytes + 64);
   std::vector<SwitchOutput> out;
   while (!stopping_) {
-    struct pollfd p = {udp_fd_, POLLIN, 0};
+    int pend = pending_udp_fd_.exchange(-1);
+    if (pend >= 0) {
+      // "SET address": move the data plane to the new socket. Workers learn the port when
+      // they open a session, so sessions that are running keep talking to a closed port
+      // and must be restarted, as after a change of the reference switch's address.
+      close(udp_fd_);
+      udp_fd_ = pend;
+    }
+    const int fd = udp_fd_;
+    struct pollfd p = {fd, POLLIN, 0};
     int r = poll(&p, 1, 100);
     if (r <= 0) continue;
     for (int burst = 0; burst < 64; burst++) {
       sockaddr_in src;
       socklen_t sl = sizeof(src);
-      ssize_t n = recvfrom(udp_fd_, buf.data(), buf.size(), MSG_DONTWAIT,
-                           reinterpret_cast<sockaddr*>(&src), &sl);
+      ssize_t n = recvfrom(fd, buf.data(), buf.size(), MSG_DONTWAIT, reinterpret_cast<sockaddr*>(&src), &sl);
       if (n <= 0) break;
+      udp_rx_packets_++;
+      udp_rx_bytes_ += static_cast<uint64_t>(n);
       if (static_cast<size_t>(n) >= sizeof(WireHeader)) {
-        // Learn where this worker thread listens, like a switch learns a port.
+        // Learn where this worker thread listens, like a switch learns a port. Echo
+        // requests may come from anybody and teach nothing.
         WireHeader h;
         memcpy(&h, buf.data(), sizeof(h));
         int w = ntohs(h.worker_id);
-        if (ntohl(h.magic) == kWireMagic && w < kMaxWorkers && h.thread_id < kMaxThreads) {
+        if (ntohl(h.magic) == kWireMagic && h.type != WIRE_ECHO_REQUEST && w < kMaxWorkers &&
+            h.thread_id < kMaxThreads) {
+          std::lock_guard<std::mutex> lk(learned_mu_);
           learned_[w][h.thread_id] = src;
         }
       }
       out.clear();
       switch_.Process(buf.data(), static_cast<size_t>(n), &out);
       for (const SwitchOutput& o : out) {
-        const sockaddr_in& d = learned_[o.dest_worker][o.dest_thread];
+        sockaddr_in d = src;
+        if (!o.to_sender) {
+          std::lock_guard<std::mutex> lk(learned_mu_);
+          d = learned_[o.dest_worker][o.dest_thread];
+        }
         if (d.sin_port == 0) continue;
-        sendto(udp_fd_, o.bytes.data(), o.bytes.size(), 0,
-               reinterpret_cast<const sockaddr*>(&d), sizeof(d));
+        sendto(fd, o.bytes.data(), o.bytes.size(), 0, reinterpret_cast<const sockaddr*>(&d), sizeof(d));
+        udp_tx_packets_++;
+        udp_tx_bytes_ += o.bytes.size();
       }
     }
   }

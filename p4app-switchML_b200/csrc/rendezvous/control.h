@@ -70,10 +70,10 @@ class ControlServer {
   bool Collect(const std::string& name, int n, int rank, const std::string& token,
                std::vector<std::string>* all);
 
-  int listen_fd_ = -1;
-  int udp_fd_ = -1;
+  std::atomic<int> listen_fd_{-1};
+  std::atomic<int> udp_fd_{-1};
   uint16_t port_ = 0;
-  uint16_t udp_port_ = 0;
+  std::atomic<uint16_t> udp_port_{0};
   std::atomic<bool> stopping_{false};
   std::atomic<bool> accepting_{false};
   std::thread accept_thread_;
@@ -86,8 +86,20 @@ class ControlServer {
   SoftSwitch switch_;
   // Return address of each worker thread, learned from its data packets (only the
   // data-plane thread touches this).
-  static const int kMaxThreads = 64;
+  // The forwarding table: return address of each worker thread, learned from its data
+  // packets like a switch learns a port. Written by the data-plane thread, read by the
+  // console commands.
+  std::mutex learned_mu_;
   sockaddr_in learned_[kMaxWorkers][kMaxThreads];
+  // Per data-plane socket ("port"): totals for the console's show_ports.
+  std::atomic<uint64_t> udp_rx_packets_{0}, udp_rx_bytes_{0}, udp_tx_packets_{0}, udp_tx_bytes_{0};
+  std::atomic<uint64_t> ctl_requests_{0};
+  std::string ip_;
+  // A data-plane socket bound by "SET address", waiting to be adopted by the data-plane thread.
+  std::atomic<int> pending_udp_fd_{-1};
+  std::string RebindDataPlane(const std::string& ip, unsigned port);
+  std::string DescribePorts();
+  std::string DescribeForwarding();
 };
 
 class ControlClient {

@@ -5,6 +5,7 @@
 #include <atomic>
 #include <cmath>
 #include <cstdio>
+#include <cstddef>
 #include <cstring>
 #include <thread>
 #include <vector>
@@ -218,6 +219,50 @@ static void TestSoftSwitch() {
   send(1, 9, 1, 0, {1, 1, 1, 1});
   send(2, 9, 1, 0, {1, 1, 1, 1});
   EXPECT(out.empty() && sw.counters().egress_dropped == 3);
+  // The drops are also counted per worker, the traffic per worker thread.
+  EXPECT(sw.worker_counters(0).ingress_dropped == 1 && sw.worker_counters(1).ingress_dropped == 0);
+  EXPECT(sw.worker_counters(0).egress_dropped + sw.worker_counters(1).egress_dropped +
+         sw.worker_counters(2).egress_dropped == 3);
+  EXPECT(sw.endpoint_counters(1, 0).out_of_order == 1);          // its retransmission above
+  EXPECT(sw.endpoint_counters(1, 0).retransmitted_results == 1);
+  EXPECT(sw.endpoint_counters(0, 0).out_of_order == 1);          // the duplicate while the slot was open
+  EXPECT(sw.endpoint_counters(2, 0).results == 3 && sw.endpoint_counters(2, 0).out_of_order == 0);
+  EXPECT(sw.DescribeDropped().find(" total  1  3") != std::string::npos);
+  EXPECT(sw.DescribeEndpoints().find(" 1  0  ") != std::string::npos);
+  // Echo: answered to the sender whoever it is, payload unchanged; the drop simulator does
+  // not apply.
+  sw.SetDropProbabilities(1.0, 1.0, 1);
+  out.clear();
+  auto echo = MakePacket(17, 0, 77, 0, {123, 456}, 9999);
+  echo[offsetof(WireHeader, type)] = WIRE_ECHO_REQUEST;
+  sw.Process(echo.data(), echo.size(), &out);
+  EXPECT(out.size() == 1 && out[0].to_sender && out[0].bytes.size() == echo.size());
+  if (!out.empty()) {
+    EXPECT(out[0].bytes[offsetof(WireHeader, type)] == WIRE_ECHO_REPLY && PayloadAt(out[0], 1) == 456);
+  }
+  EXPECT(sw.counters().echo_replies == 1);
+  // Forwarding between registered workers: unicast by (worker, thread), flood to all others.
+  out.clear();
+  auto fwd = MakePacket(0, static_cast<uint16_t>(2 << 8 | 3), 5, 0, {42}, 42);
+  fwd[offsetof(WireHeader, type)] = WIRE_FORWARD;
+  sw.Process(fwd.data(), fwd.size(), &out);
+  EXPECT(out.size() == 1 && out[0].dest_worker == 2 && out[0].dest_thread == 3 && !out[0].to_sender);
+  EXPECT(!out.empty() && PayloadAt(out[0], 0) == 42);
+  out.clear();
+  fwd = MakePacket(1, static_cast<uint16_t>(kFloodWorker << 8 | 0), 5, 0, {43}, 42);
+  fwd[offsetof(WireHeader, type)] = WIRE_FORWARD;
+  sw.Process(fwd.data(), fwd.size(), &out);
+  EXPECT(out.size() == 2 && out[0].dest_worker == 0 && out[1].dest_worker == 2);
+  out.clear();
+  uint64_t malformed = sw.counters().malformed;
+  fwd = MakePacket(0, static_cast<uint16_t>(7 << 8), 5, 0, {44}, 42);  // worker 7 does not exist
+  fwd[offsetof(WireHeader, type)] = WIRE_FORWARD;
+  sw.Process(fwd.data(), fwd.size(), &out);
+  fwd = MakePacket(0, static_cast<uint16_t>(1 << 8), 5, 0, {44}, 41);  // another session
+  fwd[offsetof(WireHeader, type)] = WIRE_FORWARD;
+  sw.Process(fwd.data(), fwd.size(), &out);
+  EXPECT(out.empty() && sw.counters().malformed == malformed + 2);
+  EXPECT(sw.counters().forwarded == 1 && sw.counters().flooded == 1);
   // Single worker: every packet completes its slot at once.
   sw.SetDropProbabilities(0, 0);
   sw.Reset(1, 1, 4);

@@ -10,9 +10,11 @@ shell for the controller that rank 0 hosts in-process (or ``bin/switchml_switchd
     (switchml) set_drop_probabilities 0.01 0.01
     (switchml) show_statistics
 
-Commands that only make sense for front-panel ports of a hardware switch (show_ports,
-forwarding table, ARP/ICMP responder) have no counterpart: an NVSwitch box has no
-Ethernet data plane to configure.
+Every command of the reference shell has a counterpart. The "ports" of the software switch
+are its two sockets and one virtual port per worker; its forwarding table is the set of
+return addresses it learned from the workers' packets; a worker thread's endpoint takes the
+place of a queue pair. GPU workers (backend = cuda) meet through the same controller but
+move their data over NVLink, so the data-plane tables stay empty for them.
 """
 import argparse
 import cmd
@@ -56,6 +58,38 @@ class Cli(cmd.Cmd):
         self._send("SHOW workers")
 
     do_show_udp_workers = do_show_workers
+
+    def do_show_rdma_workers(self, arg):
+        "Workers of the current session (this switch has one kind of worker; same table as show_udp_workers)."
+        self._send("SHOW workers")
+
+    def do_show_ports(self, arg):
+        "Sockets of the switch and one virtual port per worker, with state and packet/byte counters."
+        self._send("SHOW ports")
+
+    def do_show_forwarding_table(self, arg):
+        "Where results for each (worker, thread) are sent: addresses learned from the workers' packets."
+        self._send("SHOW forwarding")
+
+    def do_show_switch_address(self, arg):
+        "Address of the controller and UDP port of the data plane."
+        self._send("SHOW address")
+
+    def do_set_switch_address(self, arg):
+        "set_switch_address <ip> <udp port>: move the data plane; sessions started afterwards use it."
+        parts = arg.split()
+        if len(parts) != 2:
+            self.stdout.write("usage: set_switch_address <ip> <udp port>\n")
+            return
+        self._send("SET address %s %s" % (parts[0], parts[1]))
+
+    def do_show_dropped_packets(self, arg):
+        "Packets lost to the drop simulator, per worker, on ingress and egress."
+        self._send("SHOW dropped")
+
+    def do_show_queue_pairs_counters(self, arg):
+        "Per worker thread: packets received, packets outside the expected order, results, retransmitted results."
+        self._send("SHOW qp")
 
     def do_show_statistics(self, arg):
         "Broadcast / retransmit / consumed / dropped packet counters of the switch."

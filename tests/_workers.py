@@ -46,6 +46,8 @@ def udp_worker(rank, n, ctl_port, udp_port, numel, dtype, threads, packet_numel,
         if rank == 0:
             from switchml_b200.utils.cli import controller_command
             switch_stats = controller_command("127.0.0.1", ctl_port, "SHOW statistics")
+            stats["switch_tables"] = {t: controller_command("127.0.0.1", ctl_port, "SHOW " + t)
+                                      for t in ("ports", "forwarding", "qp", "dropped", "address", "workers")}
         ctx.stop()
         q.put((rank, "ok", outs, stats, switch_stats))
     except Exception:

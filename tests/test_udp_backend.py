@@ -78,6 +78,33 @@ def test_packet_loss_is_recovered_by_retransmission(ports):
     assert "retransmit" in sw and "ingress_dropped" in sw
     dropped = sum(int(line.split()[1]) for line in sw.splitlines() if "dropped" in line)
     assert dropped > 0
+    # the same loss, per worker and per worker thread (show_dropped_packets, show_queue_pairs_counters)
+    tables = res[0][1]["switch_tables"]
+    rows = [l.split() for l in tables["dropped"].splitlines()[1:]]
+    assert [r[0] for r in rows] == ["0", "1", "total"]
+    assert sum(int(r[1]) + int(r[2]) for r in rows[:2]) == int(rows[2][1]) + int(rows[2][2]) == dropped
+    qp = [l.split() for l in tables["qp"].splitlines()[1:]]
+    assert len(qp) == 4, tables["qp"]                      # 2 workers x 2 threads
+    assert sum(int(r[3]) for r in qp) > 0                  # retransmissions arrive outside the expected order
+    assert sum(int(r[5]) for r in qp) > 0                  # and some are answered from the retained copy
+
+
+def test_switch_tables_of_a_live_session(ports):
+    res = _run(2, ports, 20000, threads=2, packet_numel=64, jobs=1)
+    t = res[0][1]["switch_tables"]
+    fwd = [l.split() for l in t["forwarding"].splitlines()[1:]]
+    assert sorted((r[0], r[1]) for r in fwd) == [("0", "0"), ("0", "1"), ("1", "0"), ("1", "1")]
+    assert all(r[2].startswith("127.0.0.1:") for r in fwd)
+    assert len({r[2] for r in fwd}) == 4                   # one return port per worker thread
+    lines = {l.split()[0]: l.split() for l in t["ports"].splitlines()[1:]}
+    assert lines["control"][1] == "127.0.0.1:%d/tcp" % ports[0] and lines["control"][2] == "up"
+    assert lines["data"][1] == "127.0.0.1:%d/udp" % ports[1] and int(lines["data"][3]) > 0
+    assert lines["worker0"][1:4] == ["2", "endpoint(s)", "up"] and lines["worker1"][3] == "up"
+    packets = -(-20000 // 64)
+    assert int(lines["worker1"][4]) >= packets             # rx packets of worker 1
+    assert "udp_port %d" % ports[1] in t["address"]
+    qp = [l.split() for l in t["qp"].splitlines()[1:]]
+    assert sum(int(r[2]) for r in qp) >= 2 * packets and all(int(r[3]) == 0 or int(r[5]) >= 0 for r in qp)
 
 
 def test_console_against_standalone_controller(ports):
@@ -91,9 +118,52 @@ def test_console_against_standalone_controller(ports):
         for c in ("ping", "set_drop_probabilities 0.5 0.25 3", "show_drop_probabilities", "show_statistics",
                   "show_bitmap 3", "show_workers", "reset_workers", "bogus", "history"):
             cli.onecmd(cli.precmd(c))
+        # every command of the reference's shell exists (controller/cli.py:136-660)
+        for name in ("show_ports", "set_switch_address", "show_switch_address", "show_forwarding_table",
+                     "set_drop_probabilities", "show_drop_probabilities", "show_dropped_packets",
+                     "show_rdma_workers", "show_udp_workers", "show_queue_pairs_counters", "show_bitmap",
+                     "show_statistics", "reset_workers", "history", "exit"):
+            assert hasattr(cli, "do_" + name), name
+        for c in ("show_ports", "show_forwarding_table", "show_dropped_packets", "show_queue_pairs_counters",
+                  "show_rdma_workers", "show_switch_address"):
+            cli.onecmd(cli.precmd(c))
         text = out.getvalue()
+        assert "127.0.0.1:%d/udp  up" % ports[1] in text and "udp_port %d" % ports[1] in text
+        assert " total  0  0" in text
         assert "ingress 0.5" in text and "egress 0.25" in text
         assert "broadcast 0" in text and "slot 3 set0 0 set1 0" in text
         assert "Unknown syntax: bogus" in text and "set_drop_probabilities" in text
+
+        # The data plane answers echo requests (the switch's ping), also after it has moved.
+        def echo(port):
+            import socket
+            import struct
+            pkt = struct.pack("!IBBHIHHbBH", 0x534d4c31, 3, 0, 5, 1234, 0, 2, 0, 1, 0) + b"switchml"
+            with socket.socket(socket.AF_INET, socket.SOCK_DGRAM) as so:
+                so.settimeout(2.0)
+                so.sendto(pkt, ("127.0.0.1", port))
+                try:
+                    data, _ = so.recvfrom(2048)
+                except (socket.timeout, ConnectionError):
+                    return None
+            return data
+
+        reply = echo(ports[1])
+        assert reply is not None and reply[4] == 4 and reply[5:] == struct_tail(reply)
+        from conftest import free_port
+        moved = free_port()
+        out.truncate(0)
+        cli.onecmd("set_switch_address 127.0.0.1 %d" % moved)
+        cli.onecmd("show_switch_address")
+        assert "udp_port %d" % moved in out.getvalue()
+        assert echo(moved) is not None and echo(ports[1]) is None
+        cli.onecmd("set_switch_address 127.0.0.1")
+        assert "usage: set_switch_address" in out.getvalue()
     finally:
         lib().sml_controller_stop(srv)
+
+
+def struct_tail(reply):
+    """Everything after the type byte of an echo reply must be what was sent."""
+    import struct
+    return struct.pack("!BHIHHbBH", 0, 5, 1234, 0, 2, 0, 1, 0) + b"switchml"
