@@ -96,10 +96,12 @@ def _switchd_worker(rank, n, ctl_port, udp_port, q):
         q.put((rank, repr(e), None))
 
 
-def test_workers_with_standalone_switchd(built):
+def test_workers_with_standalone_switchd(built, tmp_path):
     ctl, udp = free_port(), free_port()
+    log = tmp_path / "switchd.log"
     d = subprocess.Popen([os.path.join(BIN, "switchml_switchd"), "--ip", "127.0.0.1", "--port", str(ctl),
-                          "--udp-port", str(udp), "--log-level", "0"], stdout=subprocess.PIPE, text=True)
+                          "--udp-port", str(udp), "--log-level", "0", "--log-file", str(log)],
+                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
     try:
         time.sleep(0.5)
         ctx = mp.get_context("spawn")
@@ -116,3 +118,5 @@ def test_workers_with_standalone_switchd(built):
         d.send_signal(signal.SIGTERM)
         out, _ = d.communicate(timeout=10)
     assert "broadcast" in out
+    text = log.read_text()
+    assert "data on UDP %d" % udp in text and "switchml_switchd stopped" in text
