@@ -328,18 +328,62 @@ void CudaBackend::SymmetricReset() {
   heap_used_ = 0;
 }
 
+// nullptr if kernels may dereference `p`, else the reason why not.
+static const char* GpuCannotAccess(const void* p) {
+  if (p == nullptr) return "null pointer";
+  cudaPointerAttributes at;
+  if (cudaPointerGetAttributes(&at, p) != cudaSuccess) {
+    cudaGetLastError();
+    return "the address is unknown to CUDA";
+  }
+  if (at.type == cudaMemoryTypeUnregistered) return "the address is ordinary (pageable) host memory";
+  return nullptr;
+}
+
 void CudaBackend::LaunchJob(const std::shared_ptr<Job>& job, cudaStream_t stream, InFlight* f, bool capturing) {
   const CudaBackendConfig& c = config_.backend_.cuda;
-  const Tensor& t = job->tensor_;
+  Tensor t = job->tensor_;
+  const Tensor& user = job->tensor_;
+  // The kernels dereference both pointers on the GPU: refuse anything the GPU cannot be
+  // trusted to reach (ordinary malloc'ed host memory) instead of launching into a fault.
+  // Device, managed and pinned (cudaHostAlloc / cudaHostRegister) memory pass.
+  if (t.numel > 0) {
+    const char* why = GpuCannotAccess(t.in_ptr);
+    if (!why && t.out_ptr != t.in_ptr) why = GpuCannotAccess(t.out_ptr);
+    if (why) {
+      f->launch_error = std::string("backend = cuda needs device, managed or pinned memory: ") + why;
+      return;
+    }
+  }
+  // uint8: widen into int32 scratch of the stream's memory pool, reduce that in place,
+  // narrow into the caller's output. With one worker the sum is the input itself.
+  void* widened = nullptr;
+  if (t.data_type == UINT8 && n_ > 1 && t.numel > 0) {
+    if (capturing) {
+      f->launch_error = "uint8 jobs cannot be captured into a CUDA graph";
+      return;
+    }
+    cudaError_t we = cudaMallocAsync(&widened, t.numel * 4, stream);
+    if (we == cudaSuccess) we = kernels::LaunchWidenU8(t.in_ptr, widened, t.numel, stream);
+    if (we != cudaSuccess) {
+      f->launch_error = std::string("uint8 staging failed: ") + cudaGetErrorString(we);
+      cudaGetLastError();
+      if (widened) cudaFreeAsync(widened, stream);
+      return;
+    }
+    t.in_ptr = t.out_ptr = widened;
+    t.data_type = INT32;
+  }
+  const bool integer = t.data_type == INT32 || t.data_type == UINT8;
   kernels::JobArgs a;
   memset(&a, 0, sizeof(a));
   a.in = t.in_ptr;
   a.out = t.out_ptr;
   a.numel = t.numel;
   a.elem_type = t.data_type == FLOAT32 ? kernels::ELEM_F32
-              : t.data_type == INT32 ? kernels::ELEM_I32 : kernels::ELEM_BF16;
-  a.mode = (t.data_type != INT32 && c.mode == "int32_quant") ? kernels::MODE_QUANT : kernels::MODE_SUM;
-  a.post_scale = c.average && t.data_type != INT32 ? 1.0f / static_cast<float>(n_) : 1.0f;
+              : t.data_type == BFLOAT16 ? kernels::ELEM_BF16 : kernels::ELEM_I32;
+  a.mode = (!integer && c.mode == "int32_quant") ? kernels::MODE_QUANT : kernels::MODE_SUM;
+  a.post_scale = c.average && !integer ? 1.0f / static_cast<float>(n_) : 1.0f;
   a.tune = static_cast<int>(c.tune);
   size_t esz = DataTypeSize(t.data_type);
   size_t bytes = t.numel * esz;
@@ -392,18 +436,22 @@ void CudaBackend::LaunchJob(const std::shared_ptr<Job>& job, cudaStream_t stream
   // One NVTX range per job: shows up in timeline tools, costs nothing without one.
   char range[96];
   snprintf(range, sizeof(range), "switchml job %llu: %llu x %s", static_cast<unsigned long long>(job->id_),
-           static_cast<unsigned long long>(t.numel), DataTypeName(t.data_type));
+           static_cast<unsigned long long>(t.numel), DataTypeName(user.data_type));
   SML_NVTX_PUSH(range);
   bool plain_copy = n_ == 1 && a.mode == kernels::MODE_SUM && a.post_scale == 1.0f && !nothing_to_do;
   if (t.numel > 0 && plain_copy) e = kernels::LaunchLocalCopy(t.in_ptr, t.out_ptr, bytes, stream);
   else if (t.numel > 0 && !nothing_to_do) e = kernels::LaunchAllReduce(job_ctx, a, plan, stream);
   SML_NVTX_POP();
+  if (widened) {
+    if (e == cudaSuccess) e = kernels::LaunchNarrowI32(widened, user.out_ptr, user.numel, stream);
+    cudaFreeAsync(widened, stream);
+  }
   if (e == cudaSuccess && f->done) e = cudaEventRecord(f->done, stream);
   if (e != cudaSuccess) {
     f->launch_error = std::string("kernel launch failed: ") + cudaGetErrorString(e);
     cudaGetLastError();
   }
-  SML_VLOG(2) << "job " << job->id_ << ": " << t.numel << " x " << DataTypeName(t.data_type)
+  SML_VLOG(2) << "job " << job->id_ << ": " << t.numel << " x " << DataTypeName(user.data_type)
               << " algo " << a.algo << " mode " << a.mode << " channels " << plan.channels
               << " epochs " << plan.epochs;
   if (f->done) {
@@ -576,6 +624,17 @@ Backend* CreateCudaBackend(Context& context, Config& config) {
 }
 
 // ---------------------------------------------------------------------------------------
+
+int ConvertU8OnDevice(bool widen, const void* in, void* out, unsigned long long numel, void* stream,
+                      std::string* error) {
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e = widen ? kernels::LaunchWidenU8(in, out, numel, s) : kernels::LaunchNarrowI32(in, out, numel, s);
+  if (e != cudaSuccess) {
+    if (error) *error = cudaGetErrorString(e);
+    cudaGetLastError();
+  }
+  return static_cast<int>(e);
+}
 
 int EmulatedAllReduce(int nranks, void* const* in_ptrs, void* const* out_ptrs,
                       unsigned long long numel, int elem_type, int mode, int algo, int block_numel,

@@ -55,5 +55,12 @@ int EmulatedAllReduce(int nranks, void* const* in_ptrs, void* const* out_ptrs,
                       size_t slot_bytes, int slots_per_channel, int channels, float post_scale,
                       int repeats, std::string* error);
 
+// The uint8 <-> int32 conversion kernels on their own (no Context needed), enqueued on
+// `stream` (a cudaStream_t, nullptr = default stream) of the current device. `widen`
+// zero-extends `numel` bytes into int32, otherwise the low byte of each int32 is kept.
+// Returns 0 or the CUDA error code.
+int ConvertU8OnDevice(bool widen, const void* in, void* out, unsigned long long numel, void* stream,
+                      std::string* error);
+
 }  // namespace switchml
 #endif  // SWITCHML_CUDA_BACKEND_H_

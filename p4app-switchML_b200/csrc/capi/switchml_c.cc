@@ -111,7 +111,7 @@ int sml_config_check(const char* ini_text, char* buf, size_t len) {
 
 int64_t sml_allreduce_async(void* in, void* out, uint64_t numel, int dtype, void* stream) {
   try {
-    if (dtype < 0 || dtype > 2) return Fail("bad dtype");
+    if (dtype < 0 || dtype > 3) return Fail("bad dtype");
     std::shared_ptr<Job> job = Context::GetInstance().AllReduceAsync(
         in, out, numel, static_cast<DataType>(dtype), SUM, stream);
     std::lock_guard<std::mutex> lk(g_jobs_mu);
@@ -125,7 +125,7 @@ int64_t sml_allreduce_async(void* in, void* out, uint64_t numel, int dtype, void
 
 int sml_allreduce(void* in, void* out, uint64_t numel, int dtype) {
   try {
-    if (dtype < 0 || dtype > 2) return Fail("bad dtype");
+    if (dtype < 0 || dtype > 3) return Fail("bad dtype");
     std::shared_ptr<Job> job =
         Context::GetInstance().AllReduce(in, out, numel, static_cast<DataType>(dtype), SUM);
     if (job->GetJobStatus() != FINISHED) return Fail("job failed: " + job->failure_reason_);
@@ -244,6 +244,13 @@ int sml_emu_allreduce(int nranks, void* const* in_ptrs, void* const* out_ptrs, u
   std::string err;
   int r = EmulatedAllReduce(nranks, in_ptrs, out_ptrs, numel, elem_type, mode, algo, block_numel,
                             slot_bytes, slots_per_channel, channels, post_scale, repeats, &err);
+  if (r != 0) g_error = err;
+  return r;
+}
+
+int sml_convert_u8(int widen, const void* in, void* out, uint64_t numel, void* stream) {
+  std::string err;
+  int r = ConvertU8OnDevice(widen != 0, in, out, numel, stream, &err);
   if (r != 0) g_error = err;
   return r;
 }

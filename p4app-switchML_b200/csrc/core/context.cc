@@ -2,6 +2,8 @@
 // Parity: reference client_lib/src/context.cc:36-197.
 #include "switchml/context.h"
 
+#include <vector>
+
 #include "switchml/log.h"
 #include "switchml/version.h"
 
@@ -102,8 +104,23 @@ std::shared_ptr<Job> Context::AllReduceAsync(void* in_ptr, void* out_ptr, uint64
   t.data_type = data_type;
   ExtraJobInfo extra;
   extra.allreduce_operation = op;
+  // uint8 on host memory (CPU backends): the job works on an int32 copy, which is narrowed
+  // into `out_ptr` when the job succeeds. The cuda backend widens on the device itself.
+  std::shared_ptr<std::vector<int32_t>> widened;
+  if (data_type == UINT8 && config_.general_.backend != "cuda") {
+    const uint8_t* src = static_cast<const uint8_t*>(in_ptr);
+    widened = std::make_shared<std::vector<int32_t>>(src, src + numel);
+    t.in_ptr = t.out_ptr = widened->data();
+    t.data_type = INT32;
+  }
   std::shared_ptr<Job> job = std::make_shared<Job>(t, ALLREDUCE, extra);
   job->producer_stream_ = stream;
+  if (widened) {
+    uint8_t* dst = static_cast<uint8_t*>(out_ptr);
+    job->on_success_ = [widened, dst] {
+      for (size_t i = 0; i < widened->size(); i++) dst[i] = static_cast<uint8_t>((*widened)[i]);
+    };
+  }
   {
     std::lock_guard<std::mutex> jl(jobs_mutex_);
     number_of_current_jobs_++;
@@ -149,6 +166,10 @@ void Context::FinishJob(const std::shared_ptr<Job>& job, bool ok, const std::str
   JobStatus s = job->GetJobStatus();
   if (s != FINISHED && s != FAILED) {
     if (ok) {
+      if (job->on_success_) {
+        job->on_success_();
+        job->on_success_ = nullptr;
+      }
       stats_.IncJobsFinishedNum();
       job->SetJobStatus(FINISHED);
     } else {

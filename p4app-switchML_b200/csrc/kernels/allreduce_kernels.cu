@@ -883,6 +883,51 @@ __global__ void __launch_bounds__(kThreads) LocalCopyKernel(const char* in, char
   }
 }
 
+// uint8 -> int32 (zero extended) and back (low byte kept, i.e. the sum modulo 256): uint8
+// tensors make the trip as int32. 16 elements per thread and step when the byte side is
+// 16-byte aligned (the int32 side is scratch memory and always is), else one by one.
+__global__ void __launch_bounds__(kThreads) WidenU8Kernel(const unsigned char* in, int* out, size_t n) {
+  const size_t tid = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const size_t nthreads = static_cast<size_t>(gridDim.x) * blockDim.x;
+  size_t done = 0;
+  if (Aligned16(in) && Aligned16(out)) {
+    const size_t nvec = n / 16;
+    const uint4* s = reinterpret_cast<const uint4*>(in);
+    int4* d = reinterpret_cast<int4*>(out);
+    for (size_t i = tid; i < nvec; i += nthreads) {
+      const uint4 v = s[i];
+      const unsigned w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+      for (int k = 0; k < 4; k++)
+        d[4 * i + k] = make_int4(w[k] & 0xff, (w[k] >> 8) & 0xff, (w[k] >> 16) & 0xff, w[k] >> 24);
+    }
+    done = nvec * 16;
+  }
+  for (size_t i = done + tid; i < n; i += nthreads) out[i] = in[i];
+}
+
+__global__ void __launch_bounds__(kThreads) NarrowI32Kernel(const int* in, unsigned char* out, size_t n) {
+  const size_t tid = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const size_t nthreads = static_cast<size_t>(gridDim.x) * blockDim.x;
+  size_t done = 0;
+  if (Aligned16(in) && Aligned16(out)) {
+    const size_t nvec = n / 16;
+    const int4* s = reinterpret_cast<const int4*>(in);
+    uint4* d = reinterpret_cast<uint4*>(out);
+    for (size_t i = tid; i < nvec; i += nthreads) {
+      unsigned w[4];
+#pragma unroll
+      for (int k = 0; k < 4; k++) {
+        const int4 v = s[4 * i + k];
+        w[k] = (v.x & 0xff) | ((v.y & 0xff) << 8) | ((v.z & 0xff) << 16) | (static_cast<unsigned>(v.w) << 24);
+      }
+      d[i] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    done = nvec * 16;
+  }
+  for (size_t i = done + tid; i < n; i += nthreads) out[i] = static_cast<unsigned char>(in[i]);
+}
+
 __global__ void WaitProbeKernel(const RankCtx ctx) {
   __shared__ int s_failed;
   if (threadIdx.x == 0) s_failed = 0;
@@ -1070,6 +1115,26 @@ cudaError_t LaunchLocalCopy(const void* in, void* out, size_t bytes, cudaStream_
   if (bytes == 0 || in == out) return cudaSuccess;
   int blocks = 148 * 4;
   LocalCopyKernel<<<blocks, kThreads, 0, stream>>>(static_cast<const char*>(in), static_cast<char*>(out), bytes);
+  return cudaGetLastError();
+}
+
+static int ElementwiseBlocks(size_t n) {
+  size_t want = (n / 16 + kThreads - 1) / kThreads;
+  if (want < 1) want = 1;
+  return static_cast<int>(want < 148 * 8 ? want : 148 * 8);
+}
+
+cudaError_t LaunchWidenU8(const void* in, void* out, size_t numel, cudaStream_t stream) {
+  if (numel == 0) return cudaSuccess;
+  WidenU8Kernel<<<ElementwiseBlocks(numel), kThreads, 0, stream>>>(static_cast<const unsigned char*>(in),
+                                                                  static_cast<int*>(out), numel);
+  return cudaGetLastError();
+}
+
+cudaError_t LaunchNarrowI32(const void* in, void* out, size_t numel, cudaStream_t stream) {
+  if (numel == 0) return cudaSuccess;
+  NarrowI32Kernel<<<ElementwiseBlocks(numel), kThreads, 0, stream>>>(static_cast<const int*>(in),
+                                                                    static_cast<unsigned char*>(out), numel);
   return cudaGetLastError();
 }
 

@@ -110,6 +110,10 @@ cudaError_t LaunchAllReduceEmulated(const RankCtx* ctxs_dev, const JobArgs* jobs
                                     cudaStream_t stream);
 // Single worker, plain sum, out of place: copy `bytes` bytes with one kernel.
 cudaError_t LaunchLocalCopy(const void* in, void* out, size_t bytes, cudaStream_t stream);
+// uint8 tensors travel as int32: zero-extend `numel` bytes into int32 scratch, and keep the
+// low byte of every int32 on the way back (the sum modulo 256).
+cudaError_t LaunchWidenU8(const void* in, void* out, size_t numel, cudaStream_t stream);
+cudaError_t LaunchNarrowI32(const void* in, void* out, size_t numel, cudaStream_t stream);
 // A kernel whose only job is to wait for a flag nobody sets: checks that a bounded wait
 // gives up, reports STATUS_TIMEOUT and leaves the context usable.
 cudaError_t LaunchWaitProbe(const RankCtx& ctx, cudaStream_t stream);

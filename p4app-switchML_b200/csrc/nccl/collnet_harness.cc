@@ -6,7 +6,7 @@
 // configuration (switchml.cfg, SWITCHML_RANK, SWITCHML_NUM_WORKERS).
 //
 //   collnet_harness --plugin lib/libnccl-net-switchml.so --exchange-dir /tmp/x [--numel 5000]
-//                   [--device cpu|gpu] [--rounds 3]
+//                   [--device cpu|pinned|gpu] [--rounds 3]
 //
 // Prints "collnet harness ok" and exits 0 when every result equals the expected sum.
 #include <cuda_runtime.h>
@@ -30,6 +30,8 @@
 namespace {
 
 int g_log_lines = 0;
+
+enum Memory { kHost, kPinned, kDevice };
 
 void Logger(smlNcclDebugLogLevel level, unsigned long flags, const char* file, int line, const char* fmt, ...) {
   ++g_log_lines;
@@ -73,7 +75,8 @@ bool WaitDone(smlNcclCollNet_v8_t* net, void* request, int* size, double limit_s
 // Run one allreduce of `count` elements of T whose value on rank r is base + r.
 template <typename T>
 int OneRound(smlNcclCollNet_v8_t* net, void* comm, smlNcclDataType_t type, int count, int rank, int nranks, int base,
-             bool gpu) {
+             Memory mem) {
+  const bool gpu = mem == kDevice;
   std::vector<T> send(count), recv(count, T(0));
   for (int i = 0; i < count; ++i) send[i] = static_cast<T>(base + rank + (i % 3));
   void* s = send.data();
@@ -83,6 +86,12 @@ int OneRound(smlNcclCollNet_v8_t* net, void* comm, smlNcclDataType_t type, int c
     EXPECT(cudaMalloc(&s, bytes) == cudaSuccess && cudaMalloc(&r, bytes) == cudaSuccess);
     EXPECT(cudaMemcpy(s, send.data(), bytes, cudaMemcpyHostToDevice) == cudaSuccess);
     EXPECT(cudaMemset(r, 0, bytes) == cudaSuccess);
+  } else if (mem == kPinned) {
+    // What NCCL hands a plugin as NCCL_PTR_HOST: page-locked memory the GPU can reach.
+    EXPECT(cudaHostAlloc(&s, bytes, cudaHostAllocMapped) == cudaSuccess);
+    EXPECT(cudaHostAlloc(&r, bytes, cudaHostAllocMapped) == cudaSuccess);
+    memcpy(s, send.data(), bytes);
+    memset(r, 0, bytes);
   }
   const int ptr_type = gpu ? SML_NCCL_PTR_CUDA : SML_NCCL_PTR_HOST;
   void *smh = nullptr, *rmh = nullptr, *req = nullptr;
@@ -97,8 +106,10 @@ int OneRound(smlNcclCollNet_v8_t* net, void* comm, smlNcclDataType_t type, int c
   CHECK_OK(net->iflush(comm, r, static_cast<int>(bytes), rmh, &freq));
   if (freq) EXPECT(WaitDone(net, freq, &size, 5.0));
   if (gpu) EXPECT(cudaMemcpy(recv.data(), r, bytes, cudaMemcpyDeviceToHost) == cudaSuccess);
+  if (mem == kPinned) memcpy(recv.data(), r, bytes);
   for (int i = 0; i < count; ++i) {
-    const long expect = static_cast<long>(nranks) * (base + (i % 3)) + static_cast<long>(nranks) * (nranks - 1) / 2;
+    long expect = static_cast<long>(nranks) * (base + (i % 3)) + static_cast<long>(nranks) * (nranks - 1) / 2;
+    if (type == smlNcclUint8) expect &= 0xff;
     const double got = static_cast<double>(recv[i]);
     const double tol = sizeof(T) == 4 && type == smlNcclFloat32 ? 1e-2 * expect + 1e-3 : 0.0;
     if (got < expect - tol || got > expect + tol) {
@@ -111,6 +122,9 @@ int OneRound(smlNcclCollNet_v8_t* net, void* comm, smlNcclDataType_t type, int c
   if (gpu) {
     cudaFree(s);
     cudaFree(r);
+  } else if (mem == kPinned) {
+    cudaFreeHost(s);
+    cudaFreeHost(r);
   }
   return 0;
 }
@@ -123,12 +137,15 @@ int main(int argc, char** argv) {
       .Add("exchange-dir", "", "Directory visible to every rank, used to pass the listen handles around.")
       .Add("numel", "5000", "Elements per allreduce.")
       .Add("rounds", "3", "Allreduces per data type.")
-      .Add("device", "cpu", "cpu or gpu (gpu needs backend = cuda).");
+      .Add("device", "cpu", "Where the buffers live: cpu (ordinary host memory), pinned (page-locked host memory, "
+                            "the only host memory backend = cuda accepts) or gpu.");
   if (!flags.Parse(argc, argv, "collnet_harness: drives the NCCL collective-network plugin without NCCL")) return 2;
   const std::string dir = flags.Str("exchange-dir");
   const int count = static_cast<int>(flags.U64("numel"));
   const int rounds = static_cast<int>(flags.U64("rounds"));
-  const bool gpu = flags.Str("device") == "gpu";
+  const std::string where = flags.Str("device");
+  const Memory mem = where == "gpu" ? kDevice : where == "pinned" ? kPinned : kHost;
+  const bool gpu = mem == kDevice;
 
   void* lib = dlopen(flags.Str("plugin").c_str(), RTLD_NOW | RTLD_LOCAL);
   if (lib == nullptr) {
@@ -212,13 +229,13 @@ int main(int argc, char** argv) {
   EXPECT(comm != nullptr);
 
   for (int i = 0; i < rounds; ++i) {
-    if (OneRound<float>(net, comm, smlNcclFloat32, count, rank, nranks, 1 + i, gpu)) return 1;
-    if (OneRound<int32_t>(net, comm, smlNcclInt32, count, rank, nranks, 100 + i, gpu)) return 1;
-    if (!gpu && OneRound<uint8_t>(net, comm, smlNcclUint8, count, rank, nranks, 1 + i, false)) return 1;
+    if (OneRound<float>(net, comm, smlNcclFloat32, count, rank, nranks, 1 + i, mem)) return 1;
+    if (OneRound<int32_t>(net, comm, smlNcclInt32, count, rank, nranks, 100 + i, mem)) return 1;
+    if (OneRound<uint8_t>(net, comm, smlNcclUint8, count, rank, nranks, 1 + i, mem)) return 1;
   }
 
   // Unsupported requests come back as errors, not as jobs.
-  {
+  if (mem == kHost) {
     std::vector<double> d(8, 1.0);
     void *mh = nullptr, *req = nullptr;
     CHECK_OK(net->regMr(comm, d.data(), 64, SML_NCCL_PTR_HOST, &mh));
@@ -231,6 +248,6 @@ int main(int argc, char** argv) {
   CHECK_OK(net->closeListen(listen_comm));
   EXPECT(switchml::Context::GetInstance().GetContextState() != switchml::Context::RUNNING);
   printf("collnet harness ok: rank %d of %d, %d rounds of %d elements on the %s, %d log lines\n", rank, nranks, rounds,
-         count, gpu ? "gpu" : "cpu", g_log_lines);
+         count, gpu ? "gpu" : (mem == kPinned ? "pinned host memory" : "cpu"), g_log_lines);
   return 0;
 }

@@ -4,7 +4,8 @@
 // Counterpart of the reference's frameworks_integration/nccl_plugin/switchml_plugin.cc
 // (init starts the context :135-141, one device :147-151, reduceSupport :247-253, regMr as a
 // book-keeping no-op :258-287, iallreduce -> AllReduceAsync with uint8 widened to int32
-// :293-343, test polls the job :361-387). Differences, all deliberate:
+// :293-343, test polls the job :361-387; the widening lives in the context here, on the
+// host for the CPU backends and in a kernel for backend = cuda). Differences, all deliberate:
 //   * written against version 8 of NCCL's plugin interface, which a stock NCCL loads; the
 //     reference needs a patched NCCL 2.8;
 //   * listen/connect need no point-to-point ring of NCCL's own transport: the context has
@@ -62,7 +63,6 @@ struct Request {
   smlNcclDataType_t data_type = smlNcclFloat32;
   void* recv = nullptr;
   int count = 0;
-  std::vector<int32_t> widened;  // uint8 payload as int32, in place
   std::shared_ptr<switchml::Job> job;
 };
 
@@ -126,7 +126,7 @@ int TypeSize(smlNcclDataType_t t) {
 bool TypeSupported(smlNcclDataType_t t) {
   switch (t) {
     case smlNcclInt32: case smlNcclFloat32: return true;
-    case smlNcclUint8: return true;  // PyTorch reduces uint8 flags across workers; widened to int32
+    case smlNcclUint8: return true;  // PyTorch reduces uint8 flags across workers; summed as int32
     case smlNcclBfloat16: return BackendIsCuda();
     default: return false;
   }
@@ -256,33 +256,20 @@ smlNcclResult_t PluginIallreduce(void* coll_comm, void* send, void* recv, int co
     PLUGIN_WARN("iallreduce: the buffers lie outside their registered regions");
     return smlNcclInvalidArgument;
   }
-  const bool on_device = (smh && smh->type == SML_NCCL_PTR_CUDA) || (rmh && rmh->type == SML_NCCL_PTR_CUDA);
   auto req = std::make_unique<Request>();
   req->data_type = type;
   req->recv = recv;
   req->count = count;
   switchml::DataType dt = switchml::FLOAT32;
-  void* in = send;
-  void* out = recv;
   switch (type) {
     case smlNcclFloat32: dt = switchml::FLOAT32; break;
     case smlNcclInt32: dt = switchml::INT32; break;
     case smlNcclBfloat16: dt = switchml::BFLOAT16; break;
-    case smlNcclUint8: {
-      if (on_device) {
-        PLUGIN_WARN("iallreduce: uint8 is widened on the host and needs host memory");
-        return smlNcclInvalidArgument;
-      }
-      const uint8_t* s = static_cast<const uint8_t*>(send);
-      req->widened.assign(s, s + count);
-      dt = switchml::INT32;
-      in = out = req->widened.data();
-      break;
-    }
+    case smlNcclUint8: dt = switchml::UINT8; break;  // widened to int32 inside the context
     default: return smlNcclInvalidArgument;
   }
   try {
-    req->job = Context::GetInstance().AllReduceAsync(in, out, static_cast<uint64_t>(count), dt, switchml::SUM);
+    req->job = Context::GetInstance().AllReduceAsync(send, recv, static_cast<uint64_t>(count), dt, switchml::SUM);
   } catch (const std::exception& e) {
     PLUGIN_WARN("iallreduce: %s", e.what());
     return smlNcclInternalError;
@@ -339,10 +326,6 @@ smlNcclResult_t PluginTest(void* request, int* done, int* size) {
   if (st != switchml::FINISHED) {
     *done = 0;
     return smlNcclSuccess;
-  }
-  if (req->data_type == smlNcclUint8) {
-    uint8_t* r = static_cast<uint8_t*>(req->recv);
-    for (int i = 0; i < req->count; ++i) r[i] = static_cast<uint8_t>(req->widened[i]);
   }
   *done = 1;
   if (size) *size = req->count * TypeSize(req->data_type);

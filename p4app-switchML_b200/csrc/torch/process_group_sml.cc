@@ -39,11 +39,12 @@ switchml::DataType ToSwitchML(const at::Tensor& t) {
   switch (t.scalar_type()) {
     case at::kFloat: return switchml::FLOAT32;
     case at::kInt: return switchml::INT32;
+    case at::kByte: return switchml::UINT8;  // PyTorch reduces uint8 flags across workers
     case at::kBFloat16:
       TORCH_CHECK(t.is_cuda(), "SwitchML reduces bfloat16 tensors only on the GPU");
       return switchml::BFLOAT16;
     default:
-      TORCH_CHECK(false, "SwitchML supports float32, int32 and (CUDA) bfloat16 tensors, got ", t.scalar_type());
+      TORCH_CHECK(false, "SwitchML supports float32, int32, uint8 and (CUDA) bfloat16 tensors, got ", t.scalar_type());
   }
 }
 

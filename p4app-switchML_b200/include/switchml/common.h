@@ -23,6 +23,9 @@ enum DataType {
   FLOAT32 = 0,   // IEEE binary32
   INT32 = 1,     // two's complement, wrapping add
   BFLOAT16 = 2,  // GPU backends only; accumulated in float32
+  UINT8 = 3,     // travels widened to int32 and is narrowed (wrapping) on return, like the
+                 // reference's NCCL plugin does for PyTorch's uint8 flag reductions
+                 // (nccl_plugin/switchml_plugin.cc:328-337,371-377)
 };
 
 static inline uint16_t DataTypeSize(DataType t) {
@@ -32,6 +35,8 @@ static inline uint16_t DataTypeSize(DataType t) {
       return 4;
     case BFLOAT16:
       return 2;
+    case UINT8:
+      return 1;
   }
   return 0;
 }
@@ -41,6 +46,7 @@ static inline const char* DataTypeName(DataType t) {
     case FLOAT32: return "float32";
     case INT32: return "int32";
     case BFLOAT16: return "bfloat16";
+    case UINT8: return "uint8";
   }
   return "?";
 }

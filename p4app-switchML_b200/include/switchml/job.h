@@ -18,6 +18,8 @@
 #include <mutex>
 #include <string>
 
+#include <functional>
+
 #include "switchml/common.h"
 
 namespace switchml {
@@ -84,6 +86,9 @@ class Job {
   void* ready_event_ = nullptr;
   // Human-readable reason when FAILED.
   std::string failure_reason_;
+  // Run once by the context right before a successful job turns FINISHED (uint8 jobs on
+  // host memory narrow their int32 working copy into the caller's buffer here).
+  std::function<void()> on_success_;
 
  private:
   static std::atomic<JobId> next_id_;

@@ -11,7 +11,7 @@
 extern "C" {
 #endif
 
-/* data types: 0 float32, 1 int32, 2 bfloat16 (cuda backend only) */
+/* data types: 0 float32, 1 int32, 2 bfloat16 (cuda backend only), 3 uint8 (summed as int32, low byte returned) */
 /* job status: 0 INIT, 1 QUEUED, 2 RUNNING, 3 FINISHED, 4 FAILED */
 /* context state: 0 CREATED, 1 STARTING, 2 RUNNING, 3 STOPPING, 4 STOPPED */
 
@@ -64,6 +64,11 @@ void sml_oracle_quant_allreduce(const float* const* inputs, int num_workers, uin
 void sml_oracle_int_allreduce(const int32_t* const* inputs, int num_workers, uint64_t numel,
                               int32_t* out);
 void sml_static_slice(uint64_t numel, int parts, int index, uint64_t* offset, uint64_t* length);
+
+/* uint8 tensors travel as int32. widen != 0: zero-extend `numel` bytes at `in` into int32 at
+ * `out`; widen == 0: keep the low byte of `numel` int32 at `in`. Device pointers of the
+ * current CUDA device; the kernel is enqueued on `stream` (a cudaStream_t). */
+int sml_convert_u8(int widen, const void* in, void* out, uint64_t numel, void* stream);
 
 /* `nranks` virtual ranks on the current CUDA device in one cooperative kernel.
  * elem_type 0 f32 / 1 i32 / 2 bf16; mode 0 sum / 1 quant; algo 0 staged / 1 one-shot. */

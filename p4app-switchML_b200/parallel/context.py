@@ -12,6 +12,7 @@ class DataType(enum.IntEnum):
     FLOAT32 = 0
     INT32 = 1
     BFLOAT16 = 2
+    UINT8 = 3
 
 
 class JobStatus(enum.IntEnum):
@@ -39,9 +40,9 @@ def _describe(t):
     if torch is not None and isinstance(t, torch.Tensor):
         if not t.is_contiguous():
             raise ValueError("tensor must be contiguous")
-        code = {torch.float32: 0, torch.int32: 1, torch.bfloat16: 2}.get(t.dtype)
+        code = {torch.float32: 0, torch.int32: 1, torch.bfloat16: 2, torch.uint8: 3}.get(t.dtype)
         if code is None:
-            raise TypeError("unsupported dtype %s (float32, int32, bfloat16)" % t.dtype)
+            raise TypeError("unsupported dtype %s (float32, int32, bfloat16, uint8)" % t.dtype)
         stream = None
         if t.is_cuda:
             stream = torch.cuda.current_stream(t.device).cuda_stream
@@ -50,9 +51,9 @@ def _describe(t):
     if isinstance(t, np.ndarray):
         if not t.flags["C_CONTIGUOUS"]:
             raise ValueError("array must be C-contiguous")
-        code = {np.dtype("float32"): 0, np.dtype("int32"): 1}.get(t.dtype)
+        code = {np.dtype("float32"): 0, np.dtype("int32"): 1, np.dtype("uint8"): 3}.get(t.dtype)
         if code is None:
-            raise TypeError("unsupported dtype %s (float32, int32)" % t.dtype)
+            raise TypeError("unsupported dtype %s (float32, int32, uint8)" % t.dtype)
         return t.ctypes.data, t.size, code, None, False
     raise TypeError("expected a torch.Tensor or numpy.ndarray")
 

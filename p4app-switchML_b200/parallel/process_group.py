@@ -24,7 +24,7 @@ import torch.distributed as dist
 from .context import Context, JobStatus
 from ..utils.config import make_config, load_config_file
 
-_SUPPORTED = (torch.float32, torch.int32, torch.bfloat16)
+_SUPPORTED = (torch.float32, torch.int32, torch.bfloat16, torch.uint8)
 
 
 class WorkSML(dist._Work):

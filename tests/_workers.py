@@ -33,6 +33,12 @@ def udp_worker(rank, n, ctl_port, udp_port, numel, dtype, threads, packet_numel,
             # the operator CLI path: tell the switch to lose packets both ways
             from switchml_b200.utils.cli import controller_command
             controller_command("127.0.0.1", ctl_port, "SET drop %g %g 99" % (drop, drop))
+        # uint8 flags, the way PyTorch reduces them: summed as int32, low byte returned
+        flags = ((np.arange(1000) * (rank + 3)) % 256).astype(np.uint8)
+        summed = np.zeros_like(flags)
+        ctx.all_reduce(flags, summed)
+        want = (sum(((np.arange(1000) * (r + 3)) % 256) for r in range(n)) % 256).astype(np.uint8)
+        assert np.array_equal(summed, want), "uint8 allreduce"
         outs = []
         for j in range(jobs):
             x = rank_data(rank, numel, dtype, seed=j)
@@ -90,6 +96,16 @@ def cuda_worker(rank, n, ctl_port, transport, mode, q, heap_mb=64, launch="inlin
             t = torch.from_numpy(xi[rank]).cuda()
             ctx.all_reduce(t)
             assert np.array_equal(t.cpu().numpy(), int_allreduce_oracle(xi)), "int mismatch at %d" % numel
+            report["cases"] += 1
+            # uint8: summed as int32, low byte returned; out of place from an odd offset
+            xu = [np.random.default_rng(7 * numel + r).integers(0, 256, numel + 3, dtype=np.uint8) for r in range(n)]
+            tu = torch.from_numpy(xu[rank]).cuda()
+            ou = torch.full((numel + 5,), 77, dtype=torch.uint8, device="cuda")
+            ctx.all_reduce(tu[3:], ou[1:1 + numel])
+            want_u = (sum(a[3:].astype(np.int64) for a in xu) & 0xff).astype(np.uint8)
+            assert np.array_equal(ou[1:1 + numel].cpu().numpy(), want_u), "uint8 mismatch at %d" % numel
+            assert int(ou[0]) == 77 and bool((ou[1 + numel:] == 77).all()), "uint8 wrote outside its output"
+            assert np.array_equal(tu.cpu().numpy(), xu[rank]), "uint8 touched its input"
             report["cases"] += 1
             # bf16 in place
             xb = [torch.from_numpy(a).bfloat16() for a in xs]

@@ -51,6 +51,20 @@ def test_odd_sizes_inplace_int(ctx, numel, ppp):
         assert np.array_equal(x, want)
 
 
+def test_uint8_is_summed_as_int32_and_narrowed(ctx):
+    """uint8 tensors make the trip as int32 and come back modulo 256 (the dummy backend
+    multiplies by the number of workers)."""
+    assert ctx.start(sml.make_config("dummy", rank=0, num_workers=3, packet_numel=64, bandwidth=0))
+    x = (np.arange(700) % 256).astype(np.uint8)
+    y = np.zeros_like(x)
+    job = ctx.all_reduce_async(x, y)
+    assert job.wait(10000) == sml.JobStatus.FINISHED
+    assert np.array_equal(y, ((np.arange(700) % 256) * 3 % 256).astype(np.uint8))
+    assert np.array_equal(x, (np.arange(700) % 256).astype(np.uint8)), "the input must stay untouched"
+    ctx.all_reduce(x)  # in place
+    assert np.array_equal(x, y)
+
+
 def test_async_jobs_and_stats(ctx):
     assert ctx.start(sml.make_config("dummy", num_workers=4, packet_numel=256, bandwidth=0))
     xs = [np.full(1 << 15, float(i + 1), dtype=np.float32) for i in range(8)]

@@ -135,3 +135,53 @@ def test_jobs_can_be_captured_in_a_cuda_graph_and_replayed(ctx):
     ctx.all_reduce(large, out_l)
     assert np.array_equal(out_l.cpu().numpy(), quant_allreduce_oracle([large.cpu().numpy()], 256))
     assert ctx.get_stats()["backend"]["device_timeouts"] == 0
+
+
+@pytest.mark.parametrize("launch", ["worker", "inline"])
+def test_ordinary_host_memory_is_refused_not_dereferenced(ctx, launch):
+    """The kernels read their operands on the GPU. A pointer to pageable host memory fails
+    the job on the host, before anything is launched; pinned memory is accepted."""
+    assert ctx.start(sml.make_config("cuda", packet_numel=256, mode="float_sum", launch=launch))
+    x = np.ones(1000, dtype=np.float32)
+    job = ctx.all_reduce_async(x)
+    assert job.wait(10000) == sml.JobStatus.FAILED
+    assert "pageable" in job.error()
+    d = torch.ones(1000, device="cuda")
+    job = ctx.all_reduce_async(d, x)  # good input, bad output
+    assert job.wait(10000) == sml.JobStatus.FAILED and "pageable" in job.error()
+    assert float(x.sum()) == 1000.0
+    p = torch.arange(1000, dtype=torch.float32).pin_memory()
+    q = torch.zeros(1000, dtype=torch.float32).pin_memory()
+    job = ctx.all_reduce_async(p.numpy(), q.numpy())
+    assert job.wait(10000) == sml.JobStatus.FINISHED, job.error()
+    torch.cuda.synchronize()
+    assert torch.equal(p, q)
+    y = torch.empty_like(d)
+    assert ctx.all_reduce_async(d, y).wait(10000) == sml.JobStatus.FINISHED  # the context still works
+    assert torch.equal(y.cpu(), d.cpu())
+
+
+@pytest.mark.parametrize("numel,offset", [(1, 0), (15, 0), (16, 0), (4099, 0), (4099, 3), ((1 << 22) + 7, 0),
+                                          ((1 << 22) + 7, 5), (1 << 24, 16)])
+def test_uint8_widen_and_narrow_kernels(numel, offset):
+    from switchml_b200.ops.elementwise import widen_u8, narrow_i32
+    g = torch.Generator(device="cuda").manual_seed(numel)
+    base = torch.randint(0, 256, (numel + offset + 9,), device="cuda", dtype=torch.uint8, generator=g)
+    src = base[offset:offset + numel]
+    wide = widen_u8(src)
+    assert wide.dtype == torch.int32 and torch.equal(wide.cpu(), src.cpu().to(torch.int32))
+    sums = wide * 5 - 300  # what an aggregate may look like: beyond a byte, also negative
+    out = torch.full((numel + offset + 9,), 201, dtype=torch.uint8, device="cuda")
+    narrow_i32(sums, out[offset:offset + numel])
+    want = (sums.cpu().to(torch.int64) & 0xff).to(torch.uint8)
+    assert torch.equal(out[offset:offset + numel].cpu(), want)
+    assert bool((out[:offset] == 201).all()) and bool((out[offset + numel:] == 201).all())
+
+
+def test_uint8_allreduce_single_rank(ctx):
+    assert ctx.start(sml.make_config("cuda", packet_numel=256, mode="int32_quant", launch="inline"))
+    x = torch.randint(0, 256, (100003,), device="cuda", dtype=torch.uint8)
+    y = torch.zeros_like(x)
+    ctx.all_reduce(x, y)
+    torch.cuda.synchronize()
+    assert torch.equal(x, y)

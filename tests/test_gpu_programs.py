@@ -59,5 +59,5 @@ def test_nccl_collnet_plugin_on_gpu(cuda_cfg):
         pytest.skip("plugin not built")
     out = _run([exe, "--plugin", plugin, "--device", "gpu", "--numel", "300000", "--rounds", "2"], cuda_cfg)
     assert "ptrSupport 0x3" in out and "collnet harness ok" in out and "on the gpu" in out
-    out = _run([exe, "--plugin", plugin, "--device", "cpu", "--numel", "5000", "--rounds", "1"], cuda_cfg)
-    assert "collnet harness ok" in out
+    out = _run([exe, "--plugin", plugin, "--device", "pinned", "--numel", "5000", "--rounds", "1"], cuda_cfg)
+    assert "collnet harness ok" in out and "pinned host memory" in out
