@@ -16,6 +16,11 @@ class NativeError(RuntimeError):
 
 
 def library_path(name="libswitchml_b200.so"):
+    """lib/<name>; SWITCHML_B200_LIBRARY names another build of the main library (the checked
+    build of ``build.py --checked``)."""
+    override = os.environ.get("SWITCHML_B200_LIBRARY")
+    if override and name == "libswitchml_b200.so":
+        return override
     return os.path.join(_HERE, "lib", name)
 
 
@@ -25,6 +30,7 @@ def _declare(l):
     sig = {
         "sml_version": (c.c_char_p, []),
         "sml_last_error": (c.c_char_p, []),
+        "sml_checked_build": (i32, []),
         "sml_set_verbosity": (None, [i32]),
         "sml_start": (i32, [c.c_char_p, i32]),
         "sml_start_file": (i32, [c.c_char_p]),

@@ -8,6 +8,7 @@ Products (all inside this directory, never installed elsewhere):
     lib/libswitchml_b200.so        core + CPU backends + CUDA backend + C interface
     lib/libswitchml_gemm.so        tcgen05 weight-gradient GEMM (loaded on demand)
     lib/torch_switchml.so          native c10d backend for PyTorch (python build.py --torch)
+    build-checked/libswitchml_b200.so   the library with the kernels' bounds checks (--checked)
     lib/libnccl-net-switchml.so    NCCL collective-network plugin (bin/collnet_harness drives it)
     bin/switchml_switchd           stand-alone controller / software switch
     bin/hello_world, bin/allreduce_benchmark, bin/dnn_benchmark, bin/core_tests
@@ -183,6 +184,45 @@ def build_sanitized(kind, verbose=False):
     return exe
 
 
+def build_checked(verbose=False, jobs=None):
+    """build-checked/libswitchml_b200.so: the main library with -DSWITCHML_CHECKED, i.e. with
+    the geometry checks of the aggregation kernels compiled in (a violation sets
+    STATUS_BOUNDS and skips the access; nothing traps). Load it instead of lib/ by putting
+    its path into SWITCHML_B200_LIBRARY. compute-sanitizer's role where that tool is not
+    to be had."""
+    out = os.path.join(ROOT, "build-checked")
+    obj_dir = os.path.join(out, "obj")
+    os.makedirs(obj_dir, exist_ok=True)
+    hdr = _headers_mtime()
+    target = os.path.join(out, "libswitchml_b200.so")
+
+    def one(src):
+        path = os.path.join(ROOT, src)
+        obj = os.path.join(obj_dir, src.replace("/", "_") + ".o")
+        if os.path.exists(obj) and os.path.getmtime(obj) > max(os.path.getmtime(path), hdr):
+            return obj, None
+        if src.endswith(".cu"):
+            cmd = [NVCC] + ARCH + ["-lineinfo", "-std=c++17", "-Xcompiler", "-fPIC,-Wall"] + OPT + \
+                  ["-DSWITCHML_CHECKED"] + INCLUDES + ["-c", path, "-o", obj]
+        else:
+            cmd = ["g++", "-std=c++17", "-fPIC", "-Wall", "-Wextra", "-Wno-unused-parameter", "-pthread"] + \
+                  OPT + ["-DSWITCHML_CHECKED"] + INCLUDES + ["-c", path, "-o", obj]
+        if verbose:
+            print(" ".join(cmd), flush=True)
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        return obj, (None if r.returncode == 0 else "FAILED: %s\n%s%s" % (" ".join(cmd), r.stdout, r.stderr))
+
+    with cf.ThreadPoolExecutor(max_workers=jobs or max(1, os.cpu_count() or 2)) as ex:
+        results = list(ex.map(one, LIB_SOURCES))
+    errors = [e for _, e in results if e]
+    if errors:
+        raise RuntimeError("\n".join(errors))
+    objs = [o for o, _ in results]
+    if not os.path.exists(target) or any(os.path.getmtime(o) > os.path.getmtime(target) for o in objs):
+        _link([NVCC] + ARCH + ["-shared", "-o", target] + objs + ["-lpthread", "-ldl", "-lrt"], verbose)
+    return target
+
+
 def build_torch_extension(verbose=False):
     """lib/torch_switchml.so: the native c10d backend. Needs the headers and libraries of the
     installed PyTorch; returns None (with a note) when they are not usable."""
@@ -225,6 +265,8 @@ if __name__ == "__main__":
     ap.add_argument("--jobs", type=int, default=None)
     ap.add_argument("-v", "--verbose", action="store_true")
     ap.add_argument("--sanitize", choices=["thread", "address", "undefined"], default=SANITIZE or None)
+    ap.add_argument("--checked", action="store_true",
+                    help="also build build-checked/libswitchml_b200.so with the kernels' geometry checks")
     ap.add_argument("--torch", action="store_true", help="also build lib/torch_switchml.so (native c10d backend)")
     a = ap.parse_args()
     if a.clean:
@@ -234,6 +276,8 @@ if __name__ == "__main__":
         sys.exit(0)
     try:
         print(build(a.jobs, a.verbose))
+        if a.checked:
+            print(build_checked(a.verbose, a.jobs))
         if a.torch:
             print(build_torch_extension(a.verbose))
     except RuntimeError as e:

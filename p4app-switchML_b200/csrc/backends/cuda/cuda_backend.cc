@@ -224,6 +224,7 @@ void CudaBackend::SetupWorker() {
   size_t bytes = kernels::StagingBytes(ctx_.slot_bytes, ctx_.slots_per_channel, ctx_.block_numel,
                                        max_channels_, ctx_.oneshot_bytes, n_, &ctx_.data_offset,
                                        &ctx_.exp_offset, &ctx_.oneshot_offset);
+  ctx_.stage_bytes = kernels::ReportedStageBytes(bytes);
   // Two GPUs exchange less data with plain peer loads/stores (N bytes each way) than
   // through the switch (1.5 N); from three GPUs on the in-switch reduction wins.
   bool want_mc = c.transport == "nvls" || (c.transport == "auto" && n_ > 2);
@@ -402,6 +403,7 @@ void CudaBackend::LaunchJob(const std::shared_ptr<Job>& job, cudaStream_t stream
     a.algo = kernels::ALGO_ZEROCOPY;
     for (int p = 0; p < n_; p++) a.user_peer[p] = static_cast<char*>(heap_.peers[p]);
     a.user_mc = static_cast<char*>(heap_.multicast);
+    a.user_bytes = heap_.bytes;
     a.in_offset = static_cast<const char*>(t.in_ptr) - static_cast<const char*>(heap_.local);
     a.out_offset = static_cast<const char*>(t.out_ptr) - static_cast<const char*>(heap_.local);
   } else if (bytes <= c.oneshot_max_bytes) {
@@ -564,6 +566,8 @@ void CudaBackend::CompletionLoop() {
             o << "a peer did not arrive within " << config_.backend_.cuda.wait_timeout_ms
               << " ms (channel " << (st >> 8) << ", phase " << ((st >> 4) & 0xf) << ")";
             stats.AddTimeouts(0, 1);
+          } else if ((st & 0xf) == kernels::STATUS_BOUNDS) {
+            o << "checked build: a tile of channel " << (st >> 8) << " would reach outside its region";
           } else {
             o << "kernel status " << st;
           }
@@ -625,6 +629,8 @@ Backend* CreateCudaBackend(Context& context, Config& config) {
 
 // ---------------------------------------------------------------------------------------
 
+bool KernelsCheckedBuild() { return kernels::CheckedBuild(); }
+
 int ConvertU8OnDevice(bool widen, const void* in, void* out, unsigned long long numel, void* stream,
                       std::string* error) {
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -671,6 +677,7 @@ int EmulatedAllReduce(int nranks, void* const* in_ptrs, void* const* out_ptrs,
   size_t bytes = StagingBytes(slot_bytes, slots_per_channel, block_numel, max_channels,
                               oneshot_bytes, nranks, &proto.data_offset, &proto.exp_offset,
                               &proto.oneshot_offset);
+  proto.stage_bytes = ReportedStageBytes(bytes);
   std::vector<char*> stage(nranks, nullptr);
   int* status = nullptr;
   unsigned long long* counters = nullptr;

@@ -55,6 +55,10 @@ int EmulatedAllReduce(int nranks, void* const* in_ptrs, void* const* out_ptrs,
                       size_t slot_bytes, int slots_per_channel, int channels, float post_scale,
                       int repeats, std::string* error);
 
+// True if the kernels were compiled with -DSWITCHML_CHECKED (geometry checks before every
+// tile; a violation sets STATUS_BOUNDS instead of touching memory).
+bool KernelsCheckedBuild();
+
 // The uint8 <-> int32 conversion kernels on their own (no Context needed), enqueued on
 // `stream` (a cudaStream_t, nullptr = default stream) of the current device. `widen`
 // zero-extends `numel` bytes into int32, otherwise the low byte of each int32 is kept.

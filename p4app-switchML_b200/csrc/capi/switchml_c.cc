@@ -51,6 +51,7 @@ extern "C" {
 
 const char* sml_version(void) { return SWITCHML_VERSION; }
 const char* sml_last_error(void) { return g_error.c_str(); }
+int sml_checked_build(void) { return KernelsCheckedBuild() ? 1 : 0; }
 void sml_set_verbosity(int v) { SetVerbosity(v); }
 
 int sml_start(const char* ini_text, int apply_env) {

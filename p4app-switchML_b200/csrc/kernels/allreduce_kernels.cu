@@ -24,6 +24,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "kernels/allreduce_kernels.h"
 #include "kernels/device_sync.cuh"
@@ -258,6 +259,23 @@ __device__ __forceinline__ void RoleCopy(const Role& role, void* dst, const void
   }
 }
 
+// Checked build (-DSWITCHML_CHECKED): before a tile, a one-shot buffer or a symmetric tensor
+// is touched, its geometry is verified against the sizes of the regions it indexes. A
+// violation stores STATUS_BOUNDS with the channel in the status word, marks the CTA as
+// failed and skips the work: nothing out of range is dereferenced and nothing traps. The
+// condition depends only on launch arguments that are the same on every rank, so all
+// threads of the CTA, and the same channel on the peers, take the same way out.
+#ifdef SWITCHML_CHECKED
+#define SML_GEOMETRY_CHECK(CTX, CHANNEL, FAILED, COND)                      \
+  if (!(COND)) {                                                            \
+    ReportStatus((CTX), STATUS_BOUNDS | ((CHANNEL) << 8));                  \
+    *(FAILED) = 1;                                                          \
+    return;                                                                 \
+  }
+#else
+#define SML_GEOMETRY_CHECK(CTX, CHANNEL, FAILED, COND)
+#endif
+
 template <int ELEM, int MODE, int kLoadWarps = kDefaultLoadWarps, int kReduceWarps = kDefaultReduceWarps,
           int kUnrollLink = kDefaultUnrollLink>
 __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
@@ -312,6 +330,12 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
     const size_t slot_index = static_cast<size_t>(channel) * S + slot;
     const size_t slot_off = ctx.data_offset + slot_index * ctx.slot_bytes;  // same on all ranks
     const size_t exp_off = ctx.exp_offset + slot_index * blocks_per_slot * 4;
+    SML_GEOMETRY_CHECK(ctx, channel, failed,
+                       len > 0 && len <= slot_elems && pos + len <= job.numel &&
+                       slot_off >= ctx.data_offset && slot_off + ctx.slot_bytes <= ctx.stage_bytes &&
+                       (MODE != MODE_QUANT ||
+                        (blocks_per_slot <= static_cast<size_t>(kMaxBlocksPerSlot) &&
+                         exp_off + blocks_per_slot * 4 <= ctx.oneshot_offset)));
     float* sf = s_sf + static_cast<size_t>(slot) * blocks_per_slot;
 
     if (which == 0) {
@@ -595,6 +619,9 @@ __device__ void RunOneShot(const RankCtx& ctx, const JobArgs& job, int channel,
   };
   const char* in = static_cast<const char*>(job.in) + c0 * esz;
   const size_t bytes = len * esz;
+  SML_GEOMETRY_CHECK(ctx, channel, s_failed,
+                     c0 * esz + bytes <= ctx.oneshot_bytes && job.oneshot_parity >= 0 && job.oneshot_parity < 3 &&
+                     buf_off(ctx.nranks - 1) + bytes <= ctx.data_offset && ctx.data_offset <= ctx.stage_bytes);
 
   if (MODE == MODE_SUM && ctx.use_multimem) {
     // Pull variant: every rank parks its input at the same offset of its own buffer, and
@@ -725,6 +752,9 @@ __device__ void RunZeroCopy(const RankCtx& ctx, const JobArgs& job, int channel,
   const int esz = ELEM == ELEM_BF16 ? 2 : 4;
   const size_t vec_elems = 16 / esz;
   const unsigned long long epoch = base + 1;
+  SML_GEOMETRY_CHECK(ctx, channel, s_failed,
+                     job.in_offset + job.numel * esz <= job.user_bytes &&
+                     job.out_offset + job.numel * esz <= job.user_bytes);
   // Everybody's input must be complete before anybody reads it.
   if (!ChannelBarrier(ctx, channel, 0, epoch, s_failed)) return;
 
@@ -1006,6 +1036,22 @@ size_t StagingBytes(size_t slot_bytes, int slots_per_channel, int block_numel, i
   return off;
 }
 
+bool CheckedBuild() {
+#ifdef SWITCHML_CHECKED
+  return true;
+#else
+  return false;
+#endif
+}
+
+size_t ReportedStageBytes(size_t actual) {
+#ifdef SWITCHML_CHECKED
+  const char* e = getenv("SWITCHML_CHECKED_PRETEND_STAGE_BYTES");
+  if (e && *e) return static_cast<size_t>(strtoull(e, nullptr, 0));
+#endif
+  return actual;
+}
+
 LaunchPlan PlanLaunch(const RankCtx& ctx, const JobArgs& job, int requested_channels,
                       int max_channels) {
   LaunchPlan p;
@@ -1227,6 +1273,7 @@ extern "C" int switchml_local_allreduce_noalloc(const void* in, void* out,
                                 kNoAllocChannels, ctx.oneshot_bytes, 1, &ctx.data_offset,
                                 &ctx.exp_offset, &ctx.oneshot_offset);
   if (staging > kNoAllocAuxOffset) return SWITCHML_NOALLOC_BAD_ARGUMENT;  // cannot happen for the limits above
+  ctx.stage_bytes = staging;
   ctx.counters = reinterpret_cast<unsigned long long*>(scratch + kNoAllocAuxOffset);
   ctx.status = reinterpret_cast<int*>(scratch + kNoAllocAuxOffset + 256);
   ctx.epoch_words = reinterpret_cast<unsigned long long*>(scratch + kNoAllocAuxOffset + 320);  // 8 channels

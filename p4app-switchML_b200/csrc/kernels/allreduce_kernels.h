@@ -38,6 +38,7 @@ enum Status : int {
   STATUS_OK = 0,
   STATUS_TIMEOUT = 1,  // a bounded wait ran out; bits 8.. hold the channel, 4..7 the phase
   STATUS_BAD_ARGS = 2,
+  STATUS_BOUNDS = 3,   // checked build only: a tile or buffer would reach outside its region (bits 8.. = channel)
 };
 
 // What a rank's kernel needs to reach its peers. Passed by value.
@@ -55,6 +56,7 @@ struct RankCtx {
   int block_numel;               // quantisation block (= packet_numel)
   float quant_base;              // quant::QuantBase(nranks): scale factor at exponent 0
   size_t oneshot_bytes;          // capacity of one rank's one-shot buffer (per parity)
+  size_t stage_bytes;            // size of one rank's staging region (what the checked build verifies against)
   unsigned long long timeout_ns; // budget of every wait
   int* status;                   // device-visible status word (0 = ok)
   unsigned long long* counters;  // [0] tiles processed, [1] wait iterations, [2] timeouts
@@ -79,6 +81,7 @@ struct JobArgs {
   char* user_peer[kMaxRanks];
   char* user_mc;
   size_t in_offset, out_offset;
+  size_t user_bytes;  // size of the symmetric user region (checked build)
 };
 
 // Geometry chosen on the host; identical on every rank for the same job.
@@ -96,6 +99,14 @@ size_t SlotElems(const RankCtx& ctx, int elem_type, int mode);
 size_t StagingBytes(size_t slot_bytes, int slots_per_channel, int block_numel, int max_channels,
                     size_t oneshot_bytes, int nranks, size_t* data_offset, size_t* exp_offset,
                     size_t* oneshot_offset);
+// The value for RankCtx::stage_bytes: `actual`, the size of the region. In a checked build
+// the environment variable SWITCHML_CHECKED_PRETEND_STAGE_BYTES replaces it, so that a test
+// can watch the geometry checks refuse every tile (the memory itself stays as large as it
+// was, and a refused tile is not touched anyway).
+size_t ReportedStageBytes(size_t actual);
+// True if the library was compiled with -DSWITCHML_CHECKED.
+bool CheckedBuild();
+
 LaunchPlan PlanLaunch(const RankCtx& ctx, const JobArgs& job, int requested_channels,
                       int max_channels);
 // Enqueue the job on `stream`. Returns cudaSuccess or the launch error.

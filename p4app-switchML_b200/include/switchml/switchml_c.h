@@ -17,6 +17,8 @@ extern "C" {
 
 const char* sml_version(void);
 const char* sml_last_error(void);
+/* 1 if the library was compiled with -DSWITCHML_CHECKED (kernels verify their geometry). */
+int sml_checked_build(void);
 void sml_set_verbosity(int v);
 
 /* Lifecycle (switchml::Context::Start / Stop). `ini_text` is the content of a
