@@ -90,19 +90,84 @@ class GradientBuckets:
         self.jobs = []
 
 
+def broadcast_tensors(ctx, tensors, src=0, chunk_numel=1 << 24):
+    """Give every worker rank `src`'s values of `tensors`, in place, with the one collective
+    SwitchML has: `src` contributes its values, everybody else zeros, and the sum is the
+    broadcast. Exact with ``mode = float_sum`` and for integers; with the quantised mode the
+    values come back rounded to the block's fixed-point grid, the same on every rank
+    (`src` included), which is what data-parallel training needs.
+
+    Floating-point tensors travel as float32, integer tensors as int32 (values must fit),
+    bool as uint8. Tensors are packed into flat messages of at most `chunk_numel` elements.
+    """
+    cfg = ctx.config_dump()
+    rank, n = _config_int(cfg, "rank"), _config_int(cfg, "num_workers")
+    averaged = "average = true" in cfg or "average = 1" in cfg
+    if n <= 1:
+        return
+    groups = {}
+    for t in tensors:
+        if t.numel() == 0:
+            continue
+        wire = torch.float32 if t.is_floating_point() else (torch.uint8 if t.dtype == torch.bool else torch.int32)
+        groups.setdefault((wire, t.device), []).append(t)
+    for (wire, device), group in groups.items():
+        batch, count = [], 0
+        for t in group + [None]:
+            if t is not None and (not batch or count + t.numel() <= chunk_numel):
+                batch.append(t)
+                count += t.numel()
+                continue
+            flat = torch.zeros(count, dtype=wire, device=device)
+            if rank == src:
+                off = 0
+                for b in batch:
+                    flat[off:off + b.numel()].copy_(b.detach().reshape(-1))
+                    off += b.numel()
+            job = ctx.all_reduce(flat)
+            if flat.is_cuda:
+                job.stream_wait(None)
+            job.release()
+            if averaged and wire == torch.float32:
+                flat.mul_(float(n))
+            off = 0
+            with torch.no_grad():
+                for b in batch:
+                    b.copy_(flat[off:off + b.numel()].view_as(b))
+                    off += b.numel()
+            batch, count = ([t], t.numel()) if t is not None else ([], 0)
+
+
+def _config_int(dump, key):
+    for line in dump.splitlines():
+        parts = line.split("=")
+        if len(parts) == 2 and parts[0].strip() == key:
+            return int(parts[1].strip())
+    raise KeyError(key)
+
+
 class DistributedDataParallel(torch.nn.Module):
-    """Wraps a module: broadcasts nothing (ranks must start from the same weights, e.g.
-    the same seed), averages gradients across workers during backward.
+    """Wraps a module: gives every worker rank 0's parameters and buffers when it is built
+    (``broadcast_parameters``), sums or averages gradients across workers during backward.
 
     Configure the context with ``average = true`` in [backend.cuda] to get the mean; with
-    the default the gradients are summed, like a raw SwitchML allreduce.
+    the default the gradients are summed, like a raw SwitchML allreduce. ``no_sync()``
+    skips the reduction for the backward passes inside it (gradient accumulation); the
+    accumulated gradients are reduced by the first backward pass outside.
+    ``broadcast_parameters="auto"`` broadcasts unless the backend is the dummy one, which
+    has no peers and multiplies every job by ``num_workers``.
     """
 
-    def __init__(self, module, ctx, bucket_mb=25, overlap=True, symmetric="auto"):
+    def __init__(self, module, ctx, bucket_mb=25, overlap=True, symmetric="auto", broadcast_parameters="auto"):
         super().__init__()
         self.module = module
         self.ctx = ctx
         self.overlap = overlap
+        self._sync = True
+        if broadcast_parameters == "auto":
+            broadcast_parameters = "backend = dummy" not in ctx.config_dump()
+        if broadcast_parameters:
+            self.sync_parameters()
         self.buckets = GradientBuckets(module.parameters(), ctx, bucket_mb, symmetric)
         self._pending = [0] * len(self.buckets.buckets)
         self._armed = False
@@ -114,8 +179,28 @@ class DistributedDataParallel(torch.nn.Module):
             p.register_post_accumulate_grad_hook(self._on_grad)
         self._callback_queued = False
 
+    def sync_parameters(self, src=0):
+        """Overwrite parameters and buffers with those of rank `src` (see broadcast_tensors)."""
+        state = [p.data for p in self.module.parameters()] + [b.data for b in self.module.buffers()]
+        broadcast_tensors(self.ctx, state, src)
+
+    def no_sync(self):
+        """Context manager: backward passes inside accumulate gradients locally."""
+        ddp = self
+
+        class _NoSync:
+            def __enter__(self):
+                self.previous = ddp._sync
+                ddp._sync = False
+
+            def __exit__(self, *exc):
+                ddp._sync = self.previous
+                return False
+
+        return _NoSync()
+
     def forward(self, *args, **kwargs):
-        if torch.is_grad_enabled():
+        if torch.is_grad_enabled() and self._sync:
             self._pending = [len(g) for g in self.buckets.bucket_params]
             self._armed = True
             self._callback_queued = False

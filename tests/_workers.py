@@ -183,13 +183,16 @@ def cuda_worker(rank, n, ctl_port, transport, mode, q, heap_mb=64, launch="inlin
         # DDP wrapper: overlapped, bucketed reduction must equal the mean of the local gradients
         if mode == "float_sum":
             from switchml_b200.parallel.ddp import DistributedDataParallel
-            torch.manual_seed(0)
-            model = torch.nn.Sequential(torch.nn.Linear(256, 512), torch.nn.ReLU(), torch.nn.Linear(512, 512),
-                                        torch.nn.ReLU(), torch.nn.Linear(512, 16)).cuda()
-            ref_model = torch.nn.Sequential(torch.nn.Linear(256, 512), torch.nn.ReLU(), torch.nn.Linear(512, 512),
-                                            torch.nn.ReLU(), torch.nn.Linear(512, 16)).cuda()
-            ref_model.load_state_dict(model.state_dict())
+            def make(seed):
+                torch.manual_seed(seed)
+                return torch.nn.Sequential(torch.nn.Linear(256, 512), torch.nn.ReLU(), torch.nn.Linear(512, 512),
+                                           torch.nn.ReLU(), torch.nn.Linear(512, 16)).cuda()
+            model = make(rank)          # every rank starts from other weights ...
             ddp = DistributedDataParallel(model, ctx, bucket_mb=0.5, overlap=True)
+            ref_model = make(0)         # ... and the wrapper hands out rank 0's, exactly in float_sum mode
+            for p, rp in zip(model.parameters(), ref_model.parameters()):
+                assert torch.equal(p, rp), "parameters were not broadcast from rank 0"
+            report["cases"] += 1
             for it in range(3):
                 ddp.zero_grad()
                 xs_all = [torch.randn(32, 256, generator=torch.Generator().manual_seed(10 * r + it)) for r in range(n)]
@@ -392,5 +395,49 @@ def native_pg_cuda_worker(rank, n, port, ctl_port, cfg_dir, q):
         assert float(tb.float().mean()) == float(n)
         dist.destroy_process_group()
         q.put((rank, "ok", None))
+    except Exception:
+        q.put((rank, "error", traceback.format_exc()))
+
+
+def ddp_broadcast_worker(rank, n, ctl_port, udp_port, q):
+    """DDP wrapper over the UDP backend on CPU tensors: ranks start from different weights,
+    the wrapper gives everybody rank 0's; then one synchronised step and one accumulated
+    (no_sync) step are compared with gradients computed from all ranks' data."""
+    try:
+        import torch
+        import switchml_b200 as sml
+        from switchml_b200.parallel.ddp import DistributedDataParallel
+        ctx = sml.Context.get_instance()
+        assert ctx.start(sml.make_config("udp", rank=rank, num_workers=n, packet_numel=64, num_worker_threads=2,
+                                         max_outstanding_packets=64, controller_port=ctl_port, switch_port=udp_port,
+                                         worker_port=0))
+
+        def make(seed):
+            torch.manual_seed(seed)
+            m = torch.nn.Sequential(torch.nn.Linear(12, 32), torch.nn.BatchNorm1d(32), torch.nn.Tanh(),
+                                    torch.nn.Linear(32, 4))
+            m[1].num_batches_tracked.fill_(seed)
+            return m
+        model = make(100 + rank)                      # every rank starts somewhere else
+        ddp = DistributedDataParallel(model, ctx, bucket_mb=0.001)
+        state = {k: v.clone() for k, v in model.state_dict().items()}
+        xs = [torch.randn(6, 12, generator=torch.Generator().manual_seed(50 + r)) for r in range(n)]
+        # one synchronised step
+        ddp.zero_grad()
+        ddp(xs[rank]).square().mean().backward()
+        g1 = [p.grad.clone() for p in model.parameters()]
+        # accumulate one local pass, then a synchronised one: reduced gradient = sum over ranks of both passes
+        ddp.zero_grad()
+        with ddp.no_sync():
+            ddp(xs[rank]).square().mean().backward()
+        local_only = [p.grad.clone() for p in model.parameters()]
+        submitted = ctx.get_stats()["jobs_submitted"]
+        ddp(2 * xs[rank]).square().mean().backward()
+        g2 = [p.grad.clone() for p in model.parameters()]
+        assert ctx.get_stats()["jobs_submitted"] - submitted == len(ddp.buckets.buckets)
+        ctx.stop()
+        # numpy, not tensors: a tensor in a queue is a handle to shared memory of this process
+        q.put((rank, "ok", {"state": {k: v.numpy() for k, v in state.items()}, "g1": [g.numpy() for g in g1],
+                            "g2": [g.numpy() for g in g2], "local": [g.numpy() for g in local_only]}))
     except Exception:
         q.put((rank, "error", traceback.format_exc()))

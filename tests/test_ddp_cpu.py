@@ -66,3 +66,75 @@ def test_unused_parameters_are_still_reduced(ctx):
     # every bucket is submitted, so all workers issue the same jobs in the same order
     assert ctx.get_stats()["jobs_submitted"] - before == len(ddp.buckets.buckets)
     assert float(net.unused.weight.grad.abs().sum()) == 0.0
+
+
+def test_no_sync_accumulates_locally(ctx):
+    m, ref = _model(), _model()
+    ddp = DistributedDataParallel(m, ctx, bucket_mb=0.01)
+    x = torch.randn(8, 20)
+    ddp.zero_grad()
+    before = ctx.get_stats()["jobs_submitted"]
+    with ddp.no_sync():
+        ddp(x).square().mean().backward()
+        ddp(x).square().mean().backward()
+    assert ctx.get_stats()["jobs_submitted"] == before, "no job may be submitted inside no_sync()"
+    ref(x).square().mean().backward()
+    for p, rp in zip(m.parameters(), ref.parameters()):
+        assert torch.allclose(p.grad, 2.0 * rp.grad, rtol=1e-5, atol=1e-7)      # two local passes
+    ddp(x).square().mean().backward()                                           # third pass, reduced with the rest
+    for p, rp in zip(m.parameters(), ref.parameters()):
+        assert torch.allclose(p.grad, 2.0 * 3.0 * rp.grad, rtol=1e-5, atol=1e-7)  # x2: the dummy "sum" of 2 workers
+
+
+def test_parameters_are_broadcast_and_gradients_summed_across_real_workers():
+    """Two processes over the UDP backend and the software switch."""
+    import multiprocessing as mp
+    from conftest import free_port
+    from _workers import ddp_broadcast_worker
+    ports = (free_port(), free_port())
+    mpc = mp.get_context("spawn")
+    q = mpc.Queue()
+    procs = [mpc.Process(target=ddp_broadcast_worker, args=(r, 2, ports[0], ports[1], q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = {}
+    try:
+        for _ in range(2):
+            rank, status, payload = q.get(timeout=180)
+            assert status == "ok", payload
+            got[rank] = {"state": {k: torch.from_numpy(v) for k, v in payload["state"].items()},
+                         **{k: [torch.from_numpy(g) for g in payload[k]] for k in ("g1", "g2", "local")}}
+    finally:
+        for p in procs:
+            p.join(timeout=30)
+            if p.is_alive():
+                p.kill()
+    # same state everywhere, and it is rank 0's initial one (up to the fixed-point grid of the quantised trip)
+    torch.manual_seed(100)
+    want = torch.nn.Sequential(torch.nn.Linear(12, 32), torch.nn.BatchNorm1d(32), torch.nn.Tanh(),
+                               torch.nn.Linear(32, 4)).state_dict()
+    for k, v in got[0]["state"].items():
+        assert torch.equal(v, got[1]["state"][k]), k
+        if k.endswith("num_batches_tracked"):
+            assert int(v) == 100
+        else:
+            assert torch.allclose(v, want[k], rtol=0, atol=1e-6), k
+    # gradients: identical on both ranks and equal to the sum of the local ones
+    model = torch.nn.Sequential(torch.nn.Linear(12, 32), torch.nn.BatchNorm1d(32), torch.nn.Tanh(),
+                                torch.nn.Linear(32, 4))
+    model.load_state_dict(got[0]["state"])
+    xs = [torch.randn(6, 12, generator=torch.Generator().manual_seed(50 + r)) for r in range(2)]
+    total = None
+    for r in range(2):
+        model.zero_grad()
+        model.train()
+        model(xs[r]).square().mean().backward()
+        grads = [p.grad.clone() for p in model.parameters()]
+        total = grads if total is None else [a + b for a, b in zip(total, grads)]
+    for a, b, t in zip(got[0]["g1"], got[1]["g1"], total):
+        assert torch.equal(a, b)
+        assert torch.allclose(a, t, rtol=1e-4, atol=1e-6)
+    for a, b in zip(got[0]["g2"], got[1]["g2"]):
+        assert torch.equal(a, b)
+    assert not all(torch.equal(a, b) for a, b in zip(got[0]["local"], got[1]["local"])), \
+        "inside no_sync() the gradients must stay local"
