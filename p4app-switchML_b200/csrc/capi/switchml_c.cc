@@ -82,10 +82,9 @@ int sml_start_file(const char* path) {
 
 int sml_stop(void) {
   try {
-    {
-      std::lock_guard<std::mutex> lk(g_jobs_mu);
-      g_jobs.clear();
-    }
+    // Job handles outlive the context: Stop() fails what is still queued or running, and the
+    // caller must be able to read the status and the reason afterwards. sml_job_release()
+    // is what frees a handle.
     Context::GetInstance().Stop();
     return 0;
   } catch (const std::exception& e) {

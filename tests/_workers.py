@@ -441,3 +441,37 @@ def ddp_broadcast_worker(rank, n, ctl_port, udp_port, q):
                             "g2": [g.numpy() for g in g2], "local": [g.numpy() for g in local_only]}))
     except Exception:
         q.put((rank, "error", traceback.format_exc()))
+
+
+def stop_during_loss_worker(rank, n, ctl_port, udp_port, q):
+    """Total packet loss after one good job: the next job cannot finish, its retransmission
+    timers keep firing, and Context.stop() fails it in bounded time instead of hanging."""
+    try:
+        import threading
+        import time
+        import numpy as np
+        import switchml_b200 as sml
+        from switchml_b200.utils.cli import controller_command
+        ctx = sml.Context.get_instance()
+        assert ctx.start(sml.make_config("udp", rank=rank, num_workers=n, packet_numel=64, num_worker_threads=2,
+                                         max_outstanding_packets=64, controller_port=ctl_port, switch_port=udp_port,
+                                         worker_port=0, timeout=5))
+        x = np.ones(100000, dtype=np.float32)
+        ctx.all_reduce(x)
+        assert float(x[0]) == float(n)
+        if rank == 0:
+            controller_command("127.0.0.1", ctl_port, "SET drop 1.0 1.0 1")
+        time.sleep(0.3)                       # both ranks submit after the switch went deaf
+        job = ctx.all_reduce_async(x)
+        early = job.wait(timeout_ms=800)      # still running: nothing comes back
+        seen = {}
+        waiter = threading.Thread(target=lambda: seen.update(status=job.wait()))
+        waiter.start()
+        t0 = time.time()
+        ctx.stop()
+        waiter.join(10)
+        timeouts = sum(ctx.get_stats()["timeouts"])   # the worker threads report when their slice ends
+        q.put((rank, "ok", {"early": int(early), "final": int(seen.get("status", -1)), "error": job.error(),
+                            "stop_seconds": time.time() - t0, "timeouts": timeouts}))
+    except Exception:
+        q.put((rank, "error", traceback.format_exc()))

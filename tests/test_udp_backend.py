@@ -89,6 +89,28 @@ def test_packet_loss_is_recovered_by_retransmission(ports):
     assert sum(int(r[5]) for r in qp) > 0                  # and some are answered from the retained copy
 
 
+def test_stop_fails_a_job_that_total_loss_keeps_from_finishing(ports):
+    from _workers import stop_during_loss_worker
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=stop_during_loss_worker, args=(r, 2, ports[0], ports[1], q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    try:
+        for _ in range(2):
+            rank, status, info = q.get(timeout=120)
+            assert status == "ok", info
+            assert info["early"] == int(sml.JobStatus.RUNNING)
+            assert info["final"] == int(sml.JobStatus.FAILED) and info["error"], info
+            assert info["stop_seconds"] < 10.0
+            assert info["timeouts"] > 0, "the retransmission timers must have fired meanwhile"
+    finally:
+        for p in procs:
+            p.join(timeout=30)
+            if p.is_alive():
+                p.kill()
+
+
 def test_switch_tables_of_a_live_session(ports):
     res = _run(2, ports, 20000, threads=2, packet_numel=64, jobs=1)
     t = res[0][1]["switch_tables"]
