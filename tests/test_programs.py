@@ -120,3 +120,19 @@ def test_workers_with_standalone_switchd(built, tmp_path):
     assert "broadcast" in out
     text = log.read_text()
     assert "data on UDP %d" % udp in text and "switchml_switchd stopped" in text
+
+
+def test_switchd_console_on_standard_input(built, tmp_path):
+    """The daemon's own shell (the reference controller runs its CLI in-process)."""
+    ctl, udp = free_port(), free_port()
+    cmds = "ping\nshow_switch_address\nset_drop_probabilities 0.25 0.5 7\nshow_drop_probabilities\n" \
+           "show_ports\nbogus\nhelp\nexit\n"
+    r = subprocess.run([os.path.join(BIN, "switchml_switchd"), "--ip", "127.0.0.1", "--port", str(ctl),
+                        "--udp-port", str(udp), "--log-level", "0", "--log-file", "", "--console", "true"],
+                       input=cmds, capture_output=True, text=True, timeout=60, cwd=tmp_path)
+    assert r.returncode == 0, r.stdout + r.stderr
+    out = r.stdout
+    assert "udp_port %d" % udp in out and "ingress 0.25" in out and "egress 0.5" in out
+    assert "127.0.0.1:%d/udp  up" % udp in out
+    assert "unknown command: bogus" in out and "show_queue_pairs_counters" in out
+    assert out.count("(switchml) ") >= 8
