@@ -229,6 +229,9 @@ def pg_worker(rank, n, port, q):
         work = dist.all_reduce(ti, async_op=True)
         work.wait()
         assert int(ti[0]) == sum(r + 1 for r in range(n)), "int allreduce"
+        tu = torch.full((77,), 250 + rank, dtype=torch.uint8)
+        dist.all_reduce(tu)
+        assert int(tu[0]) == sum(250 + r for r in range(n)) % 256, "uint8 allreduce"
         d = torch.ones(4, dtype=torch.float64) * rank          # unsupported dtype: Gloo fallback
         dist.all_reduce(d)
         assert float(d[0]) == sum(range(n)), "fallback"
@@ -350,6 +353,9 @@ def native_pg_worker(rank, n, port, ctl_port, udp_port, cfg_dir, q):
         fut = w.get_future()
         fut.wait()
         assert int(ti[7]) == sum(r + 5 for r in range(n))
+        tu = torch.full((100,), 200 + rank, dtype=torch.uint8)    # flags as PyTorch reduces them: modulo 256
+        dist.all_reduce(tu)
+        assert int(tu[3]) == sum(200 + r for r in range(n)) % 256
         try:
             dist.all_reduce(torch.ones(4, dtype=torch.float64))
             raised = False
