@@ -13,9 +13,10 @@
 //   BCAST <n> <rank> <root> <u64>    everyone receives root's value
 //   GATHER <n> <rank> <token>        everyone receives all n tokens, ordered by rank
 //   UDPSESSION <session> <rank> <n> <packet_numel> <ip> <port0> <nthreads>
-//   SHOW workers|statistics|drop|bitmap <slot>     (CLI)
-//   SET drop <ingress> <egress> [seed]             (CLI)
-//   RESET                                           (CLI)
+//   SHOW workers|statistics|drop|dropped|qp|ports|forwarding|address|bitmap <slot>   (CLI)
+//   SET drop <ingress> <egress> [seed] | SET address <ip> <udp port>                 (CLI)
+//   RESET | PING                                                                      (CLI)
+// (docs/control_protocol.md is the full description, the counterpart of switchml.proto.)
 // Collective requests are matched by arrival order, so all workers must issue them in
 // the same sequence (they do: one per setup step).
 #ifndef SWITCHML_RENDEZVOUS_CONTROL_H_
