@@ -18,3 +18,11 @@ from .utils.config import make_config, load_config_file  # noqa: F401
 from .parallel.context import Context, Job, DataType, JobStatus, ContextState  # noqa: F401
 
 __version__ = lib().sml_version().decode()
+
+
+def set_verbosity(level, vmodule=None):
+    """Log verbosity 0..4 of the native library; `vmodule` ("udp_backend=3,control=2") gives
+    single source files their own level (the reference exposes glog's --v / --vmodule)."""
+    lib().sml_set_verbosity(int(level))
+    if vmodule is not None:
+        lib().sml_set_vmodule(str(vmodule).encode())

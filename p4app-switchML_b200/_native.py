@@ -32,6 +32,7 @@ def _declare(l):
         "sml_last_error": (c.c_char_p, []),
         "sml_checked_build": (i32, []),
         "sml_set_verbosity": (None, [i32]),
+        "sml_set_vmodule": (None, [c.c_char_p]),
         "sml_start": (i32, [c.c_char_p, i32]),
         "sml_start_file": (i32, [c.c_char_p]),
         "sml_stop": (i32, []),

@@ -34,7 +34,7 @@ CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
 NVCC = os.path.join(CUDA_HOME, "bin", "nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 DEBUG = os.environ.get("DEBUG", "0") == "1"
-OPT = ["-O0", "-g"] if DEBUG else ["-O3"]
+OPT = ["-O0", "-g", "-DSWITCHML_DEBUG"] if DEBUG else ["-O3"]
 DEFS = ["-DSWITCHML_CHECKED"] if os.environ.get("SWITCHML_CHECKED", "0") == "1" else []
 # SANITIZE=thread|address builds the host code (and bin/core_tests) under that sanitizer into
 # build-<name>/; used by the CPU race/memory checks, never for the GPU library in lib/.

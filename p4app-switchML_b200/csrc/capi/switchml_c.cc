@@ -53,6 +53,7 @@ const char* sml_version(void) { return SWITCHML_VERSION; }
 const char* sml_last_error(void) { return g_error.c_str(); }
 int sml_checked_build(void) { return KernelsCheckedBuild() ? 1 : 0; }
 void sml_set_verbosity(int v) { SetVerbosity(v); }
+void sml_set_vmodule(const char* spec) { SetVModule(spec); }
 
 int sml_start(const char* ini_text, int apply_env) {
   try {

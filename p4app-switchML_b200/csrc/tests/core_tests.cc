@@ -31,6 +31,45 @@ static int g_failures = 0;
     }                                                                        \
   } while (0)
 
+static int g_sink_lines = 0;
+static void CountingSink(int, const char*) { g_sink_lines++; }
+
+static void TestLogging() {
+  const int before = GetVerbosity();
+  SetLogSink(CountingSink);
+  SetVerbosity(1);
+  g_sink_lines = 0;
+  SML_VLOG(1) << "printed";
+  SML_VLOG(2) << "not printed";
+  SML_VLOG_IF(1, false) << "not printed";
+  EXPECT(g_sink_lines == 1);
+  // Per-module level: this file may speak up to 3, everything else keeps level 1.
+  SetVModule("core_tests=3,control=0");
+  EXPECT(SML_VLOG_IS_ON(3) && !SML_VLOG_IS_ON(4));
+  EXPECT(VlogIsOn("/somewhere/csrc/rendezvous/control.cc", 0) && !VlogIsOn("csrc/rendezvous/control.cc", 1));
+  EXPECT(VlogIsOn("udp_backend.cc", 1) && !VlogIsOn("udp_backend.cc", 2));
+  EXPECT(!VlogIsOn("core_tests_more.cc", 3));  // whole names only
+  SML_VLOG(3) << "printed";
+  EXPECT(g_sink_lines == 2);
+  SetVModule("");
+  EXPECT(!SML_VLOG_IS_ON(2));
+  SML_DVLOG(0) << "only in debug builds";
+#ifdef SWITCHML_DEBUG
+  EXPECT(g_sink_lines == 3);
+#else
+  EXPECT(g_sink_lines == 2);
+#endif
+  bool threw = false;
+  try {
+    SML_CHECK(1 + 1 == 3) << "arithmetic";
+  } catch (const FatalError& e) {
+    threw = std::string(e.what()).find("arithmetic") != std::string::npos;
+  }
+  EXPECT(threw);
+  SetLogSink(nullptr);
+  SetVerbosity(before);
+}
+
 static void TestStaticSlice() {
   // 10 elements over 4 threads: 3,3,2,2 at offsets 0,3,6,8 (remainder to the first threads)
   Numel off, len;
@@ -373,7 +412,7 @@ static void TestContextDummy() {
 int main() {
   SetVerbosity(0);
   struct { const char* name; void (*fn)(); } tests[] = {
-      {"static_slice", TestStaticSlice}, {"barrier", TestBarrier}, {"job_fsm", TestJobFsm},
+      {"logging", TestLogging}, {"static_slice", TestStaticSlice}, {"barrier", TestBarrier}, {"job_fsm", TestJobFsm},
       {"timeout_queue", TestTimeoutQueue}, {"soft_switch", TestSoftSwitch},
       {"quant_math", TestQuantMath}, {"control_plane", TestControlPlane},
       {"context_dummy", TestContextDummy},

@@ -7,8 +7,13 @@
 //   SML_VLOG(n) << ...;                         printed when n <= verbosity
 //   SML_CHECK(cond) << ...;                     FATAL when cond is false
 //
+//   SML_DVLOG(n), SML_DVLOG_IF(n, cond)         the same, but compiled in only with
+//                                               -DSWITCHML_DEBUG (DEBUG=1 builds), like glog's DVLOG
+//
 // Verbosity comes from the environment variable SWITCHML_V (default 0) or
-// SetVerbosity(). FATAL raises an exception instead of aborting so that language
+// SetVerbosity(). Single source files can be given their own level, like glog's --vmodule
+// that the reference exposes: SWITCHML_VMODULE="udp_backend=3,control=2" or SetVModule();
+// a module is the file's name without directory and extension. FATAL raises an exception instead of aborting so that language
 // bindings can surface the message; uncaught it still terminates the process.
 #ifndef SWITCHML_LOG_H_
 #define SWITCHML_LOG_H_
@@ -28,6 +33,10 @@ enum LogSeverity { LOG_INFO = 0, LOG_WARNING = 1, LOG_ERROR = 2, LOG_FATAL = 3 }
 
 int GetVerbosity();
 void SetVerbosity(int v);
+// Per-file levels: "name=level,name=level"; an empty string removes them all.
+void SetVModule(const char* spec);
+// True if a SML_VLOG(n) in `file` prints.
+bool VlogIsOn(const char* file, int n);
 // Redirect log lines to a callback (used by tests); nullptr restores stderr.
 void SetLogSink(void (*sink)(int severity, const char* line));
 
@@ -57,11 +66,18 @@ struct LogVoidify {
 #define SML_LOG_FATAL ::switchml::LogMessage(__FILE__, __LINE__, ::switchml::LOG_FATAL).stream()
 #define SML_LOG(sev) SML_LOG_##sev
 
-#define SML_VLOG_IS_ON(n) ((n) <= ::switchml::GetVerbosity())
+#define SML_VLOG_IS_ON(n) (::switchml::VlogIsOn(__FILE__, (n)))
 #define SML_VLOG(n) \
   !SML_VLOG_IS_ON(n) ? (void)0 : ::switchml::LogVoidify() & SML_LOG(INFO)
 #define SML_VLOG_IF(n, cond) \
   !(SML_VLOG_IS_ON(n) && (cond)) ? (void)0 : ::switchml::LogVoidify() & SML_LOG(INFO)
+#ifdef SWITCHML_DEBUG
+#define SML_DVLOG(n) SML_VLOG(n)
+#define SML_DVLOG_IF(n, cond) SML_VLOG_IF(n, cond)
+#else
+#define SML_DVLOG(n) true ? (void)0 : ::switchml::LogVoidify() & SML_LOG(INFO)
+#define SML_DVLOG_IF(n, cond) true ? (void)0 : ::switchml::LogVoidify() & SML_LOG(INFO)
+#endif
 #define SML_CHECK(cond) \
   (cond) ? (void)0 : ::switchml::LogVoidify() & SML_LOG(FATAL) << "Check failed: " #cond " "
 

@@ -20,6 +20,8 @@ const char* sml_last_error(void);
 /* 1 if the library was compiled with -DSWITCHML_CHECKED (kernels verify their geometry). */
 int sml_checked_build(void);
 void sml_set_verbosity(int v);
+/* per-file verbosity, "name=level,name=level" (file name without directory and extension) */
+void sml_set_vmodule(const char* spec);
 
 /* Lifecycle (switchml::Context::Start / Stop). `ini_text` is the content of a
  * switchml.cfg; NULL or "" searches the default files. apply_env != 0 lets
