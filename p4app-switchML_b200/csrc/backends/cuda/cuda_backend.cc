@@ -15,6 +15,7 @@
 #include <chrono>
 #include <condition_variable>
 #include <cstdio>
+#include <cctype>
 #include <cstdlib>
 #include <cstring>
 #include <deque>
@@ -122,6 +123,7 @@ class CudaBackend : public CudaBackendInterface {
  private:
   void LauncherLoop();
   void CompletionLoop();
+  void BindServiceThread(const char* what);
   // Enqueue the kernels of `job` on `stream`; fills `f`. Caller holds launch_mu_.
   // `capturing`: the stream is being captured into a CUDA graph; nothing that belongs to
   // this one submission (events, status slot, buffer parity) may end up in the launch.
@@ -513,8 +515,27 @@ bool CudaBackend::OnSubmit(const std::shared_ptr<Job>& job) {
   return true;
 }
 
+// [backend.cuda] numa_bind: keep a service thread on the cores next to the GPU (the reference
+// pins its RDMA worker threads to the NIC's NUMA node, rdma_worker_thread.cc:77).
+void CudaBackend::BindServiceThread(const char* what) {
+  if (!config_.backend_.cuda.numa_bind) return;
+  char bus[32] = {0};
+  if (cudaDeviceGetPCIBusId(bus, sizeof(bus), device_) != cudaSuccess) {
+    cudaGetLastError();
+    return;
+  }
+  for (char* p = bus; *p; ++p) *p = static_cast<char>(tolower(*p));  // sysfs spells bus ids in lower case
+  int node = GetDeviceNuma(bus);
+  if (node < 0 || !BindToNumaNode(node)) {
+    SML_VLOG(1) << what << " thread: no NUMA binding (device " << bus << ", node " << node << ")";
+  } else {
+    SML_VLOG(1) << what << " thread bound to NUMA node " << node << " of device " << bus;
+  }
+}
+
 void CudaBackend::LauncherLoop() {
   cudaSetDevice(device_);
+  BindServiceThread("launcher");
   JobSlice js;
   while (context_.GetContextState() == Context::RUNNING && context_.GetJobSlice(0, js)) {
     InFlight f;
@@ -539,6 +560,7 @@ void CudaBackend::LauncherLoop() {
 
 void CudaBackend::CompletionLoop() {
   cudaSetDevice(device_);
+  BindServiceThread("completion");
   Stats& stats = context_.GetStats();
   for (;;) {
     InFlight f;

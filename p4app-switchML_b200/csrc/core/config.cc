@@ -117,6 +117,7 @@ bool Config::LoadFromString(const std::string& text, const std::string& origin) 
   opts["backend.cuda.launch"] = SML_OPT_STRING(backend_.cuda.launch);
   opts["backend.cuda.rendezvous_dir"] = SML_OPT_STRING(backend_.cuda.rendezvous_dir);
   opts["backend.cuda.tune"] = SML_OPT_UNSIGNED(backend_.cuda.tune);
+  opts["backend.cuda.numa_bind"] = SML_OPT_BOOL(backend_.cuda.numa_bind);
   opts["backend.cuda.wait_timeout_ms"] = [this](const std::string& v) {
     return ParseDouble(v, &backend_.cuda.wait_timeout_ms);
   };
@@ -347,7 +348,8 @@ std::string Config::ToString() const {
       << "    average = " << (c.average ? "true" : "false") << "\n"
       << "    launch = " << c.launch << "\n"
       << "    rendezvous_dir = " << c.rendezvous_dir << "\n"
-      << "    wait_timeout_ms = " << c.wait_timeout_ms << "\n";
+      << "    wait_timeout_ms = " << c.wait_timeout_ms << "\n"
+      << "    numa_bind = " << (c.numa_bind ? "true" : "false") << "\n";
   }
   for (const auto& kv : ignored_) o << "  (ignored) " << kv.first << " = " << kv.second << "\n";
   return o.str();

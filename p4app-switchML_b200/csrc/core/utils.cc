@@ -87,4 +87,30 @@ int GetDeviceNuma(const std::string& pci_bus_id) {
   return node;
 }
 
+bool GetCoresNuma(int node, int* out, int max_out, int* count) {
+  *count = 0;
+  if (node < 0) return false;
+  std::string path = "/sys/devices/system/node/node" + std::to_string(node) + "/cpulist";
+  FILE* f = fopen(path.c_str(), "r");
+  if (!f) return false;
+  char buf[4096];
+  size_t n = fread(buf, 1, sizeof(buf) - 1, f);
+  fclose(f);
+  buf[n] = 0;
+  std::string spec(buf);
+  while (!spec.empty() && (spec.back() == '\n' || spec.back() == ' ')) spec.pop_back();
+  std::string err;
+  return ParseCoreList(spec, &err, out, max_out, count) && *count > 0;
+}
+
+bool BindToNumaNode(int node) {
+  int ids[1024], count = 0;
+  if (!GetCoresNuma(node, ids, 1024, &count)) return false;
+  cpu_set_t set;
+  CPU_ZERO(&set);
+  for (int i = 0; i < count; i++)
+    if (ids[i] >= 0 && ids[i] < CPU_SETSIZE) CPU_SET(ids[i], &set);
+  return sched_setaffinity(0, sizeof(set), &set) == 0;
+}
+
 }  // namespace switchml

@@ -70,6 +70,20 @@ static void TestLogging() {
   SetVerbosity(before);
 }
 
+static void TestNumaHelpers() {
+  int ids[1024], count = 0;
+  // Node 0 exists on every Linux machine with NUMA information; without it the helpers say no.
+  if (GetCoresNuma(0, ids, 1024, &count)) {
+    EXPECT(count > 0 && ids[0] >= 0);
+    std::thread t([] { EXPECT(BindToNumaNode(0)); });
+    t.join();
+  } else {
+    EXPECT(count == 0 && !BindToNumaNode(0));
+  }
+  EXPECT(!GetCoresNuma(-1, ids, 1024, &count) && !GetCoresNuma(4095, ids, 1024, &count));
+  EXPECT(GetDeviceNuma("ffff:ff:1f.7") == -1);
+}
+
 static void TestStaticSlice() {
   // 10 elements over 4 threads: 3,3,2,2 at offsets 0,3,6,8 (remainder to the first threads)
   Numel off, len;
@@ -412,7 +426,7 @@ static void TestContextDummy() {
 int main() {
   SetVerbosity(0);
   struct { const char* name; void (*fn)(); } tests[] = {
-      {"logging", TestLogging}, {"static_slice", TestStaticSlice}, {"barrier", TestBarrier}, {"job_fsm", TestJobFsm},
+      {"logging", TestLogging}, {"numa_helpers", TestNumaHelpers}, {"static_slice", TestStaticSlice}, {"barrier", TestBarrier}, {"job_fsm", TestJobFsm},
       {"timeout_queue", TestTimeoutQueue}, {"soft_switch", TestSoftSwitch},
       {"quant_math", TestQuantMath}, {"control_plane", TestControlPlane},
       {"context_dummy", TestContextDummy},

@@ -42,6 +42,11 @@ bool ParseCoreList(const std::string& spec, std::string* error, int* out, int ma
 bool BindToCore(int core);
 // NUMA node of a PCI device given its sysfs bus id ("0000:1b:00.0"), -1 if unknown.
 int GetDeviceNuma(const std::string& pci_bus_id);
+// The CPU cores of a NUMA node (sysfs cpulist; the reference parses `lscpu` for the same,
+// rdma_utils.h:135-170). False if the node is unknown.
+bool GetCoresNuma(int node, int* out, int max_out, int* count);
+// Restrict the calling thread to the cores of `node`; false if unknown or refused.
+bool BindToNumaNode(int node);
 
 }  // namespace switchml
 #endif  // SWITCHML_UTILS_H_

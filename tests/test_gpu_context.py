@@ -185,3 +185,15 @@ def test_uint8_allreduce_single_rank(ctx):
     ctx.all_reduce(x, y)
     torch.cuda.synchronize()
     assert torch.equal(x, y)
+
+
+def test_service_threads_can_be_bound_to_the_gpus_numa_node(ctx):
+    """numa_bind = true only narrows the CPU affinity of the launcher and completion threads
+    (or does nothing where the machine has no NUMA information); jobs run as before."""
+    assert ctx.start(sml.make_config("cuda", packet_numel=256, mode="float_sum", launch="worker", numa_bind=True))
+    assert "numa_bind = true" in ctx.config_dump()
+    x = torch.randn(1 << 20, device="cuda")
+    y = torch.empty_like(x)
+    for _ in range(3):
+        assert ctx.all_reduce_async(x, y).wait(20000) == sml.JobStatus.FINISHED
+    assert torch.equal(x, y)
