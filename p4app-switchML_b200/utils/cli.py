@@ -77,8 +77,9 @@ class Cli(cmd.Cmd):
 
     def do_set_switch_address(self, arg):
         "set_switch_address <ip> <udp port>: move the data plane; sessions started afterwards use it."
+        from .common import validate_ip, validate_port
         parts = arg.split()
-        if len(parts) != 2:
+        if len(parts) != 2 or not validate_ip(parts[0]) or not validate_port(parts[1]):
             self.stdout.write("usage: set_switch_address <ip> <udp port>\n")
             return
         self._send("SET address %s %s" % (parts[0], parts[1]))
@@ -105,9 +106,10 @@ class Cli(cmd.Cmd):
 
     def do_set_drop_probabilities(self, arg):
         "set_drop_probabilities <ingress> <egress> [seed]: lose packets on purpose (0..1)."
+        from .common import validate_probability
         parts = arg.split()
-        if len(parts) < 2:
-            self.stdout.write("usage: set_drop_probabilities <ingress> <egress> [seed]\n")
+        if len(parts) < 2 or not all(validate_probability(p) for p in parts[:2]):
+            self.stdout.write("usage: set_drop_probabilities <ingress> <egress> [seed], probabilities in [0, 1]\n")
             return
         self._send("SET drop " + " ".join(parts[:3]))
 

@@ -64,3 +64,21 @@ def test_make_config_routes_keys():
     text = sml.make_config("dummy", rank=0, num_workers=2, packet_numel=64, bandwidth=0)
     assert "[general]" in text and "packet_numel = 64" in text.split("[backend.dummy]")[0]
     assert "bandwidth = 0" in text.split("[backend.dummy]")[1]
+
+
+def test_wire_constants_and_validators():
+    from switchml_b200.utils.common import (HEADER, PacketSize, WireType, pack_header, unpack_header, validate_ip,
+                                            validate_port, validate_probability)
+    assert HEADER.size == 20
+    assert [s.numel for s in PacketSize] == [32, 64, 128, 256] and PacketSize.from_numel(256) is PacketSize.MTU_1024
+    with pytest.raises(ValueError):
+        PacketSize.from_numel(100)
+    raw = pack_header(WireType.DATA, worker=3, thread=2, pkt_id=77, pool_index=0x8005, numel=64, exponent=-4,
+                      job_tag=300, session=0x12345)
+    h = unpack_header(raw + b"\0" * 256)
+    assert h == {"type": 0, "job_tag": 300 & 0xFF, "worker": 3, "pkt_id": 77, "slot": 5, "set": 1, "numel": 64,
+                 "exponent": -4, "thread": 2, "session_lo": 0x2345}
+    assert unpack_header(b"short") is None and unpack_header(b"\0" * 20) is None
+    assert validate_ip("10.0.0.1") and not validate_ip("10.0.0.256") and not validate_ip("ten")
+    assert validate_port("48864") and not validate_port("70000") and not validate_port("x")
+    assert validate_probability("0.5") and not validate_probability("-0.1") and not validate_probability("2")

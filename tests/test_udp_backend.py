@@ -157,10 +157,11 @@ def test_console_against_standalone_controller(ports):
         assert "Unknown syntax: bogus" in text and "set_drop_probabilities" in text
 
         # The data plane answers echo requests (the switch's ping), also after it has moved.
+        from switchml_b200.utils.common import WireType, pack_header, unpack_header
+
         def echo(port):
             import socket
-            import struct
-            pkt = struct.pack("!IBBHIHHbBH", 0x534d4c31, 3, 0, 5, 1234, 0, 2, 0, 1, 0) + b"switchml"
+            pkt = pack_header(WireType.ECHO_REQUEST, worker=5, thread=1, pkt_id=1234, numel=2) + b"switchml"
             with socket.socket(socket.AF_INET, socket.SOCK_DGRAM) as so:
                 so.settimeout(2.0)
                 so.sendto(pkt, ("127.0.0.1", port))
@@ -171,7 +172,10 @@ def test_console_against_standalone_controller(ports):
             return data
 
         reply = echo(ports[1])
-        assert reply is not None and reply[4] == 4 and reply[5:] == struct_tail(reply)
+        assert reply is not None and reply[5:] == struct_tail(reply)
+        head = unpack_header(reply)
+        assert head["type"] == WireType.ECHO_REPLY and head["worker"] == 5 and head["thread"] == 1
+        assert head["pkt_id"] == 1234 and head["numel"] == 2
         from conftest import free_port
         moved = free_port()
         out.truncate(0)
@@ -180,7 +184,10 @@ def test_console_against_standalone_controller(ports):
         assert "udp_port %d" % moved in out.getvalue()
         assert echo(moved) is not None and echo(ports[1]) is None
         cli.onecmd("set_switch_address 127.0.0.1")
-        assert "usage: set_switch_address" in out.getvalue()
+        cli.onecmd("set_switch_address 300.1.1.1 5000")
+        assert out.getvalue().count("usage: set_switch_address") == 2
+        cli.onecmd("set_drop_probabilities 1.5 0")
+        assert "probabilities in [0, 1]" in out.getvalue()
     finally:
         lib().sml_controller_stop(srv)
 
