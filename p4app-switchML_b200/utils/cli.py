@@ -121,6 +121,42 @@ class Cli(cmd.Cmd):
         "Check that the controller answers."
         self._send("PING")
 
+    def do_ping_switch(self, arg):
+        "ping_switch [count]: echo requests to the UDP data plane, with round-trip times (the switch's ICMP echo)."
+        import socket
+        import time
+        from .common import WireType, pack_header, unpack_header
+        try:
+            fields = controller_command(self.ip, self.port, "SHOW address").split()
+            where = (fields[fields.index("ip") + 1], int(fields[fields.index("udp_port") + 1]))
+            count = int(arg.strip() or 3)
+        except Exception as e:
+            self.stdout.write("error: %s\n" % e)
+            return
+        if where[0] == "0.0.0.0":
+            where = (self.ip, where[1])
+        if where[1] == 0:
+            self.stdout.write("this controller has no data plane\n")
+            return
+        answered = 0
+        with socket.socket(socket.AF_INET, socket.SOCK_DGRAM) as so:
+            so.settimeout(1.0)
+            for seq in range(count):
+                payload = b"ping%04d" % seq
+                t0 = time.perf_counter()
+                try:
+                    so.sendto(pack_header(WireType.ECHO_REQUEST, worker=0, pkt_id=seq, numel=2) + payload, where)
+                    data, _ = so.recvfrom(2048)
+                except (socket.timeout, OSError):
+                    self.stdout.write("seq %d: no answer from %s:%d\n" % (seq, where[0], where[1]))
+                    continue
+                head = unpack_header(data)
+                if head and head["type"] == WireType.ECHO_REPLY and data.endswith(payload):
+                    answered += 1
+                    self.stdout.write("seq %d: reply from %s:%d in %.3f ms\n"
+                                      % (seq, where[0], where[1], (time.perf_counter() - t0) * 1e3))
+        self.stdout.write("%d of %d echo requests answered\n" % (answered, count))
+
     def do_history(self, arg):
         "Commands entered so far."
         for i, h in enumerate(self._history):

@@ -183,6 +183,8 @@ def test_console_against_standalone_controller(ports):
         cli.onecmd("show_switch_address")
         assert "udp_port %d" % moved in out.getvalue()
         assert echo(moved) is not None and echo(ports[1]) is None
+        cli.onecmd("ping_switch 2")
+        assert "2 of 2 echo requests answered" in out.getvalue()
         cli.onecmd("set_switch_address 127.0.0.1")
         cli.onecmd("set_switch_address 300.1.1.1 5000")
         assert out.getvalue().count("usage: set_switch_address") == 2
