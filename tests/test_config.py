@@ -82,3 +82,14 @@ def test_wire_constants_and_validators():
     assert validate_ip("10.0.0.1") and not validate_ip("10.0.0.256") and not validate_ip("ten")
     assert validate_port("48864") and not validate_port("70000") and not validate_port("x")
     assert validate_probability("0.5") and not validate_probability("-0.1") and not validate_probability("2")
+
+
+def test_api_reference_is_up_to_date():
+    """docs/api.md is generated from the public headers; regenerate it after editing them."""
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = os.path.join(root, "p4app-switchML_b200", "docs", "make_api_reference.py")
+    r = subprocess.run([sys.executable, script, "--check"], capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr
