@@ -45,7 +45,7 @@ INCLUDES = ["-I" + os.path.join(ROOT, "include"), "-I" + os.path.join(ROOT, "csr
 LIB_SOURCES = [
     "csrc/core/log.cc", "csrc/core/config.cc", "csrc/core/job.cc", "csrc/core/utils.cc",
     "csrc/core/stats.cc", "csrc/core/scheduler.cc", "csrc/core/context.cc", "csrc/core/backend.cc",
-    "csrc/ppp/cpu_exponent_quantizer_ppp.cc",
+    "csrc/ppp/cpu_exponent_quantizer_ppp.cc", "csrc/simd/simd_kernels.cc",
     "csrc/backends/dummy/dummy_backend.cc",
     "csrc/backends/softswitch/soft_switch.cc", "csrc/backends/softswitch/udp_backend.cc",
     "csrc/rendezvous/control.cc",

@@ -5,6 +5,8 @@
 
 #include <cstddef>
 #include <cstring>
+
+#include "simd/simd_kernels.h"
 #include <sstream>
 
 namespace switchml {
@@ -82,11 +84,7 @@ void SoftSwitch::Emit(const SlotSet& s, uint16_t pool_index, int dest_worker, in
   h.thread_id = static_cast<uint8_t>(dest_thread);
   h.session_lo = htons(static_cast<uint16_t>(session_id_));
   memcpy(o.bytes.data(), &h, sizeof(h));
-  uint32_t* p = reinterpret_cast<uint32_t*>(o.bytes.data() + sizeof(h));
-  for (uint16_t i = 0; i < s.numel; i++) {
-    uint32_t be = htonl(static_cast<uint32_t>(s.values[i]));
-    memcpy(p + i, &be, 4);
-  }
+  simd::Swap32(s.values.data(), s.numel, reinterpret_cast<int32_t*>(o.bytes.data() + sizeof(h)));
   worker_counters_[dest_worker].tx_packets++;
   worker_counters_[dest_worker].tx_bytes += o.bytes.size();
   out->push_back(std::move(o));
@@ -149,12 +147,8 @@ void SoftSwitch::Process(const uint8_t* data, size_t len, std::vector<SwitchOutp
   const uint8_t* payload = data + sizeof(h);
   if (cur.remaining == 0) {
     // First packet of a new use of this slot set: overwrite.
-    cur.values.resize(numel);
-    for (uint16_t i = 0; i < numel; i++) {
-      uint32_t be;
-      memcpy(&be, payload + 4 * i, 4);
-      cur.values[i] = static_cast<int32_t>(ntohl(be));
-    }
+    cur.values.assign(numel, 0);
+    simd::AddWire(payload, numel, cur.values.data());
     cur.exponent = h.exponent;
     cur.numel = numel;
     cur.pkt_id = ntohl(h.pkt_id);
@@ -163,12 +157,7 @@ void SoftSwitch::Process(const uint8_t* data, size_t len, std::vector<SwitchOutp
     cur.remaining = static_cast<uint32_t>(num_workers_ - 1);
   } else {
     uint16_t n = numel < cur.numel ? numel : cur.numel;
-    for (uint16_t i = 0; i < n; i++) {
-      uint32_t be;
-      memcpy(&be, payload + 4 * i, 4);
-      // wrapping add, as the switch register ALUs do
-      cur.values[i] = static_cast<int32_t>(static_cast<uint32_t>(cur.values[i]) + ntohl(be));
-    }
+    simd::AddWire(payload, n, cur.values.data());  // wrapping add, as the switch register ALUs do
     if (h.exponent > cur.exponent) cur.exponent = h.exponent;
     cur.remaining--;
   }

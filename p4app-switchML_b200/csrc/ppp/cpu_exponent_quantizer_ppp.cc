@@ -7,6 +7,7 @@
 #include <algorithm>
 #include <cmath>
 
+#include "simd/simd_kernels.h"
 #include "switchml/log.h"
 #include "switchml/quant_math.h"
 
@@ -59,18 +60,16 @@ void CpuExponentQuantizerPPP::PreprocessSingle(uint64_t ltu_id, void* entries_pt
       uint64_t k = ltu_id - batch_;
       const float* x = in + k * ltu_numel_;
       Numel n = LtuNumel(k);
-      float sf = scale_[k];
-      for (Numel i = 0; i < n; i++) wire[i] = htonl(static_cast<uint32_t>(quant::Quantize(x[i], sf)));
+      simd::QuantizeToWire(x, n, scale_[k], wire);
     }
     if (ltu_id < total_ltus_) {
       // Exponent: of the LTU with this id, sent one batch early.
-      float m = BlockMaxAbs(in + ltu_id * ltu_numel_, LtuNumel(ltu_id));
+      float m = simd::BlockMaxAbs(in + ltu_id * ltu_numel_, LtuNumel(ltu_id));
       *static_cast<int8_t*>(extra_info) = static_cast<int8_t>(quant::LocalExponent(m));
     }
   } else if (t.data_type == INT32) {
     const int32_t* x = static_cast<const int32_t*>(t.in_ptr) + ltu_id * ltu_numel_;
-    Numel n = LtuNumel(ltu_id);
-    for (Numel i = 0; i < n; i++) wire[i] = htonl(static_cast<uint32_t>(x[i]));
+    simd::Swap32(x, LtuNumel(ltu_id), wire);
   } else {
     SML_LOG(FATAL) << "worker thread " << worker_tid_ << ": unsupported data type "
                    << DataTypeName(t.data_type);
@@ -86,10 +85,7 @@ void CpuExponentQuantizerPPP::PostprocessSingle(uint64_t ltu_id, void* entries_p
       uint64_t k = ltu_id - batch_;
       float* y = static_cast<float*>(t.out_ptr) + k * ltu_numel_;
       Numel n = LtuNumel(k);
-      float sf = scale_[k];
-      for (Numel i = 0; i < n; i++) {
-        y[i] = quant::Dequantize(static_cast<int32_t>(ntohl(static_cast<uint32_t>(wire[i]))), sf);
-      }
+      simd::DequantizeFromWire(wire, n, scale_[k], y);
     }
     if (ltu_id < total_ltus_) {
       int e = *static_cast<const int8_t*>(extra_info);
@@ -97,8 +93,7 @@ void CpuExponentQuantizerPPP::PostprocessSingle(uint64_t ltu_id, void* entries_p
     }
   } else if (t.data_type == INT32) {
     int32_t* y = static_cast<int32_t*>(t.out_ptr) + ltu_id * ltu_numel_;
-    Numel n = LtuNumel(ltu_id);
-    for (Numel i = 0; i < n; i++) y[i] = static_cast<int32_t>(ntohl(static_cast<uint32_t>(wire[i])));
+    simd::Swap32(wire, LtuNumel(ltu_id), y);
   } else {
     SML_LOG(FATAL) << "worker thread " << worker_tid_ << ": unsupported data type "
                    << DataTypeName(t.data_type);

@@ -14,6 +14,7 @@
 #include "backends/timeout_queue.h"
 #include "ppp/cpu_exponent_quantizer_ppp.h"
 #include "rendezvous/control.h"
+#include "simd/simd_kernels.h"
 #include "switchml/context.h"
 #include "switchml/log.h"
 #include "switchml/quant_math.h"
@@ -68,6 +69,55 @@ static void TestLogging() {
   EXPECT(threw);
   SetLogSink(nullptr);
   SetVerbosity(before);
+}
+
+static void TestSimdMatchesScalar() {
+  // Whatever the AVX-512 loops compute must be what the scalar loops compute, bit for bit,
+  // including NaN, infinities, denormals, values that saturate and every tail length.
+  simd::Enable(true);
+  if (!simd::Enabled()) {
+    printf("  (no avx512f+avx512bw on this CPU: scalar loops only)\n");
+    return;
+  }
+  std::vector<float> x(1000);
+  uint32_t seed = 12345;
+  auto next = [&] { seed = seed * 1664525u + 1013904223u; return seed; };
+  for (size_t i = 0; i < x.size(); i++) {
+    uint32_t bits = next();
+    memcpy(&x[i], &bits, 4);  // random bit patterns: all exponents, NaNs, infinities, denormals
+  }
+  x[3] = 0.0f; x[4] = -0.0f; x[5] = 1e30f; x[6] = -1e30f; x[7] = 0.5f; x[8] = 1.5f; x[9] = 2.5f; x[10] = -2.5f;
+  const float sfs[] = {1.0f, 1073741823.5f, 3.0e-30f, 2.5e9f, quant::ScaleFactor(-3, 8), quant::ScaleFactor(127, 3)};
+  for (size_t n : {size_t(0), size_t(1), size_t(15), size_t(16), size_t(17), size_t(64), size_t(255), size_t(1000)}) {
+    for (float sf : sfs) {
+      std::vector<int32_t> a(n + 1, 0x5a5a5a5a), b(n + 1, 0x5a5a5a5a);
+      std::vector<float> ya(n + 1, -1.0f), yb(n + 1, -1.0f);
+      simd::Enable(true);
+      float ma = simd::BlockMaxAbs(x.data(), n);
+      simd::QuantizeToWire(x.data(), n, sf, a.data());
+      simd::DequantizeFromWire(a.data(), n, sf, ya.data());
+      simd::Enable(false);
+      float mb = simd::BlockMaxAbs(x.data(), n);
+      simd::QuantizeToWire(x.data(), n, sf, b.data());
+      simd::DequantizeFromWire(b.data(), n, sf, yb.data());
+      EXPECT(memcmp(&ma, &mb, 4) == 0);
+      EXPECT(memcmp(a.data(), b.data(), (n + 1) * 4) == 0);   // n + 1: nothing written past the end
+      EXPECT(memcmp(ya.data(), yb.data(), (n + 1) * 4) == 0);
+    }
+    std::vector<int32_t> in(n), s1(n + 1, 7), s2(n + 1, 7), acc1(n + 1, 1000), acc2(n + 1, 1000);
+    for (size_t i = 0; i < n; i++) in[i] = static_cast<int32_t>(next());
+    std::vector<uint8_t> wire(4 * n + 3);
+    memcpy(wire.data() + 1, in.data(), 4 * n);   // odd address on purpose
+    simd::Enable(true);
+    simd::Swap32(in.data(), n, s1.data());
+    simd::AddWire(wire.data() + 1, n, acc1.data());
+    simd::Enable(false);
+    simd::Swap32(in.data(), n, s2.data());
+    simd::AddWire(wire.data() + 1, n, acc2.data());
+    EXPECT(s1 == s2 && acc1 == acc2);
+    if (n) EXPECT(static_cast<uint32_t>(s1[0]) == htonl(static_cast<uint32_t>(in[0])));
+  }
+  simd::Enable(true);
 }
 
 static void TestNumaHelpers() {
@@ -426,7 +476,7 @@ static void TestContextDummy() {
 int main() {
   SetVerbosity(0);
   struct { const char* name; void (*fn)(); } tests[] = {
-      {"logging", TestLogging}, {"numa_helpers", TestNumaHelpers}, {"static_slice", TestStaticSlice}, {"barrier", TestBarrier}, {"job_fsm", TestJobFsm},
+      {"logging", TestLogging}, {"numa_helpers", TestNumaHelpers}, {"simd_matches_scalar", TestSimdMatchesScalar}, {"static_slice", TestStaticSlice}, {"barrier", TestBarrier}, {"job_fsm", TestJobFsm},
       {"timeout_queue", TestTimeoutQueue}, {"soft_switch", TestSoftSwitch},
       {"quant_math", TestQuantMath}, {"control_plane", TestControlPlane},
       {"context_dummy", TestContextDummy},
