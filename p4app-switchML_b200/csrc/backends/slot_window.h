@@ -32,8 +32,12 @@ struct SlotPacket {
 class SlotTransport {
  public:
   virtual ~SlotTransport() {}
-  // Hand one filled packet to the wire. `first_use` is false for a retransmission.
+  // Hand one filled packet to the wire. The transport may hold it back until Flush(); the
+  // packet's payload stays untouched until the slot has been answered.
   virtual void Send(const SlotPacket& p, bool retransmission) = 0;
+  // Put everything handed to Send() on the wire now (transports that send in bursts, like
+  // the reference's tx buffer with its drain timer, dpdk_worker_thread.cc:121-133,282-288).
+  virtual void Flush() {}
   // Collect results that arrived; for each, copy payload/exponent into the matching
   // slot's SlotPacket (found through `slots`) and append the slot index to `ready`.
   // May block briefly. Returns false when the transport was shut down.
@@ -82,6 +86,7 @@ SlotWindowResult RunSlotWindow(const JobSlice& js, PrePostProcessor& ppp, SlotTr
     tr.Send(slots[i], false);
     res.sent++;
   }
+  tr.Flush();
   uint64_t answered = 0;
   std::vector<int> ready;
   while (answered < total) {
@@ -90,6 +95,7 @@ SlotWindowResult RunSlotWindow(const JobSlice& js, PrePostProcessor& ppp, SlotTr
     if (!tr.Poll(slots, &ready)) { res.ok = false; break; }
     if (ready.empty()) {
       uint64_t t = tr.OnIdle(slots);
+      if (t) tr.Flush();
       res.timeouts += t;
       res.sent += t;
       continue;
@@ -108,6 +114,7 @@ SlotWindowResult RunSlotWindow(const JobSlice& js, PrePostProcessor& ppp, SlotTr
         res.sent++;
       }
     }
+    tr.Flush();
   }
   tr.EndSlice();
   ppp.CleanupJobSlice();

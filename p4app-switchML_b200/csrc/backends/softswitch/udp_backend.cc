@@ -28,7 +28,19 @@ class UdpTransport : public SlotTransport {
   UdpTransport(const Config& cfg, WorkerTid tid, int fd, uint64_t session_id, int window)
       : cfg_(cfg), tid_(tid), fd_(fd), session_id_(session_id), window_(window),
         set_bits_(window, 0), answered_(window, 0) {
-    buf_.resize(kWireMaxBytes + 64);
+    tx_headers_.resize(kBurst);
+    tx_iov_.resize(2 * kBurst);
+    tx_msgs_.resize(kBurst);
+    rx_buf_.resize(static_cast<size_t>(kBurst) * kRxStride);
+    rx_iov_.resize(kBurst);
+    rx_msgs_.resize(kBurst);
+    for (int i = 0; i < kBurst; i++) {
+      rx_iov_[i].iov_base = rx_buf_.data() + static_cast<size_t>(i) * kRxStride;
+      rx_iov_[i].iov_len = kRxStride;
+      memset(&rx_msgs_[i], 0, sizeof(mmsghdr));
+      rx_msgs_[i].msg_hdr.msg_iov = &rx_iov_[i];
+      rx_msgs_[i].msg_hdr.msg_iovlen = 1;
+    }
   }
 
   void BeginSlice(const JobSlice& js, uint64_t, int batch) override {
@@ -52,7 +64,10 @@ class UdpTransport : public SlotTransport {
     }
     uint16_t pool_index = static_cast<uint16_t>(tid_ * window_ + phys) |
                           (set_bits_[phys] ? kSetBit : 0);
-    WireHeader h;
+    // Header and payload leave as two pieces of one datagram (no copy); the burst goes out
+    // with one system call in Flush().
+    if (tx_count_ == kBurst) Flush();
+    WireHeader& h = tx_headers_[tx_count_];
     h.magic = htonl(kWireMagic);
     h.type = WIRE_DATA;
     h.job_tag = job_tag_;
@@ -63,10 +78,29 @@ class UdpTransport : public SlotTransport {
     h.exponent = p.exponent;
     h.thread_id = static_cast<uint8_t>(tid_);
     h.session_lo = htons(static_cast<uint16_t>(session_id_));
-    memcpy(buf_.data(), &h, sizeof(h));
-    memcpy(buf_.data() + sizeof(h), p.payload, p.numel * 4u);
-    send(fd_, buf_.data(), sizeof(h) + p.numel * 4u, 0);
+    iovec* v = &tx_iov_[2 * tx_count_];
+    v[0].iov_base = &h;
+    v[0].iov_len = sizeof(h);
+    v[1].iov_base = p.payload;
+    v[1].iov_len = p.numel * 4u;
+    memset(&tx_msgs_[tx_count_], 0, sizeof(mmsghdr));
+    tx_msgs_[tx_count_].msg_hdr.msg_iov = v;
+    tx_msgs_[tx_count_].msg_hdr.msg_iovlen = 2;
+    tx_count_++;
     timers_->Push(p.slot, std::chrono::steady_clock::now());
+  }
+
+  void Flush() override {
+    int done = 0;
+    while (done < tx_count_) {
+      int r = sendmmsg(fd_, tx_msgs_.data() + done, static_cast<unsigned>(tx_count_ - done), 0);
+      if (r <= 0) {
+        if (r < 0 && (errno == EINTR)) continue;
+        break;  // a lost datagram is what the retransmission timers are for
+      }
+      done += r;
+    }
+    tx_count_ = 0;
   }
 
   bool Poll(std::vector<SlotPacket>& slots, std::vector<int>* ready) override {
@@ -74,17 +108,18 @@ class UdpTransport : public SlotTransport {
     int r = poll(&pf, 1, 1);
     if (r < 0 && errno != EINTR) return false;
     if (r <= 0) return true;
-    for (int burst = 0; burst < 64; burst++) {
-      ssize_t n = recv(fd_, buf_.data(), buf_.size(), MSG_DONTWAIT);
-      if (n <= 0) break;
+    int got = recvmmsg(fd_, rx_msgs_.data(), kBurst, MSG_DONTWAIT, nullptr);
+    for (int m = 0; m < got; m++) {
+      const uint8_t* data = rx_buf_.data() + static_cast<size_t>(m) * kRxStride;
+      size_t n = rx_msgs_[m].msg_len;
       WireHeader h;
-      if (static_cast<size_t>(n) < sizeof(h)) { ready->push_back(-1); continue; }
-      memcpy(&h, buf_.data(), sizeof(h));
+      if (n < sizeof(h)) { ready->push_back(-1); continue; }
+      memcpy(&h, data, sizeof(h));
       uint16_t numel = ntohs(h.numel);
       uint16_t pool_index = ntohs(h.pool_index);
       int phys = static_cast<int>(pool_index & ~kSetBit) - tid_ * window_;
       bool ok = ntohl(h.magic) == kWireMagic && (h.type == WIRE_RESULT || h.type == WIRE_RESULT_RETX) &&
-                static_cast<size_t>(n) == sizeof(h) + numel * 4u && phys >= 0 && phys < window_ &&
+                n == sizeof(h) + numel * 4u && phys >= 0 && phys < window_ &&
                 h.job_tag == job_tag_;
       int s = -1;
       if (ok) {
@@ -95,7 +130,7 @@ class UdpTransport : public SlotTransport {
       }
       if (!ok) { ready->push_back(-1); continue; }  // duplicate, stale job or foreign packet
       SlotPacket& p = slots[s];
-      memcpy(p.payload, buf_.data() + sizeof(h), numel * 4u);
+      memcpy(p.payload, data + sizeof(h), numel * 4u);
       p.exponent = h.exponent;
       mark_answered(s);
       ready->push_back(s);
@@ -132,7 +167,17 @@ class UdpTransport : public SlotTransport {
   uint8_t job_tag_ = 0;
   std::vector<uint8_t> set_bits_;
   std::vector<uint8_t> answered_;
-  std::vector<uint8_t> buf_;
+  // Bursts of up to kBurst datagrams per system call in both directions (the reference's
+  // burst_rx / burst_tx of 64, config.cc:86-88).
+  static const int kBurst = 64;
+  static const size_t kRxStride = (kWireMaxBytes + 63) / 64 * 64;
+  std::vector<WireHeader> tx_headers_;
+  std::vector<iovec> tx_iov_;
+  std::vector<mmsghdr> tx_msgs_;
+  int tx_count_ = 0;
+  std::vector<uint8_t> rx_buf_;
+  std::vector<iovec> rx_iov_;
+  std::vector<mmsghdr> rx_msgs_;
   std::unique_ptr<TimeoutQueue> timers_;
 };
 

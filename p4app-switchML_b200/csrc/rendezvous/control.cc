@@ -437,8 +437,22 @@ std::string ControlServer::Handle(const std::string& line) {
 }
 
 void ControlServer::DataPlaneLoop() {
-  std::vector<uint8_t> buf(kWireMaxBytes + 64);
+  // Datagrams are received and sent in bursts, one system call per burst (the reference's
+  // workers use rx/tx bursts of 64, config.cc:86-88; the hardware switch needs none).
+  const int kBurst = 64;
+  const size_t kStride = (kWireMaxBytes + 63) / 64 * 64;
+  std::vector<uint8_t> rx(static_cast<size_t>(kBurst) * kStride);
+  std::vector<sockaddr_in> from(kBurst);
+  std::vector<iovec> rx_iov(kBurst);
+  std::vector<mmsghdr> rx_msgs(kBurst);
+  for (int i = 0; i < kBurst; i++) {
+    rx_iov[i].iov_base = rx.data() + static_cast<size_t>(i) * kStride;
+    rx_iov[i].iov_len = kStride;
+  }
   std::vector<SwitchOutput> out;
+  std::vector<sockaddr_in> to;
+  std::vector<iovec> tx_iov;
+  std::vector<mmsghdr> tx_msgs;
   while (!stopping_) {
     int pend = pending_udp_fd_.exchange(-1);
     if (pend >= 0) {
@@ -452,18 +466,28 @@ void ControlServer::DataPlaneLoop() {
     struct pollfd p = {fd, POLLIN, 0};
     int r = poll(&p, 1, 100);
     if (r <= 0) continue;
-    for (int burst = 0; burst < 64; burst++) {
-      sockaddr_in src;
-      socklen_t sl = sizeof(src);
-      ssize_t n = recvfrom(fd, buf.data(), buf.size(), MSG_DONTWAIT, reinterpret_cast<sockaddr*>(&src), &sl);
-      if (n <= 0) break;
+    for (int i = 0; i < kBurst; i++) {
+      memset(&rx_msgs[i], 0, sizeof(mmsghdr));
+      rx_msgs[i].msg_hdr.msg_iov = &rx_iov[i];
+      rx_msgs[i].msg_hdr.msg_iovlen = 1;
+      rx_msgs[i].msg_hdr.msg_name = &from[i];
+      rx_msgs[i].msg_hdr.msg_namelen = sizeof(sockaddr_in);
+    }
+    int got = recvmmsg(fd, rx_msgs.data(), kBurst, MSG_DONTWAIT, nullptr);
+    if (got <= 0) continue;
+    out.clear();
+    to.clear();
+    for (int m = 0; m < got; m++) {
+      const uint8_t* data = rx.data() + static_cast<size_t>(m) * kStride;
+      const size_t n = rx_msgs[m].msg_len;
+      const sockaddr_in& src = from[m];
       udp_rx_packets_++;
-      udp_rx_bytes_ += static_cast<uint64_t>(n);
-      if (static_cast<size_t>(n) >= sizeof(WireHeader)) {
+      udp_rx_bytes_ += n;
+      if (n >= sizeof(WireHeader)) {
         // Learn where this worker thread listens, like a switch learns a port. Echo
         // requests may come from anybody and teach nothing.
         WireHeader h;
-        memcpy(&h, buf.data(), sizeof(h));
+        memcpy(&h, data, sizeof(h));
         int w = ntohs(h.worker_id);
         if (ntohl(h.magic) == kWireMagic && h.type != WIRE_ECHO_REQUEST && w < kMaxWorkers &&
             h.thread_id < kMaxThreads) {
@@ -471,19 +495,43 @@ void ControlServer::DataPlaneLoop() {
           learned_[w][h.thread_id] = src;
         }
       }
-      out.clear();
-      switch_.Process(buf.data(), static_cast<size_t>(n), &out);
-      for (const SwitchOutput& o : out) {
+      const size_t before = out.size();
+      switch_.Process(data, n, &out);
+      for (size_t o = before; o < out.size(); o++) {
         sockaddr_in d = src;
-        if (!o.to_sender) {
+        if (!out[o].to_sender) {
           std::lock_guard<std::mutex> lk(learned_mu_);
-          d = learned_[o.dest_worker][o.dest_thread];
+          d = learned_[out[o].dest_worker][out[o].dest_thread];
         }
-        if (d.sin_port == 0) continue;
-        sendto(fd, o.bytes.data(), o.bytes.size(), 0, reinterpret_cast<const sockaddr*>(&d), sizeof(d));
-        udp_tx_packets_++;
-        udp_tx_bytes_ += o.bytes.size();
+        to.push_back(d);
       }
+    }
+    // One sendmmsg for everything this burst produced (destinations that were never learned
+    // are skipped).
+    tx_iov.resize(out.size());
+    tx_msgs.resize(out.size());
+    size_t count = 0;
+    for (size_t o = 0; o < out.size(); o++) {
+      if (to[o].sin_port == 0) continue;
+      tx_iov[count].iov_base = out[o].bytes.data();
+      tx_iov[count].iov_len = out[o].bytes.size();
+      memset(&tx_msgs[count], 0, sizeof(mmsghdr));
+      tx_msgs[count].msg_hdr.msg_iov = &tx_iov[count];
+      tx_msgs[count].msg_hdr.msg_iovlen = 1;
+      tx_msgs[count].msg_hdr.msg_name = &to[o];
+      tx_msgs[count].msg_hdr.msg_namelen = sizeof(sockaddr_in);
+      udp_tx_bytes_ += out[o].bytes.size();
+      count++;
+    }
+    udp_tx_packets_ += count;
+    size_t done = 0;
+    while (done < count) {
+      int sent = sendmmsg(fd, tx_msgs.data() + done, static_cast<unsigned>(count - done), 0);
+      if (sent <= 0) {
+        if (sent < 0 && errno == EINTR) continue;
+        break;  // the workers' retransmission timers cover what was not sent
+      }
+      done += static_cast<size_t>(sent);
     }
   }
 }
