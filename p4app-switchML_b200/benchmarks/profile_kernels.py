@@ -9,7 +9,10 @@ emulated in one cooperative launch over peer memory, 2^24 elements per rank: inp
 outputs of 512 MiB together exceed the 126 MB L2 while staying far below a few GB);
 wgrad / wgrad_2cta (tcgen05 weight-gradient GEMM, one CTA per 128x256 tile / two CTAs per
 256x256 tile, BERT FFN shape 8192 x 4096 x 1024);
-wgrad_fc6 (VGG fc6 shape, K = 32: output-bandwidth bound). Prints CUDA-event timings.
+wgrad_fc6 (VGG fc6 shape, K = 32: output-bandwidth bound);
+local_copy (what `bench.py --gpus 1` times: a one-worker, out-of-place float_sum allreduce of
+2^26 elements through the Context, i.e. LocalCopyKernel over 256 MiB in and 256 MiB out).
+Prints CUDA-event timings.
 """
 import argparse
 import os
@@ -41,7 +44,23 @@ def main():
     ap.add_argument("--ranks", type=int, default=4)
     ap.add_argument("--log2-numel", type=int, default=24)
     a = ap.parse_args()
-    if a.kernel.startswith("allreduce"):
+    if a.kernel == "local_copy":
+        import switchml_b200 as sml
+        ctx = sml.Context.get_instance()
+        assert ctx.start(sml.make_config("cuda", packet_numel=256, mode="float_sum", launch="inline"))
+        numel = 1 << 26
+        x = torch.rand(numel, device="cuda")
+        y = torch.empty_like(x)
+
+        def one():
+            job = ctx.all_reduce_async(x, y)
+            job.stream_wait()
+            job.release()
+        ms = timed(one, a.iters)
+        assert torch.equal(x, y)
+        ctx.stop()
+        print("local_copy: %d elements, %.4f ms, %.0f GB/s read+write" % (numel, ms, 2 * numel * 4 / ms / 1e6))
+    elif a.kernel.startswith("allreduce"):
         from switchml_b200.ops.emulation import emulated_allreduce
         numel = 1 << a.log2_numel
         dtype = torch.int32 if a.kernel == "allreduce_int" else torch.float32

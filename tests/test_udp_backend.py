@@ -198,3 +198,68 @@ def struct_tail(reply):
     """Everything after the type byte of an echo reply must be what was sent."""
     import struct
     return struct.pack("!BHIHHbBH", 0, 5, 1234, 0, 2, 0, 1, 0) + b"switchml"
+
+
+def test_switch_survives_malformed_and_hostile_datagrams(ports):
+    """The data plane parses bytes from the network: random garbage, truncated packets,
+    lengths that do not match, slots and workers out of range, foreign sessions and
+    forwarding to nowhere must all be counted and dropped, and service must go on."""
+    import random
+    import socket
+    from switchml_b200._native import lib
+    from switchml_b200.utils.cli import controller_command
+    from switchml_b200.utils.common import HEADER, WIRE_MAGIC, WireType, pack_header, unpack_header
+    srv = lib().sml_controller_start(b"127.0.0.1", ports[0], ports[1])
+    assert srv
+    try:
+        session = 0xABCD1234
+        for rank in range(2):
+            controller_command("127.0.0.1", ports[0], "UDPSESSION %d %d 2 64 127.0.0.1 0 1" % (session, rank))
+        rng = random.Random(7)
+        sent = 0
+        with socket.socket(socket.AF_INET, socket.SOCK_DGRAM) as so:
+            def send(b):
+                nonlocal sent
+                so.sendto(b, ("127.0.0.1", ports[1]))
+                sent += 1
+            for _ in range(300):                                   # pure noise of every length
+                send(bytes(rng.getrandbits(8) for _ in range(rng.randrange(0, 1100))))
+            good = pack_header(WireType.DATA, worker=0, pkt_id=1, pool_index=3, numel=64, session=session)
+            for cut in range(0, HEADER.size + 8):                  # truncated
+                send((good + b"\0" * 256)[:cut])
+            send(good + b"\0" * 252)                               # payload shorter than numel says
+            send(good + b"\0" * 260)                               # longer
+            send(pack_header(WireType.DATA, worker=0, numel=60000, session=session) + b"\0" * 1024)
+            send(pack_header(WireType.DATA, worker=31, numel=64, session=session) + b"\0" * 256)   # not registered
+            send(pack_header(WireType.DATA, worker=0, pool_index=0x7FFF, numel=64, session=session) + b"\0" * 256)
+            send(pack_header(WireType.DATA, worker=0, numel=64, session=session + 1) + b"\0" * 256)  # other session
+            send(pack_header(WireType.RESULT, worker=0, numel=64, session=session) + b"\0" * 256)    # not for a switch
+            send(pack_header(9, worker=0, numel=0, session=session))                                  # unknown type
+            send(pack_header(WireType.FORWARD, worker=0, pool_index=(7 << 8), session=session) + b"x")   # no such worker
+            send(pack_header(WireType.FORWARD, worker=5, pool_index=(1 << 8), session=session) + b"x")   # sender unknown
+            send(HEADER.pack(WIRE_MAGIC ^ 1, 0, 0, 0, 0, 0, 64, 0, 0, session & 0xFFFF) + b"\0" * 256)   # wrong magic
+            for _ in range(300):                                   # valid header, every other field random
+                numel = rng.randrange(0, 300)
+                head = HEADER.pack(WIRE_MAGIC, rng.randrange(0, 8), rng.getrandbits(8), rng.getrandbits(16),
+                                   rng.getrandbits(32), rng.getrandbits(16), numel, rng.randrange(-128, 128),
+                                   rng.getrandbits(8), rng.getrandbits(16))
+                send(head + bytes(4 * min(numel, 256)))
+            # and it still answers
+            so.settimeout(2.0)
+            so.sendto(pack_header(WireType.ECHO_REQUEST, worker=1, pkt_id=99) + b"alive", ("127.0.0.1", ports[1]))
+            deadline = 50
+            while deadline:
+                data, _ = so.recvfrom(2048)
+                head = unpack_header(data)
+                if head and head["type"] == WireType.ECHO_REPLY and head["pkt_id"] == 99:
+                    break
+                deadline -= 1                                      # replies to random echo requests come first
+            assert deadline, "no echo reply after the flood"
+        assert controller_command("127.0.0.1", ports[0], "PING") == ""
+        stats = dict(l.split() for l in controller_command("127.0.0.1", ports[0], "SHOW statistics").splitlines())
+        assert int(stats["malformed"]) >= 330, stats
+        assert int(stats["broadcast"]) == 0 and int(stats["forwarded"]) == 0, stats
+        ports_table = controller_command("127.0.0.1", ports[0], "SHOW ports")
+        assert int(ports_table.splitlines()[2].split()[3]) >= sent
+    finally:
+        lib().sml_controller_stop(srv)
