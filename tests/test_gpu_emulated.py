@@ -117,3 +117,39 @@ def test_unaligned_views_and_out_of_place():
     for x, k in zip(xs, keep):
         assert torch.equal(x, k), "inputs must stay untouched"
     assert torch.allclose(outs[0], keep[0] + keep[1])
+
+
+def _random_quant_cases(worker_counts, cases, seed):
+    rng = np.random.default_rng(seed)
+    for case in range(cases):
+        n = int(rng.choice(worker_counts))
+        block = int(rng.choice([32, 64, 256, 1024]))
+        algo = "oneshot" if case % 4 == 3 else "staged"
+        numel = int(rng.integers(1, 40000 if algo == "oneshot" else 400000))
+        slot_bytes = int(rng.choice([8, 16, 64])) * 4 * block
+        channels = int(rng.choice([0, 1, 3, 7]))
+        xs = []
+        for r in range(n):
+            x = rng.standard_normal(numel).astype(np.float32) * np.float32(2.0 ** int(rng.integers(-30, 30)))
+            for z in rng.integers(0, max(1, numel // block), size=2) * block:   # some all-zero blocks
+                x[z:z + block] = 0.0
+            xs.append(x)
+        outs = emulated_allreduce([torch.from_numpy(x).cuda() for x in xs], mode="quant", algo=algo,
+                                  block_numel=block, slot_bytes=slot_bytes, channels=channels)
+        want = quant_allreduce_oracle(xs, block)
+        for r, o in enumerate(outs):
+            assert np.array_equal(o.cpu().numpy().view(np.uint32), want.view(np.uint32)), \
+                "case %d: n=%d numel=%d block=%d algo=%s slot=%d channels=%d rank %d" % (
+                    case, n, numel, block, algo, slot_bytes, channels, r)
+
+
+def test_quant_random_shapes_against_oracle():
+    """Randomly drawn lengths, block sizes, slot sizes, channel counts and value scales (fixed
+    seed) for 2, 4 and 8 workers: every rank must hold the oracle's bits."""
+    _random_quant_cases([2, 4, 8], 18, 20240607)
+
+
+def test_quant_worker_counts_that_are_not_powers_of_two():
+    """3, 5, 6 and 7 workers: the scale factor is not a power of two any more (K = 2^31-1-256
+    keeps the sum inside int32) and shards do not divide tiles evenly."""
+    _random_quant_cases([3, 5, 6, 7], 12, 977)
