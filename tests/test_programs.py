@@ -136,3 +136,13 @@ def test_switchd_console_on_standard_input(built, tmp_path):
     assert "127.0.0.1:%d/udp  up" % udp in out
     assert "unknown command: bogus" in out and "show_queue_pairs_counters" in out
     assert out.count("(switchml) ") >= 8
+
+
+def test_python_hello_world_example(tmp_path):
+    import sys
+    script = os.path.join(PKG, "examples", "python", "hello_world.py")
+    r = subprocess.run([sys.executable, script, "--num-tensors", "3", "--numel", "5000"], capture_output=True,
+                       text=True, timeout=120, cwd=tmp_path)
+    assert r.returncode == 0, r.stdout + r.stderr
+    assert "Data verified successfully: 3 tensors of 5000 elements, 2 workers, backend dummy" in r.stdout
+    assert "Finished jobs: #3#" in r.stdout
