@@ -63,6 +63,7 @@ def _declare(l):
                                     i32, i32, c.c_float, i32]),
         "sml_convert_u8": (i32, [i32, vp, vp, u64, vp]),
         "sml_controller_start": (vp, [c.c_char_p, i32, i32]),
+        "sml_controller_start_pipes": (vp, [c.c_char_p, i32, i32, i32]),
         "sml_controller_port": (i32, [vp]),
         "sml_controller_udp_port": (i32, [vp]),
         "sml_controller_stop": (None, [vp]),

@@ -114,6 +114,7 @@ int main(int argc, char** argv) {
   f.Add("ip", "0.0.0.0", "Address to listen on (TCP control and UDP data).")
       .Add("port", "50099", "TCP port of the control plane.")
       .Add("udp-port", "48864", "UDP port of the aggregation data plane (0xBEE0).")
+      .Add("pipes", "4", "Data-plane threads, each with its own socket on udp-port, udp-port + 1, ... (1..8).")
       .Add("drop-ingress", "0", "Probability of dropping a packet on arrival.")
       .Add("drop-egress", "0", "Probability of dropping each result copy.")
       .Add("log-file", "switchml.log", "Also append the log to this file (empty: stderr only).")
@@ -127,7 +128,8 @@ int main(int argc, char** argv) {
     else switchml::SetLogSink(LogSink);
   }
   switchml::ControlServer server;
-  if (!server.Start(f.Str("ip"), static_cast<uint16_t>(f.U64("port")), static_cast<uint16_t>(f.U64("udp-port")))) return 1;
+  if (!server.Start(f.Str("ip"), static_cast<uint16_t>(f.U64("port")), static_cast<uint16_t>(f.U64("udp-port")),
+                    static_cast<int>(f.U64("pipes")))) return 1;
   server.soft_switch().SetDropProbabilities(f.F64("drop-ingress"), f.F64("drop-egress"));
   signal(SIGINT, OnSignal);
   signal(SIGTERM, OnSignal);

@@ -17,7 +17,7 @@ SoftSwitch::SoftSwitch(uint32_t num_slots) : num_slots_(num_slots), rng_(0x5eed)
 }
 
 void SoftSwitch::Reset(uint64_t session_id, int num_workers, int packet_numel) {
-  std::lock_guard<std::mutex> lk(mu_);
+  std::unique_lock<std::shared_mutex> lk(state_mu_);
   for (int k = 0; k < 2; k++) {
     for (SlotSet& s : sets_[k]) s = SlotSet();
   }
@@ -32,27 +32,28 @@ void SoftSwitch::Reset(uint64_t session_id, int num_workers, int packet_numel) {
 }
 
 bool SoftSwitch::AddWorker(int rank) {
-  std::lock_guard<std::mutex> lk(mu_);
+  std::unique_lock<std::shared_mutex> lk(state_mu_);
   if (rank < 0 || rank >= num_workers_ || rank >= kMaxWorkers) return false;
   registered_ |= 1u << rank;
   return true;
 }
 
 void SoftSwitch::SetDropProbabilities(double ingress, double egress, uint64_t seed) {
-  std::lock_guard<std::mutex> lk(mu_);
+  std::unique_lock<std::shared_mutex> lk(state_mu_);
   drop_ingress_ = ingress < 0 ? 0 : (ingress > 1 ? 1 : ingress);
   drop_egress_ = egress < 0 ? 0 : (egress > 1 ? 1 : egress);
   if (seed) rng_.seed(seed);
 }
 
 void SoftSwitch::GetDropProbabilities(double* ingress, double* egress) const {
-  std::lock_guard<std::mutex> lk(mu_);
+  std::shared_lock<std::shared_mutex> lk(state_mu_);
   *ingress = drop_ingress_;
   *egress = drop_egress_;
 }
 
 bool SoftSwitch::Roll(double p) {
   if (p <= 0) return false;
+  std::lock_guard<std::mutex> lk(rng_mu_);
   return std::uniform_real_distribution<double>(0.0, 1.0)(rng_) < p;
 }
 
@@ -91,7 +92,7 @@ void SoftSwitch::Emit(const SlotSet& s, uint16_t pool_index, int dest_worker, in
 }
 
 void SoftSwitch::Process(const uint8_t* data, size_t len, std::vector<SwitchOutput>* out) {
-  std::lock_guard<std::mutex> lk(mu_);
+  std::shared_lock<std::shared_mutex> state(state_mu_);
   WireHeader h;
   if (len < sizeof(h)) { counters_.malformed++; return; }
   memcpy(&h, data, sizeof(h));
@@ -121,6 +122,7 @@ void SoftSwitch::Process(const uint8_t* data, size_t len, std::vector<SwitchOutp
 
   int k = (pool_index & kSetBit) ? 1 : 0;
   uint32_t slot = pool_index & ~kSetBit;
+  std::lock_guard<std::mutex> slot_lock(slot_mu_[slot % kStripes]);  // both sets of the slot
   SlotSet& cur = sets_[k][slot];
   SlotSet& other = sets_[1 - k][slot];
   uint32_t bit = 1u << worker;
@@ -223,28 +225,29 @@ void SoftSwitch::ProcessOther(const WireHeader& h, const uint8_t* data, size_t l
 }
 
 SwitchCounters SoftSwitch::counters() const {
-  std::lock_guard<std::mutex> lk(mu_);
+  std::shared_lock<std::shared_mutex> lk(state_mu_);
   return counters_;
 }
 
 WorkerCounters SoftSwitch::worker_counters(int rank) const {
-  std::lock_guard<std::mutex> lk(mu_);
+  std::shared_lock<std::shared_mutex> lk(state_mu_);
   return worker_counters_[rank];
 }
 
 EndpointCounters SoftSwitch::endpoint_counters(int rank, int thread) const {
-  std::lock_guard<std::mutex> lk(mu_);
+  std::shared_lock<std::shared_mutex> lk(state_mu_);
   if (rank < 0 || rank >= kMaxWorkers || thread < 0 || thread >= kMaxThreads) return EndpointCounters();
   return endpoint_counters_[rank][thread];
 }
 
 uint32_t SoftSwitch::Bitmap(uint32_t slot, int set) const {
-  std::lock_guard<std::mutex> lk(mu_);
+  std::shared_lock<std::shared_mutex> lk(state_mu_);
+  std::lock_guard<std::mutex> slot_lock(slot_mu_[(slot % num_slots_) % kStripes]);
   return sets_[set & 1][slot % num_slots_].bitmap;
 }
 
 std::string SoftSwitch::DescribeWorkers() const {
-  std::lock_guard<std::mutex> lk(mu_);
+  std::shared_lock<std::shared_mutex> lk(state_mu_);
   std::ostringstream o;
   o << "session " << session_id_ << ": " << num_workers_ << " worker(s), packet_numel "
     << packet_numel_ << "\n rank  registered  rx_pkts  rx_bytes  tx_pkts  tx_bytes\n";
@@ -257,7 +260,7 @@ std::string SoftSwitch::DescribeWorkers() const {
 }
 
 std::string SoftSwitch::DescribeStatistics() const {
-  std::lock_guard<std::mutex> lk(mu_);
+  std::shared_lock<std::shared_mutex> lk(state_mu_);
   std::ostringstream o;
   o << "broadcast " << counters_.broadcast << "\nretransmit " << counters_.retransmit
     << "\nconsumed " << counters_.consumed << "\nignored " << counters_.ignored
@@ -269,7 +272,7 @@ std::string SoftSwitch::DescribeStatistics() const {
 }
 
 std::string SoftSwitch::DescribeDropped() const {
-  std::lock_guard<std::mutex> lk(mu_);
+  std::shared_lock<std::shared_mutex> lk(state_mu_);
   std::ostringstream o;
   o << " rank  ingress_dropped  egress_dropped\n";
   for (int w = 0; w < num_workers_; w++)
@@ -280,7 +283,7 @@ std::string SoftSwitch::DescribeDropped() const {
 }
 
 std::string SoftSwitch::DescribeEndpoints() const {
-  std::lock_guard<std::mutex> lk(mu_);
+  std::shared_lock<std::shared_mutex> lk(state_mu_);
   std::ostringstream o;
   o << " rank  thread  rx_pkts  out_of_order  results  retransmitted_results\n";
   for (int w = 0; w < num_workers_; w++) {

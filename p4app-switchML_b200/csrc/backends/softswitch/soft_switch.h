@@ -9,13 +9,20 @@
 // using one set acknowledges the other, which is what makes retransmissions idempotent.
 //
 // The class has no sockets: Process() takes one packet and appends the packets to emit.
-// The UDP front end lives in rendezvous/control_server.cc; tests drive it directly.
+// The UDP front end lives in rendezvous/control.cc; tests drive it directly.
+//
+// Process() may be called from several threads at once (the front end can run several
+// "pipes", each with its own socket, like the pipes of the switch ASIC): the session state
+// is read under a shared lock, every slot belongs to one of 64 lock stripes, and the
+// counters are atomic. Opening or resetting a session takes the state lock exclusively.
 #ifndef SWITCHML_SOFT_SWITCH_H_
 #define SWITCHML_SOFT_SWITCH_H_
 
+#include <atomic>
 #include <cstdint>
 #include <mutex>
 #include <random>
+#include <shared_mutex>
 #include <string>
 #include <vector>
 
@@ -30,18 +37,34 @@ struct SwitchOutput {
   bool to_sender = false;      // send to the address the input came from (echo replies)
 };
 
+// A 64-bit event counter that several pipes may bump at once; reads and copies are
+// snapshots (relaxed: the numbers are statistics, nothing synchronises on them).
+struct Counter {
+  std::atomic<uint64_t> v{0};
+  Counter() {}
+  Counter(uint64_t x) : v(x) {}
+  Counter(const Counter& o) : v(o.v.load(std::memory_order_relaxed)) {}
+  Counter& operator=(const Counter& o) {
+    v.store(o.v.load(std::memory_order_relaxed), std::memory_order_relaxed);
+    return *this;
+  }
+  void operator++(int) { v.fetch_add(1, std::memory_order_relaxed); }
+  void operator+=(uint64_t x) { v.fetch_add(x, std::memory_order_relaxed); }
+  operator uint64_t() const { return v.load(std::memory_order_relaxed); }
+};
+
 struct SwitchCounters {
   // per slot and set, like the counters behind the reference CLI's show_statistics
-  uint64_t broadcast = 0, retransmit = 0, consumed = 0, ignored = 0;
-  uint64_t ingress_dropped = 0, egress_dropped = 0, malformed = 0;
-  uint64_t echo_replies = 0, forwarded = 0, flooded = 0;
+  Counter broadcast, retransmit, consumed, ignored;
+  Counter ingress_dropped, egress_dropped, malformed;
+  Counter echo_replies, forwarded, flooded;
 };
 
 struct WorkerCounters {
-  uint64_t rx_packets = 0, rx_bytes = 0, tx_packets = 0, tx_bytes = 0;
+  Counter rx_packets, rx_bytes, tx_packets, tx_bytes;
   // packets of this worker lost to the drop simulator (reference: per-queue-pair dropped
   // counter of p4/drop_simulator.p4, shown by the CLI's show_dropped_packets)
-  uint64_t ingress_dropped = 0, egress_dropped = 0;
+  Counter ingress_dropped, egress_dropped;
 };
 
 // Per (worker, worker thread): the counterpart of the reference's per-queue-pair counters
@@ -49,7 +72,7 @@ struct WorkerCounters {
 // endpoint plays the role of a queue pair; a packet for a slot use that was already absorbed
 // or finished is what a sequence violation is there: a packet outside the expected order.
 struct EndpointCounters {
-  uint64_t rx_packets = 0, out_of_order = 0, results = 0, retransmitted_results = 0;
+  Counter rx_packets, out_of_order, results, retransmitted_results;
 };
 
 class SoftSwitch {
@@ -100,7 +123,10 @@ class SoftSwitch {
   // Echo and forwarding: everything that is not aggregation traffic.
   void ProcessOther(const WireHeader& h, const uint8_t* data, size_t len, std::vector<SwitchOutput>* out);
 
-  mutable std::mutex mu_;
+  static const int kStripes = 64;
+  mutable std::shared_mutex state_mu_;        // session state: shared in Process(), exclusive to change it
+  mutable std::mutex slot_mu_[kStripes];      // slot s is guarded by stripe s % kStripes
+  std::mutex rng_mu_;
   uint32_t num_slots_;
   std::vector<SlotSet> sets_[2];
   int num_workers_ = 0;

@@ -220,7 +220,10 @@ void UdpBackend::SetupWorker() {
   const UdpBackendConfig& u = config_.backend_.udp;
   if (g.rank == 0 && u.spawn_switch) {
     server_.reset(new ControlServer());
-    SML_CHECK(server_->Start(g.controller_ip_str, g.controller_port, u.switch_port))
+    // One pipe per worker thread unless told otherwise: a pipe then serves the same thread of
+    // every worker and never shares a slot stripe's lock with another pipe for long.
+    int pipes = u.switch_pipes ? static_cast<int>(u.switch_pipes) : std::min<int>(g.num_worker_threads, 8);
+    SML_CHECK(server_->Start(g.controller_ip_str, g.controller_port, u.switch_port, pipes))
         << "cannot start the in-process controller/software switch";
   }
   SML_CHECK(client_.Connect(g.controller_ip_str, g.controller_port)) << "controller unreachable";
@@ -253,21 +256,23 @@ void UdpBackend::SetupWorker() {
   if (g.rank == 0) {
     SML_CHECK(client_.CreateUdpSession(session_id_, g.rank, g.num_workers, g.packet_numel,
                                        u.worker_ip_str, u.worker_port, g.num_worker_threads,
-                                       &sw_ip, &switch_udp_port_)) << "session setup failed";
+                                       &sw_ip, &switch_udp_ports_)) << "session setup failed";
     SML_CHECK(client_.Barrier(g.num_workers)) << "barrier failed";
   } else {
     SML_CHECK(client_.Barrier(g.num_workers)) << "barrier failed";
     SML_CHECK(client_.CreateUdpSession(session_id_, g.rank, g.num_workers, g.packet_numel,
                                        u.worker_ip_str, u.worker_port, g.num_worker_threads,
-                                       &sw_ip, &switch_udp_port_)) << "session setup failed";
+                                       &sw_ip, &switch_udp_ports_)) << "session setup failed";
   }
-  sockaddr_in sw;
-  memset(&sw, 0, sizeof(sw));
-  sw.sin_family = AF_INET;
-  inet_pton(AF_INET, u.switch_ip_str.c_str(), &sw.sin_addr);
-  sw.sin_port = htons(switch_udp_port_);
-  for (int fd : fds_) {
-    SML_CHECK(connect(fd, reinterpret_cast<sockaddr*>(&sw), sizeof(sw)) == 0)
+  // Worker thread t talks to pipe t mod pipes: its slots are then always served by the
+  // same pipe of the switch.
+  for (size_t t = 0; t < fds_.size(); t++) {
+    sockaddr_in sw;
+    memset(&sw, 0, sizeof(sw));
+    sw.sin_family = AF_INET;
+    inet_pton(AF_INET, u.switch_ip_str.c_str(), &sw.sin_addr);
+    sw.sin_port = htons(switch_udp_ports_[t % switch_udp_ports_.size()]);
+    SML_CHECK(connect(fds_[t], reinterpret_cast<sockaddr*>(&sw), sizeof(sw)) == 0)
         << "connect to switch: " << strerror(errno);
   }
   // Make sure the data plane answers before any job depends on it: one echo request per
@@ -276,7 +281,8 @@ void UdpBackend::SetupWorker() {
   // touch echo traffic, so a missing answer means a wrong address or a closed port.
   for (int t = 0; t < g.num_worker_threads; t++) {
     SML_CHECK(EchoSwitch(fds_[t], static_cast<uint16_t>(g.rank), static_cast<uint8_t>(t), session_id_, 2000))
-        << "the software switch does not answer on UDP " << u.switch_ip_str << ":" << switch_udp_port_;
+        << "the software switch does not answer on UDP " << u.switch_ip_str << ":"
+        << switch_udp_ports_[t % switch_udp_ports_.size()];
   }
   SML_CHECK(client_.Barrier(g.num_workers)) << "barrier failed";
 

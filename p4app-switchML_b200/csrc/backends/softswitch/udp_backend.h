@@ -39,7 +39,7 @@ class UdpBackend : public Backend {
   std::vector<std::thread> threads_;
   std::vector<int> fds_;
   uint64_t session_id_ = 0;
-  uint16_t switch_udp_port_ = 0;
+  std::vector<uint16_t> switch_udp_ports_;  // one per pipe of the switch; thread t uses [t % size]
 };
 
 }  // namespace switchml

@@ -257,8 +257,12 @@ int sml_convert_u8(int widen, const void* in, void* out, uint64_t numel, void* s
 }
 
 void* sml_controller_start(const char* ip, int port, int udp_port) {
+  return sml_controller_start_pipes(ip, port, udp_port, 1);
+}
+
+void* sml_controller_start_pipes(const char* ip, int port, int udp_port, int pipes) {
   ControlServer* s = new ControlServer();
-  if (!s->Start(ip ? ip : "127.0.0.1", static_cast<uint16_t>(port), static_cast<uint16_t>(udp_port))) {
+  if (!s->Start(ip ? ip : "127.0.0.1", static_cast<uint16_t>(port), static_cast<uint16_t>(udp_port), pipes)) {
     delete s;
     Fail("cannot start the controller");
     return nullptr;

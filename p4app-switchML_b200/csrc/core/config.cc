@@ -101,6 +101,7 @@ bool Config::LoadFromString(const std::string& text, const std::string& origin) 
   opts["backend.udp.worker_port"] = SML_OPT_UNSIGNED(backend_.udp.worker_port);
   opts["backend.udp.spawn_switch"] = SML_OPT_BOOL(backend_.udp.spawn_switch);
   opts["backend.udp.pool_size"] = SML_OPT_UNSIGNED(backend_.udp.pool_size);
+  opts["backend.udp.switch_pipes"] = SML_OPT_UNSIGNED(backend_.udp.switch_pipes);
   opts["backend.udp.cores"] = SML_OPT_STRING(backend_.udp.cores);
 
   opts["backend.cuda.device"] = [this](const std::string& v) {
@@ -247,6 +248,7 @@ void Config::Validate() {
     SML_CHECK(g.max_outstanding_packets / g.num_worker_threads <= backend_.udp.pool_size)
         << "window per worker thread exceeds backend.udp.pool_size";
     SML_CHECK(g.max_outstanding_packets <= 16384) << "the software switch has 16384 slots";
+    SML_CHECK(backend_.udp.switch_pipes <= 8) << "backend.udp.switch_pipes must be between 0 (automatic) and 8";
     if (!backend_.udp.cores.empty()) {
       int ids[256], count = 0;
       std::string err;
@@ -333,6 +335,7 @@ std::string Config::ToString() const {
       << "    worker_port = " << u.worker_port << "\n"
       << "    spawn_switch = " << (u.spawn_switch ? "true" : "false") << "\n"
       << "    pool_size = " << u.pool_size << "\n"
+      << "    switch_pipes = " << u.switch_pipes << "\n"
       << "    cores = " << u.cores << "\n";
   } else if (g.backend == "cuda") {
     const CudaBackendConfig& c = backend_.cuda;

@@ -82,7 +82,15 @@ bool ReadLine(int fd, std::string* buf, std::string* line, const std::atomic<boo
 
 }  // namespace
 
-ControlServer::ControlServer() { memset(learned_, 0, sizeof(learned_)); }
+ControlServer::ControlServer() {
+  memset(learned_, 0, sizeof(learned_));
+  for (int i = 0; i < kMaxPipes; i++) {
+    udp_fds_[i] = -1;
+    pending_udp_fds_[i] = -1;
+    udp_ports_[i] = 0;
+    udp_rx_packets_[i] = udp_rx_bytes_[i] = udp_tx_packets_[i] = udp_tx_bytes_[i] = 0;
+  }
+}
 
 // A bound, non-connected UDP socket with large buffers, or -1 with the reason in *err.
 static int BindUdp(const std::string& ip, unsigned port, uint16_t* bound, std::string* err) {
@@ -111,7 +119,7 @@ static int BindUdp(const std::string& ip, unsigned port, uint16_t* bound, std::s
 }
 ControlServer::~ControlServer() { Stop(); }
 
-bool ControlServer::Start(const std::string& ip, uint16_t port, uint16_t udp_port) {
+bool ControlServer::Start(const std::string& ip, uint16_t port, uint16_t udp_port, int pipes) {
   listen_fd_ = socket(AF_INET, SOCK_STREAM, 0);
   if (listen_fd_ < 0) return false;
   int one = 1;
@@ -134,25 +142,45 @@ bool ControlServer::Start(const std::string& ip, uint16_t port, uint16_t udp_por
   port_ = ntohs(a.sin_port);
 
   ip_ = ip;
+  pipes_ = 0;
   if (udp_port) {
-    uint16_t bound = 0;
-    std::string err;
-    int fd = BindUdp(ip, udp_port, &bound, &err);
-    if (fd < 0) {
-      SML_LOG(ERROR) << "software switch: cannot bind UDP port " << udp_port << ": " << err;
-      close(listen_fd_);
-      listen_fd_ = -1;
-      return false;
+    if (pipes < 1) pipes = 1;
+    if (pipes > kMaxPipes) pipes = kMaxPipes;
+    for (int i = 0; i < pipes; i++) {
+      uint16_t bound = 0;
+      std::string err;
+      int fd = BindUdp(ip, udp_port + i, &bound, &err);
+      if (fd < 0 && i > 0) {
+        // The neighbouring port is taken: any free port does, the workers are told the
+        // actual port of every pipe when they open their session.
+        SML_VLOG(1) << "software switch: UDP port " << udp_port + i << " is taken (" << err << "), pipe " << i
+                    << " gets a port chosen by the kernel";
+        fd = BindUdp(ip, 0, &bound, &err);
+      }
+      if (fd < 0) {
+        SML_LOG(ERROR) << "software switch: cannot bind UDP port " << udp_port + i << ": " << err;
+        for (int j = 0; j < i; j++) {
+          close(udp_fds_[j]);
+          udp_fds_[j] = -1;
+        }
+        close(listen_fd_);
+        listen_fd_ = -1;
+        return false;
+      }
+      udp_fds_[i] = fd;
+      udp_ports_[i] = bound;
     }
-    udp_fd_ = fd;
-    udp_port_ = bound;
-    data_thread_ = std::thread(&ControlServer::DataPlaneLoop, this);
+    pipes_ = pipes;
+    stopping_ = false;
+    for (int i = 0; i < pipes; i++) data_threads_.emplace_back(&ControlServer::DataPlaneLoop, this, i);
   }
   stopping_ = false;
   accepting_ = true;
   accept_thread_ = std::thread(&ControlServer::AcceptLoop, this);
   SML_VLOG(1) << "control server listening on " << ip << ":" << port_
-              << (udp_port_ ? " (software switch on UDP " + std::to_string(udp_port_) + ")" : "");
+              << (pipes_ ? " (software switch on UDP " + std::to_string(udp_ports_[0].load()) + ", " +
+                               std::to_string(pipes_) + " pipe(s))"
+                         : "");
   return true;
 }
 
@@ -164,7 +192,7 @@ void ControlServer::StopAccepting() {
 }
 
 void ControlServer::Stop() {
-  if (listen_fd_ < 0 && udp_fd_ < 0 && !accept_thread_.joinable() && conn_threads_.empty()) return;
+  if (listen_fd_ < 0 && udp_fds_[0] < 0 && !accept_thread_.joinable() && conn_threads_.empty()) return;
   stopping_ = true;
   {
     // Release anybody blocked in a collective.
@@ -175,7 +203,9 @@ void ControlServer::Stop() {
     }
   }
   if (accept_thread_.joinable()) accept_thread_.join();
-  if (data_thread_.joinable()) data_thread_.join();
+  for (auto& t : data_threads_)
+    if (t.joinable()) t.join();
+  data_threads_.clear();
   std::vector<std::thread> threads;
   {
     std::lock_guard<std::mutex> lk(conn_mu_);
@@ -184,11 +214,14 @@ void ControlServer::Stop() {
   }
   for (auto& t : threads) t.join();
   if (listen_fd_ >= 0) close(listen_fd_);
-  if (udp_fd_ >= 0) close(udp_fd_);
-  int pend = pending_udp_fd_.exchange(-1);
-  if (pend >= 0) close(pend);
+  for (int i = 0; i < kMaxPipes; i++) {
+    if (udp_fds_[i] >= 0) close(udp_fds_[i]);
+    udp_fds_[i] = -1;
+    int pend = pending_udp_fds_[i].exchange(-1);
+    if (pend >= 0) close(pend);
+  }
+  pipes_ = 0;
   listen_fd_ = -1;
-  udp_fd_ = -1;
 }
 
 void ControlServer::AcceptLoop() {
@@ -253,22 +286,34 @@ bool ControlServer::Collect(const std::string& name, int n, int rank, const std:
 }
 
 std::string ControlServer::RebindDataPlane(const std::string& ip, unsigned port) {
-  if (udp_fd_ < 0) return "ERR no software switch in this server";
-  uint16_t bound = 0;
-  std::string err;
-  int fd = BindUdp(ip, port, &bound, &err);
-  if (fd < 0) return "ERR cannot bind " + ip + ":" + std::to_string(port) + ": " + err;
-  int previous = pending_udp_fd_.exchange(fd);
-  if (previous >= 0) close(previous);
-  // The data-plane thread adopts the socket between two bursts (it polls with 100 ms).
-  for (int i = 0; i < 200 && pending_udp_fd_.load() == fd && !stopping_; i++) usleep(5 * 1000);
-  if (pending_udp_fd_.load() == fd) return "ERR the data plane did not pick up the new socket";
+  if (pipes_ == 0) return "ERR no software switch in this server";
+  // All pipes move: to port, port + 1, ... First bind them all, then hand them over.
+  int fds[kMaxPipes];
+  uint16_t bound[kMaxPipes];
+  for (int i = 0; i < pipes_; i++) {
+    std::string err;
+    fds[i] = BindUdp(ip, port ? port + i : 0, &bound[i], &err);
+    if (fds[i] < 0 && i > 0) fds[i] = BindUdp(ip, 0, &bound[i], &err);
+    if (fds[i] < 0) {
+      for (int j = 0; j < i; j++) close(fds[j]);
+      return "ERR cannot bind " + ip + ":" + std::to_string(port + i) + ": " + err;
+    }
+  }
+  for (int i = 0; i < pipes_; i++) {
+    int previous = pending_udp_fds_[i].exchange(fds[i]);
+    if (previous >= 0) close(previous);
+  }
+  // The data-plane threads adopt the sockets between two bursts (they poll with 100 ms).
+  for (int i = 0; i < pipes_; i++) {
+    for (int tries = 0; tries < 200 && pending_udp_fds_[i].load() == fds[i] && !stopping_; tries++) usleep(5 * 1000);
+    if (pending_udp_fds_[i].load() == fds[i]) return "ERR the data plane did not pick up the new socket";
+  }
   {
     std::lock_guard<std::mutex> lk(learned_mu_);
     ip_ = ip;
   }
-  udp_port_ = bound;
-  return "OK " + std::to_string(bound);
+  for (int i = 0; i < pipes_; i++) udp_ports_[i] = bound[i];
+  return "OK " + std::to_string(bound[0]);
 }
 
 static std::string AddrText(const sockaddr_in& a) {
@@ -289,9 +334,11 @@ std::string ControlServer::DescribePorts() {
   o << " port  address  state  rx_pkts  rx_bytes  tx_pkts  tx_bytes\n";
   o << " control  " << ip << ":" << port_ << "/tcp  " << (listen_fd_ >= 0 ? "up" : "closed") << "  "
     << ctl_requests_.load() << "  -  -  -\n";
-  o << " data  " << ip << ":" << udp_port_.load() << "/udp  " << (udp_fd_ >= 0 ? "up" : "absent") << "  "
-    << udp_rx_packets_.load() << "  " << udp_rx_bytes_.load() << "  " << udp_tx_packets_.load() << "  "
-    << udp_tx_bytes_.load() << "\n";
+  for (int i = 0; i < (pipes_ ? pipes_ : 1); i++) {
+    o << " data" << (i ? std::to_string(i) : "") << "  " << ip << ":" << udp_ports_[i].load() << "/udp  "
+      << (udp_fds_[i] >= 0 ? "up" : "absent") << "  " << udp_rx_packets_[i].load() << "  " << udp_rx_bytes_[i].load()
+      << "  " << udp_tx_packets_[i].load() << "  " << udp_tx_bytes_[i].load() << "\n";
+  }
   for (int w = 0; w < switch_.num_workers(); w++) {
     int endpoints = 0;
     {
@@ -368,7 +415,7 @@ std::string ControlServer::Handle(const std::string& line) {
     std::string ip;
     unsigned port0 = 0;
     in >> session >> rank >> n >> packet_numel >> ip >> port0 >> nthreads;
-    if (udp_fd_ < 0) return "ERR no software switch in this server";
+    if (pipes_ == 0) return "ERR no software switch in this server";
     if (n < 1 || n > kMaxWorkers || rank < 0 || rank >= n) return "ERR bad rank or num_workers";
     if (packet_numel < 1 || packet_numel > kMaxPacketNumel) return "ERR bad packet_numel";
     // Rank 0 opens the session and wipes the switch; the others join afterwards (the
@@ -377,7 +424,10 @@ std::string ControlServer::Handle(const std::string& line) {
     if (switch_.session_id() != session) return "ERR unknown session";
     if (!switch_.AddWorker(rank)) return "ERR cannot add worker";
     (void)ip; (void)port0; (void)nthreads;  // return addresses are learned from the data packets
-    return "OK " + std::to_string(udp_port_);
+    // One UDP port per pipe; worker thread t uses the (t mod pipes)-th.
+    std::string reply = "OK";
+    for (int i = 0; i < pipes_; i++) reply += " " + std::to_string(udp_ports_[i].load());
+    return reply;
   }
   if (cmd == "SHOW") {
     std::string what;
@@ -405,7 +455,7 @@ std::string ControlServer::Handle(const std::string& line) {
         ip = ip_;
       }
       text = "ip " + ip + " control_port " + std::to_string(port_) + " udp_port " +
-             std::to_string(udp_port_.load()) + "\n";
+             std::to_string(udp_ports_[0].load()) + " pipes " + std::to_string(pipes_) + "\n";
     } else return "ERR unknown table";
     return "OK " + HexEncode(text);
   }
@@ -436,7 +486,7 @@ std::string ControlServer::Handle(const std::string& line) {
   return "ERR unknown command '" + cmd + "'";
 }
 
-void ControlServer::DataPlaneLoop() {
+void ControlServer::DataPlaneLoop(int pipe) {
   // Datagrams are received and sent in bursts, one system call per burst (the reference's
   // workers use rx/tx bursts of 64, config.cc:86-88; the hardware switch needs none).
   const int kBurst = 64;
@@ -454,15 +504,15 @@ void ControlServer::DataPlaneLoop() {
   std::vector<iovec> tx_iov;
   std::vector<mmsghdr> tx_msgs;
   while (!stopping_) {
-    int pend = pending_udp_fd_.exchange(-1);
+    int pend = pending_udp_fds_[pipe].exchange(-1);
     if (pend >= 0) {
       // "SET address": move the data plane to the new socket. Workers learn the port when
       // they open a session, so sessions that are running keep talking to a closed port
       // and must be restarted, as after a change of the reference switch's address.
-      close(udp_fd_);
-      udp_fd_ = pend;
+      close(udp_fds_[pipe]);
+      udp_fds_[pipe] = pend;
     }
-    const int fd = udp_fd_;
+    const int fd = udp_fds_[pipe];
     struct pollfd p = {fd, POLLIN, 0};
     int r = poll(&p, 1, 100);
     if (r <= 0) continue;
@@ -481,8 +531,8 @@ void ControlServer::DataPlaneLoop() {
       const uint8_t* data = rx.data() + static_cast<size_t>(m) * kStride;
       const size_t n = rx_msgs[m].msg_len;
       const sockaddr_in& src = from[m];
-      udp_rx_packets_++;
-      udp_rx_bytes_ += n;
+      udp_rx_packets_[pipe]++;
+      udp_rx_bytes_[pipe] += n;
       if (n >= sizeof(WireHeader)) {
         // Learn where this worker thread listens, like a switch learns a port. Echo
         // requests may come from anybody and teach nothing.
@@ -520,10 +570,10 @@ void ControlServer::DataPlaneLoop() {
       tx_msgs[count].msg_hdr.msg_iovlen = 1;
       tx_msgs[count].msg_hdr.msg_name = &to[o];
       tx_msgs[count].msg_hdr.msg_namelen = sizeof(sockaddr_in);
-      udp_tx_bytes_ += out[o].bytes.size();
+      udp_tx_bytes_[pipe] += out[o].bytes.size();
       count++;
     }
-    udp_tx_packets_ += count;
+    udp_tx_packets_[pipe] += count;
     size_t done = 0;
     while (done < count) {
       int sent = sendmmsg(fd, tx_msgs.data() + done, static_cast<unsigned>(count - done), 0);
@@ -619,15 +669,18 @@ bool ControlClient::AllGather(int n, int rank, const std::string& token,
 bool ControlClient::CreateUdpSession(uint64_t session_id, int rank, int num_workers,
                                      int packet_numel, const std::string& my_ip, uint16_t port0,
                                      int nthreads, std::string* switch_ip,
-                                     uint16_t* switch_udp_port) {
+                                     std::vector<uint16_t>* switch_udp_ports) {
   std::ostringstream o;
   o << "UDPSESSION " << session_id << " " << rank << " " << num_workers << " " << packet_numel
     << " " << my_ip << " " << port0 << " " << nthreads;
   std::string r;
   if (!RoundTrip(o.str(), &r)) return false;
   (void)switch_ip;
-  *switch_udp_port = static_cast<uint16_t>(atoi(r.c_str()));
-  return true;
+  switch_udp_ports->clear();
+  std::istringstream ports(r);
+  unsigned p;
+  while (ports >> p) switch_udp_ports->push_back(static_cast<uint16_t>(p));
+  return !switch_udp_ports->empty();
 }
 
 bool ControlClient::Command(const std::string& line, std::string* reply) {

@@ -43,15 +43,20 @@ class ControlServer {
   ControlServer();
   ~ControlServer();
   // Listen on ip:port (port 0 = pick one). `udp_port` > 0 also starts the software
-  // switch data plane on that UDP port. Returns false if a socket cannot be bound.
-  bool Start(const std::string& ip, uint16_t port, uint16_t udp_port = 0);
+  // switch data plane on that UDP port. With `pipes` > 1 the data plane runs that many
+  // threads, each with a socket of its own on udp_port, udp_port + 1, ... (the switch ASIC
+  // has four pipes, too); worker thread t talks to pipe t mod pipes, so a slot is always
+  // served by the same pipe. Returns false if a socket cannot be bound.
+  bool Start(const std::string& ip, uint16_t port, uint16_t udp_port = 0, int pipes = 1);
   void Stop();
   // Close the listening socket but keep serving the connections that exist. A rank that
   // restarts right after the final barrier of a shutdown then cannot reach the old server
   // by accident; it retries until the next one listens.
   void StopAccepting();
   uint16_t port() const { return port_; }
-  uint16_t udp_port() const { return udp_port_; }
+  uint16_t udp_port() const { return udp_ports_[0]; }
+  int pipes() const { return pipes_; }
+  static const int kMaxPipes = 8;
   SoftSwitch& soft_switch() { return switch_; }
 
  private:
@@ -65,20 +70,21 @@ class ControlServer {
   };
   void AcceptLoop();
   void Serve(int fd);
-  void DataPlaneLoop();
+  void DataPlaneLoop(int pipe);
   std::string Handle(const std::string& line);
   // Blocks until `n` callers contributed; returns all tokens ordered by rank.
   bool Collect(const std::string& name, int n, int rank, const std::string& token,
                std::vector<std::string>* all);
 
   std::atomic<int> listen_fd_{-1};
-  std::atomic<int> udp_fd_{-1};
+  std::atomic<int> udp_fds_[kMaxPipes];
+  int pipes_ = 0;  // 0: no data plane
   uint16_t port_ = 0;
-  std::atomic<uint16_t> udp_port_{0};
+  std::atomic<uint16_t> udp_ports_[kMaxPipes];
   std::atomic<bool> stopping_{false};
   std::atomic<bool> accepting_{false};
   std::thread accept_thread_;
-  std::thread data_thread_;
+  std::vector<std::thread> data_threads_;
   std::mutex conn_mu_;
   std::vector<std::thread> conn_threads_;
   std::vector<int> conn_fds_;
@@ -93,11 +99,12 @@ class ControlServer {
   std::mutex learned_mu_;
   sockaddr_in learned_[kMaxWorkers][kMaxThreads];
   // Per data-plane socket ("port"): totals for the console's show_ports.
-  std::atomic<uint64_t> udp_rx_packets_{0}, udp_rx_bytes_{0}, udp_tx_packets_{0}, udp_tx_bytes_{0};
+  std::atomic<uint64_t> udp_rx_packets_[kMaxPipes], udp_rx_bytes_[kMaxPipes], udp_tx_packets_[kMaxPipes],
+      udp_tx_bytes_[kMaxPipes];
   std::atomic<uint64_t> ctl_requests_{0};
   std::string ip_;
   // A data-plane socket bound by "SET address", waiting to be adopted by the data-plane thread.
-  std::atomic<int> pending_udp_fd_{-1};
+  std::atomic<int> pending_udp_fds_[kMaxPipes];
   std::string RebindDataPlane(const std::string& ip, unsigned port);
   std::string DescribePorts();
   std::string DescribeForwarding();
@@ -120,7 +127,7 @@ class ControlClient {
   bool AllGather(int num_workers, int rank, const std::string& token, std::vector<std::string>* all);
   bool CreateUdpSession(uint64_t session_id, int rank, int num_workers, int packet_numel,
                         const std::string& my_ip, uint16_t port0, int nthreads,
-                        std::string* switch_ip, uint16_t* switch_udp_port);
+                        std::string* switch_ip, std::vector<uint16_t>* switch_udp_ports);  // one port per pipe
   // Send a raw command line (CLI); returns the reply without the leading "OK ".
   bool Command(const std::string& line, std::string* reply);
 

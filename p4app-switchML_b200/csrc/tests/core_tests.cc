@@ -376,6 +376,54 @@ static void TestSoftSwitch() {
   EXPECT(out.size() == 1 && PayloadAt(out[0], 3) == 8);
 }
 
+static void TestSoftSwitchConcurrentPipes() {
+  // Four threads feed the switch at once, each playing all three workers of "its" slots
+  // (what a pipe of the data plane does), while a fifth reads tables: every slot must
+  // complete exactly once with the right sum, and the counters must add up.
+  const int kPipes = 4, kSlotsPerPipe = 16, kRounds = 200, kWorkers = 3;
+  SoftSwitch sw(256);
+  sw.Reset(77, kWorkers, 4);
+  for (int w = 0; w < kWorkers; w++) EXPECT(sw.AddWorker(w));
+  std::atomic<int> wrong{0};
+  std::atomic<bool> reading{true};
+  std::thread reader([&] {
+    while (reading) {
+      (void)sw.DescribeStatistics();
+      (void)sw.DescribeWorkers();
+      (void)sw.Bitmap(3, 0);
+      (void)sw.counters();
+    }
+  });
+  std::vector<std::thread> pipes;
+  for (int p = 0; p < kPipes; p++) {
+    pipes.emplace_back([&, p] {
+      std::vector<SwitchOutput> out;
+      for (int round = 0; round < kRounds; round++) {
+        for (int s = 0; s < kSlotsPerPipe; s++) {
+          uint16_t idx = static_cast<uint16_t>(p * kSlotsPerPipe + s) | ((round & 1) ? kSetBit : 0);
+          out.clear();
+          for (int w = 0; w < kWorkers; w++) {
+            auto pkt = MakePacket(w, idx, static_cast<uint32_t>(round), static_cast<int8_t>(w),
+                                  {w + 1, round, p, s}, 77);
+            pkt[offsetof(WireHeader, thread_id)] = static_cast<uint8_t>(p);
+            sw.Process(pkt.data(), pkt.size(), &out);
+          }
+          if (out.size() != static_cast<size_t>(kWorkers) || PayloadAt(out[0], 0) != 6 ||
+              PayloadAt(out[0], 1) != 3 * round || PayloadAt(out[2], 3) != 3 * s) wrong++;
+        }
+      }
+    });
+  }
+  for (auto& t : pipes) t.join();
+  reading = false;
+  reader.join();
+  EXPECT(wrong == 0);
+  const uint64_t slots_done = static_cast<uint64_t>(kPipes) * kSlotsPerPipe * kRounds;
+  EXPECT(sw.counters().broadcast == slots_done && sw.counters().consumed == slots_done * (kWorkers - 1));
+  EXPECT(sw.worker_counters(1).rx_packets == slots_done && sw.worker_counters(2).tx_packets == slots_done);
+  EXPECT(sw.endpoint_counters(0, 3).rx_packets == static_cast<uint64_t>(kSlotsPerPipe) * kRounds);
+}
+
 static void TestQuantMath() {
   using namespace quant;
   EXPECT(LocalExponent(0.0f) == -126);
@@ -477,7 +525,7 @@ int main() {
   SetVerbosity(0);
   struct { const char* name; void (*fn)(); } tests[] = {
       {"logging", TestLogging}, {"numa_helpers", TestNumaHelpers}, {"simd_matches_scalar", TestSimdMatchesScalar}, {"static_slice", TestStaticSlice}, {"barrier", TestBarrier}, {"job_fsm", TestJobFsm},
-      {"timeout_queue", TestTimeoutQueue}, {"soft_switch", TestSoftSwitch},
+      {"timeout_queue", TestTimeoutQueue}, {"soft_switch", TestSoftSwitch}, {"soft_switch_concurrent_pipes", TestSoftSwitchConcurrentPipes},
       {"quant_math", TestQuantMath}, {"control_plane", TestControlPlane},
       {"context_dummy", TestContextDummy},
   };

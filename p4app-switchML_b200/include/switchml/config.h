@@ -50,6 +50,8 @@ struct UdpBackendConfig {
   uint16_t worker_port = 4000;              // thread t binds worker_port + t (0 = ephemeral)
   bool spawn_switch = true;                 // rank 0 hosts the switch in-process
   uint32_t pool_size = 8192;                // switch slots per worker thread (x2 sets)
+  uint32_t switch_pipes = 0;                // data-plane threads of the in-process switch on ports switch_port, +1, ...;
+                                            // 0 = one per worker thread, at most 8
   std::string cores = "";                   // e.g. "0-3" or "0,2,4,6": pin worker thread t to the t-th core
 };
 

@@ -82,6 +82,8 @@ int sml_emu_allreduce(int nranks, void* const* in_ptrs, void* const* out_ptrs, u
 
 /* Stand-alone controller / software switch (what rank 0 otherwise hosts in-process). */
 void* sml_controller_start(const char* ip, int port, int udp_port);
+/* the same with `pipes` data-plane threads on udp_port, udp_port + 1, ... */
+void* sml_controller_start_pipes(const char* ip, int port, int udp_port, int pipes);
 int sml_controller_port(void* server);
 int sml_controller_udp_port(void* server);
 void sml_controller_stop(void* server);

@@ -75,10 +75,17 @@ def test_benchmark_stops_on_sigint(built, cfg_dir):
     (cfg_dir / "switchml.cfg").write_text(text)
     p = subprocess.Popen([os.path.join(BIN, "allreduce_benchmark"), "--tensor-numel", "4000000", "--num-jobs", "50"],
                          cwd=cfg_dir, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
-    time.sleep(1.5)
+    # Interrupt once jobs are in flight (the first lines of output say so), not after a guess
+    # of how long start-up takes.
+    head = ""
+    while "Submitting" not in head:
+        line = p.stdout.readline()
+        assert line, "the benchmark ended early:\n" + head
+        head += line
+    time.sleep(0.5)
     p.send_signal(signal.SIGINT)
     out, _ = p.communicate(timeout=30)
-    assert p.returncode == 0 and "stopping the context" in out
+    assert p.returncode == 0 and "stopping the context" in head + out
 
 
 def _switchd_worker(rank, n, ctl_port, udp_port, q):

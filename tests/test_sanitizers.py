@@ -27,4 +27,4 @@ def test_native_tests_under_sanitizer(kind):
     out = r.stdout + r.stderr
     assert r.returncode == 0, out[-3000:]
     assert "ThreadSanitizer" not in out and "AddressSanitizer" not in out, out[-3000:]
-    assert out.count("ok  ") == 11
+    assert out.count("ok  ") == 12
