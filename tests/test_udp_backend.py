@@ -263,3 +263,50 @@ def test_switch_survives_malformed_and_hostile_datagrams(ports):
         assert int(ports_table.splitlines()[2].split()[3]) >= sent
     finally:
         lib().sml_controller_stop(srv)
+
+
+def test_controller_with_two_pipes(ports):
+    """Two data-plane threads with a socket each: both answer echo requests, both are listed
+    as ports, a session request returns both ports, and moving the switch moves both."""
+    import socket
+    from conftest import free_port
+    from switchml_b200._native import lib
+    from switchml_b200.utils.cli import controller_command
+    from switchml_b200.utils.common import WireType, pack_header, unpack_header
+    srv = lib().sml_controller_start_pipes(b"127.0.0.1", ports[0], ports[1], 2)
+    assert srv
+    try:
+        def table():
+            rows = [l.split() for l in controller_command("127.0.0.1", ports[0], "SHOW ports").splitlines()[1:]]
+            return {r[0]: r for r in rows}
+
+        def echo(port):
+            with socket.socket(socket.AF_INET, socket.SOCK_DGRAM) as so:
+                so.settimeout(2.0)
+                so.sendto(pack_header(WireType.ECHO_REQUEST, worker=0, pkt_id=port) + b"hi", ("127.0.0.1", port))
+                try:
+                    head = unpack_header(so.recvfrom(2048)[0])
+                except (socket.timeout, ConnectionError):
+                    return False
+                return head["type"] == WireType.ECHO_REPLY and head["pkt_id"] == port & 0xFFFFFFFF
+
+        rows = table()
+        assert "data" in rows and "data1" in rows and rows["data"][2] == rows["data1"][2] == "up"
+        pipe_ports = [int(rows[k][1].split(":")[1].split("/")[0]) for k in ("data", "data1")]
+        assert pipe_ports[0] == ports[1] and pipe_ports[1] != pipe_ports[0]
+        assert all(echo(p) for p in pipe_ports)
+        rows = table()
+        assert int(rows["data"][3]) == 1 and int(rows["data1"][3]) == 1          # one datagram each
+        assert "pipes 2" in controller_command("127.0.0.1", ports[0], "SHOW address")
+        from switchml_b200._native import lib as _lib  # the session reply carries one port per pipe
+        import ctypes
+        buf = ctypes.create_string_buffer(256)
+        n = _lib().sml_controller_command(b"127.0.0.1", ports[0], b"UDPSESSION 5 0 1 64 127.0.0.1 0 2", buf, len(buf))
+        assert n >= 0 and [int(x) for x in buf.value.decode().split()] == pipe_ports
+        moved = free_port()
+        assert controller_command("127.0.0.1", ports[0], "SET address 127.0.0.1 %d" % moved) == str(moved)
+        rows = table()
+        new_ports = [int(rows[k][1].split(":")[1].split("/")[0]) for k in ("data", "data1")]
+        assert new_ports[0] == moved and all(echo(p) for p in new_ports) and not echo(pipe_ports[0])
+    finally:
+        lib().sml_controller_stop(srv)
