@@ -24,7 +24,7 @@ import switchml_b200.parallel.process_group  # noqa: E402,F401  (registers "sml"
 
 
 def main():
-    backends = ["sml", "gloo"] + (["mpi"] if dist.is_mpi_available() else []) + (["nccl"] if dist.is_nccl_available() else [])
+    backends = ["sml", "sml_native", "gloo"] + (["mpi"] if dist.is_mpi_available() else []) + (["nccl"] if dist.is_nccl_available() else [])
     ap = argparse.ArgumentParser("AllReduce PyTorch Benchmark")
     ap.add_argument("-n", "--num-workers", type=int, default=int(os.environ.get("WORLD_SIZE", 1)))
     ap.add_argument("-r", "--rank", type=int, default=int(os.environ.get("RANK", 0)))
@@ -60,6 +60,12 @@ def main():
     port = int(os.environ.get("MASTER_PORT", 23456))
     os.environ.setdefault("MASTER_ADDR", a.rank0_ip)
     os.environ.setdefault("MASTER_PORT", str(port))
+    if a.backend == "sml_native":
+        # The C++ c10d backend (lib/torch_switchml.so); it takes its settings from switchml.cfg /
+        # SWITCHML_CONFIG, SWITCHML_RANK and SWITCHML_NUM_WORKERS like any C++ program.
+        os.environ.setdefault("SWITCHML_RANK", str(a.rank))
+        os.environ.setdefault("SWITCHML_NUM_WORKERS", str(a.num_workers))
+        import switchml_b200.parallel.native_process_group  # noqa: F401
     dist.init_process_group(a.backend, rank=a.rank, world_size=a.num_workers,
                             init_method="tcp://%s:%d" % (a.rank0_ip, port))
 
