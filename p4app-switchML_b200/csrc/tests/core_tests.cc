@@ -107,7 +107,7 @@ static void TestSimdMatchesScalar() {
     std::vector<int32_t> in(n), s1(n + 1, 7), s2(n + 1, 7), acc1(n + 1, 1000), acc2(n + 1, 1000);
     for (size_t i = 0; i < n; i++) in[i] = static_cast<int32_t>(next());
     std::vector<uint8_t> wire(4 * n + 3);
-    memcpy(wire.data() + 1, in.data(), 4 * n);   // odd address on purpose
+    if (n) memcpy(wire.data() + 1, in.data(), 4 * n);   // odd address on purpose
     simd::Enable(true);
     simd::Swap32(in.data(), n, s1.data());
     simd::AddWire(wire.data() + 1, n, acc1.data());

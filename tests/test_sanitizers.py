@@ -1,4 +1,4 @@
-"""Host code under ThreadSanitizer and AddressSanitizer: the native unit tests (threads of
+"""Host code under ThreadSanitizer, AddressSanitizer and UndefinedBehaviorSanitizer: the native unit tests (threads of
 the dummy backend, scheduler barrier, control-plane collectives, software switch) must run
 clean. The reference has no sanitizer configuration; this is the race detector of the
 host side."""
@@ -19,12 +19,12 @@ def _build_module():
     return mod
 
 
-@pytest.mark.parametrize("kind", ["thread", "address"])
+@pytest.mark.parametrize("kind", ["thread", "address", "undefined"])
 def test_native_tests_under_sanitizer(kind):
     exe = _build_module().build_sanitized(kind)
     env = dict(os.environ, TSAN_OPTIONS="halt_on_error=0", ASAN_OPTIONS="detect_leaks=0")
     r = subprocess.run([exe], capture_output=True, text=True, timeout=300, env=env)
     out = r.stdout + r.stderr
     assert r.returncode == 0, out[-3000:]
-    assert "ThreadSanitizer" not in out and "AddressSanitizer" not in out, out[-3000:]
+    assert "ThreadSanitizer" not in out and "AddressSanitizer" not in out and "runtime error" not in out, out[-3000:]
     assert out.count("ok  ") == 12
