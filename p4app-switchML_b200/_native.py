@@ -41,6 +41,7 @@ def _declare(l):
         "sml_config_check": (i32, [c.c_char_p, c.c_char_p, c.c_size_t]),
         "sml_allreduce_async": (i64, [vp, vp, u64, i32, vp]),
         "sml_allreduce": (i32, [vp, vp, u64, i32]),
+        "sml_broadcast_async": (i64, [vp, u64, i32, i32, vp]),
         "sml_job_wait": (i32, [i64, c.c_double]),
         "sml_job_status": (i32, [i64]),
         "sml_job_stream_wait": (i32, [i64, vp]),

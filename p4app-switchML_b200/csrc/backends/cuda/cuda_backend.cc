@@ -378,6 +378,17 @@ void CudaBackend::LaunchJob(const std::shared_ptr<Job>& job, cudaStream_t stream
     t.data_type = INT32;
   }
   const bool integer = t.data_type == INT32 || t.data_type == UINT8;
+  // A broadcast is a sum to which everybody but the root contributes zeros: clear this
+  // rank's buffer in stream order, in front of the kernel; never average.
+  const bool broadcast = job->job_type_ == BROADCAST;
+  if (broadcast && rank_ != job->extra_job_info_.broadcast_root && t.numel > 0) {
+    cudaError_t ce = cudaMemsetAsync(t.in_ptr, 0, t.numel * DataTypeSize(t.data_type), stream);
+    if (ce != cudaSuccess) {
+      f->launch_error = std::string("broadcast: clearing the buffer failed: ") + cudaGetErrorString(ce);
+      cudaGetLastError();
+      return;
+    }
+  }
   kernels::JobArgs a;
   memset(&a, 0, sizeof(a));
   a.in = t.in_ptr;
@@ -386,7 +397,7 @@ void CudaBackend::LaunchJob(const std::shared_ptr<Job>& job, cudaStream_t stream
   a.elem_type = t.data_type == FLOAT32 ? kernels::ELEM_F32
               : t.data_type == BFLOAT16 ? kernels::ELEM_BF16 : kernels::ELEM_I32;
   a.mode = (!integer && c.mode == "int32_quant") ? kernels::MODE_QUANT : kernels::MODE_SUM;
-  a.post_scale = c.average && !integer ? 1.0f / static_cast<float>(n_) : 1.0f;
+  a.post_scale = c.average && !integer && !broadcast ? 1.0f / static_cast<float>(n_) : 1.0f;
   a.tune = static_cast<int>(c.tune);
   size_t esz = DataTypeSize(t.data_type);
   size_t bytes = t.numel * esz;
@@ -469,8 +480,8 @@ void CudaBackend::LaunchJob(const std::shared_ptr<Job>& job, cudaStream_t stream
 }
 
 bool CudaBackend::OnSubmit(const std::shared_ptr<Job>& job) {
-  if (job->job_type_ != ALLREDUCE) {
-    context_.NotifyJobCompletion(job, false, "only ALLREDUCE jobs are supported");
+  if (job->job_type_ != ALLREDUCE && job->job_type_ != BROADCAST) {
+    context_.NotifyJobCompletion(job, false, "only ALLREDUCE and BROADCAST jobs are supported");
     return true;
   }
   if (config_.general_.instant_job_completion) {

@@ -124,6 +124,20 @@ int64_t sml_allreduce_async(void* in, void* out, uint64_t numel, int dtype, void
   }
 }
 
+int64_t sml_broadcast_async(void* ptr, uint64_t numel, int dtype, int root, void* stream) {
+  try {
+    if (dtype < 0 || dtype > 3) return Fail("bad dtype");
+    std::shared_ptr<Job> job =
+        Context::GetInstance().BroadcastAsync(ptr, numel, static_cast<DataType>(dtype), root, stream);
+    std::lock_guard<std::mutex> lk(g_jobs_mu);
+    int64_t h = g_next_handle++;
+    g_jobs[h] = job;
+    return h;
+  } catch (const std::exception& e) {
+    return Fail(e.what());
+  }
+}
+
 int sml_allreduce(void* in, void* out, uint64_t numel, int dtype) {
   try {
     if (dtype < 0 || dtype > 3) return Fail("bad dtype");

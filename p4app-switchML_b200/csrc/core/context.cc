@@ -2,6 +2,8 @@
 // Parity: reference client_lib/src/context.cc:36-197.
 #include "switchml/context.h"
 
+#include <cstring>
+#include <string>
 #include <vector>
 
 #include "switchml/log.h"
@@ -134,6 +136,50 @@ std::shared_ptr<Job> Context::AllReduceAsync(void* in_ptr, void* out_ptr, uint64
   bool taken = backend_->OnSubmit(job);
   if (!taken && !scheduler_->EnqueueJob(job)) {
     FinishJob(job, false, "scheduler stopped");
+  }
+  return job;
+}
+
+std::shared_ptr<Job> Context::BroadcastAsync(void* ptr, uint64_t numel, DataType data_type, int root,
+                                             void* stream) {
+  SML_CHECK(context_state_ == RUNNING) << "BroadcastAsync called while the context is not running";
+  const GeneralConfig& g = config_.general_;
+  Tensor t;
+  t.in_ptr = t.out_ptr = ptr;
+  t.numel = numel;
+  t.data_type = data_type;
+  ExtraJobInfo extra;
+  extra.broadcast_root = root;
+  std::shared_ptr<Job> job = std::make_shared<Job>(t, BROADCAST, extra);
+  job->producer_stream_ = stream;
+  {
+    std::lock_guard<std::mutex> jl(jobs_mutex_);
+    number_of_current_jobs_++;
+  }
+  stats_.IncJobsSubmittedNum();
+  stats_.AppendJobSubmittedNumel(numel);
+  const bool cuda = g.backend == "cuda";
+  if (root < 0 || root >= static_cast<int>(g.num_workers)) {
+    FinishJob(job, false, "broadcast root " + std::to_string(root) + " is not a rank of this session");
+  } else if (data_type == UINT8 || (data_type == BFLOAT16 && !cuda)) {
+    FinishJob(job, false, std::string("broadcast does not take ") + DataTypeName(data_type) + " tensors here");
+  } else if (g.num_workers == 1) {
+    job->SetJobStatus(JobStatus::RUNNING);
+    FinishJob(job, true, "");
+  } else if (g.backend == "dummy") {
+    // No peers to hear from: the root keeps what it has, anybody else cannot be served.
+    if (static_cast<int>(g.rank) == root) {
+      job->SetJobStatus(JobStatus::RUNNING);
+      FinishJob(job, true, "");
+    } else {
+      FinishJob(job, false, "the dummy backend has no peers to receive a broadcast from");
+    }
+  } else {
+    // Host memory: the zeros are written here; device memory: the cuda backend enqueues the
+    // clearing in stream order in front of the kernel.
+    if (!cuda && static_cast<int>(g.rank) != root) memset(ptr, 0, numel * DataTypeSize(data_type));
+    bool taken = backend_->OnSubmit(job);
+    if (!taken && !scheduler_->EnqueueJob(job)) FinishJob(job, false, "scheduler stopped");
   }
   return job;
 }

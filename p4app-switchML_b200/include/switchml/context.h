@@ -50,6 +50,15 @@ class Context {
                                       DataType data_type, AllReduceOperation op, void* stream);
   std::shared_ptr<Job> AllReduce(void* in_ptr, void* out_ptr, uint64_t numel, DataType data_type,
                                  AllReduceOperation op);
+  // Every worker's `ptr` ends up with the values of rank `root` (a job type the reference
+  // declares but does not implement). Done with the one collective the fabric has: the
+  // other workers contribute zeros to a sum. Exact for INT32 and with mode = float_sum; with
+  // the quantised mode all workers, the root included, get the same values rounded to the
+  // block's fixed-point grid. The buffer of a non-root worker is overwritten at once.
+  // FLOAT32, INT32 and (cuda) BFLOAT16; the dummy backend has no peers and fails the job
+  // unless there is one worker.
+  std::shared_ptr<Job> BroadcastAsync(void* ptr, uint64_t numel, DataType data_type, int root,
+                                      void* stream = nullptr);
   void WaitForAllJobs();
 
   ContextState GetContextState();

@@ -1,7 +1,8 @@
 // Job: one submitted collective and its lifecycle.
 //
 // Parity: reference client_lib/src/job.h:37-148 and job.cc:29-57 — JobType
-// {ALLREDUCE, BROADCAST (declared, not implemented)}, AllReduceOperation {SUM},
+// {ALLREDUCE, BROADCAST (only declared in the reference, implemented here)},
+// AllReduceOperation {SUM},
 // monotone JobStatus INIT→QUEUED→RUNNING→FINISHED|FAILED (going backwards is a fatal
 // error), ids from a process-wide counter, WaitToComplete() blocking on a condition
 // variable, JobSlice = (job, sub-tensor).
@@ -26,7 +27,8 @@ namespace switchml {
 
 enum JobType {
   ALLREDUCE = 0,
-  BROADCAST = 1,  // declared for API parity; submitting one fails the job
+  BROADCAST = 1,  // "Not yet supported" in the reference (job.h:39); here: the root's values reach every
+                  // worker as a sum in which all other workers contribute zeros
 };
 
 enum AllReduceOperation {
@@ -35,6 +37,7 @@ enum AllReduceOperation {
 
 union ExtraJobInfo {
   AllReduceOperation allreduce_operation;
+  int broadcast_root;  // BROADCAST jobs: rank whose values are handed out
 };
 
 enum JobStatus {

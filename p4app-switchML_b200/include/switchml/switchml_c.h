@@ -39,6 +39,9 @@ int sml_config_check(const char* ini_text, char* buf, size_t len);
  * positive handle, or -1. Handles must be released. */
 int64_t sml_allreduce_async(void* in, void* out, uint64_t numel, int dtype, void* stream);
 int sml_allreduce(void* in, void* out, uint64_t numel, int dtype);
+/* every worker's buffer receives the values of rank `root`; returns a job handle like
+ * sml_allreduce_async (Context::BroadcastAsync) */
+int64_t sml_broadcast_async(void* ptr, uint64_t numel, int dtype, int root, void* stream);
 /* Wait up to timeout_ms (< 0: forever). Returns the job status. */
 int sml_job_wait(int64_t job, double timeout_ms);
 int sml_job_status(int64_t job);

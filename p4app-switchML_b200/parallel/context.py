@@ -153,6 +153,24 @@ class Context:
             raise NativeError("allreduce failed: " + job.error())
         return job
 
+    def broadcast_async(self, tensor, root=0, stream=None):
+        """Every worker's `tensor` receives rank `root`'s values, in place
+        (``Context::BroadcastAsync``: a sum to which the other workers contribute zeros)."""
+        ptr, numel, code, cur_stream, _ = _describe(tensor)
+        if stream is not None:
+            cur_stream = getattr(stream, "cuda_stream", stream)
+        h = lib().sml_broadcast_async(ctypes.c_void_p(ptr), numel, code, int(root), ctypes.c_void_p(cur_stream or 0))
+        if h < 0:
+            raise NativeError(last_error())
+        return Job(h, (tensor,))
+
+    def broadcast(self, tensor, root=0):
+        job = self.broadcast_async(tensor, root)
+        st = job.wait()
+        if st != JobStatus.FINISHED:
+            raise NativeError("broadcast failed: " + job.error())
+        return job
+
     def wait_for_all_jobs(self):
         lib().sml_wait_all()
 

@@ -481,3 +481,79 @@ def stop_during_loss_worker(rank, n, ctl_port, udp_port, q):
                             "stop_seconds": time.time() - t0, "timeouts": timeouts}))
     except Exception:
         q.put((rank, "error", traceback.format_exc()))
+
+
+def broadcast_udp_worker(rank, n, ctl_port, udp_port, q):
+    """Context.broadcast over the UDP backend: exact for int32, the same rounded values on
+    every rank for float32; bad arguments fail the job without hurting the context."""
+    try:
+        import numpy as np
+        import switchml_b200 as sml
+        ctx = sml.Context.get_instance()
+        assert ctx.start(sml.make_config("udp", rank=rank, num_workers=n, packet_numel=64, num_worker_threads=2,
+                                         max_outstanding_packets=64, controller_port=ctl_port, switch_port=udp_port,
+                                         worker_port=0))
+        out = {}
+        for root in range(n):
+            xi = np.arange(5000, dtype=np.int32) * (rank + 1) - 77 * rank
+            ctx.broadcast(xi, root)
+            out["int%d" % root] = xi
+            xf = np.random.default_rng(100 + rank).standard_normal(3333).astype(np.float32)
+            ctx.broadcast(xf, root)
+            out["float%d" % root] = xf
+        bad = ctx.broadcast_async(np.zeros(4, dtype=np.float32), root=n)
+        assert bad.wait(5000) == sml.JobStatus.FAILED and "not a rank" in bad.error()
+        bad = ctx.broadcast_async(np.zeros(4, dtype=np.uint8), root=0)
+        assert bad.wait(5000) == sml.JobStatus.FAILED
+        x = np.full(100, rank + 1.0, dtype=np.float32)
+        ctx.all_reduce(x)                                   # still in step with the others
+        assert float(x[0]) == sum(r + 1.0 for r in range(n))
+        ctx.stop()
+        q.put((rank, "ok", out))
+    except Exception:
+        q.put((rank, "error", traceback.format_exc()))
+
+
+def broadcast_cuda_worker(rank, n, ctl_port, mode, q):
+    """Context.broadcast on GPUs: the root's tensor reaches every rank, also when the context
+    averages its allreduces and also for tensors of the symmetric heap."""
+    try:
+        import torch
+        import switchml_b200 as sml
+        torch.cuda.set_device(rank)
+        ctx = sml.Context.get_instance()
+        assert ctx.start(sml.make_config("cuda", rank=rank, num_workers=n, packet_numel=256, device=rank,
+                                         controller_port=ctl_port, mode=mode, launch="inline", average=True,
+                                         symm_heap_mb=16, wait_timeout_ms=20000))
+        for root in range(n):
+            for numel in (1, 1000, 300007, (1 << 21) + 5):
+                g = torch.Generator().manual_seed(1000 * root + numel)        # what the root holds
+                want = torch.randn(numel, generator=g)
+                x = want.cuda() if rank == root else torch.full((numel,), float(rank + 5), device="cuda")
+                ctx.broadcast(x, root)
+                torch.cuda.synchronize()
+                if mode == "float_sum":
+                    assert torch.equal(x.cpu(), want), "float broadcast root %d numel %d" % (root, numel)
+                else:
+                    assert torch.allclose(x.cpu(), want, rtol=0, atol=2.0 ** -20 * float(want.abs().max()) + 1e-30)
+                if rank == root:
+                    xi = (torch.arange(numel, dtype=torch.int32) * 7 - root).cuda()
+                else:
+                    xi = torch.zeros(numel, dtype=torch.int32, device="cuda") - 1
+                ctx.broadcast(xi, root)
+                torch.cuda.synchronize()
+                assert torch.equal(xi.cpu(), torch.arange(numel, dtype=torch.int32) * 7 - root), "int broadcast"
+            s = ctx.symmetric_empty(70001, torch.float32)
+            s.copy_(torch.full((70001,), 3.25 if rank == root else -1.0))
+            ctx.broadcast(s, root)
+            torch.cuda.synchronize()
+            assert float(s.min()) == 3.25 and float(s.max()) == 3.25, "symmetric broadcast"
+            ctx.symmetric_reset()
+        y = torch.full((1000,), float(rank + 1), device="cuda")
+        ctx.all_reduce(y)                                   # allreduces still average
+        torch.cuda.synchronize()
+        assert abs(float(y[0]) - sum(r + 1.0 for r in range(n)) / n) < 1e-5
+        ctx.stop()
+        q.put((rank, "ok", None))
+    except Exception:
+        q.put((rank, "error", traceback.format_exc()))

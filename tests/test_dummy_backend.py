@@ -122,3 +122,20 @@ def test_api_misuse(ctx):
     ctx.stop()
     assert ctx.state() == sml.ContextState.STOPPED
     assert ctx.start(sml.make_config("dummy", bandwidth=0))  # restart works
+
+
+def test_broadcast_on_the_dummy_backend(ctx):
+    """One worker: trivially done. Several "workers" of the dummy backend never meet, so only
+    the root can be served."""
+    assert ctx.start(sml.make_config("dummy", rank=0, num_workers=1, bandwidth=0))
+    x = np.arange(10, dtype=np.float32)
+    ctx.broadcast(x, 0)
+    assert np.array_equal(x, np.arange(10, dtype=np.float32))
+    ctx.stop()
+    assert ctx.start(sml.make_config("dummy", rank=1, num_workers=2, bandwidth=0))
+    assert ctx.broadcast_async(x, root=1).wait(5000) == sml.JobStatus.FINISHED
+    job = ctx.broadcast_async(x, root=0)
+    assert job.wait(5000) == sml.JobStatus.FAILED and "no peers" in job.error()
+    assert np.array_equal(x, np.arange(10, dtype=np.float32))
+    stats = ctx.get_stats()
+    assert stats["jobs_submitted"] == 2 and stats["jobs_finished"] == 1 and stats["jobs_failed"] == 1

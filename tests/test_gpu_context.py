@@ -197,3 +197,14 @@ def test_service_threads_can_be_bound_to_the_gpus_numa_node(ctx):
     for _ in range(3):
         assert ctx.all_reduce_async(x, y).wait(20000) == sml.JobStatus.FINISHED
     assert torch.equal(x, y)
+
+
+def test_broadcast_single_rank(ctx):
+    assert ctx.start(sml.make_config("cuda", packet_numel=256, mode="int32_quant", launch="inline"))
+    x = torch.randn(100003, device="cuda")
+    keep = x.clone()
+    ctx.broadcast(x, 0)
+    torch.cuda.synchronize()
+    assert torch.equal(x, keep)
+    job = ctx.broadcast_async(x, root=1)
+    assert job.wait(5000) == sml.JobStatus.FAILED and "not a rank" in job.error()

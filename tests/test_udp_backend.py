@@ -310,3 +310,31 @@ def test_controller_with_two_pipes(ports):
         assert new_ports[0] == moved and all(echo(p) for p in new_ports) and not echo(pipe_ports[0])
     finally:
         lib().sml_controller_stop(srv)
+
+
+def test_broadcast_between_real_workers(ports):
+    from _workers import broadcast_udp_worker
+    n = 3
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=broadcast_udp_worker, args=(r, n, ports[0], ports[1], q)) for r in range(n)]
+    for p in procs:
+        p.start()
+    got = {}
+    try:
+        for _ in range(n):
+            rank, status, out = q.get(timeout=180)
+            assert status == "ok", out
+            got[rank] = out
+    finally:
+        for p in procs:
+            p.join(timeout=30)
+            if p.is_alive():
+                p.kill()
+    for root in range(n):
+        want_int = np.arange(5000, dtype=np.int32) * (root + 1) - 77 * root
+        want_float = np.random.default_rng(100 + root).standard_normal(3333).astype(np.float32)
+        for r in range(n):
+            assert np.array_equal(got[r]["int%d" % root], want_int), (root, r)
+            assert np.array_equal(got[r]["float%d" % root], got[0]["float%d" % root]), "ranks must agree bit for bit"
+            assert np.max(np.abs(got[r]["float%d" % root] - want_float)) < 1e-6
