@@ -91,25 +91,25 @@ class GradientBuckets:
 
 
 def broadcast_tensors(ctx, tensors, src=0, chunk_numel=1 << 24):
-    """Give every worker rank `src`'s values of `tensors`, in place, with the one collective
-    SwitchML has: `src` contributes its values, everybody else zeros, and the sum is the
-    broadcast. Exact with ``mode = float_sum`` and for integers; with the quantised mode the
-    values come back rounded to the block's fixed-point grid, the same on every rank
-    (`src` included), which is what data-parallel training needs.
+    """Give every worker rank `src`'s values of `tensors`, in place, through
+    ``Context.broadcast`` (a sum to which everybody but `src` contributes zeros). Exact with
+    ``mode = float_sum`` and for integers; with the quantised mode the values come back
+    rounded to the block's fixed-point grid, the same on every rank (`src` included), which
+    is what data-parallel training needs.
 
     Floating-point tensors travel as float32, integer tensors as int32 (values must fit),
-    bool as uint8. Tensors are packed into flat messages of at most `chunk_numel` elements.
+    bool as int32 as well. Tensors are packed into flat messages of at most `chunk_numel`
+    elements.
     """
     cfg = ctx.config_dump()
     rank, n = _config_int(cfg, "rank"), _config_int(cfg, "num_workers")
-    averaged = "average = true" in cfg or "average = 1" in cfg
     if n <= 1:
         return
     groups = {}
     for t in tensors:
         if t.numel() == 0:
             continue
-        wire = torch.float32 if t.is_floating_point() else (torch.uint8 if t.dtype == torch.bool else torch.int32)
+        wire = torch.float32 if t.is_floating_point() else torch.int32
         groups.setdefault((wire, t.device), []).append(t)
     for (wire, device), group in groups.items():
         batch, count = [], 0
@@ -118,18 +118,16 @@ def broadcast_tensors(ctx, tensors, src=0, chunk_numel=1 << 24):
                 batch.append(t)
                 count += t.numel()
                 continue
-            flat = torch.zeros(count, dtype=wire, device=device)
+            flat = torch.empty(count, dtype=wire, device=device)
             if rank == src:
                 off = 0
                 for b in batch:
                     flat[off:off + b.numel()].copy_(b.detach().reshape(-1))
                     off += b.numel()
-            job = ctx.all_reduce(flat)
+            job = ctx.broadcast(flat, src)
             if flat.is_cuda:
                 job.stream_wait(None)
             job.release()
-            if averaged and wire == torch.float32:
-                flat.mul_(float(n))
             off = 0
             with torch.no_grad():
                 for b in batch:
