@@ -156,6 +156,10 @@ def build(jobs=None, verbose=False, programs=True):
             _link([NVCC] + ARCH + ["-o", exe] + pobjs +
                   ["-L" + LIB, "-lswitchml_b200", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../lib",
                    "-lpthread", "-ldl", "-lrt"], verbose)
+    # A checked build that exists is kept in step with the sources (it exports the same C
+    # interface as the main library and would otherwise go stale without anybody noticing).
+    if os.path.isdir(os.path.join(ROOT, "build-checked")):
+        build_checked(verbose, jobs)
     return main_lib
 
 

@@ -28,3 +28,15 @@ def test_native_tests_under_sanitizer(kind):
     assert r.returncode == 0, out[-3000:]
     assert "ThreadSanitizer" not in out and "AddressSanitizer" not in out and "runtime error" not in out, out[-3000:]
     assert out.count("ok  ") == 12
+
+
+def test_checked_build_loads_and_exports_the_whole_c_interface():
+    """build-checked/ is built from the same sources with -DSWITCHML_CHECKED; the Python
+    binding must be able to load it in place of lib/ (every declared function present)."""
+    import sys
+    lib = _build_module().build_checked()
+    code = ("import sys; sys.path.insert(0, %r); import switchml_b200; from switchml_b200._native import lib; "
+            "assert lib().sml_checked_build() == 1; print('checked library ok')" % ROOT)
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=300,
+                       env=dict(os.environ, SWITCHML_B200_LIBRARY=lib))
+    assert r.returncode == 0 and "checked library ok" in r.stdout, r.stdout + r.stderr
