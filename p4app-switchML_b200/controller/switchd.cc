@@ -61,6 +61,7 @@ static std::string Translate(const std::string& line) {
       {"show_queue_pairs_counters", "SHOW qp", false},
       {"show_bitmap", "SHOW bitmap", true},
       {"show_statistics", "SHOW statistics", false},
+      {"show_slot", "SHOW slot", true},
       {"set_drop_probabilities", "SET drop", true},
       {"show_drop_probabilities", "SHOW drop", false},
       {"show_dropped_packets", "SHOW dropped", false},

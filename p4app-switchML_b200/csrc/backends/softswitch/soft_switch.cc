@@ -139,9 +139,11 @@ void SoftSwitch::Process(const uint8_t* data, size_t len, std::vector<SwitchOutp
     // absorbed and the aggregate is still waiting for others: nothing to do.
     if (cur.complete) {
       counters_.retransmit++;
+      cur.n_retransmit++;
       Emit(cur, pool_index, worker, h.thread_id, WIRE_RESULT_RETX, out);
     } else {
       counters_.ignored++;
+      cur.n_ignored++;
     }
     return;
   }
@@ -167,9 +169,11 @@ void SoftSwitch::Process(const uint8_t* data, size_t len, std::vector<SwitchOutp
   if (cur.remaining == 0) {
     cur.complete = true;
     counters_.broadcast++;
+    cur.n_broadcast++;
     for (int w = 0; w < num_workers_; w++) Emit(cur, pool_index, w, h.thread_id, WIRE_RESULT, out);
   } else {
     counters_.consumed++;
+    cur.n_consumed++;
   }
 }
 
@@ -268,6 +272,20 @@ std::string SoftSwitch::DescribeStatistics() const {
     << counters_.egress_dropped << "\nmalformed " << counters_.malformed << "\necho_replies "
     << counters_.echo_replies << "\nforwarded " << counters_.forwarded << "\nflooded "
     << counters_.flooded << "\n";
+  return o.str();
+}
+
+std::string SoftSwitch::DescribeSlot(uint32_t slot) const {
+  std::shared_lock<std::shared_mutex> lk(state_mu_);
+  slot %= num_slots_;
+  std::lock_guard<std::mutex> slot_lock(slot_mu_[slot % kStripes]);
+  std::ostringstream o;
+  o << " set  bitmap  missing  complete  broadcast  retransmit  consumed  ignored\n";
+  for (int k = 0; k < 2; k++) {
+    const SlotSet& s = sets_[k][slot];
+    o << " " << k << "  " << s.bitmap << "  " << s.remaining << "  " << (s.complete ? "yes" : "no") << "  "
+      << s.n_broadcast << "  " << s.n_retransmit << "  " << s.n_consumed << "  " << s.n_ignored << "\n";
+  }
   return o.str();
 }
 

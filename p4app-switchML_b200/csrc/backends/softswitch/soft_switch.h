@@ -103,6 +103,10 @@ class SoftSwitch {
   std::string DescribeWorkers() const;
   std::string DescribeStatistics() const;
   std::string DescribeDropped() const;
+  // One slot: bitmap, missing packets and the per-slot counters of both sets (the reference
+  // keeps four counters per slot and set in the next-step selector,
+  // p4/next_step_selector.p4:37-40, shown by the CLI's show_statistics).
+  std::string DescribeSlot(uint32_t slot) const;
   std::string DescribeEndpoints() const;
 
  private:
@@ -114,6 +118,9 @@ class SoftSwitch {
     uint32_t pkt_id = 0;
     uint8_t job_tag = 0;
     bool complete = false;   // values hold a finished aggregate (the retained copy)
+    // per slot and set: finished aggregates sent out, answers to retransmissions, packets
+    // absorbed while waiting for others, duplicates ignored (reset with the session)
+    uint32_t n_broadcast = 0, n_retransmit = 0, n_consumed = 0, n_ignored = 0;
     std::vector<int32_t> values;  // host order
   };
 

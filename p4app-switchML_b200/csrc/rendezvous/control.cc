@@ -444,6 +444,10 @@ std::string ControlServer::Handle(const std::string& line) {
       in >> slot;
       text = "slot " + std::to_string(slot) + " set0 " + std::to_string(switch_.Bitmap(slot, 0)) +
              " set1 " + std::to_string(switch_.Bitmap(slot, 1)) + "\n";
+    } else if (what == "slot") {
+      uint32_t slot = 0;
+      in >> slot;
+      text = switch_.DescribeSlot(slot);
     } else if (what == "dropped") text = switch_.DescribeDropped();
     else if (what == "qp") text = switch_.DescribeEndpoints();
     else if (what == "ports") text = DescribePorts();

@@ -13,7 +13,7 @@
 //   BCAST <n> <rank> <root> <u64>    everyone receives root's value
 //   GATHER <n> <rank> <token>        everyone receives all n tokens, ordered by rank
 //   UDPSESSION <session> <rank> <n> <packet_numel> <ip> <port0> <nthreads>
-//   SHOW workers|statistics|drop|dropped|qp|ports|forwarding|address|bitmap <slot>   (CLI)
+//   SHOW workers|statistics|drop|dropped|qp|ports|forwarding|address|bitmap <s>|slot <s>   (CLI)
 //   SET drop <ingress> <egress> [seed] | SET address <ip> <udp port>                 (CLI)
 //   RESET | PING                                                                      (CLI)
 // (docs/control_protocol.md is the full description, the counterpart of switchml.proto.)

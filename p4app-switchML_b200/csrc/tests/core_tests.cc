@@ -305,6 +305,10 @@ static void TestSoftSwitch() {
   send(0, 5, 228, 1, {1, 1, 1, 1});
   send(1, 5, 228, 1, {1, 1, 1, 1});
   EXPECT(out.size() == 3 && PayloadAt(out[0], 0) == 9);
+  // Per-slot counters of slot 5 so far: set 0 finished twice (one retransmission answered, one
+  // duplicate ignored), set 1 once.
+  EXPECT(sw.DescribeSlot(5).find(" 0  7  0  yes  2  1  4  1") != std::string::npos);
+  EXPECT(sw.DescribeSlot(5).find(" 1  0  0  yes  1  0  2  0") != std::string::npos);
   // Wrong session, unknown worker, short packet: counted as malformed, no output.
   out.clear();
   auto bad = MakePacket(0, 5, 1, 0, {1}, 43);

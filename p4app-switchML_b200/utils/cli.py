@@ -93,8 +93,11 @@ class Cli(cmd.Cmd):
         self._send("SHOW qp")
 
     def do_show_statistics(self, arg):
-        "Broadcast / retransmit / consumed / dropped packet counters of the switch."
-        self._send("SHOW statistics")
+        "show_statistics [slot]: packet counters of the switch, or of both sets of one slot."
+        if arg.strip():
+            self._send("SHOW slot %s" % arg.split()[0])
+        else:
+            self._send("SHOW statistics")
 
     def do_show_bitmap(self, arg):
         "show_bitmap <slot>: the worker bitmaps of both sets of a slot."

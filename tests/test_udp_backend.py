@@ -147,11 +147,12 @@ def test_console_against_standalone_controller(ports):
                      "show_statistics", "reset_workers", "history", "exit"):
             assert hasattr(cli, "do_" + name), name
         for c in ("show_ports", "show_forwarding_table", "show_dropped_packets", "show_queue_pairs_counters",
-                  "show_rdma_workers", "show_switch_address"):
+                  "show_rdma_workers", "show_switch_address", "show_statistics 3"):
             cli.onecmd(cli.precmd(c))
         text = out.getvalue()
         assert "127.0.0.1:%d/udp  up" % ports[1] in text and "udp_port %d" % ports[1] in text
         assert " total  0  0" in text
+        assert " set  bitmap  missing  complete  broadcast  retransmit  consumed  ignored" in text
         assert "ingress 0.5" in text and "egress 0.25" in text
         assert "broadcast 0" in text and "slot 3 set0 0 set1 0" in text
         assert "Unknown syntax: bogus" in text and "set_drop_probabilities" in text
