@@ -61,7 +61,7 @@ PROGRAMS = {
     "hello_world": ["examples/hello_world/main.cc"],
     "allreduce_benchmark": ["benchmarks/allreduce_benchmark.cc"],
     "dnn_benchmark": ["benchmarks/dnn_benchmark.cc"],
-    "core_tests": ["csrc/tests/core_tests.cc"],
+    "core_tests": ["csrc/tests/core_tests.cc", "csrc/tests/flag_protocol_model.cc"],
     "collnet_harness": ["csrc/nccl/collnet_harness.cc"],
 }
 
@@ -176,7 +176,8 @@ def build_sanitized(kind, verbose=False):
     with open(stub, "w") as f:
         f.write('#include "backends/cuda/cuda_backend.h"\n#include "switchml/log.h"\nnamespace switchml {\n'
                 'Backend* CreateCudaBackend(Context&, Config&) { SML_LOG(FATAL) << "no cuda in this build"; return nullptr; }\n}\n')
-    srcs = [os.path.join(ROOT, s) for s in HOST_ONLY + ["csrc/core/backend.cc", "csrc/tests/core_tests.cc"]] + [stub]
+    srcs = [os.path.join(ROOT, s) for s in HOST_ONLY + ["csrc/core/backend.cc", "csrc/tests/core_tests.cc",
+                                                         "csrc/tests/flag_protocol_model.cc"]] + [stub]
     exe = os.path.join(out, "core_tests")
     cmd = ["g++", "-std=c++17", "-O1", "-g", "-fno-omit-frame-pointer", "-fsanitize=" + kind, "-pthread"] + \
           INCLUDES + srcs + ["-o", exe]

@@ -23,6 +23,10 @@
 
 using namespace switchml;
 
+namespace switchml {
+int RunFlagProtocolModel();  // flag_protocol_model.cc
+}
+
 static int g_failures = 0;
 #define EXPECT(cond)                                                         \
   do {                                                                       \
@@ -428,6 +432,13 @@ static void TestSoftSwitchConcurrentPipes() {
   EXPECT(sw.endpoint_counters(0, 3).rx_packets == static_cast<uint64_t>(kSlotsPerPipe) * kRounds);
 }
 
+static void TestFlagProtocolModel() {
+  // The cross-GPU flag protocol of the aggregation kernels as a host model with real threads
+  // (three roles per channel and rank): bit-exact against the oracle, and race-free when this
+  // binary is built with -fsanitize=thread.
+  EXPECT(RunFlagProtocolModel() == 0);
+}
+
 static void TestQuantMath() {
   using namespace quant;
   EXPECT(LocalExponent(0.0f) == -126);
@@ -530,7 +541,7 @@ int main() {
   struct { const char* name; void (*fn)(); } tests[] = {
       {"logging", TestLogging}, {"numa_helpers", TestNumaHelpers}, {"simd_matches_scalar", TestSimdMatchesScalar}, {"static_slice", TestStaticSlice}, {"barrier", TestBarrier}, {"job_fsm", TestJobFsm},
       {"timeout_queue", TestTimeoutQueue}, {"soft_switch", TestSoftSwitch}, {"soft_switch_concurrent_pipes", TestSoftSwitchConcurrentPipes},
-      {"quant_math", TestQuantMath}, {"control_plane", TestControlPlane},
+      {"quant_math", TestQuantMath}, {"flag_protocol_model", TestFlagProtocolModel}, {"control_plane", TestControlPlane},
       {"context_dummy", TestContextDummy},
   };
   for (auto& t : tests) {

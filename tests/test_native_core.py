@@ -20,6 +20,7 @@ def test_core_tests_binary():
     _build()
     r = subprocess.run([os.path.join(PKG, "bin", "core_tests")], capture_output=True, text=True, timeout=120)
     assert r.returncode == 0, r.stdout + r.stderr
-    for name in ("static_slice", "barrier", "job_fsm", "timeout_queue", "soft_switch", "quant_math",
+    for name in ("logging", "numa_helpers", "simd_matches_scalar", "static_slice", "barrier", "job_fsm",
+                 "timeout_queue", "soft_switch", "soft_switch_concurrent_pipes", "quant_math", "flag_protocol_model",
                  "control_plane", "context_dummy"):
         assert "ok   " + name in r.stdout

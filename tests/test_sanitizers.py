@@ -27,7 +27,7 @@ def test_native_tests_under_sanitizer(kind):
     out = r.stdout + r.stderr
     assert r.returncode == 0, out[-3000:]
     assert "ThreadSanitizer" not in out and "AddressSanitizer" not in out and "runtime error" not in out, out[-3000:]
-    assert out.count("ok  ") == 12
+    assert out.count("ok  ") == 13
 
 
 def test_checked_build_loads_and_exports_the_whole_c_interface():
