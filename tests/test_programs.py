@@ -153,3 +153,18 @@ def test_python_hello_world_example(tmp_path):
     assert r.returncode == 0, r.stdout + r.stderr
     assert "Data verified successfully: 3 tensors of 5000 elements, 2 workers, backend dummy" in r.stdout
     assert "Finished jobs: #3#" in r.stdout
+
+
+def test_dnn_model_generator_matches_parameter_counts(tmp_path):
+    """benchmarks/make_dnn_model_csv.py: one line per parameter-owning module, the numel column
+    adds up to the model's parameter count, and dnn_benchmark accepts the file."""
+    import sys
+    script = os.path.join(PKG, "benchmarks", "make_dnn_model_csv.py")
+    r = subprocess.run([sys.executable, script, "--model", "resnet50", "--batch", "8"], capture_output=True, text=True,
+                       timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    rows = [l.split(",") for l in r.stdout.strip().splitlines()[1:]]
+    assert sum(int(x[1]) for x in rows) == 25557032          # ResNet-50
+    assert all(int(x[2]) >= 2000 and int(x[3]) >= int(x[2]) for x in rows)
+    shipped = open(os.path.join(PKG, "benchmarks", "models", "bert_large.csv")).read().strip().splitlines()[1:]
+    assert sum(int(l.split(",")[1]) for l in shipped) == 335174458   # BERT-large with the MLM head
