@@ -19,6 +19,12 @@
 //     tile to the output, which frees the slot;
 //   * each channel keeps the epoch it has reached in a word of its own and advances it when a
 //     job ends, so consecutive jobs need no host-side epoch bookkeeping.
+// A second variant, not yet in the kernels, is modelled as well ("piggyback"): the exponents of
+// tile k+1 travel with the payload of tile k - the reference sends the exponent of a block one
+// batch ahead of its payload for the same reason (cpu_exponent_quantizer_ppp.cc:115-156) - so
+// that only the first tile of a job needs the exponent barrier (phase 0) and every other tile
+// gets by with two all-to-all waits instead of three. It needs one exponent slot more than data
+// slots. The model shows that this ordering is race-free and gives the same bits.
 // The arithmetic is switchml/quant_math.h, so the result must equal the CPU oracle bit for bit.
 // The model has teeth: letting the reducer wait for phase 0 instead of phase 1 makes
 // ThreadSanitizer report data races on the slots and the results differ from the oracle.
@@ -43,6 +49,8 @@ const int kPhases = 3;
 
 struct Geometry {
   int ranks, channels, slots, block, tile;  // tile: elements, a multiple of ranks * block
+  bool piggyback;                           // exponents of tile k+1 ride with the payload of tile k
+  int exp_slots() const { return slots + 1; }
 };
 
 struct RankMemory {
@@ -54,7 +62,7 @@ struct RankMemory {
   std::atomic<int> failed{0};
   RankMemory(const Geometry& g)
       : flags(static_cast<size_t>(g.channels) * kPhases * g.ranks), data(static_cast<size_t>(g.channels) * g.slots * g.tile),
-        exps(static_cast<size_t>(g.channels) * g.slots * (g.tile / g.block)), epoch_words(g.channels, 0),
+        exps(static_cast<size_t>(g.channels) * g.exp_slots() * (g.tile / g.block)), epoch_words(g.channels, 0),
         stored(g.channels) {
     for (auto& f : flags) f.store(0);
     for (auto& s : stored) s.store(0);
@@ -70,8 +78,10 @@ struct Model {
   int32_t* Data(int rank, int channel, int slot) {
     return mem[rank]->data.data() + (static_cast<size_t>(channel) * g.slots + slot) * g.tile;
   }
-  int32_t* Exps(int rank, int channel, int slot) {
-    return mem[rank]->exps.data() + (static_cast<size_t>(channel) * g.slots + slot) * (g.tile / g.block);
+  // exponent slot of tile k: a ring one deeper than the data slots
+  int32_t* Exps(int rank, int channel, size_t k) {
+    return mem[rank]->exps.data() +
+           (static_cast<size_t>(channel) * g.exp_slots() + k % g.exp_slots()) * (g.tile / g.block);
   }
   void Signal(int me, int channel, int phase, uint64_t epoch) {
     for (int p = 0; p < g.ranks; p++) Flag(p, channel, phase, me).store(epoch, std::memory_order_release);
@@ -130,25 +140,37 @@ void Loader(Model& m, int me, int c, const float* in, size_t numel) {
       std::this_thread::yield();
     }
     const size_t nblocks = (len + g.block - 1) / g.block;
-    int32_t* my_exp = m.Exps(me, c, slot);
-    for (size_t b = 0; b < nblocks; b++) {
-      float mx = 0.f;
-      for (size_t i = b * g.block; i < std::min<size_t>(len, (b + 1) * g.block); i++) {
-        float v = fabsf(in[pos + i]);
-        if (v > mx) mx = v;
+    auto publish_exponents = [&](size_t tile) {
+      const size_t tpos = r.begin + tile * g.tile, tlen = std::min<size_t>(g.tile, r.end - tpos);
+      int32_t* my_exp = m.Exps(me, c, tile);
+      for (size_t b = 0; b * g.block < tlen; b++) {
+        float mx = 0.f;
+        for (size_t i = b * g.block; i < std::min<size_t>(tlen, (b + 1) * g.block); i++) {
+          float v = fabsf(in[tpos + i]);
+          if (v > mx) mx = v;
+        }
+        my_exp[b] = quant::LocalExponent(mx);
       }
-      my_exp[b] = quant::LocalExponent(mx);
+    };
+    if (!g.piggyback || k == 0) {
+      publish_exponents(k);
+      m.Signal(me, c, 0, epoch);
+      if (!m.Wait(me, c, 0, epoch)) return;
+    } else {
+      // everybody's exponents of this tile came with their payload of the previous one
+      if (!m.Wait(me, c, 1, epoch - 1)) return;
     }
-    m.Signal(me, c, 0, epoch);
-    if (!m.Wait(me, c, 0, epoch)) return;
     int32_t* mine = m.Data(me, c, slot);
     for (size_t b = 0; b < nblocks; b++) {
       int e = quant::kZeroExponent;
-      for (int p = 0; p < g.ranks; p++) e = std::max(e, static_cast<int>(m.Exps(p, c, slot)[b]));
+      for (int p = 0; p < g.ranks; p++) e = std::max(e, static_cast<int>(m.Exps(p, c, k)[b]));
       const float sf = quant::ScaleFactor(e, g.ranks);
       for (size_t i = b * g.block; i < std::min<size_t>(len, (b + 1) * g.block); i++)
         mine[i] = quant::Quantize(in[pos + i], sf);
     }
+    // The exponent slot of tile k+1 was last used by tile k-S, which this rank's storer has
+    // copied out (checked above), so every rank is done reading it.
+    if (g.piggyback && k + 1 < ntiles) publish_exponents(k + 1);
     m.Signal(me, c, 1, epoch);
   }
 }
@@ -169,7 +191,7 @@ void Reducer(Model& m, int me, int c, size_t numel) {
       uint32_t acc = 0;
       for (int p = 0; p < g.ranks; p++) acc += static_cast<uint32_t>(m.Data(p, c, slot)[i]);
       int e = quant::kZeroExponent;
-      for (int p = 0; p < g.ranks; p++) e = std::max(e, static_cast<int>(m.Exps(p, c, slot)[i / g.block]));
+      for (int p = 0; p < g.ranks; p++) e = std::max(e, static_cast<int>(m.Exps(p, c, k)[i / g.block]));
       const float y = quant::Dequantize(static_cast<int32_t>(acc), quant::ScaleFactor(e, g.ranks));
       int32_t bits;
       memcpy(&bits, &y, 4);
@@ -227,7 +249,8 @@ int RunFlagProtocolModel() {
   int failures = 0;
   uint32_t seed = 99;
   auto next = [&] { seed = seed * 1664525u + 1013904223u; return seed; };
-  const Geometry geometries[] = {{2, 2, 2, 64, 256}, {3, 2, 2, 64, 384}, {4, 3, 3, 32, 256}};
+  const Geometry geometries[] = {{2, 2, 2, 64, 256, false}, {3, 2, 2, 64, 384, false}, {4, 3, 3, 32, 256, false},
+                                 {2, 2, 2, 64, 256, true},  {3, 1, 2, 64, 384, true},  {4, 3, 3, 32, 256, true}};
   for (const Geometry& g : geometries) {
     Model m;
     m.g = g;
