@@ -85,6 +85,11 @@ class Job:
     def error(self):
         return read_string(lib().sml_job_error, self._h)
 
+    def __repr__(self):
+        if not self._h:
+            return "<switchml Job released>"
+        return "<switchml Job handle=%d %s>" % (self._h, self.status().name)
+
     def release(self):
         if self._h:
             lib().sml_job_release(self._h)
@@ -125,6 +130,24 @@ class Context:
 
     def state(self):
         return ContextState(lib().sml_state())
+
+    def running(self, config_text=None, apply_env=False):
+        """``with ctx.running(config):`` starts the context and stops it when the block ends,
+        also when the block raises."""
+        ctx = self
+
+        class _Running:
+            def __enter__(self):
+                if not ctx.start(config_text, apply_env):
+                    raise NativeError("the context did not start: " + last_error())
+                return ctx
+
+            def __exit__(self, *exc):
+                if ctx.state() == ContextState.RUNNING:
+                    ctx.stop()
+                return False
+
+        return _Running()
 
     def config_dump(self):
         return read_string(lib().sml_config_dump)

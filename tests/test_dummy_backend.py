@@ -139,3 +139,20 @@ def test_broadcast_on_the_dummy_backend(ctx):
     assert np.array_equal(x, np.arange(10, dtype=np.float32))
     stats = ctx.get_stats()
     assert stats["jobs_submitted"] == 2 and stats["jobs_finished"] == 1 and stats["jobs_failed"] == 1
+
+
+def test_running_context_manager_and_job_repr():
+    c = sml.Context.get_instance()
+    with c.running(sml.make_config("dummy", num_workers=2, bandwidth=0)) as ctx:
+        x = np.ones(100, dtype=np.float32)
+        job = ctx.all_reduce_async(x)
+        job.wait()
+        assert "FINISHED" in repr(job)
+        job.release()
+        assert "released" in repr(job)
+        assert float(x[0]) == 2.0
+    assert c.state() == sml.ContextState.STOPPED
+    with pytest.raises(ZeroDivisionError):
+        with c.running(sml.make_config("dummy", bandwidth=0)):
+            1 / 0
+    assert c.state() == sml.ContextState.STOPPED
