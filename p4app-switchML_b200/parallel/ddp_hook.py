@@ -12,11 +12,23 @@ import torch
 
 
 class SwitchMLHookState:
+    """`average` = True (what DDP expects of a hook): the bucket ends up holding the mean over
+    the workers. If the context already averages (``average = true`` in [backend.cuda]) nothing
+    is added; otherwise the hook divides the sum by the number of workers."""
+
     def __init__(self, ctx, average=True):
         self.ctx = ctx
         self.average = average
         self.stream = None
         self.jobs = []
+        dump = ctx.config_dump()
+        self.num_workers = 1
+        for line in dump.splitlines():
+            parts = line.split("=")
+            if len(parts) == 2 and parts[0].strip() == "num_workers":
+                self.num_workers = int(parts[1].strip())
+        self.context_averages = "backend = cuda" in dump and "average = true" in dump
+        self.divide = bool(average) and not self.context_averages and self.num_workers > 1
 
 
 def switchml_allreduce_hook(state, bucket):
@@ -25,6 +37,8 @@ def switchml_allreduce_hook(state, bucket):
         job = state.ctx.all_reduce_async(buf)
         job.wait()
         job.release()
+        if state.divide:
+            buf.div_(state.num_workers)
         fut = torch.futures.Future()
         fut.set_result(buf)
         return fut
@@ -41,6 +55,8 @@ def switchml_allreduce_hook(state, bucket):
         job = state.ctx.all_reduce_async(buf, stream=state.stream)
         job.stream_wait(state.stream)
         state.jobs.append(job)
+        if state.divide:
+            buf.div_(state.num_workers)
         # set_result records an event on the current (side) stream; whoever waits on the
         # future is ordered after the reduction.
         fut.set_result(buf)

@@ -557,3 +557,41 @@ def broadcast_cuda_worker(rank, n, ctl_port, mode, q):
         q.put((rank, "ok", None))
     except Exception:
         q.put((rank, "error", traceback.format_exc()))
+
+
+def ddp_hook_cpu_worker(rank, n, ctl_port, udp_port, dist_port, q):
+    """PyTorch DDP on CPU tensors (Gloo for its own bookkeeping) with the SwitchML comm hook
+    over the UDP backend: the gradients must be the mean of the workers' local gradients."""
+    try:
+        import torch
+        import torch.distributed as dist
+        import switchml_b200 as sml
+        from switchml_b200.parallel.ddp_hook import SwitchMLHookState, switchml_allreduce_hook
+        dist.init_process_group("gloo", rank=rank, world_size=n, init_method="tcp://127.0.0.1:%d" % dist_port)
+        ctx = sml.Context.get_instance()
+        assert ctx.start(sml.make_config("udp", rank=rank, num_workers=n, packet_numel=64, num_worker_threads=2,
+                                         max_outstanding_packets=64, controller_port=ctl_port, switch_port=udp_port,
+                                         worker_port=0))
+
+        def make():
+            torch.manual_seed(0)
+            return torch.nn.Sequential(torch.nn.Linear(16, 64), torch.nn.ReLU(), torch.nn.Linear(64, 4))
+        model, ref = make(), make()
+        ddp = torch.nn.parallel.DistributedDataParallel(model, bucket_cap_mb=0.005)
+        state = SwitchMLHookState(ctx)
+        assert state.divide and state.num_workers == n
+        ddp.register_comm_hook(state, switchml_allreduce_hook)
+        for it in range(2):
+            xs = [torch.randn(8, 16, generator=torch.Generator().manual_seed(3 * r + it)) for r in range(n)]
+            ddp.zero_grad()
+            ddp(xs[rank]).square().mean().backward()
+            ref.zero_grad()
+            for r in range(n):
+                (ref(xs[r]).square().mean() / n).backward()
+            for p, rp in zip(model.parameters(), ref.parameters()):
+                assert torch.allclose(p.grad, rp.grad, rtol=1e-4, atol=1e-6), "hook gradient != mean of local gradients"
+        ctx.stop()
+        dist.destroy_process_group()
+        q.put((rank, "ok", None))
+    except Exception:
+        q.put((rank, "error", traceback.format_exc()))

@@ -138,3 +138,26 @@ def test_parameters_are_broadcast_and_gradients_summed_across_real_workers():
         assert torch.equal(a, b)
     assert not all(torch.equal(a, b) for a, b in zip(got[0]["local"], got[1]["local"])), \
         "inside no_sync() the gradients must stay local"
+
+
+def test_torch_ddp_with_the_comm_hook_on_cpu():
+    """torch's own DistributedDataParallel, two processes, gradients reduced by the SwitchML
+    comm hook over the UDP backend."""
+    import multiprocessing as mp
+    from conftest import free_port
+    from _workers import ddp_hook_cpu_worker
+    ports = (free_port(), free_port(), free_port())
+    mpc = mp.get_context("spawn")
+    q = mpc.Queue()
+    procs = [mpc.Process(target=ddp_hook_cpu_worker, args=(r, 2, ports[0], ports[1], ports[2], q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    try:
+        for _ in range(2):
+            rank, status, info = q.get(timeout=180)
+            assert status == "ok", info
+    finally:
+        for p in procs:
+            p.join(timeout=30)
+            if p.is_alive():
+                p.kill()
