@@ -6,6 +6,7 @@
 
 Products (all inside this directory, never installed elsewhere):
     lib/libswitchml_b200.so        core + CPU backends + CUDA backend + C interface
+    lib/libswitchml_b200.a         the same as a static archive
     lib/libswitchml_gemm.so        tcgen05 weight-gradient GEMM (loaded on demand)
     lib/torch_switchml.so          native c10d backend for PyTorch (python build.py --torch)
     build-checked/libswitchml_b200.so   the library with the kernels' bounds checks (--checked)
@@ -137,6 +138,13 @@ def build(jobs=None, verbose=False, programs=True):
     if newer(main_lib, objs):
         # cudart is linked statically, so the library loads on machines without a driver.
         _link([NVCC] + ARCH + ["-shared", "-o", main_lib] + objs + ["-lpthread", "-ldl", "-lrt"], verbose)
+    # The same objects as a static archive (the reference's product is libswitchml-client.a);
+    # link it with nvcc, or with g++ plus -lcudart_static -ldl -lrt -lpthread.
+    static_lib = os.path.join(LIB, "libswitchml_b200.a")
+    if newer(static_lib, objs):
+        if os.path.exists(static_lib):
+            os.remove(static_lib)
+        _link(["ar", "rcs", static_lib] + objs, verbose)
     if gemm:
         gemm_lib = os.path.join(LIB, "libswitchml_gemm.so")
         gobjs = [_obj_path(s) for s in gemm]

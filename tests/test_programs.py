@@ -168,3 +168,34 @@ def test_dnn_model_generator_matches_parameter_counts(tmp_path):
     assert all(int(x[2]) >= 2000 and int(x[3]) >= int(x[2]) for x in rows)
     shipped = open(os.path.join(PKG, "benchmarks", "models", "bert_large.csv")).read().strip().splitlines()[1:]
     assert sum(int(l.split(",")[1]) for l in shipped) == 335174458   # BERT-large with the MLM head
+
+
+def test_static_archive_links_with_plain_gcc(built, cfg_dir):
+    """lib/libswitchml_b200.a (the reference ships its client library as a static archive):
+    a user program links against it with g++ and the static CUDA runtime, no nvcc needed."""
+    import shutil
+    cuda_lib = "/usr/local/cuda/lib64"
+    archive = os.path.join(PKG, "lib", "libswitchml_b200.a")
+    if not (os.path.exists(archive) and os.path.exists(os.path.join(cuda_lib, "libcudart_static.a")) and shutil.which("g++")):
+        pytest.skip("no static archive or no static CUDA runtime")
+    src = cfg_dir / "user.cc"
+    src.write_text('''
+        #include <cstdio>
+        #include <vector>
+        #include "switchml/context.h"
+        int main() {
+          switchml::Context& c = switchml::Context::GetInstance();
+          if (!c.Start()) return 1;
+          std::vector<float> x(1000, 1.5f);
+          auto job = c.AllReduce(x.data(), x.data(), x.size(), switchml::FLOAT32, switchml::SUM);
+          c.Stop();
+          printf("sum %g status %d\\\\n", x[0], static_cast<int>(job->GetJobStatus()));
+          return 0;
+        }''')
+    exe = cfg_dir / "user"
+    r = subprocess.run(["g++", "-std=c++17", "-I" + os.path.join(PKG, "include"), str(src), archive, "-L" + cuda_lib,
+                        "-lcudart_static", "-ldl", "-lrt", "-lpthread", "-o", str(exe)], capture_output=True, text=True,
+                       timeout=300)
+    assert r.returncode == 0, r.stderr[-3000:]
+    r = subprocess.run([str(exe)], cwd=cfg_dir, capture_output=True, text=True, timeout=60)
+    assert r.returncode == 0 and "sum 4.5 status 3" in r.stdout, r.stdout + r.stderr   # 3 dummy workers, FINISHED
