@@ -6,15 +6,25 @@
         --master-port 29500 bench.py --gpus 8 --steps 20 --warmup 5
     python bench.py --impl reference ...        # the reference's own NCCL path
 
-One step = one SUM allreduce of a float32 tensor of 2^28 elements (the default of the
-reference's benchmark tools, benchmarks/allreduce_benchmark/main.cc:101) through the
-public Context API. ATE/s = numel / time per step; bus GB/s = 4*numel/time * 2(n-1)/n.
-The timed region is bracketed by a barrier and a device synchronisation, timed with CUDA
-events on the launching stream, and the slowest rank counts. Rank 0 prints one JSON line.
+One step = one SUM allreduce, in place, of an ordinary float32 device tensor of 2^28
+elements: what the reference's benchmark script runs
+(benchmarks/allreduce_pytorch_benchmark/allreduce_pytorch_benchmark.py:112-127, default size
+from benchmarks/allreduce_benchmark/main.cc:101). ATE/s = numel / time per step; bus GB/s =
+4*numel/time * 2(n-1)/n. The timed region is bracketed by a barrier and a device
+synchronisation, timed with CUDA events on the launching stream, and the slowest rank
+counts. Rank 0 prints one JSON line. Both arms print the same ``config``.
+
+Named extras of this library's arm: the same allreduce on tensors of the symmetric heap
+(reduced in place over NVLink without staging), and the exact integer mode (per-block
+exponent fixed point) with a bit-for-bit check against the CPU oracle.
 
 The end-to-end figure ("e2e") times the same allreduce for a caller whose data lives in
-pinned host memory: every step copies the input host→device, reduces it and reads the
-result back device→host, through switchml_b200.parallel.host_pipeline.HostAllReduce.
+pinned host memory: every step brings the input host→device, reduces it and returns the
+result device→host. This library's arm measures two ways of doing that through its public
+API (copies and kernels pipelined over chunks; one kernel that reads and writes the pinned
+buffers itself) and reports the faster; the reference arm copies, calls the script's
+``dist.all_reduce`` and copies back, the staging pattern of the reference's PyTorch plugin
+(frameworks_integration/pytorch_plugin/ProcessGroupSML.cpp:117-163).
 
 Other workloads (same JSON shape): --workload resnet50 | vgg19 | bert (synthetic DDP
 training, images/s or tokens/s).
@@ -34,7 +44,63 @@ if ROOT not in sys.path:
 PUBLISHED_ATE = 2.82e9  # SwitchML-RDMA, 8 workers, read off the reference's benchmark figure
 
 
-from switchml_b200.utils.clocks import ClockSampler  # noqa: E402
+class SmiSampler:
+    """SM clocks and throttle reasons from ``nvidia-smi`` while a region runs (reads only).
+
+    Standard library only, so that the reference arm imports nothing of this repository."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index=0):
+        self.gpu, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits", "-lms", "25",
+                 "-i", str(self.gpu)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.time(), line.strip()))
+
+    def stop(self, window=None):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        time.sleep(0.05)
+        lines = self.lines
+        if window and lines:
+            inside = [l for l in lines if window[0] <= l[0] <= window[1] + 0.06]
+            if len(inside) < 3:  # region shorter than the sampling period: the nearest samples
+                mid = 0.5 * (window[0] + window[1])
+                inside = sorted(lines, key=lambda l: abs(l[0] - mid))[:5]
+            lines = inside
+        sm, smax, power, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for _, line in lines:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])), smax.append(float(f[2])), power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
 
 
 def dist_env():
@@ -46,94 +112,88 @@ def dist_env():
     return rank, world, local, addr, port
 
 
-def max_over_ranks(value, world):
-    import torch
-    import torch.distributed as dist
-    if world == 1:
-        return value
-    t = torch.tensor([value], dtype=torch.float64, device="cuda")
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    return float(t.item())
-
-
-def barrier(world):
-    import torch
-    import torch.distributed as dist
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-
-
-def start_context(args, rank, world, local, addr, port, heap_mb=0):
-    import switchml_b200 as sml
-    ctx = sml.Context.get_instance()
-    opts = dict(packet_numel=args.packet_numel, device=local, controller_ip=addr,
-                controller_port=port + 101, mode=args.mode, transport=args.transport, launch="inline",
-                symm_heap_mb=heap_mb, wait_timeout_ms=30000)
-    if args.slot_bytes:
-        opts["slot_bytes"] = args.slot_bytes
-    if args.channels:
-        opts["channels"] = args.channels
-    if not ctx.start(sml.make_config("cuda", rank=rank, num_workers=world, **opts)):
-        raise RuntimeError("Context.start failed")
-    return ctx
+def workload_config(numel, esz, dtype_name, world):
+    """The ``config`` entry, identical in both arms."""
+    return {"model": "allreduce_microbenchmark", "numel": numel, "tensor_bytes": numel * esz,
+            "dtype": dtype_name, "op": "SUM", "placement": "in place, ordinary device tensor",
+            "global_batch": None, "seq_len": None, "parallelism": "dp%d" % world,
+            "l2": "the tensor (%d MiB) is larger than the 126 MB L2" % (numel * esz >> 20),
+            "e2e": "pinned host input -> device -> allreduce -> pinned host output, every step",
+            "single_gpu_note": None if world > 1 else
+            "with one worker an in-place SUM changes nothing: neither arm moves data in the device-timed "
+            "region (NCCL returns at once, this library launches no kernel); the end-to-end figure and "
+            "the named extras are the measurements that do work at n_gpus = 1"}
 
 
 # ------------------------------------------------------------------------------------------
 def bench_allreduce(args):
+    import numpy as np
     import torch
     import torch.distributed as dist
     rank, world, local, addr, port = dist_env()
     if world != args.gpus:
         raise SystemExit("--gpus %d but WORLD_SIZE is %d (launch with torch.distributed.run)" % (args.gpus, world))
     torch.cuda.set_device(local)
+    import switchml_b200 as sml
     from switchml_b200.utils.numa import bind_to_device_numa
-    numa_node = bind_to_device_numa(local)  # pinned host buffers end up next to the GPU
+    numa_node = bind_to_device_numa(local)  # pinned host buffers allocated from here on sit next to the GPU
     if world > 1:
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local))
     numel = args.numel
     dtype = {"float32": torch.float32, "int32": torch.int32, "bfloat16": torch.bfloat16}[args.dtype]
     esz = torch.empty((), dtype=dtype).element_size()
-    heap_mb = 0
-    if args.symmetric:
-        heap_mb = (2 * numel * esz >> 20) + 64
-    ctx = start_context(args, rank, world, local, addr, port, heap_mb)
+
+    def max_over_ranks(value):
+        if world == 1:
+            return value
+        t = torch.tensor([value], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def start_context(mode, heap_mb):
+        ctx = sml.Context.get_instance()
+        opts = dict(packet_numel=args.packet_numel, device=local, controller_ip=addr,
+                    controller_port=port + 101, mode=mode, transport=args.transport, launch="inline",
+                    symm_heap_mb=heap_mb, wait_timeout_ms=30000)
+        if args.slot_bytes:
+            opts["slot_bytes"] = args.slot_bytes
+        if args.channels:
+            opts["channels"] = args.channels
+        if not ctx.start(sml.make_config("cuda", rank=rank, num_workers=world, **opts)):
+            raise RuntimeError("Context.start failed")
+        return ctx
 
     g = torch.Generator(device="cuda").manual_seed(1234 + rank)
 
-    def make_tensors(symmetric):
-        if symmetric:
-            a, b = ctx.symmetric_empty(numel, dtype), ctx.symmetric_empty(numel, dtype)
-        else:
-            a = torch.empty(numel, dtype=dtype, device="cuda")
-            b = torch.empty(numel, dtype=dtype, device="cuda")
+    def fill(t):
         if dtype == torch.int32:
-            a.copy_(torch.randint(-2 ** 20, 2 ** 20, (numel,), generator=g, device="cuda", dtype=torch.int32))
+            t.copy_(torch.randint(-2 ** 20, 2 ** 20, (numel,), generator=g, device="cuda", dtype=torch.int32))
         else:
-            a.copy_((torch.rand(numel, generator=g, device="cuda") * 2 - 1).to(dtype))
-        return a, b
+            t.copy_((torch.rand(numel, generator=g, device="cuda") * 2 - 1).to(dtype))
+        return t
 
-    sampler = ClockSampler(local)
+    def launches(ctx):
+        return ctx.get_stats()["backend"].get("kernel_launches", 0)
+
+    sampler = SmiSampler(local)
     if rank == 0:
         sampler.start()  # nvidia-smi needs a moment to start: launch it before the warm-up
 
-    def measure(x, y, steps, want_clocks):
-        """W warm-up jobs, a correctness check against NCCL, then `steps` timed jobs."""
+    def measure(ctx, x, y, steps, want_clocks=False):
+        """W warm-up jobs, then `steps` timed jobs (y None = in place). Returns ms per step
+        (device time, slowest rank), kernels launched in the timed region, clocks."""
         jobs = [ctx.all_reduce_async(x, y) for _ in range(args.warmup)]  # enqueued on the current stream
-        barrier(world)
+        barrier()
         for j in jobs:
             assert j.wait() == 3, j.error()
             j.release()
-        check = None
-        if world > 1 and dtype != torch.int32:
-            ref = x.clone().float()
-            dist.all_reduce(ref)
-            err = (y.float() - ref).abs().max().item()
-            scale = ref.abs().max().item()
-            check = {"max_abs_err_vs_nccl": err, "max_abs": scale}
-            assert err <= 1e-3 * max(scale, 1.0), "allreduce result is wrong: err %g" % err
-            del ref
-        barrier(world)
+        barrier()
+        k0 = launches(ctx)
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         w0 = time.time()
         start.record()
@@ -141,65 +201,161 @@ def bench_allreduce(args):
         stop.record()
         torch.cuda.synchronize()
         w1 = time.time()
-        barrier(world)
+        barrier()
         clocks = sampler.stop((w0, w1)) if (rank == 0 and want_clocks) else None
-        t = max_over_ranks(start.elapsed_time(stop), world) / steps
+        dev_ms = start.elapsed_time(stop)
         for j in jobs:
             assert j.wait() == 3, j.error()
             j.release()
-        return t, check, clocks
+        k1 = launches(ctx)
+        if k1 == k0:
+            dev_ms = max(dev_ms, (w1 - w0) * 1e3)  # nothing ran on the device: the host's time per call
+        return max_over_ranks(dev_ms) / steps, k1 - k0, clocks
 
-    # Secondary measurement first: ordinary device tensors, which go through the staging ring.
-    plain_ms = None
-    if args.symmetric and args.mode == "float_sum":
-        px, py = make_tensors(False)
-        plain_ms, _, _ = measure(px, py, max(3, args.steps // 2), False)
-        del px, py
-    x, y = make_tensors(bool(args.symmetric) and args.mode == "float_sum")
-    ms, check, clocks = measure(x, y, args.steps, True)
+    heap_mb = (2 * numel * esz >> 20) + 64 if args.symmetric else 0
+    ctx = start_context("float_sum", heap_mb)
+    multimem = ctx.uses_multimem()
+
+    # ---- correctness of the headline path against NCCL, on values that are still small ----
+    x = fill(torch.empty(numel, dtype=dtype, device="cuda"))
+    check = None
+    if world > 1:
+        ref = x.clone()
+        dist.all_reduce(ref)
+        mine = x.clone()
+        j = ctx.all_reduce_async(mine)
+        assert j.wait() == 3, j.error()
+        j.release()
+        torch.cuda.synchronize()
+        if dtype == torch.int32:
+            bad = int((mine != ref).sum().item())
+            check = {"int32_mismatches_vs_nccl": bad}
+            assert bad == 0, "int32 allreduce differs from NCCL in %d elements" % bad
+        else:
+            err = (mine.float() - ref.float()).abs().max().item()
+            scale = ref.float().abs().max().item()
+            check = {"max_abs_err_vs_nccl": err, "max_abs": scale}
+            assert err <= 1e-3 * max(scale, 1.0), "allreduce result is wrong: err %g" % err
+        del ref, mine
+
+    # ---- headline: ordinary tensor, in place (the reference script's call) ----
+    ms, head_launches, clocks = measure(ctx, x, None, args.steps, True)
+    total_launches = head_launches
+    breakdown = {"headline_in_place": head_launches}
+
+    # ---- extra: tensors of the symmetric heap, out of place ----
+    symmetric = None
+    if args.symmetric:
+        sx, sy = fill(ctx.symmetric_empty(numel, dtype)), ctx.symmetric_empty(numel, dtype)
+        s_ms, s_launches, _ = measure(ctx, sx, sy, max(3, args.steps // 2))
+        symmetric = {"note": "tensors from Context.symmetric_empty, out of place; with several workers they are "
+                             "reduced over NVLink where they lie, with one worker this is a device copy",
+                     "ms_per_step": s_ms, "ate_per_worker": numel / (s_ms * 1e-3),
+                     "bus_gbs": esz * numel / (s_ms * 1e-3) * (2.0 * (world - 1) / world) / 1e9}
+        total_launches += s_launches
+        breakdown["symmetric_tensors"] = s_launches
+        del sx, sy
+        ctx.symmetric_reset()
 
     # ---- end to end: pinned host -> device -> allreduce -> pinned host ----
     hx = torch.empty(numel, dtype=dtype, pin_memory=True)
     hy = torch.empty(numel, dtype=dtype, pin_memory=True)
-    hx.copy_(x)
+    hx.copy_(fill(x))
+    torch.cuda.synchronize()
+    e2e_steps = args.e2e_steps
+
+    def time_host(fn, steps):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        barrier()
+        k0 = launches(ctx)
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            fn()  # returns when the result is in host memory
+        torch.cuda.synchronize()
+        t = (time.perf_counter() - t0) / steps
+        return max_over_ranks(t * 1e3), launches(ctx) - k0
+
+    # ceiling: nothing but the two copies, at the same time, on every GPU at once
+    dx = torch.empty(numel, dtype=dtype, device="cuda")
+    s_up, s_down = torch.cuda.Stream(), torch.cuda.Stream()
+
+    def copies_only():
+        with torch.cuda.stream(s_up):
+            dx.copy_(hx, non_blocking=True)
+        with torch.cuda.stream(s_down):
+            hy.copy_(x, non_blocking=True)
+        s_up.synchronize()
+        s_down.synchronize()
+
+    ceiling_ms, _ = time_host(copies_only, max(2, e2e_steps // 2))
+    del dx
+
     from switchml_b200.parallel.host_pipeline import HostAllReduce
+    variants = {}
     pipe = HostAllReduce(ctx, numel, dtype, chunk_numel=args.e2e_chunk)
-    for _ in range(max(1, min(args.warmup, 3))):
-        pipe.run(hx, hy)
-    torch.cuda.synchronize()
-    barrier(world)
-    t0 = time.perf_counter()
-    for _ in range(args.e2e_steps):
-        pipe.run(hx, hy)  # returns when the result is in host memory
-    torch.cuda.synchronize()
-    e2e_s = (time.perf_counter() - t0) / args.e2e_steps
-    e2e_ms = max_over_ranks(e2e_s * 1e3, world)
-    e2e_launches = pipe.launches_per_run
+    variants["pipelined_copies"] = time_host(lambda: pipe.run(hx, hy), e2e_steps)
     pipe.close()
+    store_out = HostAllReduce(ctx, numel, dtype, chunk_numel=args.e2e_chunk, direct="out")
+    variants["copy_in_kernel_stores_to_pinned"] = time_host(lambda: store_out.run(hx, hy), e2e_steps)
+    store_out.close()
+    direct = HostAllReduce(ctx, numel, dtype, direct=True)
+    variants["kernel_on_pinned_memory"] = time_host(lambda: direct.run(hx, hy), e2e_steps)
+    direct.close()
+    e2e_check = None
+    if world > 1 and dtype != torch.int32:
+        ref = x.clone()
+        dist.all_reduce(ref)
+        e2e_check = (hy.cuda().float() - ref.float()).abs().max().item()
+        assert e2e_check <= 1e-3 * max(ref.float().abs().max().item(), 1.0), "end-to-end result is wrong"
+        del ref
+    best = min(variants, key=lambda k: variants[k][0])
+    e2e_ms, e2e_launches = variants[best]
+    total_launches += e2e_launches
+    breakdown["e2e"] = e2e_launches
 
     stats = ctx.get_stats()
-    multimem = ctx.uses_multimem()
     ctx.stop()
-    # Secondary measurement: the exact, order-independent integer mode (SwitchML's block
-    # fixed point), ordinary tensors, same size. It needs its own context (mode is a setting).
+
+    # ---- extra: the exact, order-independent integer mode (SwitchML's block fixed point) ----
     quant = None
-    if args.mode == "float_sum" and dtype == torch.float32 and args.quant_steps > 0:
-        del x, y
-        saved_mode, args.mode = args.mode, "int32_quant"
-        ctx = start_context(args, rank, world, local, addr, port, 0)
-        args.mode = saved_mode
-        qx, qy = make_tensors(False)
-        q_ms, _, _ = measure(qx, qy, args.quant_steps, False)
-        quant = {"note": "int32_quant mode (per-block exponent fixed point, exact integer sum), ordinary tensors",
-                 "ms_per_step": q_ms, "ate_per_worker": numel / (q_ms * 1e-3), "steps": args.quant_steps}
-        del qx, qy
+    if dtype == torch.float32 and args.quant_steps > 0:
+        ctx = start_context("int32_quant", 0)
+        # bit-for-bit against the CPU oracle on a small odd-sized tensor with zero blocks
+        from switchml_b200.ops.oracle import quant_allreduce_oracle
+        small = (1 << 20) + 1
+        rng = [np.random.RandomState(77 + r) for r in range(world)]
+        ins = [(r_.rand(small).astype(np.float32) * 2 - 1) * np.float32(10.0 ** (i - 2)) for i, r_ in enumerate(rng)]
+        for a in ins:
+            a[4096:8192] = 0.0
+            a[-257:-1] = 0.0
+        want = quant_allreduce_oracle(ins, args.packet_numel)
+        t_in = torch.from_numpy(ins[rank]).cuda()
+        t_out = torch.empty_like(t_in)
+        j = ctx.all_reduce_async(t_in, t_out)
+        assert j.wait() == 3, j.error()
+        j.release()
+        torch.cuda.synchronize()
+        mismatches = int((t_out.cpu().numpy().view(np.uint32) != want.view(np.uint32)).sum())
+        mismatches = int(max_over_ranks(float(mismatches)))
+        assert mismatches == 0, "int32_quant result differs from the oracle in %d elements" % mismatches
+        y = torch.empty(numel, dtype=dtype, device="cuda")
+        q_ms, q_launches, _ = measure(ctx, fill(x), y, args.quant_steps)
+        qstats = ctx.get_stats()["backend"]
+        quant = {"note": "int32_quant mode (per-block exponent fixed point, exact integer sum), ordinary tensors, "
+                         "out of place", "ms_per_step": q_ms, "ate_per_worker": numel / (q_ms * 1e-3),
+                 "steps": args.quant_steps, "oracle_check": {"numel": small, "mismatched_bits": mismatches},
+                 "channel0_ns": qstats.get("channel0_ns")}
+        total_launches += q_launches
+        breakdown["int32_quant"] = q_launches
+        del y
         ctx.stop()
     if world > 1:
         dist.destroy_process_group()
     if rank != 0:
         return
     ate = numel / (ms * 1e-3)  # per worker, the reference's definition
-    bus = esz * numel / (ms * 1e-3) * (2.0 * (world - 1) / world) / 1e9
     out = {
         "metric": "allreduce_ate_per_s", "value": ate * world, "unit": "elements/s", "n_gpus": world,
         "value_definition": "whole-job aggregate: n_gpus x numel / time per allreduce; ate_per_worker = numel / time "
@@ -210,25 +366,23 @@ def bench_allreduce(args):
         "scaling": "weak", "vs_baseline": ate / PUBLISHED_ATE, "dtype": "fp32" if args.dtype == "float32" else args.dtype,
         "data": "synthetic U(-1,1) seeded per rank",
         "impl": "switchml_b200",
-        "config": {"model": "allreduce_microbenchmark", "numel": numel, "tensor_bytes": numel * esz,
-                   "global_batch": None, "seq_len": None, "parallelism": "dp%d" % world,
-                   "op": "SUM", "mode": args.mode, "transport": "nvls" if multimem else ("p2p" if world > 1 else "local"),
-                   "symmetric_buffers": bool(args.symmetric) and args.mode == "float_sum", "packet_numel": args.packet_numel,
-                   "l2": "input and output tensors (%d MiB each) are larger than the 126 MB L2" % (numel * esz >> 20),
-                   "placement": "out of place (input -> output), so repeated steps keep their values bounded",
-                   "single_gpu_note": None if world > 1 else
-                   "with one worker the sum is a copy: one pass over input and output at HBM speed; NCCL's "
-                   "in-place allreduce on a single rank returns without touching the data"},
-        "bus_gbs": bus, "alg_gbs": esz * numel / (ms * 1e-3) / 1e9,
+        "config": workload_config(numel, esz, args.dtype, world),
+        "impl_details": {"mode": "float_sum", "transport": "nvls" if multimem else ("p2p" if world > 1 else "local"),
+                         "packet_numel": args.packet_numel,
+                         "channel0_ns": stats["backend"].get("channel0_ns")},
+        "bus_gbs": esz * numel / (ms * 1e-3) * (2.0 * (world - 1) / world) / 1e9,
+        "alg_gbs": esz * numel / (ms * 1e-3) / 1e9,
+        "symmetric_tensors": symmetric,
         "int32_quant": quant,
-        "plain_tensors": None if plain_ms is None else {
-            "note": "same allreduce on ordinary torch tensors (staged through the slot ring)",
-            "ms_per_step": plain_ms, "ate_per_worker": numel / (plain_ms * 1e-3)},
         "e2e": {"value": world * numel / (e2e_ms * 1e-3), "unit": "elements/s", "ms_per_step": e2e_ms,
                 "ate_per_worker": numel / (e2e_ms * 1e-3),
                 "h2d_bytes_per_step": numel * esz, "d2h_bytes_per_step": numel * esz,
-                "steps": args.e2e_steps, "gpu_launches_per_step": e2e_launches, "host_numa_node": numa_node},
-        "gpu_launches": args.steps,
+                "steps": e2e_steps, "gpu_launches_per_step": e2e_launches / e2e_steps, "path": best,
+                "variants_ms": {k: v[0] for k, v in variants.items()},
+                "copy_ceiling_ms": ceiling_ms, "host_numa_node": numa_node,
+                "max_abs_err_vs_nccl": e2e_check},
+        "gpu_launches": total_launches,
+        "gpu_launches_by_region": breakdown,
         "clocks": clocks, "check": check,
         "stats": {"jobs_finished": stats["jobs_finished"], "jobs_failed": stats["jobs_failed"],
                   "tiles": stats["backend"]["tiles"]},
@@ -240,9 +394,12 @@ def bench_allreduce(args):
 def bench_reference(args):
     """Run the reference's own benchmark script, unmodified, on its NCCL backend.
 
-    The script times with the host clock around ``work.wait()``, which for NCCL does not
-    wait for the GPU, so the device time is taken here with CUDA events recorded around
-    the script's own ``dist.all_reduce`` calls (the calls themselves are untouched)."""
+    Nothing of this repository's package is imported here. The script times with the host
+    clock around ``work.wait()``, which for NCCL does not wait for the GPU, so the device
+    time is taken with CUDA events recorded around the script's own ``dist.all_reduce``
+    calls (the calls themselves are untouched). Afterwards, on the process group the script
+    created, the end-to-end loop: pinned host -> device copy, ``dist.all_reduce``, device ->
+    pinned host copy, one after the other as the reference's PyTorch plugin stages them."""
     rank, world, local, addr, port = dist_env()
     script = os.path.join(ROOT, "baseline", "_ref", "benchmarks", "allreduce_pytorch_benchmark",
                           "allreduce_pytorch_benchmark.py")
@@ -283,11 +440,12 @@ def bench_reference(args):
     os.environ.pop("TORCHELASTIC_USE_AGENT_STORE", None)
     old_argv, old_stdout = sys.argv, sys.stdout
     sys.argv = argv
-    sampler = ClockSampler(local)
+    sampler = SmiSampler(local)
     if rank == 0:
         sampler.start()
     log = open(os.devnull, "w")
     sys.stdout = log
+    w0 = time.time()
     try:
         runpy.run_path(script, run_name="__main__")
     finally:
@@ -295,18 +453,47 @@ def bench_reference(args):
         sys.argv = old_argv
         dist.all_reduce = real_all_reduce
     torch.cuda.synchronize()
-    clocks = sampler.stop() if rank == 0 else None
+    w1 = time.time()
+    clocks = sampler.stop((w0, w1)) if rank == 0 else None
     timed = events[args.warmup:]
     total_ms = timed[0][0].elapsed_time(timed[-1][1])
     ms = total_ms / len(timed)
-    if world > 1:
-        t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+
+    def max_over_ranks(value):
+        if world == 1:
+            return value
+        t = torch.tensor([value], dtype=torch.float64, device="cuda")
         real_all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
+        return float(t.item())
+
+    ms = max_over_ranks(ms)
+
+    # ---- end to end on the script's process group ----
+    numel = args.numel
+    dtype = torch.float32 if args.dtype == "float32" else torch.int32
+    hx = torch.rand(numel, dtype=torch.float32).to(dtype).pin_memory()
+    hy = torch.empty(numel, dtype=dtype, pin_memory=True)
+    d = torch.empty(numel, dtype=dtype, device="cuda")
+
+    def step():
+        d.copy_(hx, non_blocking=True)
+        real_all_reduce(d, op=dist.ReduceOp.SUM)
+        hy.copy_(d, non_blocking=True)
+        torch.cuda.synchronize()  # the result is in host memory
+
+    for _ in range(2):
+        step()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(args.e2e_steps):
+        step()
+    e2e_ms = max_over_ranks((time.perf_counter() - t0) / args.e2e_steps * 1e3)
+    if world > 1:
         dist.destroy_process_group()
     if rank != 0:
         return
-    numel = args.numel
     ate = numel / (ms * 1e-3)
     print(json.dumps({
         "impl": "reference", "metric": "allreduce_ate_per_s", "value": ate * world, "unit": "elements/s",
@@ -314,10 +501,14 @@ def bench_reference(args):
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": ate / PUBLISHED_ATE,
         "dtype": "fp32" if args.dtype == "float32" else args.dtype, "data": "synthetic (script's --random)",
-        "config": {"model": "allreduce_microbenchmark", "numel": numel, "parallelism": "dp%d" % world,
-                   "backend": "nccl via dev_root/benchmarks/allreduce_pytorch_benchmark (unmodified)",
-                   "timing": "CUDA events around the script's dist.all_reduce calls"},
+        "config": workload_config(numel, 4, args.dtype, world),
+        "impl_details": {"backend": "nccl via dev_root/benchmarks/allreduce_pytorch_benchmark (unmodified)",
+                         "timing": "CUDA events around the script's dist.all_reduce calls"},
         "bus_gbs": 4 * numel / (ms * 1e-3) * (2.0 * (world - 1) / world) / 1e9,
+        "e2e": {"value": world * numel / (e2e_ms * 1e-3), "unit": "elements/s", "ms_per_step": e2e_ms,
+                "ate_per_worker": numel / (e2e_ms * 1e-3), "h2d_bytes_per_step": numel * 4,
+                "d2h_bytes_per_step": numel * 4, "steps": args.e2e_steps,
+                "path": "pinned host -> device copy, dist.all_reduce (NCCL), device -> pinned host copy"},
         "clocks": clocks,
     }), flush=True)
 
@@ -331,17 +522,17 @@ def main():
     ap.add_argument("--workload", default="allreduce", choices=["allreduce", "resnet50", "vgg19", "bert"])
     ap.add_argument("--numel", type=int, default=1 << 28)
     ap.add_argument("--dtype", default="float32", choices=["float32", "int32", "bfloat16"])
-    ap.add_argument("--mode", default=os.environ.get("SWITCHML_MODE", "float_sum"),
-                    choices=["int32_quant", "float_sum"])
+    ap.add_argument("--mode", default=os.environ.get("SWITCHML_MODE", "float_sum"), choices=["int32_quant", "float_sum"],
+                    help="training workloads: aggregation mode of the gradient allreduce (the allreduce workload "
+                         "measures float_sum as the headline and int32_quant as a named extra)")
     ap.add_argument("--transport", default="auto", choices=["auto", "nvls", "p2p"])
     ap.add_argument("--symmetric", type=int, default=1,
-                    help="1: the tensors are allocated with Context.symmetric_empty (reduced in place over NVLink, "
-                         "float_sum mode); 0: ordinary torch tensors through the staging ring")
+                    help="1: also measure tensors allocated with Context.symmetric_empty (reduced where they lie)")
     ap.add_argument("--packet-numel", type=int, default=256)
     ap.add_argument("--slot-bytes", type=int, default=0, help="0 = library default")
     ap.add_argument("--channels", type=int, default=0)
     ap.add_argument("--e2e-steps", type=int, default=5)
-    ap.add_argument("--quant-steps", type=int, default=5, help="steps of the secondary int32_quant measurement (0 = skip)")
+    ap.add_argument("--quant-steps", type=int, default=5, help="steps of the int32_quant measurement (0 = skip)")
     ap.add_argument("--e2e-chunk", type=int, default=1 << 24)
     ap.add_argument("--batch", type=int, default=0, help="per-GPU batch for the training workloads")
     ap.add_argument("--ddp", default="sml", choices=["sml", "torch"], help="training workloads: this library or PyTorch DDP/NCCL")

@@ -151,9 +151,16 @@ class CudaBackend : public CudaBackendInterface {
   int* host_status_ = nullptr;  // pinned ring of status words
 
   std::mutex launch_mu_;  // serialises launches: one job order on every rank
+  // launch = inline: all jobs share the staging slots, the flag pad and the per-channel
+  // epochs, so two jobs must never run on the GPU at the same time. A job submitted on a
+  // stream other than the previous job's is ordered after that job through this event.
+  cudaEvent_t order_event_ = nullptr;
+  cudaStream_t order_stream_ = nullptr;
+  bool order_valid_ = false;
   unsigned long long epoch_base_ = 0;
   int oneshot_parity_ = 0;
   unsigned long long launched_jobs_ = 0;
+  unsigned long long kernel_launches_ = 0;  // kernels of this library enqueued so far (under launch_mu_)
 
   std::shared_ptr<EventPool> events_ = std::make_shared<EventPool>();
 
@@ -252,6 +259,8 @@ void CudaBackend::SetupWorker() {
   int lo = 0, hi = 0;
   cudaDeviceGetStreamPriorityRange(&lo, &hi);
   SML_CUDA_CHECK(cudaStreamCreateWithPriority(&comm_stream_, cudaStreamNonBlocking, hi));
+  SML_CUDA_CHECK(cudaEventCreateWithFlags(&order_event_, cudaEventDisableTiming));
+  order_valid_ = false;
   SML_CUDA_CHECK(cudaMalloc(&dev_counters_, 16 * sizeof(unsigned long long)));
   SML_CUDA_CHECK(cudaMemset(dev_counters_, 0, 16 * sizeof(unsigned long long)));
   SML_CUDA_CHECK(cudaMalloc(&dev_epochs_, kernels::kMaxChannels * sizeof(unsigned long long)));
@@ -267,6 +276,7 @@ void CudaBackend::SetupWorker() {
   epoch_base_ = 0;
   oneshot_parity_ = 0;
   launched_jobs_ = 0;
+  kernel_launches_ = 0;
   failed_ = false;
   SML_CUDA_CHECK(cudaDeviceSynchronize());
   if (n_ > 1) SML_CHECK(client_.Barrier(n_)) << "barrier failed";
@@ -301,6 +311,9 @@ void CudaBackend::CleanupWorker() {
   if (staging_.local) allocator_->Destroy(&staging_, peers_alive);
   if (comm_stream_) cudaStreamDestroy(comm_stream_);
   comm_stream_ = nullptr;
+  if (order_event_) cudaEventDestroy(order_event_);
+  order_event_ = nullptr;
+  order_valid_ = false;
   if (dev_counters_) cudaFree(dev_counters_);
   if (dev_epochs_) cudaFree(dev_epochs_);
   dev_epochs_ = nullptr;
@@ -456,6 +469,7 @@ void CudaBackend::LaunchJob(const std::shared_ptr<Job>& job, cudaStream_t stream
   bool plain_copy = n_ == 1 && a.mode == kernels::MODE_SUM && a.post_scale == 1.0f && !nothing_to_do;
   if (t.numel > 0 && plain_copy) e = kernels::LaunchLocalCopy(t.in_ptr, t.out_ptr, bytes, stream);
   else if (t.numel > 0 && !nothing_to_do) e = kernels::LaunchAllReduce(job_ctx, a, plan, stream);
+  if (t.numel > 0 && !nothing_to_do && e == cudaSuccess) kernel_launches_ += widened ? 3 : 1;
   SML_NVTX_POP();
   if (widened) {
     if (e == cudaSuccess) e = kernels::LaunchNarrowI32(widened, user.out_ptr, user.numel, stream);
@@ -510,7 +524,18 @@ bool CudaBackend::OnSubmit(const std::shared_ptr<Job>& job) {
     std::lock_guard<std::mutex> lk(launch_mu_);
     job->SetJobStatus(QUEUED);
     job->SetJobStatus(RUNNING);
+    // Not while capturing: an event recorded outside the capture cannot be waited on inside
+    // it. A captured job is ordered by the graph it becomes part of; whoever replays that
+    // graph next to other jobs of this context orders the two.
+    if (!capturing && order_valid_ && order_stream_ != user_stream)
+      cudaStreamWaitEvent(user_stream, order_event_, 0);
     LaunchJob(job, user_stream, &f, capturing);
+    if (!capturing && cudaEventRecord(order_event_, user_stream) == cudaSuccess) {
+      order_stream_ = user_stream;
+      order_valid_ = true;
+    } else if (!capturing) {
+      cudaGetLastError();
+    }
   }
   if (capturing) {
     // The kernels now live in the graph under capture and run whenever it is replayed;
@@ -631,7 +656,8 @@ std::string CudaBackend::ExtraStatsJson() {
   std::ostringstream o;
   o << "{\"device\":" << device_ << ",\"multimem\":" << (ctx_.use_multimem ? "true" : "false")
     << ",\"tiles\":" << c[0] << ",\"wait_spins\":" << c[1] << ",\"device_timeouts\":" << c[2]
-    << ",\"jobs_launched\":" << launched_jobs_ << ",\"epoch\":" << epoch_base_
+    << ",\"jobs_launched\":" << launched_jobs_ << ",\"kernel_launches\":" << kernel_launches_
+    << ",\"epoch\":" << epoch_base_
     << ",\"channel0_ns\":{\"loader_wait\":" << c[3] << ",\"loader_work\":" << c[4]
     << ",\"reducer_wait\":" << c[5] << ",\"reducer_work\":" << c[6] << ",\"storer_wait\":" << c[7]
     << ",\"storer_work\":" << c[8] << "}}";

@@ -105,6 +105,7 @@ void SoftSwitch::Process(const uint8_t* data, size_t len, std::vector<SwitchOutp
   }
   if (ntohl(h.magic) != kWireMagic || h.type != WIRE_DATA || numel > kMaxPacketNumel ||
       len != sizeof(h) + numel * 4u || worker >= num_workers_ || worker >= kMaxWorkers ||
+      h.thread_id >= kMaxThreads ||  // the return port is looked up by (worker, thread): refuse what the table cannot hold
       !(registered_ & (1u << worker)) || ntohs(h.session_lo) != static_cast<uint16_t>(session_id_) ||
       (pool_index & ~kSetBit) >= num_slots_) {
     counters_.malformed++;
@@ -117,8 +118,8 @@ void SoftSwitch::Process(const uint8_t* data, size_t len, std::vector<SwitchOutp
     worker_counters_[worker].ingress_dropped++;
     return;
   }
-  EndpointCounters* ep = h.thread_id < kMaxThreads ? &endpoint_counters_[worker][h.thread_id] : nullptr;
-  if (ep) ep->rx_packets++;
+  EndpointCounters* ep = &endpoint_counters_[worker][h.thread_id];
+  ep->rx_packets++;
 
   int k = (pool_index & kSetBit) ? 1 : 0;
   uint32_t slot = pool_index & ~kSetBit;
@@ -133,7 +134,7 @@ void SoftSwitch::Process(const uint8_t* data, size_t len, std::vector<SwitchOutp
   other.bitmap &= ~bit;
 
   if (seen) {
-    if (ep) ep->out_of_order++;
+    ep->out_of_order++;
     // A retransmission. If the slot is finished the worker lost the result: send it again
     // from the retained copy, to that worker only. Otherwise the first copy was already
     // absorbed and the aggregate is still waiting for others: nothing to do.

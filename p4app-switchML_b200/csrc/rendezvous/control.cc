@@ -554,8 +554,13 @@ void ControlServer::DataPlaneLoop(int pipe) {
       for (size_t o = before; o < out.size(); o++) {
         sockaddr_in d = src;
         if (!out[o].to_sender) {
-          std::lock_guard<std::mutex> lk(learned_mu_);
-          d = learned_[out[o].dest_worker][out[o].dest_thread];
+          const int dw = out[o].dest_worker, dt = out[o].dest_thread;
+          if (dw < 0 || dw >= kMaxWorkers || dt < 0 || dt >= kMaxThreads) {
+            memset(&d, 0, sizeof(d));  // no such port: port 0 is skipped below
+          } else {
+            std::lock_guard<std::mutex> lk(learned_mu_);
+            d = learned_[dw][dt];
+          }
         }
         to.push_back(d);
       }

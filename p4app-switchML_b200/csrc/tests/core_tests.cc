@@ -321,6 +321,12 @@ static void TestSoftSwitch() {
   sw.Process(bad.data(), bad.size(), &out);
   sw.Process(bad.data(), 3, &out);
   EXPECT(out.empty() && sw.counters().malformed == 3);
+  // A valid session and worker, but a thread id beyond the return-port table: refused
+  // before any slot state is touched (slot 11 stays empty).
+  bad = MakePacket(0, 11, 1, 0, {1}, 42);
+  bad[offsetof(WireHeader, thread_id)] = 200;
+  sw.Process(bad.data(), bad.size(), &out);
+  EXPECT(out.empty() && sw.counters().malformed == 4 && sw.Bitmap(11, 0) == 0);
   // Drop simulator: everything dropped on ingress.
   sw.SetDropProbabilities(1.0, 0.0, 1);
   send(0, 9, 1, 0, {1, 1, 1, 1});

@@ -235,6 +235,9 @@ def test_switch_survives_malformed_and_hostile_datagrams(ports):
             send(pack_header(WireType.DATA, worker=0, pool_index=0x7FFF, numel=64, session=session) + b"\0" * 256)
             send(pack_header(WireType.DATA, worker=0, numel=64, session=session + 1) + b"\0" * 256)  # other session
             send(pack_header(WireType.RESULT, worker=0, numel=64, session=session) + b"\0" * 256)    # not for a switch
+            for r in range(2):                                     # valid in every field but the thread id: the
+                send(pack_header(WireType.DATA, worker=r, thread=200, pool_index=9, numel=64,  # return-port table
+                                 session=session) + b"\0" * 256)                             # has no such row
             send(pack_header(9, worker=0, numel=0, session=session))                                  # unknown type
             send(pack_header(WireType.FORWARD, worker=0, pool_index=(7 << 8), session=session) + b"x")   # no such worker
             send(pack_header(WireType.FORWARD, worker=5, pool_index=(1 << 8), session=session) + b"x")   # sender unknown
@@ -258,7 +261,8 @@ def test_switch_survives_malformed_and_hostile_datagrams(ports):
             assert deadline, "no echo reply after the flood"
         assert controller_command("127.0.0.1", ports[0], "PING") == ""
         stats = dict(l.split() for l in controller_command("127.0.0.1", ports[0], "SHOW statistics").splitlines())
-        assert int(stats["malformed"]) >= 330, stats
+        assert int(stats["malformed"]) >= 332, stats
+        assert "set0 0 set1 0" in controller_command("127.0.0.1", ports[0], "SHOW bitmap 9"), "slot 9 was touched"
         assert int(stats["broadcast"]) == 0 and int(stats["forwarded"]) == 0, stats
         ports_table = controller_command("127.0.0.1", ports[0], "SHOW ports")
         assert int(ports_table.splitlines()[2].split()[3]) >= sent
