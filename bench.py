@@ -180,6 +180,10 @@ def bench_allreduce(args):
     def launches(ctx):
         return ctx.get_stats()["backend"].get("kernel_launches", 0)
 
+    def role_budget(ctx):
+        """ns that the roles of channel 0 spent waiting / working so far (device counters)."""
+        return dict(ctx.get_stats()["backend"].get("channel0_ns") or {})
+
     sampler = SmiSampler(local)
     if rank == 0:
         sampler.start()  # nvidia-smi needs a moment to start: launch it before the warm-up
@@ -194,6 +198,7 @@ def bench_allreduce(args):
             j.release()
         barrier()
         k0 = launches(ctx)
+        b0 = role_budget(ctx)
         start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         w0 = time.time()
         start.record()
@@ -210,6 +215,8 @@ def bench_allreduce(args):
         k1 = launches(ctx)
         if k1 == k0:
             dev_ms = max(dev_ms, (w1 - w0) * 1e3)  # nothing ran on the device: the host's time per call
+        b1 = role_budget(ctx)
+        measure.budget_us_per_step = {k: round((b1[k] - b0.get(k, 0)) / steps / 1e3, 1) for k in b1}
         return max_over_ranks(dev_ms) / steps, k1 - k0, clocks
 
     heap_mb = (2 * numel * esz >> 20) + 64 if args.symmetric else 0
@@ -240,6 +247,7 @@ def bench_allreduce(args):
 
     # ---- headline: ordinary tensor, in place (the reference script's call) ----
     ms, head_launches, clocks = measure(ctx, x, None, args.steps, True)
+    head_budget = measure.budget_us_per_step
     total_launches = head_launches
     breakdown = {"headline_in_place": head_launches}
 
@@ -342,11 +350,10 @@ def bench_allreduce(args):
         assert mismatches == 0, "int32_quant result differs from the oracle in %d elements" % mismatches
         y = torch.empty(numel, dtype=dtype, device="cuda")
         q_ms, q_launches, _ = measure(ctx, fill(x), y, args.quant_steps)
-        qstats = ctx.get_stats()["backend"]
         quant = {"note": "int32_quant mode (per-block exponent fixed point, exact integer sum), ordinary tensors, "
                          "out of place", "ms_per_step": q_ms, "ate_per_worker": numel / (q_ms * 1e-3),
                  "steps": args.quant_steps, "oracle_check": {"numel": small, "mismatched_bits": mismatches},
-                 "channel0_ns": qstats.get("channel0_ns")}
+                 "channel0_us_per_step": measure.budget_us_per_step}
         total_launches += q_launches
         breakdown["int32_quant"] = q_launches
         del y
@@ -369,7 +376,7 @@ def bench_allreduce(args):
         "config": workload_config(numel, esz, args.dtype, world),
         "impl_details": {"mode": "float_sum", "transport": "nvls" if multimem else ("p2p" if world > 1 else "local"),
                          "packet_numel": args.packet_numel,
-                         "channel0_ns": stats["backend"].get("channel0_ns")},
+                         "channel0_us_per_step": head_budget},
         "bus_gbs": esz * numel / (ms * 1e-3) * (2.0 * (world - 1) / world) / 1e9,
         "alg_gbs": esz * numel / (ms * 1e-3) / 1e9,
         "symmetric_tensors": symmetric,

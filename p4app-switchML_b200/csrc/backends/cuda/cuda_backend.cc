@@ -411,7 +411,6 @@ void CudaBackend::LaunchJob(const std::shared_ptr<Job>& job, cudaStream_t stream
               : t.data_type == BFLOAT16 ? kernels::ELEM_BF16 : kernels::ELEM_I32;
   a.mode = (!integer && c.mode == "int32_quant") ? kernels::MODE_QUANT : kernels::MODE_SUM;
   a.post_scale = c.average && !integer && !broadcast ? 1.0f / static_cast<float>(n_) : 1.0f;
-  a.tune = static_cast<int>(c.tune);
   size_t esz = DataTypeSize(t.data_type);
   size_t bytes = t.numel * esz;
 
@@ -421,23 +420,40 @@ void CudaBackend::LaunchJob(const std::shared_ptr<Job>& job, cudaStream_t stream
     return heap_.local && p >= heap_.local &&
            static_cast<const char*>(p) + bytes <= static_cast<const char*>(heap_.local) + heap_.bytes;
   };
-  bool heap_ok = in_heap(t.in_ptr) && in_heap(t.out_ptr) &&
-                 (reinterpret_cast<uintptr_t>(t.in_ptr) & 15) == 0 &&
-                 (reinterpret_cast<uintptr_t>(t.out_ptr) & 15) == 0 &&
-                 (!ctx_.use_multimem || heap_.multicast);
-  if (a.mode == kernels::MODE_SUM && heap_ok && n_ > 1) {
-    a.algo = kernels::ALGO_ZEROCOPY;
+  auto heap_usable = [&](const void* p) {
+    return in_heap(p) && (reinterpret_cast<uintptr_t>(p) & 15) == 0 && (!ctx_.use_multimem || heap_.multicast);
+  };
+  const bool out_in_heap = n_ > 1 && heap_usable(t.out_ptr);
+  const bool heap_ok = out_in_heap && heap_usable(t.in_ptr);
+  auto describe_heap = [&] {
     for (int p = 0; p < n_; p++) a.user_peer[p] = static_cast<char*>(heap_.peers[p]);
     a.user_mc = static_cast<char*>(heap_.multicast);
     a.user_bytes = heap_.bytes;
     a.in_offset = static_cast<const char*>(t.in_ptr) - static_cast<const char*>(heap_.local);
     a.out_offset = static_cast<const char*>(t.out_ptr) - static_cast<const char*>(heap_.local);
-  } else if (bytes <= c.oneshot_max_bytes) {
+  };
+  // Peer-memory transport moves large messages with posted stores only, unless told otherwise.
+  const bool push = n_ > 1 && !ctx_.use_multimem && c.p2p_algo == "push" &&
+                    kernels::PushTileCapacity(ctx_, a.elem_type, a.mode) > 0;
+  if (bytes <= c.oneshot_max_bytes && !(a.mode == kernels::MODE_SUM && heap_ok)) {
     a.algo = kernels::ALGO_ONESHOT;
     a.oneshot_parity = oneshot_parity_;
     if (!capturing) oneshot_parity_ ^= 1;
+  } else if (push && bytes > c.oneshot_max_bytes) {
+    a.algo = kernels::ALGO_PUSH;
+    if (out_in_heap) {  // results go straight into every rank's output
+      a.out_zero_copy = 1;
+      describe_heap();
+    }
+  } else if (a.mode == kernels::MODE_SUM && heap_ok) {
+    a.algo = kernels::ALGO_ZEROCOPY;
+    describe_heap();
   } else {
     a.algo = kernels::ALGO_STAGED;
+    if (a.mode == kernels::MODE_QUANT && out_in_heap) {
+      a.out_zero_copy = 1;
+      describe_heap();
+    }
   }
   kernels::LaunchPlan plan = kernels::PlanLaunch(ctx_, a, c.channels, max_channels_);
   a.tile_elems = plan.tile_elems;
@@ -768,6 +784,10 @@ int EmulatedAllReduce(int nranks, void* const* in_ptrs, void* const* out_ptrs,
   if (e != cudaSuccess) {
     cleanup();
     return fail(std::string("allocation failed: ") + cudaGetErrorString(e), -3);
+  }
+  if (algo == ALGO_PUSH && PushTileCapacity(proto, elem_type, mode) == 0) {
+    cleanup();
+    return fail("ALGO_PUSH needs at least two ranks and slots of about twice nranks * max(block, 128) * 4 bytes", -1);
   }
   std::vector<RankCtx> ctxs(nranks, proto);
   std::vector<JobArgs> jobs(nranks);

@@ -117,7 +117,7 @@ bool Config::LoadFromString(const std::string& text, const std::string& origin) 
   opts["backend.cuda.average"] = SML_OPT_BOOL(backend_.cuda.average);
   opts["backend.cuda.launch"] = SML_OPT_STRING(backend_.cuda.launch);
   opts["backend.cuda.rendezvous_dir"] = SML_OPT_STRING(backend_.cuda.rendezvous_dir);
-  opts["backend.cuda.tune"] = SML_OPT_UNSIGNED(backend_.cuda.tune);
+  opts["backend.cuda.p2p_algo"] = SML_OPT_STRING(backend_.cuda.p2p_algo);
   opts["backend.cuda.numa_bind"] = SML_OPT_BOOL(backend_.cuda.numa_bind);
   opts["backend.cuda.wait_timeout_ms"] = [this](const std::string& v) {
     return ParseDouble(v, &backend_.cuda.wait_timeout_ms);
@@ -268,6 +268,8 @@ void Config::Validate() {
         << "backend.cuda.transport must be auto | nvls | p2p";
     SML_CHECK(c.mode == "int32_quant" || c.mode == "float_sum")
         << "backend.cuda.mode must be int32_quant | float_sum";
+    SML_CHECK(c.p2p_algo == "push" || c.p2p_algo == "staged")
+        << "backend.cuda.p2p_algo must be push | staged";
     SML_CHECK(c.launch == "worker" || c.launch == "inline")
         << "backend.cuda.launch must be worker | inline";
     SML_CHECK(c.slots_per_channel >= 1 && c.slots_per_channel <= 8)

@@ -29,6 +29,7 @@
 #include "kernels/allreduce_kernels.h"
 #include "kernels/device_sync.cuh"
 #include "kernels/multimem.cuh"
+#include "kernels/quant_tile.cuh"
 #include "switchml/quant_math.h"
 
 namespace switchml {
@@ -37,7 +38,7 @@ namespace kernels {
 namespace {
 
 static const int kMaxBlocksPerSlot = 8192;  // scale factors of all slots of a channel (shared memory)
-static const int kUnroll = 4;        // 16-byte vectors in flight per thread, local copies
+static const int kUnroll = 8;        // 16-byte vectors in flight per thread, local copies
 static const int kDefaultUnrollLink = 4;  // ... for staged loads that cross NVLink (8 measured slower)
 static const int kZeroCopyUnrollLink = 2;  // in-switch reduction: few requests in flight are best (8 GPUs: 2.25 ms vs 2.38 ms with 8)
 static const int kZeroCopyUnrollPeer = 16;  // plain peer loads want many (2 GPUs: 1.75 ms vs 1.91 ms with 2)
@@ -281,7 +282,7 @@ template <int ELEM, int MODE, int kLoadWarps = kDefaultLoadWarps, int kReduceWar
 __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
                           unsigned long long elems_per_channel, Epoch base, StagedShared* sh, float* s_sf) {
   constexpr int kStoreWarps = kThreads / 32 - kLoadWarps - kReduceWarps;
-  constexpr int kUnrollInt = 2 * kUnrollLink;  // 4-byte integer lanes in flight per thread
+  constexpr int kUnrollInt = 4 * kUnrollLink;  // 4-byte integer lanes in flight per thread
   const int in_esz = ELEM == ELEM_BF16 ? 2 : 4;
   const int st_esz = MODE == MODE_QUANT ? 4 : in_esz;
   const size_t slot_elems = ctx.slot_bytes / st_esz;
@@ -296,8 +297,14 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
   const size_t tile_elems = job.tile_elems;  // <= slot_elems; small jobs use small tiles
   const unsigned long long ntiles = (c1 - c0 + tile_elems - 1) / tile_elems;
   char* my_stage = ctx.stage_peer[ctx.rank];
-  const size_t blocks_per_slot = slot_elems / ctx.block_numel;
+  const size_t blocks_per_slot = ctx.slot_bytes / 4 / ctx.block_numel;
   const int shift = 31 - __clz(ctx.block_numel);  // block_numel is a power of two
+  // With two or more slots the exponents of tile k+1 travel while tile k is quantised, so the
+  // agreement never costs a wait of its own; a single slot leaves no room to run ahead.
+  const bool ahead = S >= 2;
+  // The output lies in symmetric memory: the owner of a shard broadcasts the finished values
+  // straight into every rank's output and nothing is copied out of the slot.
+  const bool direct_out = job.out_zero_copy != 0;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   Role role;
@@ -321,25 +328,35 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
       t_mark = now;
     }
   };
+  auto tile_len = [&](unsigned long long k) {
+    const unsigned long long pos = c0 + k * tile_elems;
+    return static_cast<size_t>(c1 - pos < tile_elems ? c1 - pos : tile_elems);
+  };
+  auto exp_offset_of = [&](unsigned long long k) {
+    const size_t slot_index = static_cast<size_t>(channel) * S + static_cast<size_t>(k % S);
+    return ctx.exp_offset + slot_index * blocks_per_slot * kExpWordBytes;
+  };
 
   for (unsigned long long k = 0; k < ntiles; ++k) {
     const unsigned long long pos = c0 + k * tile_elems;
     const Epoch epoch = base + k + 1;
-    const size_t len = static_cast<size_t>(c1 - pos < tile_elems ? c1 - pos : tile_elems);
+    const size_t len = tile_len(k);
     const int slot = static_cast<int>(k % S);
     const size_t slot_index = static_cast<size_t>(channel) * S + slot;
     const size_t slot_off = ctx.data_offset + slot_index * ctx.slot_bytes;  // same on all ranks
-    const size_t exp_off = ctx.exp_offset + slot_index * blocks_per_slot * 4;
+    const size_t exp_off = exp_offset_of(k);
     SML_GEOMETRY_CHECK(ctx, channel, failed,
                        len > 0 && len <= slot_elems && pos + len <= job.numel &&
                        slot_off >= ctx.data_offset && slot_off + ctx.slot_bytes <= ctx.stage_bytes &&
                        (MODE != MODE_QUANT ||
-                        (blocks_per_slot <= static_cast<size_t>(kMaxBlocksPerSlot) &&
-                         exp_off + blocks_per_slot * 4 <= ctx.oneshot_offset)));
+                        (blocks_per_slot * S <= static_cast<size_t>(kMaxBlocksPerSlot) &&
+                         exp_off + blocks_per_slot * kExpWordBytes <= ctx.oneshot_offset)) &&
+                       (!direct_out || job.out_offset + (pos + len) * in_esz <= job.user_bytes));
     float* sf = s_sf + static_cast<size_t>(slot) * blocks_per_slot;
 
     if (which == 0) {
       // ------------------------------ loader ------------------------------
+      const char* in = static_cast<const char*>(job.in) + pos * in_esz;
       // The slot is free once the tile that used it last has been copied out here; by
       // then every peer has finished reading it as well (their phase-2 signals came
       // before that copy-out).
@@ -358,133 +375,34 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
         role.Sync();
         if (*failed) return;
       }
+      if (MODE == MODE_QUANT) {
+        if (k == 0 || !ahead) {
+          // Nobody has published this tile's exponents yet: do it now and meet (phase 0).
+          // With a single slot its words are free by now: every rank consumed them before
+          // it signalled the payload of the tile before, and the copy-out awaited above
+          // came after all those signals.
+          PublishTileExponents<ELEM>(ctx, warp, kLoadWarps, lane, in, len, exp_off, epoch);
+          RoleSignal(ctx, role, channel, 0, epoch);
+          if (!RoleWait(ctx, role, channel, 0, epoch, sh)) return;
+        } else {
+          // They came with the payload signal of the tile before.
+          if (!RoleWait(ctx, role, channel, 1, epoch - 1, sh)) return;
+        }
+      }
       lap(3);
-      const char* in = static_cast<const char*>(job.in) + pos * in_esz;
       if (MODE == MODE_QUANT) {
         const size_t nblocks = (len + ctx.block_numel - 1) / ctx.block_numel;
-        int* my_exp = reinterpret_cast<int*>(my_stage + exp_off);
-        const int nwarps = kLoadWarps;
-        const size_t B = ctx.block_numel;
-        const bool vec_ok = ELEM == ELEM_F32 && Aligned16(in) && (B % 128) == 0;
-        constexpr int kBlocksPerIter = 4;  // independent blocks per warp iteration: loads in flight
-        size_t first_block = 0;
-        if (ELEM == ELEM_F32 && Aligned16(in) && B < 128) {
-          // Small blocks (32 or 64 elements): a warp reads rows of 128 elements with one
-          // float4 per lane; a block is B/4 neighbouring lanes, reduced with a butterfly.
-          const int g = static_cast<int>(B / 4);           // lanes per block: 8 or 16
-          const size_t per_row = 128 / B;                  // blocks per row: 4 or 2
-          const size_t nrows = len / 128;                  // whole rows; the rest goes the slow way
-          const float4* p4 = reinterpret_cast<const float4*>(in);
-          for (size_t r0 = static_cast<size_t>(warp) * kBlocksPerIter; r0 < nrows;
-               r0 += static_cast<size_t>(nwarps) * kBlocksPerIter) {
-            float m[kBlocksPerIter];
-#pragma unroll
-            for (int u = 0; u < kBlocksPerIter; u++) {
-              m[u] = 0.f;
-              if (r0 + u < nrows) {
-                float4 x = p4[(r0 + u) * 32 + lane];
-                m[u] = fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w)));
-              }
-            }
-#pragma unroll
-            for (int u = 0; u < kBlocksPerIter; u++) {
-              float mm = m[u];
-              for (int o = g >> 1; o > 0; o >>= 1) {
-                float t = __shfl_xor_sync(0xffffffffu, mm, o);
-                if (t > mm) mm = t;
-              }
-              if ((lane % g) == 0 && r0 + u < nrows) my_exp[(r0 + u) * per_row + lane / g] = quant::LocalExponent(mm);
-            }
-          }
-          first_block = nrows * per_row;
-        }
-        for (size_t b0 = first_block + static_cast<size_t>(warp) * kBlocksPerIter; b0 < nblocks;
-             b0 += static_cast<size_t>(nwarps) * kBlocksPerIter) {
-          float m[kBlocksPerIter];
-#pragma unroll
-          for (int u = 0; u < kBlocksPerIter; u++) {
-            m[u] = 0.f;
-            const size_t b = b0 + u;
-            if (b >= nblocks) continue;
-            const size_t base = b * B;
-            const size_t n = len - base < B ? len - base : B;
-            if (vec_ok && n == B) {
-              const float4* p4 = reinterpret_cast<const float4*>(in) + base / 4;
-              for (size_t j = lane; j < B / 4; j += 32) {
-                float4 x = p4[j];
-                m[u] = fmaxf(m[u], fmaxf(fmaxf(fabsf(x.x), fabsf(x.y)), fmaxf(fabsf(x.z), fabsf(x.w))));
-              }
-            } else {
-              for (size_t i = lane; i < n; i += 32) {
-                float v = fabsf(LoadAsFloat<ELEM>(in, base + i));
-                if (v > m[u]) m[u] = v;
-              }
-            }
-          }
-#pragma unroll
-          for (int u = 0; u < kBlocksPerIter; u++) {
-            float mm = m[u];
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-              float t = __shfl_xor_sync(0xffffffffu, mm, o);
-              if (t > mm) mm = t;
-            }
-            if (lane == 0 && b0 + u < nblocks) my_exp[b0 + u] = quant::LocalExponent(mm);
-          }
-        }
-        RoleSignal(ctx, role, channel, 0, epoch);
-        if (!RoleWait(ctx, role, channel, 0, epoch, sh)) return;
-        for (size_t b = role.tid; b < nblocks; b += role.nthreads) {
-          int e;
-          if (ctx.use_multimem) {
-            e = MultimemLdReduceMaxS32(ctx.stage_mc + exp_off + b * 4);
-          } else {
-            e = quant::kZeroExponent;
-            for (int p = 0; p < ctx.nranks; p++) {
-              int t = __ldcg(reinterpret_cast<const int*>(ctx.stage_peer[p] + exp_off) + b);
-              if (t > e) e = t;
-            }
-          }
-          sf[b] = quant::ScaleFactorFromBase(e, ctx.quant_base);
-        }
+        TileScaleFactors(ctx, role.tid, role.nthreads, exp_off, nblocks, epoch, sf, channel, failed);
         role.Sync();
-        int* q = reinterpret_cast<int*>(my_stage + slot_off);
-        if (ELEM == ELEM_F32 && Aligned16(in)) {
-          const float4* in4 = reinterpret_cast<const float4*>(in);
-          size_t nvec = len / 4;
-          const size_t nt = role.nthreads;
-          size_t i = role.tid;
-          for (; i + (kUnroll - 1) * nt < nvec; i += kUnroll * nt) {
-            float4 x[kUnroll];
-#pragma unroll
-            for (int u = 0; u < kUnroll; u++) x[u] = in4[i + u * nt];
-#pragma unroll
-            for (int u = 0; u < kUnroll; u++) {
-              float f = sf[((i + u * nt) * 4) >> shift];  // a vector never straddles a block (>= 32)
-              int4 r;
-              r.x = quant::Quantize(x[u].x, f);
-              r.y = quant::Quantize(x[u].y, f);
-              r.z = quant::Quantize(x[u].z, f);
-              r.w = quant::Quantize(x[u].w, f);
-              reinterpret_cast<int4*>(q)[i + u * nt] = r;
-            }
-          }
-          for (; i < nvec; i += nt) {
-            float4 x = in4[i];
-            float f = sf[(i * 4) >> shift];
-            int4 r;
-            r.x = quant::Quantize(x.x, f);
-            r.y = quant::Quantize(x.y, f);
-            r.z = quant::Quantize(x.z, f);
-            r.w = quant::Quantize(x.w, f);
-            reinterpret_cast<int4*>(q)[i] = r;
-          }
-          for (size_t i = nvec * 4 + role.tid; i < len; i += role.nthreads)
-            q[i] = quant::Quantize(reinterpret_cast<const float*>(in)[i], sf[i >> shift]);
-        } else {
-          for (size_t i = role.tid; i < len; i += role.nthreads)
-            q[i] = quant::Quantize(LoadAsFloat<ELEM>(in, i), sf[i >> shift]);
-        }
+        if (*failed) return;
+        QuantizeRange<ELEM, 8>(role.tid, role.nthreads, in, reinterpret_cast<int*>(my_stage + slot_off), 0, len,
+                               sf, shift);
+        // Exponents of the next tile, one tile ahead of its data. Its words belong to the
+        // slot of tile k+1-S, which every rank consumed before it signalled that tile's
+        // payload, and all those signals were awaited above (k+1-S <= k-1).
+        if (ahead && k + 1 < ntiles)
+          PublishTileExponents<ELEM>(ctx, warp, kLoadWarps, lane, in + tile_elems * in_esz, tile_len(k + 1),
+                                     exp_offset_of(k + 1), epoch + 1);
       } else {
         RoleCopy(role, my_stage + slot_off, in, len * in_esz, in_esz);
       }
@@ -497,14 +415,47 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
       size_t sb, se;
       ShardRange(len, ctx.nranks, ctx.rank, unit, &sb, &se);
       const int t = role.tid, n = role.nthreads;
+      // Where finished values go: this tile's place in the slot, or in the output itself.
+      char* const* dst_peer = direct_out ? job.user_peer : ctx.stage_peer;
+      char* dst_mc = direct_out ? job.user_mc : ctx.stage_mc;
+      const size_t dst_off = direct_out ? job.out_offset + pos * in_esz : slot_off;
+      const bool narrow = MODE == MODE_QUANT && ELEM == ELEM_BF16 && direct_out;  // results leave as bf16
       // An empty shard (short last tile) must not touch anything: rounding its bounds to
       // whole vectors would make it overlap the last vector of the previous rank's shard.
       if (sb >= se) {
+      } else if (narrow) {
+        // Two neighbouring lanes pair their results into one 32-bit store.
+        char* mc = ctx.stage_mc + slot_off;
+        for (size_t i0 = sb + (t & ~31); i0 < se; i0 += n) {
+          const size_t i = i0 + lane;
+          int v = 0;
+          if (i < se) {
+            if (ctx.use_multimem) {
+              v = MultimemLdReduceAddS32(mc + i * 4);
+            } else {
+              for (int p = 0; p < ctx.nranks; p++) v += __ldcg(reinterpret_cast<const int*>(ctx.stage_peer[p] + slot_off) + i);
+            }
+          }
+          float y = i < se ? quant::Dequantize(v, sf[i >> shift]) : 0.f;
+          if (job.post_scale != 1.0f) y *= job.post_scale;
+          const float hi = __shfl_down_sync(0xffffffffu, y, 1);
+          if ((lane & 1) == 0 && i < se) {
+            if (i + 1 < se) {
+              const unsigned pair = Float2ToBf16x2(y, hi);
+              if (ctx.use_multimem) MultimemStore4(dst_mc + dst_off + i * 2, pair);
+              else for (int p = 0; p < ctx.nranks; p++) *reinterpret_cast<unsigned*>(dst_peer[p] + dst_off + i * 2) = pair;
+            } else {
+              const unsigned short h = FloatToBf16(y);  // odd tail of the job's last tile
+              for (int p = 0; p < ctx.nranks; p++) *reinterpret_cast<unsigned short*>(dst_peer[p] + dst_off + i * 2) = h;
+            }
+          }
+        }
       } else if (MODE == MODE_QUANT || ELEM == ELEM_I32) {
         if (ctx.use_multimem) {
           // Integer in-switch adds are one 32-bit lane per instruction: let consecutive
           // lanes take consecutive words so that a warp moves one full 128-byte line.
           char* mc = ctx.stage_mc + slot_off;
+          char* out_mc = dst_mc + dst_off;
           size_t i = sb + t;
           for (; i + (kUnrollInt - 1) * n < se; i += kUnrollInt * n) {
             int v[kUnrollInt];
@@ -518,7 +469,7 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
                 if (job.post_scale != 1.0f) y *= job.post_scale;
                 bits = __float_as_uint(y);
               }
-              MultimemStore4(mc + (i + u * n) * 4, bits);
+              MultimemStore4(out_mc + (i + u * n) * 4, bits);
             }
           }
           for (; i < se; i += n) {
@@ -529,7 +480,7 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
               if (job.post_scale != 1.0f) y *= job.post_scale;
               bits = __float_as_uint(y);
             }
-            MultimemStore4(mc + i * 4, bits);
+            MultimemStore4(out_mc + i * 4, bits);
           }
         } else {
           size_t v0 = sb / 4, v1 = (se + 3) / 4;
@@ -544,7 +495,14 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
               if (job.post_scale != 1.0f) { y.x *= job.post_scale; y.y *= job.post_scale; y.z *= job.post_scale; y.w *= job.post_scale; }
               sum = make_uint4(__float_as_uint(y.x), __float_as_uint(y.y), __float_as_uint(y.z), __float_as_uint(y.w));
             }
-            BroadcastVec(ctx, ctx.stage_peer, ctx.stage_mc, slot_off + v * 16, sum);
+            if (direct_out && v * 4 + 4 > len) {
+              // the job's ragged end must not spill past the output tensor
+              const unsigned w[4] = {sum.x, sum.y, sum.z, sum.w};
+              for (size_t j = 0; v * 4 + j < len; j++)
+                for (int p = 0; p < ctx.nranks; p++) *reinterpret_cast<unsigned*>(dst_peer[p] + dst_off + (v * 4 + j) * 4) = w[j];
+            } else {
+              BroadcastVec(ctx, dst_peer, dst_mc, dst_off + v * 16, sum);
+            }
           };
           size_t v = v0 + t;
           for (; v + (kUnrollLink - 1) * n < v1; v += kUnrollLink * n) {
@@ -581,13 +539,15 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
       // ------------------------------ storer ------------------------------
       if (!RoleWait(ctx, role, channel, 2, epoch, sh)) return;
       lap(7);
-      char* out = static_cast<char*>(job.out) + pos * in_esz;
-      if (MODE == MODE_QUANT && ELEM == ELEM_BF16) {
-        const float* y = reinterpret_cast<const float*>(my_stage + slot_off);
-        unsigned short* o = reinterpret_cast<unsigned short*>(out);
-        for (size_t i = role.tid; i < len; i += role.nthreads) o[i] = FloatToBf16(y[i]);
-      } else {
-        RoleCopy(role, out, my_stage + slot_off, len * in_esz, in_esz);
+      if (!direct_out) {
+        char* out = static_cast<char*>(job.out) + pos * in_esz;
+        if (MODE == MODE_QUANT && ELEM == ELEM_BF16) {
+          const float* y = reinterpret_cast<const float*>(my_stage + slot_off);
+          unsigned short* o = reinterpret_cast<unsigned short*>(out);
+          for (size_t i = role.tid; i < len; i += role.nthreads) o[i] = FloatToBf16(y[i]);
+        } else {
+          RoleCopy(role, out, my_stage + slot_off, len * in_esz, in_esz);
+        }
       }
       role.Sync();
       if (role.tid == 0) {
@@ -599,6 +559,14 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
     }
   }
 }
+
+}  // namespace
+}  // namespace kernels
+}  // namespace switchml
+#include "kernels/push_allreduce.cuh"
+namespace switchml {
+namespace kernels {
+namespace {
 
 // ------------------------------------------------------------------------------------
 template <int ELEM, int MODE>
@@ -828,6 +796,8 @@ __device__ __forceinline__ void RunJob(const RankCtx& ctx, const JobArgs& job, i
     RunStaged<ELEM, MODE, 6, 8>(ctx, job, channel, epc, base, reinterpret_cast<StagedShared*>(s_failed), s_sf);
   else if (ALGO == ALGO_STAGED)
     RunStaged<ELEM, MODE>(ctx, job, channel, epc, base, reinterpret_cast<StagedShared*>(s_failed), s_sf);
+  else if (ALGO == ALGO_PUSH)
+    RunPush<ELEM, MODE>(ctx, job, channel, epc, base, reinterpret_cast<StagedShared*>(s_failed), s_sf);
   else if (ALGO == ALGO_ONESHOT) RunOneShot<ELEM, MODE>(ctx, job, channel, epc, base, s_failed);
   else if (ctx.use_multimem) RunZeroCopy<ELEM, kZeroCopyUnrollLink>(ctx, job, channel, epc, base, s_failed);
   else RunZeroCopy<ELEM, kZeroCopyUnrollPeer>(ctx, job, channel, epc, base, s_failed);
@@ -850,10 +820,10 @@ __device__ __forceinline__ void RunJob(const RankCtx& ctx, const JobArgs& job, i
   if (threadIdx.x == 0) (CTX).epoch_words[CHANNEL] = s_base + (JOB).epochs;
 
 template <int ELEM, int MODE, int ALGO>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 1)
 AllReduceKernel(const RankCtx ctx, const JobArgs job, unsigned long long epc) {
   __shared__ StagedShared s_state;
-  __shared__ float s_sf[(MODE == MODE_QUANT && ALGO == ALGO_STAGED) ? kMaxBlocksPerSlot : 1];
+  __shared__ float s_sf[(MODE == MODE_QUANT && (ALGO == ALGO_STAGED || ALGO == ALGO_PUSH)) ? kMaxBlocksPerSlot : 1];
   SML_EPOCH_PROLOGUE(ctx, blockIdx.x)
   RunJob<ELEM, MODE, ALGO>(ctx, job, blockIdx.x, epc, s_base, &s_state.failed, s_sf);
   SML_EPOCH_EPILOGUE(ctx, job, blockIdx.x)
@@ -861,10 +831,10 @@ AllReduceKernel(const RankCtx ctx, const JobArgs job, unsigned long long epc) {
 
 // All ranks in one grid: blockIdx.y selects the rank whose role this CTA plays.
 template <int ELEM, int MODE, int ALGO>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 1)
 AllReduceEmuKernel(const RankCtx* ctxs, const JobArgs* jobs, unsigned long long epc) {
   __shared__ StagedShared s_state;
-  __shared__ float s_sf[(MODE == MODE_QUANT && ALGO == ALGO_STAGED) ? kMaxBlocksPerSlot : 1];
+  __shared__ float s_sf[(MODE == MODE_QUANT && (ALGO == ALGO_STAGED || ALGO == ALGO_PUSH)) ? kMaxBlocksPerSlot : 1];
   __shared__ RankCtx s_ctx;
   __shared__ JobArgs s_job;
   if (threadIdx.x == 0) {
@@ -875,19 +845,6 @@ AllReduceEmuKernel(const RankCtx* ctxs, const JobArgs* jobs, unsigned long long 
   SML_EPOCH_PROLOGUE(s_ctx, blockIdx.x)
   RunJob<ELEM, MODE, ALGO>(s_ctx, s_job, blockIdx.x, epc, s_base, &s_state.failed, s_sf);
   SML_EPOCH_EPILOGUE(s_ctx, s_job, blockIdx.x)
-}
-
-// Float32 kernels with explicit pipeline parameters (role split, loads in flight): used to
-// pick the defaults by measurement ([backend.cuda] tune).
-template <int MODE, int ALGO, int LW, int RW, int UL>
-__global__ void __launch_bounds__(kThreads)
-TunedF32Kernel(const RankCtx ctx, const JobArgs job, unsigned long long epc) {
-  __shared__ StagedShared s_state;
-  __shared__ float s_sf[MODE == MODE_QUANT ? kMaxBlocksPerSlot : 1];
-  SML_EPOCH_PROLOGUE(ctx, blockIdx.x)
-  if (ALGO == ALGO_STAGED) RunStaged<ELEM_F32, MODE, LW, RW, UL>(ctx, job, blockIdx.x, epc, s_base, &s_state, s_sf);
-  else RunZeroCopy<ELEM_F32, UL>(ctx, job, blockIdx.x, epc, s_base, &s_state.failed);
-  SML_EPOCH_EPILOGUE(ctx, job, blockIdx.x)
 }
 
 // The sum over a single worker, out of place: one pass over the data, no staging.
@@ -993,6 +950,13 @@ cudaError_t LaunchOneEmu(const RankCtx* ctxs, const JobArgs* jobs, int nranks,
       if ((elem) == ELEM_I32) return FN<ELEM_I32, MODE_SUM, ALGO_ZEROCOPY>(__VA_ARGS__);    \
       return FN<ELEM_BF16, MODE_SUM, ALGO_ZEROCOPY>(__VA_ARGS__);                           \
     }                                                                                       \
+    if ((algo) == ALGO_PUSH) {                                                              \
+      if ((elem) == ELEM_I32) return FN<ELEM_I32, MODE_SUM, ALGO_PUSH>(__VA_ARGS__);        \
+      if ((elem) == ELEM_F32 && (mode) == MODE_QUANT) return FN<ELEM_F32, MODE_QUANT, ALGO_PUSH>(__VA_ARGS__); \
+      if ((elem) == ELEM_F32) return FN<ELEM_F32, MODE_SUM, ALGO_PUSH>(__VA_ARGS__);        \
+      if ((mode) == MODE_QUANT) return FN<ELEM_BF16, MODE_QUANT, ALGO_PUSH>(__VA_ARGS__);   \
+      return FN<ELEM_BF16, MODE_SUM, ALGO_PUSH>(__VA_ARGS__);                               \
+    }                                                                                       \
     if ((elem) == ELEM_I32) {                                                               \
       if ((algo) == ALGO_STAGED) return FN<ELEM_I32, MODE_SUM, ALGO_STAGED>(__VA_ARGS__);   \
       return FN<ELEM_I32, MODE_SUM, ALGO_ONESHOT>(__VA_ARGS__);                             \
@@ -1020,6 +984,21 @@ size_t SlotElems(const RankCtx& ctx, int elem_type, int mode) {
   return ctx.slot_bytes / st_esz;
 }
 
+size_t PushTileCapacity(const RankCtx& ctx, int elem_type, int mode) {
+  const size_t n = ctx.nranks;
+  if (n < 2) return 0;
+  const size_t in_esz = elem_type == ELEM_BF16 ? 2 : 4;
+  const size_t leg = mode == MODE_QUANT ? 4 : in_esz;  // bytes per element on either leg
+  // (n-1) receive areas + (n-1) result areas of tile/n elements each
+  size_t cap = ctx.slot_bytes * n / (2 * (n - 1) * leg);
+  if (mode == MODE_QUANT) {
+    const size_t by_words = ctx.slot_bytes / 4;  // one exponent word per block of the slot
+    if (cap > by_words) cap = by_words;
+  }
+  const size_t unit = n * (ctx.block_numel > 128 ? ctx.block_numel : 128);
+  return cap / unit * unit;
+}
+
 size_t StagingBytes(size_t slot_bytes, int slots_per_channel, int block_numel, int max_channels,
                     size_t oneshot_bytes, int nranks, size_t* data_offset, size_t* exp_offset,
                     size_t* oneshot_offset) {
@@ -1028,7 +1007,7 @@ size_t StagingBytes(size_t slot_bytes, int slots_per_channel, int block_numel, i
   size_t off = align(flags);
   *exp_offset = off;
   size_t blocks_per_slot = slot_bytes / 4 / block_numel;
-  off = align(off + size_t(max_channels) * slots_per_channel * blocks_per_slot * 4);
+  off = align(off + size_t(max_channels) * slots_per_channel * blocks_per_slot * kExpWordBytes);
   *oneshot_offset = off;
   off = align(off + 3 * size_t(nranks) * oneshot_bytes);  // two alternating sets + one for captured launches
   *data_offset = off;
@@ -1058,8 +1037,9 @@ LaunchPlan PlanLaunch(const RankCtx& ctx, const JobArgs& job, int requested_chan
   const unsigned long long numel = job.numel ? job.numel : 1;
   if (max_channels > kMaxChannels) max_channels = kMaxChannels;
   p.tile_elems = 0;
-  if (job.algo == ALGO_STAGED) {
-    size_t slot_elems = SlotElems(ctx, job.elem_type, job.mode);
+  if (job.algo == ALGO_STAGED || job.algo == ALGO_PUSH) {
+    size_t slot_elems = job.algo == ALGO_PUSH ? PushTileCapacity(ctx, job.elem_type, job.mode)
+                                              : SlotElems(ctx, job.elem_type, job.mode);
     int ch = requested_channels > 0 ? requested_channels : max_channels;
     if (ch > max_channels) ch = max_channels;
     // Tile: a slot for big jobs; for smaller ones shrink it so that the job still spreads
@@ -1114,39 +1094,6 @@ cudaError_t LaunchAllReduce(const RankCtx& ctx, const JobArgs& job, const Launch
                             cudaStream_t stream) {
   if (ctx.nranks < 1 || ctx.nranks > kMaxRanks || plan.channels > kMaxChannels)
     return cudaErrorInvalidValue;
-  if (job.tune > 0 && job.elem_type == ELEM_F32 && job.algo != ALGO_ONESHOT) {
-    const unsigned long long epc = plan.elems_per_channel;
-#define SML_TUNED(MODE, ALGO, LW, RW, UL) TunedF32Kernel<MODE, ALGO, LW, RW, UL><<<plan.channels, kThreads, 0, stream>>>(ctx, job, epc)
-    if (job.algo == ALGO_STAGED && job.mode == MODE_QUANT) {
-      switch (job.tune) {
-        case 1: SML_TUNED(MODE_QUANT, ALGO_STAGED, 4, 8, 4); break;
-        case 2: SML_TUNED(MODE_QUANT, ALGO_STAGED, 8, 6, 4); break;
-        case 3: SML_TUNED(MODE_QUANT, ALGO_STAGED, 6, 6, 4); break;
-        case 4: SML_TUNED(MODE_QUANT, ALGO_STAGED, 6, 8, 8); break;
-        case 5: SML_TUNED(MODE_QUANT, ALGO_STAGED, 4, 8, 8); break;
-        case 6: SML_TUNED(MODE_QUANT, ALGO_STAGED, 7, 7, 4); break;
-        default: SML_TUNED(MODE_QUANT, ALGO_STAGED, 6, 8, 4); break;
-      }
-    } else if (job.algo == ALGO_STAGED) {
-      switch (job.tune) {
-        case 1: SML_TUNED(MODE_SUM, ALGO_STAGED, 6, 6, 4); break;
-        case 2: SML_TUNED(MODE_SUM, ALGO_STAGED, 6, 6, 8); break;
-        case 3: SML_TUNED(MODE_SUM, ALGO_STAGED, 4, 8, 8); break;
-        case 4: SML_TUNED(MODE_SUM, ALGO_STAGED, 3, 10, 4); break;
-        case 5: SML_TUNED(MODE_SUM, ALGO_STAGED, 4, 8, 2); break;
-        default: SML_TUNED(MODE_SUM, ALGO_STAGED, 4, 8, 4); break;
-      }
-    } else {
-      switch (job.tune) {
-        case 1: SML_TUNED(MODE_SUM, ALGO_ZEROCOPY, 6, 6, 8); break;
-        case 2: SML_TUNED(MODE_SUM, ALGO_ZEROCOPY, 6, 6, 4); break;
-        case 3: SML_TUNED(MODE_SUM, ALGO_ZEROCOPY, 6, 6, 16); break;
-        default: SML_TUNED(MODE_SUM, ALGO_ZEROCOPY, 6, 6, 2); break;
-      }
-    }
-#undef SML_TUNED
-    return cudaGetLastError();
-  }
   SML_DISPATCH(LaunchOne, job.elem_type, job.mode, job.algo, ctx, job, plan, stream);
 }
 
@@ -1215,6 +1162,36 @@ void* g_noalloc_ptr[64] = {nullptr};  // per device: device address of g_noalloc
 
 }  // namespace
 
+// Device address of the scratch array on `dev` (the current device). Once per device, with
+// that device current: ask the runtime where the array lives. Caller holds g_noalloc_mu.
+static char* NoAllocScratch(int dev) {
+  if (!g_noalloc_ptr[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || !p) return nullptr;
+    g_noalloc_ptr[dev] = p;
+  }
+  return static_cast<char*>(g_noalloc_ptr[dev]);
+}
+
+extern "C" int switchml_noalloc_last_status(void* stream_ptr, int* status) {
+  if (!status) return SWITCHML_NOALLOC_BAD_ARGUMENT;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return SWITCHML_NOALLOC_CUDA_ERROR;
+  char* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(g_noalloc_mu);
+    scratch = NoAllocScratch(dev);
+  }
+  if (!scratch) return SWITCHML_NOALLOC_CUDA_ERROR;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_ptr);
+  int word = 0;
+  if (cudaMemcpyAsync(&word, scratch + kNoAllocAuxOffset + 256, sizeof(int), cudaMemcpyDeviceToHost, stream) != cudaSuccess ||
+      cudaStreamSynchronize(stream) != cudaSuccess)
+    return SWITCHML_NOALLOC_CUDA_ERROR;
+  *status = word;
+  return SWITCHML_NOALLOC_OK;
+}
+
 extern "C" const char* switchml_noalloc_strerror(int code) {
   switch (code) {
     case SWITCHML_NOALLOC_OK: return "ok";
@@ -1244,18 +1221,11 @@ extern "C" int switchml_local_allreduce_noalloc(const void* in, void* out,
 
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return SWITCHML_NOALLOC_CUDA_ERROR;
-  char* scratch = nullptr;
-  {
-    // Once per device, with that device current: ask the runtime where the array lives.
-    std::lock_guard<std::mutex> lk(g_noalloc_mu);
-    if (!g_noalloc_ptr[dev]) {
-      void* p = nullptr;
-      if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || !p)
-        return SWITCHML_NOALLOC_CUDA_ERROR;
-      g_noalloc_ptr[dev] = p;
-    }
-    scratch = static_cast<char*>(g_noalloc_ptr[dev]);
-  }
+  // Held until the call's three enqueues (two clears and the kernel) are on the stream, so
+  // that host threads calling at the same time cannot interleave them.
+  std::lock_guard<std::mutex> lk(g_noalloc_mu);
+  char* scratch = NoAllocScratch(dev);
+  if (!scratch) return SWITCHML_NOALLOC_CUDA_ERROR;
 
   RankCtx ctx;
   memset(&ctx, 0, sizeof(ctx));
@@ -1291,9 +1261,10 @@ extern "C" int switchml_local_allreduce_noalloc(const void* in, void* out,
   job.tile_elems = plan.tile_elems;
   job.epochs = plan.epochs;
 
-  // The array keeps the previous call's flags (epochs) and counters; this call counts its
-  // epochs from zero again, so both have to be cleared first, in stream order.
-  if (cudaMemsetAsync(scratch, 0, kFlagBytes, stream) != cudaSuccess) return SWITCHML_NOALLOC_CUDA_ERROR;
+  // The array keeps the previous call's flags (epochs), exponent words (tagged with epochs)
+  // and counters; this call counts its epochs from zero again, so all three have to be
+  // cleared first, in stream order. Flags and exponent words are neighbours.
+  if (cudaMemsetAsync(scratch, 0, ctx.oneshot_offset, stream) != cudaSuccess) return SWITCHML_NOALLOC_CUDA_ERROR;
   if (cudaMemsetAsync(scratch + kNoAllocAuxOffset, 0, 512, stream) != cudaSuccess)
     return SWITCHML_NOALLOC_CUDA_ERROR;
   if (LaunchAllReduce(ctx, job, plan, stream) != cudaSuccess) return SWITCHML_NOALLOC_CUDA_ERROR;

@@ -33,12 +33,15 @@ enum Algo : int {
   ALGO_STAGED = 0,    // copy-in, shard reduce, copy-out through the slot ring (any pointers)
   ALGO_ONESHOT = 1,   // push inputs to every rank, one barrier, reduce locally (small messages)
   ALGO_ZEROCOPY = 2,  // tensors live in symmetric memory: reduce in place, no staging (SUM only)
+  ALGO_PUSH = 3,      // peer-memory transport: shards pushed to their owners and results pushed back,
+                      // posted stores only (push_allreduce.cuh); needs at least two ranks
 };
 enum Status : int {
   STATUS_OK = 0,
   STATUS_TIMEOUT = 1,  // a bounded wait ran out; bits 8.. hold the channel, 4..7 the phase
   STATUS_BAD_ARGS = 2,
   STATUS_BOUNDS = 3,   // checked build only: a tile or buffer would reach outside its region (bits 8.. = channel)
+  STATUS_PROTOCOL = 4, // an exponent word carried the tag of another tile: the ranks are not running the same job
 };
 
 // What a rank's kernel needs to reach its peers. Passed by value.
@@ -75,9 +78,10 @@ struct JobArgs {
   unsigned epochs;      // how far the job advances the epoch counter of each channel it uses
   int trailing_barrier; // ALGO_ONESHOT: meet once more after reading, so the buffer needs no parity (graph replays)
   int oneshot_parity;
-  int tune;          // > 0: float32 SUM variant with other pipeline parameters (see LaunchAllReduce)
+  int out_zero_copy; // ALGO_STAGED / ALGO_PUSH: `out` lies in the symmetric user region (user_* and out_offset are
+                     // set): finished shards are broadcast straight into every rank's output, no copy-out
   unsigned long long tile_elems;  // ALGO_STAGED: elements per tile (<= elements of a slot)
-  // ALGO_ZEROCOPY: offsets of in/out inside the symmetric user region and its mappings
+  // ALGO_ZEROCOPY (and out_zero_copy): offsets of in/out inside the symmetric user region and its mappings
   char* user_peer[kMaxRanks];
   char* user_mc;
   size_t in_offset, out_offset;
@@ -95,6 +99,9 @@ struct LaunchPlan {
 
 // Number of elements of a slot for this element type / mode.
 size_t SlotElems(const RankCtx& ctx, int elem_type, int mode);
+// Largest tile of ALGO_PUSH that fits a slot (a multiple of nranks * max(block, 128)
+// elements), or 0 when the slots are too small for that algorithm (use ALGO_STAGED then).
+size_t PushTileCapacity(const RankCtx& ctx, int elem_type, int mode);
 // Bytes a staging region must have for `channels` channels.
 size_t StagingBytes(size_t slot_bytes, int slots_per_channel, int block_numel, int max_channels,
                     size_t oneshot_bytes, int nranks, size_t* data_offset, size_t* exp_offset,

@@ -33,7 +33,12 @@
  *    call left there. The entry point itself clears, on `stream`, the flags and counters
  *    that have to start at zero. Two calls whose work overlaps on the GPU (different
  *    streams without ordering between them) race on the scratch and give wrong results:
- *    order them on one stream or with events.
+ *    order them on one stream or with events. Host threads may call at the same time: each
+ *    call's clears and its kernel reach the stream as one unit.
+ *  - The kernel's own verdict (0 = fine, otherwise a Status code of allreduce_kernels.h in the
+ *    low four bits, e.g. 1 when one of its bounded waits gave up) stays in the scratch; the
+ *    return code of the call only covers the launch. switchml_noalloc_last_status waits for
+ *    `stream` and reads it back. It describes the call that ran last on this device.
  *  - The work is enqueued on `stream` (a cudaStream_t, NULL = default stream); the result
  *    is in `out` when the stream gets there. `in` and `out` may be the same buffer.
  */
@@ -55,7 +60,11 @@ extern "C" {
 int switchml_local_allreduce_noalloc(const void* in, void* out, unsigned long long numel,
                                      int elem_type, int mode, int block_numel, void* stream);
 
-/* Static text for a return code of the function above. */
+/* Wait for `stream`, then store the status word that the last call on the current device left
+ * in the scratch (0 = the kernel completed normally). Allocates nothing either. */
+int switchml_noalloc_last_status(void* stream, int* status);
+
+/* Static text for a return code of the functions above. */
 const char* switchml_noalloc_strerror(int code);
 
 #ifdef __cplusplus

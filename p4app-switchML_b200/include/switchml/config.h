@@ -69,7 +69,7 @@ struct CudaBackendConfig {
   std::string rendezvous_dir = "";        // directory for unix sockets (default: abstract namespace)
   double wait_timeout_ms = 10000.0;       // budget of every device-side wait for a peer
   bool numa_bind = false;                 // keep the launcher and completion threads on the GPU's NUMA node
-  uint32_t tune = 0;                      // experimental pipeline variant of the float32 SUM kernels (0 = default)
+  std::string p2p_algo = "push";          // peer-memory transport, large messages: push (posted stores only) | staged
 };
 
 class Config {

@@ -12,7 +12,7 @@ from .._native import lib, last_error, NativeError
 
 ELEM = {"float32": 0, "int32": 1, "bfloat16": 2}
 MODE = {"sum": 0, "quant": 1}
-ALGO = {"staged": 0, "oneshot": 1}
+ALGO = {"staged": 0, "oneshot": 1, "push": 3}
 
 
 def emulated_allreduce(inputs, mode="quant", algo="staged", block_numel=256, slot_bytes=131072,
@@ -29,6 +29,8 @@ def emulated_allreduce(inputs, mode="quant", algo="staged", block_numel=256, slo
         outputs = [torch.empty_like(x) for x in inputs]
     esz_unit = n * max(block_numel, 128) * 4
     slot_bytes = max(esz_unit, slot_bytes // esz_unit * esz_unit)
+    if algo == "push":  # a slot holds n-1 receive areas and n-1 result areas of one shard each
+        slot_bytes = max(slot_bytes, 2 * esz_unit)
     ins = (ctypes.c_void_p * n)(*[x.data_ptr() for x in inputs])
     outs = (ctypes.c_void_p * n)(*[o.data_ptr() for o in outputs])
     torch.cuda.synchronize()

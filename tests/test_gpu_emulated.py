@@ -27,12 +27,14 @@ def _inputs(n, numel, dtype=torch.float32, seed=0):
     return xs
 
 
-@pytest.mark.parametrize("algo", ["staged", "oneshot"])
+@pytest.mark.parametrize("algo", ["staged", "oneshot", "push"])
 @pytest.mark.parametrize("n", [1, 2, 4, 8])
 @pytest.mark.parametrize("numel", SIZES)
 def test_quant_bit_exact(n, numel, algo):
     if algo == "oneshot" and numel > (1 << 16):
         pytest.skip("one-shot is for small messages")
+    if algo == "push" and n == 1:
+        pytest.skip("pushing needs a peer")
     xs = _inputs(n, numel)
     outs = emulated_allreduce([x.cuda() for x in xs], mode="quant", algo=algo, block_numel=64,
                               slot_bytes=32768)
@@ -45,18 +47,19 @@ def test_quant_bit_exact(n, numel, algo):
     assert np.max(np.abs(want - exact)) <= n * n * 2.0 ** -30 * scale + 2.0 ** -23 * n * scale
 
 
+@pytest.mark.parametrize("algo", ["staged", "push"])
 @pytest.mark.parametrize("block", [32, 256, 1024])
-def test_quant_block_sizes_and_reuse(block):
+def test_quant_block_sizes_and_reuse(block, algo):
     # Several jobs back to back over the same staging (epochs and slot reuse).
     xs = _inputs(4, 300001, seed=3)
-    outs = emulated_allreduce([x.cuda() for x in xs], mode="quant", block_numel=block,
+    outs = emulated_allreduce([x.cuda() for x in xs], mode="quant", algo=algo, block_numel=block,
                               slot_bytes=16 * 4 * block, repeats=3, channels=3)
     want = quant_allreduce_oracle([x.numpy() for x in xs], block)
     for o in outs:
         assert np.array_equal(o.cpu().numpy(), want)
 
 
-@pytest.mark.parametrize("algo", ["staged", "oneshot"])
+@pytest.mark.parametrize("algo", ["staged", "oneshot", "push"])
 @pytest.mark.parametrize("n", [2, 8])
 def test_int32_wrapping_sum(n, algo):
     numel = 50001 if algo == "oneshot" else 777777
@@ -67,7 +70,7 @@ def test_int32_wrapping_sum(n, algo):
         assert np.array_equal(o.cpu().numpy(), want)
 
 
-@pytest.mark.parametrize("algo", ["staged", "oneshot"])
+@pytest.mark.parametrize("algo", ["staged", "oneshot", "push"])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_float_sum(dtype, algo):
     n, numel = 4, 65537 if algo == "oneshot" else 999999
@@ -81,10 +84,11 @@ def test_float_sum(dtype, algo):
         assert torch.equal(o, outs[0]), "all ranks must hold identical bits"
 
 
-def test_quant_bf16_matches_oracle_after_rounding():
+@pytest.mark.parametrize("algo", ["staged", "push"])
+def test_quant_bf16_matches_oracle_after_rounding(algo):
     n, numel = 4, 100000
     xs = _inputs(n, numel, torch.bfloat16)
-    outs = emulated_allreduce([x.cuda() for x in xs], mode="quant", block_numel=256)
+    outs = emulated_allreduce([x.cuda() for x in xs], mode="quant", algo=algo, block_numel=256)
     want = quant_allreduce_oracle([x.float().numpy() for x in xs], 256)
     want_bf16 = torch.from_numpy(want).to(torch.bfloat16)
     for o in outs:
@@ -101,11 +105,12 @@ def test_special_blocks():
     a[320:384] = 2.0 ** -100
     b = a.clone()
     b[384:448] = 7.0         # only one rank is non-zero here
-    outs = emulated_allreduce([a.cuda(), b.cuda()], mode="quant", block_numel=64, slot_bytes=8192)
     want = quant_allreduce_oracle([a.numpy(), b.numpy()], 64)
-    got = outs[0].cpu().numpy()
-    assert np.all(np.isfinite(got)) and np.array_equal(got, want)
-    assert np.all(got[:64] == 0) and got[256] == -3.0 and np.all(got[384:448] == 7.0)
+    for algo in ("staged", "push"):
+        outs = emulated_allreduce([a.cuda(), b.cuda()], mode="quant", algo=algo, block_numel=64, slot_bytes=8192)
+        got = outs[0].cpu().numpy()
+        assert np.all(np.isfinite(got)) and np.array_equal(got, want), algo
+        assert np.all(got[:64] == 0) and got[256] == -3.0 and np.all(got[384:448] == 7.0), algo
 
 
 def test_unaligned_views_and_out_of_place():
@@ -113,10 +118,17 @@ def test_unaligned_views_and_out_of_place():
     bases = [torch.randn(numel + 3).cuda() for _ in range(n)]
     xs = [b[1:1 + numel] for b in bases]            # 4-byte aligned only
     keep = [x.clone() for x in xs]
-    outs = emulated_allreduce(xs, mode="sum")
-    for x, k in zip(xs, keep):
-        assert torch.equal(x, k), "inputs must stay untouched"
-    assert torch.allclose(outs[0], keep[0] + keep[1])
+    for algo in ("staged", "push"):
+        outs = emulated_allreduce(xs, mode="sum", algo=algo)
+        for x, k in zip(xs, keep):
+            assert torch.equal(x, k), "inputs must stay untouched"
+        assert torch.allclose(outs[0], keep[0] + keep[1]) and torch.equal(outs[0], outs[1]), algo
+    # in place, unaligned, quantised: the owner reads and overwrites its own shard
+    want = quant_allreduce_oracle([k.cpu().numpy() for k in keep], 64)
+    for algo in ("staged", "push"):
+        ys = [b[1:1 + numel] for b in [k2.clone() for k2 in bases]]
+        outs = emulated_allreduce(ys, mode="quant", algo=algo, block_numel=64, slot_bytes=8192, outputs=ys)
+        assert np.array_equal(outs[0].cpu().numpy(), want) and np.array_equal(outs[1].cpu().numpy(), want), algo
 
 
 def _random_quant_cases(worker_counts, cases, seed):
@@ -124,9 +136,10 @@ def _random_quant_cases(worker_counts, cases, seed):
     for case in range(cases):
         n = int(rng.choice(worker_counts))
         block = int(rng.choice([32, 64, 256, 1024]))
-        algo = "oneshot" if case % 4 == 3 else "staged"
+        algo = ("staged", "push", "staged", "oneshot", "push")[case % 5]
         numel = int(rng.integers(1, 40000 if algo == "oneshot" else 400000))
         slot_bytes = int(rng.choice([8, 16, 64])) * 4 * block
+        slots = int(rng.choice([1, 2, 2, 3]))
         channels = int(rng.choice([0, 1, 3, 7]))
         xs = []
         for r in range(n):
@@ -135,12 +148,13 @@ def _random_quant_cases(worker_counts, cases, seed):
                 x[z:z + block] = 0.0
             xs.append(x)
         outs = emulated_allreduce([torch.from_numpy(x).cuda() for x in xs], mode="quant", algo=algo,
-                                  block_numel=block, slot_bytes=slot_bytes, channels=channels)
+                                  block_numel=block, slot_bytes=slot_bytes, slots_per_channel=slots,
+                                  channels=channels)
         want = quant_allreduce_oracle(xs, block)
         for r, o in enumerate(outs):
             assert np.array_equal(o.cpu().numpy().view(np.uint32), want.view(np.uint32)), \
-                "case %d: n=%d numel=%d block=%d algo=%s slot=%d channels=%d rank %d" % (
-                    case, n, numel, block, algo, slot_bytes, channels, r)
+                "case %d: n=%d numel=%d block=%d algo=%s slot=%d x%d channels=%d rank %d" % (
+                    case, n, numel, block, algo, slot_bytes, slots, channels, r)
 
 
 def test_quant_random_shapes_against_oracle():

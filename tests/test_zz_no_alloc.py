@@ -7,7 +7,9 @@ allocator locks. For them ``switchml_local_allreduce_noalloc`` runs the single-w
 aggregation round trip with its staging in a static device array instead of cudaMalloc'ed
 memory. This test calls it through its exported C symbol, twice in a row (the second call
 finds the first call's leftovers in the shared scratch), and checks each result against
-the ordinary entry point (``sml_emu_allreduce`` with one rank), which allocates its staging.
+the ordinary entry point (``sml_emu_allreduce`` with one rank), which allocates its staging,
+and against the CPU oracle, which shares no device code with either. After every call the
+kernel's status word is read back through ``switchml_noalloc_last_status`` and must be 0.
 The file sorts last on purpose: a run that stops at the first failure has then already
 run every other test.
 """
@@ -18,6 +20,7 @@ import torch
 
 from switchml_b200._native import lib
 from switchml_b200.ops.emulation import emulated_allreduce
+from switchml_b200.ops.oracle import quant_allreduce_oracle
 
 pytestmark = pytest.mark.gpu
 
@@ -31,6 +34,17 @@ def _entry():
     err.restype = ctypes.c_char_p
     err.argtypes = [ctypes.c_int]
     return fn, err
+
+
+def _status():
+    """The status word the kernel of the last call left behind (0 = completed normally)."""
+    fn = lib().switchml_noalloc_last_status
+    fn.restype = ctypes.c_int
+    fn.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int)]
+    word = ctypes.c_int(-1)
+    rc = fn(ctypes.c_void_p(torch.cuda.current_stream().cuda_stream), ctypes.byref(word))
+    assert rc == 0, rc
+    return word.value
 
 
 def _call(fn, x, out, mode, block):
@@ -58,13 +72,21 @@ def test_two_calls_in_a_row_match_the_allocating_entry_point():
         rc1 = _call(fn, x, first, mode, block)
         rc2 = _call(fn, x, second, mode, block)
         assert rc1 == 0 and rc2 == 0, (err(rc1), err(rc2))
+        assert _status() == 0, "the kernel reported a status"
         torch.cuda.synchronize()
         assert torch.equal(first, want), "first call differs from the allocating entry point"
         assert torch.equal(second, want), "second call differs from the allocating entry point"
+        if mode == 1:  # the CPU oracle: one worker's quantise / dequantise round trip
+            cpu = quant_allreduce_oracle([x.float().cpu().numpy()], block)
+            cpu = torch.from_numpy(cpu).to(x.dtype)
+            assert torch.equal(second.cpu(), cpu), "differs from the CPU oracle"
+        else:
+            assert torch.equal(second, x)
     # in place
     x = torch.randn(40_000, device="cuda")
     want = emulated_allreduce([x.clone()], mode="quant", block_numel=256, slot_bytes=32768)[0]
     assert _call(fn, x, x, 1, 256) == 0
+    assert _status() == 0
     torch.cuda.synchronize()
     assert torch.equal(x, want)
 
