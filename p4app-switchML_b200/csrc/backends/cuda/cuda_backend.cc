@@ -413,6 +413,7 @@ void CudaBackend::LaunchJob(const std::shared_ptr<Job>& job, cudaStream_t stream
   a.post_scale = c.average && !integer && !broadcast ? 1.0f / static_cast<float>(n_) : 1.0f;
   size_t esz = DataTypeSize(t.data_type);
   size_t bytes = t.numel * esz;
+  a.bulk_copy = t.numel > 0 && kernels::DeviceMemory(t.in_ptr) && kernels::DeviceMemory(t.out_ptr);
 
   // Pick the algorithm (identically on every rank: it depends on sizes and on whether the
   // pointers sit in the symmetric heap, which is allocated in lock step).
@@ -674,7 +675,9 @@ std::string CudaBackend::ExtraStatsJson() {
     << ",\"tiles\":" << c[0] << ",\"wait_spins\":" << c[1] << ",\"device_timeouts\":" << c[2]
     << ",\"jobs_launched\":" << launched_jobs_ << ",\"kernel_launches\":" << kernel_launches_
     << ",\"epoch\":" << epoch_base_
-    << ",\"channel0_ns\":{\"loader_wait\":" << c[3] << ",\"loader_work\":" << c[4]
+    << ",\"channel0_ns\":{\"loader_wait\":" << c[3] << ",\"loader_work\":" << c[4] + c[9] + c[10] + c[11]
+    << ",\"loader_scale_factors\":" << c[9] << ",\"loader_payload\":" << c[10] << ",\"loader_exponents_ahead\":" << c[11]
+    << ",\"loader_signal\":" << c[4]
     << ",\"reducer_wait\":" << c[5] << ",\"reducer_work\":" << c[6] << ",\"storer_wait\":" << c[7]
     << ",\"storer_work\":" << c[8] << "}}";
   return o.str();
@@ -809,6 +812,7 @@ int EmulatedAllReduce(int nranks, void* const* in_ptrs, void* const* out_ptrs,
       j.mode = mode;
       j.algo = algo;
       j.post_scale = post_scale;
+      j.bulk_copy = DeviceMemory(j.in) && DeviceMemory(j.out);
       j.oneshot_parity = it & 1;
     }
     plan = PlanLaunch(ctxs[0], jobs[0], channels, max_channels);

@@ -42,8 +42,8 @@ class SlotTransport {
   // slot's SlotPacket (found through `slots`) and append the slot index to `ready`.
   // May block briefly. Returns false when the transport was shut down.
   virtual bool Poll(std::vector<SlotPacket>& slots, std::vector<int>* ready) = 0;
-  // Called when nothing arrived; gives the transport a chance to retransmit. Returns the
-  // number of timeouts that fired.
+  // Called on every turn of the loop; gives the transport a chance to retransmit what has
+  // waited too long. Returns the number of timeouts that fired.
   virtual uint64_t OnIdle(std::vector<SlotPacket>& slots) { (void)slots; return 0; }
   // A slot received its answer (stop its timer).
   virtual void OnAnswered(int slot) { (void)slot; }
@@ -93,13 +93,17 @@ SlotWindowResult RunSlotWindow(const JobSlice& js, PrePostProcessor& ppp, SlotTr
     if (!keep_running()) { res.ok = false; break; }
     ready.clear();
     if (!tr.Poll(slots, &ready)) { res.ok = false; break; }
-    if (ready.empty()) {
+    // Timers are looked at on every turn, not only when nothing arrived: while results for
+    // other slots keep coming, a slot whose packet or result was lost must not wait for the
+    // traffic to go quiet (the reference checks its timers in every loop iteration,
+    // rdma_worker_thread.cc:283-292).
+    {
       uint64_t t = tr.OnIdle(slots);
       if (t) tr.Flush();
       res.timeouts += t;
       res.sent += t;
-      continue;
     }
+    if (ready.empty()) continue;
     for (int s : ready) {
       if (s < 0) { res.wrong++; continue; }  // duplicate or stale packet, already discarded
       SlotPacket& p = slots[s];

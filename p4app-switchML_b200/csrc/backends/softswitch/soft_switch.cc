@@ -103,7 +103,8 @@ void SoftSwitch::Process(const uint8_t* data, size_t len, std::vector<SwitchOutp
     ProcessOther(h, data, len, out);
     return;
   }
-  if (ntohl(h.magic) != kWireMagic || h.type != WIRE_DATA || numel > kMaxPacketNumel ||
+  const bool last_packet = h.type == WIRE_DATA;  // carries the message's exponent
+  if (ntohl(h.magic) != kWireMagic || (h.type != WIRE_DATA && h.type != WIRE_DATA_MORE) || numel > kMaxPacketNumel ||
       len != sizeof(h) + numel * 4u || worker >= num_workers_ || worker >= kMaxWorkers ||
       h.thread_id >= kMaxThreads ||  // the return port is looked up by (worker, thread): refuse what the table cannot hold
       !(registered_ & (1u << worker)) || ntohs(h.session_lo) != static_cast<uint16_t>(session_id_) ||
@@ -120,6 +121,7 @@ void SoftSwitch::Process(const uint8_t* data, size_t len, std::vector<SwitchOutp
   }
   EndpointCounters* ep = &endpoint_counters_[worker][h.thread_id];
   ep->rx_packets++;
+  if (last_packet) ep->rx_messages++;
 
   int k = (pool_index & kSetBit) ? 1 : 0;
   uint32_t slot = pool_index & ~kSetBit;
@@ -154,7 +156,7 @@ void SoftSwitch::Process(const uint8_t* data, size_t len, std::vector<SwitchOutp
     // First packet of a new use of this slot set: overwrite.
     cur.values.assign(numel, 0);
     simd::AddWire(payload, numel, cur.values.data());
-    cur.exponent = h.exponent;
+    cur.exponent = last_packet ? h.exponent : static_cast<int8_t>(-128);
     cur.numel = numel;
     cur.pkt_id = ntohl(h.pkt_id);
     cur.job_tag = h.job_tag;
@@ -163,7 +165,7 @@ void SoftSwitch::Process(const uint8_t* data, size_t len, std::vector<SwitchOutp
   } else {
     uint16_t n = numel < cur.numel ? numel : cur.numel;
     simd::AddWire(payload, n, cur.values.data());  // wrapping add, as the switch register ALUs do
-    if (h.exponent > cur.exponent) cur.exponent = h.exponent;
+    if (last_packet && h.exponent > cur.exponent) cur.exponent = h.exponent;
     cur.remaining--;
   }
 
@@ -304,12 +306,12 @@ std::string SoftSwitch::DescribeDropped() const {
 std::string SoftSwitch::DescribeEndpoints() const {
   std::shared_lock<std::shared_mutex> lk(state_mu_);
   std::ostringstream o;
-  o << " rank  thread  rx_pkts  out_of_order  results  retransmitted_results\n";
+  o << " rank  thread  rx_pkts  rx_msgs  out_of_order  results  retransmitted_results\n";
   for (int w = 0; w < num_workers_; w++) {
     for (int t = 0; t < kMaxThreads; t++) {
       const EndpointCounters& e = endpoint_counters_[w][t];
       if (e.rx_packets == 0 && e.results == 0 && e.retransmitted_results == 0) continue;
-      o << " " << w << "  " << t << "  " << e.rx_packets << "  " << e.out_of_order << "  " << e.results << "  "
+      o << " " << w << "  " << t << "  " << e.rx_packets << "  " << e.rx_messages << "  " << e.out_of_order << "  " << e.results << "  "
         << e.retransmitted_results << "\n";
     }
   }

@@ -72,7 +72,7 @@ struct WorkerCounters {
 // endpoint plays the role of a queue pair; a packet for a slot use that was already absorbed
 // or finished is what a sequence violation is there: a packet outside the expected order.
 struct EndpointCounters {
-  Counter rx_packets, out_of_order, results, retransmitted_results;
+  Counter rx_packets, rx_messages, out_of_order, results, retransmitted_results;  // a message ends with its exponent-carrying packet
 };
 
 class SoftSwitch {

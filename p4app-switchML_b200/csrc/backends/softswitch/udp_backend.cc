@@ -25,9 +25,13 @@ namespace {
 
 class UdpTransport : public SlotTransport {
  public:
-  UdpTransport(const Config& cfg, WorkerTid tid, int fd, uint64_t session_id, int window)
-      : cfg_(cfg), tid_(tid), fd_(fd), session_id_(session_id), window_(window),
-        set_bits_(window, 0), answered_(window, 0) {
+  // `window` slots of one message each; a message is `pkts_per_msg` datagrams of packet_numel
+  // elements on consecutive pool indices (reference rdma_worker_thread.cc:116-124).
+  UdpTransport(const Config& cfg, WorkerTid tid, int fd, uint64_t session_id, int window, int pkts_per_msg)
+      : cfg_(cfg), tid_(tid), fd_(fd), session_id_(session_id), window_(window), pkts_per_msg_(pkts_per_msg),
+        packet_numel_(static_cast<int>(cfg.general_.packet_numel)),
+        all_packets_(pkts_per_msg == 64 ? ~0ull : (1ull << pkts_per_msg) - 1),
+        set_bits_(window, 0), answered_(window, 0), missing_(window, 0) {
     tx_headers_.resize(kBurst);
     tx_iov_.resize(2 * kBurst);
     tx_msgs_.resize(kBurst);
@@ -61,32 +65,38 @@ class UdpTransport : public SlotTransport {
     if (!retransmission) {
       set_bits_[phys] ^= 1;  // every new use takes the other set
       answered_[p.slot] = 0;
+      missing_[p.slot] = all_packets_;
     }
-    uint16_t pool_index = static_cast<uint16_t>(tid_ * window_ + phys) |
-                          (set_bits_[phys] ? kSetBit : 0);
     // Header and payload leave as two pieces of one datagram (no copy); the burst goes out
-    // with one system call in Flush().
-    if (tx_count_ == kBurst) Flush();
-    WireHeader& h = tx_headers_[tx_count_];
-    h.magic = htonl(kWireMagic);
-    h.type = WIRE_DATA;
-    h.job_tag = job_tag_;
-    h.worker_id = htons(cfg_.general_.rank);
-    h.pkt_id = htonl(p.pkt_id);
-    h.pool_index = htons(pool_index);
-    h.numel = htons(p.numel);
-    h.exponent = p.exponent;
-    h.thread_id = static_cast<uint8_t>(tid_);
-    h.session_lo = htons(static_cast<uint16_t>(session_id_));
-    iovec* v = &tx_iov_[2 * tx_count_];
-    v[0].iov_base = &h;
-    v[0].iov_len = sizeof(h);
-    v[1].iov_base = p.payload;
-    v[1].iov_len = p.numel * 4u;
-    memset(&tx_msgs_[tx_count_], 0, sizeof(mmsghdr));
-    tx_msgs_[tx_count_].msg_hdr.msg_iov = v;
-    tx_msgs_[tx_count_].msg_hdr.msg_iovlen = 2;
-    tx_count_++;
+    // with one system call in Flush(). A retransmission repeats only the packets of the
+    // message that are still unanswered.
+    for (int j = 0; j < pkts_per_msg_; j++) {
+      if (!(missing_[p.slot] >> j & 1)) continue;
+      const bool last = j == pkts_per_msg_ - 1;
+      uint16_t pool_index = static_cast<uint16_t>((tid_ * window_ + phys) * pkts_per_msg_ + j) |
+                            (set_bits_[phys] ? kSetBit : 0);
+      if (tx_count_ == kBurst) Flush();
+      WireHeader& h = tx_headers_[tx_count_];
+      h.magic = htonl(kWireMagic);
+      h.type = last ? WIRE_DATA : WIRE_DATA_MORE;  // the message's one exponent rides on its last packet
+      h.job_tag = job_tag_;
+      h.worker_id = htons(cfg_.general_.rank);
+      h.pkt_id = htonl(p.pkt_id * static_cast<uint32_t>(pkts_per_msg_) + static_cast<uint32_t>(j));
+      h.pool_index = htons(pool_index);
+      h.numel = htons(static_cast<uint16_t>(packet_numel_));
+      h.exponent = last ? p.exponent : 0;
+      h.thread_id = static_cast<uint8_t>(tid_);
+      h.session_lo = htons(static_cast<uint16_t>(session_id_));
+      iovec* v = &tx_iov_[2 * tx_count_];
+      v[0].iov_base = &h;
+      v[0].iov_len = sizeof(h);
+      v[1].iov_base = p.payload + static_cast<size_t>(j) * packet_numel_;
+      v[1].iov_len = packet_numel_ * 4u;
+      memset(&tx_msgs_[tx_count_], 0, sizeof(mmsghdr));
+      tx_msgs_[tx_count_].msg_hdr.msg_iov = v;
+      tx_msgs_[tx_count_].msg_hdr.msg_iovlen = 2;
+      tx_count_++;
+    }
     timers_->Push(p.slot, std::chrono::steady_clock::now());
   }
 
@@ -117,23 +127,27 @@ class UdpTransport : public SlotTransport {
       memcpy(&h, data, sizeof(h));
       uint16_t numel = ntohs(h.numel);
       uint16_t pool_index = ntohs(h.pool_index);
-      int phys = static_cast<int>(pool_index & ~kSetBit) - tid_ * window_;
+      const int index = static_cast<int>(pool_index & ~kSetBit) - tid_ * window_ * pkts_per_msg_;
+      const int phys = index >= 0 ? index / pkts_per_msg_ : -1, j = index >= 0 ? index % pkts_per_msg_ : 0;
       bool ok = ntohl(h.magic) == kWireMagic && (h.type == WIRE_RESULT || h.type == WIRE_RESULT_RETX) &&
-                n == sizeof(h) + numel * 4u && phys >= 0 && phys < window_ &&
+                n == sizeof(h) + numel * 4u && numel == packet_numel_ && phys >= 0 && phys < window_ &&
                 h.job_tag == job_tag_;
       int s = -1;
       if (ok) {
         s = (phys - shift_ % window_ + window_) % window_;
-        ok = s < static_cast<int>(slots.size()) && !answered(s) &&
-             slots[s].pkt_id == ntohl(h.pkt_id) &&
+        ok = s < static_cast<int>(slots.size()) && !answered(s) && (missing_[s] >> j & 1) &&
+             slots[s].pkt_id * static_cast<uint32_t>(pkts_per_msg_) + static_cast<uint32_t>(j) == ntohl(h.pkt_id) &&
              ((pool_index & kSetBit) != 0) == (set_bits_[phys] != 0);
       }
       if (!ok) { ready->push_back(-1); continue; }  // duplicate, stale job or foreign packet
       SlotPacket& p = slots[s];
-      memcpy(p.payload, data + sizeof(h), numel * 4u);
-      p.exponent = h.exponent;
-      mark_answered(s);
-      ready->push_back(s);
+      memcpy(p.payload + static_cast<size_t>(j) * packet_numel_, data + sizeof(h), numel * 4u);
+      if (j == pkts_per_msg_ - 1) p.exponent = h.exponent;
+      missing_[s] &= ~(1ull << j);
+      if (missing_[s] == 0) {  // the whole message is back
+        mark_answered(s);
+        ready->push_back(s);
+      }
     }
     return true;
   }
@@ -162,11 +176,14 @@ class UdpTransport : public SlotTransport {
   int fd_;
   uint64_t session_id_;
   int window_;
+  int pkts_per_msg_, packet_numel_;
+  uint64_t all_packets_;
   int batch_ = 0;
   int shift_ = 0;
   uint8_t job_tag_ = 0;
   std::vector<uint8_t> set_bits_;
   std::vector<uint8_t> answered_;
+  std::vector<uint64_t> missing_;  // per slot: packets of the current message without a result yet
   // Bursts of up to kBurst datagrams per system call in both directions (the reference's
   // burst_rx / burst_tx of 64, config.cc:86-88).
   static const int kBurst = 64;
@@ -309,9 +326,13 @@ void UdpBackend::CleanupWorker() {
 
 void UdpBackend::WorkerLoop(WorkerTid tid, int fd) {
   const GeneralConfig& g = config_.general_;
-  int window = static_cast<int>(g.max_outstanding_packets / g.num_worker_threads);
-  int packet_numel = static_cast<int>(g.packet_numel);
-  auto ppp = PrePostProcessor::CreateInstance(config_, tid, g.packet_numel * 4, window);
+  // The unit of the window, of the timers and of the exponent is the message ([backend.udp]
+  // msg_numel, one packet unless configured otherwise).
+  const int msg_numel = static_cast<int>(config_.backend_.udp.msg_numel ? config_.backend_.udp.msg_numel : g.packet_numel);
+  const int pkts_per_msg = msg_numel / static_cast<int>(g.packet_numel);
+  int window = static_cast<int>(g.max_outstanding_packets / g.num_worker_threads) / pkts_per_msg;
+  if (window < 1) window = 1;
+  auto ppp = PrePostProcessor::CreateInstance(config_, tid, static_cast<Numel>(msg_numel) * 4, window);
   if (!config_.backend_.udp.cores.empty()) {
     int ids[256], count = 0;
     std::string err;
@@ -319,18 +340,19 @@ void UdpBackend::WorkerLoop(WorkerTid tid, int fd) {
       SML_LOG(WARNING) << "worker thread " << tid << ": cannot bind to core " << ids[tid];
     }
   }
-  UdpTransport transport(config_, tid, fd, session_id_, window);
+  UdpTransport transport(config_, tid, fd, session_id_, window, pkts_per_msg);
   std::vector<int32_t> pool;
   Stats& stats = context_.GetStats();
   auto running = [this] { return context_.GetContextState() == Context::RUNNING; };
   JobSlice js;
   while (running() && context_.GetJobSlice(tid, js)) {
     if (js.slice.numel > 0 && !g.instant_job_completion) {
-      SlotWindowResult r = RunSlotWindow(js, *ppp, transport, window, packet_numel, pool, running);
-      stats.AddTotalPktsSent(tid, r.sent);
-      stats.AddCorrectPktsReceived(tid, r.received);
+      SlotWindowResult r = RunSlotWindow(js, *ppp, transport, window, msg_numel, pool, running);
+      // the statistics count packets, as the reference's do (rdma_worker_thread.cc:187,283-292)
+      stats.AddTotalPktsSent(tid, r.sent * pkts_per_msg);
+      stats.AddCorrectPktsReceived(tid, r.received * pkts_per_msg);
       stats.AddWrongPktsReceived(tid, r.wrong);
-      stats.AddTimeouts(tid, r.timeouts);
+      stats.AddTimeouts(tid, r.timeouts * pkts_per_msg);
       if (!r.ok) js.job->failure_reason_ = "context stopped during the job";
     }
     context_.NotifyJobSliceCompletion(tid, js);

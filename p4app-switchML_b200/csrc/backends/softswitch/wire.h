@@ -28,8 +28,14 @@ enum WireType : uint8_t {
   // or floods it, p4/forwarder.p4:31-64):
   WIRE_ECHO_REQUEST = 3,  // anyone -> switch: "are you there"; payload comes back unchanged
   WIRE_ECHO_REPLY = 4,    // switch -> the sender of the request
-  WIRE_FORWARD = 5        // worker -> worker through the switch; pool_index = dest worker << 8 |
+  WIRE_FORWARD = 5,       // worker -> worker through the switch; pool_index = dest worker << 8 |
                           // dest thread, dest worker kFloodWorker = all other workers
+  // A message of several packets ([backend.udp] msg_numel) occupies consecutive pool indices and
+  // has ONE exponent, which only its last packet carries (that one is a WIRE_DATA packet); the
+  // packets in front of it say so and are aggregated without touching the exponent register,
+  // like packets whose last_packet flag is off in the reference (p4/rdma_receiver.p4:203-266,
+  // p4/switchml.p4:141-146).
+  WIRE_DATA_MORE = 6      // worker -> switch: payload only, more packets of this message follow
 };
 
 #pragma pack(push, 1)

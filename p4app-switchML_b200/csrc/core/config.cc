@@ -103,6 +103,7 @@ bool Config::LoadFromString(const std::string& text, const std::string& origin) 
   opts["backend.udp.pool_size"] = SML_OPT_UNSIGNED(backend_.udp.pool_size);
   opts["backend.udp.switch_pipes"] = SML_OPT_UNSIGNED(backend_.udp.switch_pipes);
   opts["backend.udp.cores"] = SML_OPT_STRING(backend_.udp.cores);
+  opts["backend.udp.msg_numel"] = SML_OPT_UNSIGNED(backend_.udp.msg_numel);
 
   opts["backend.cuda.device"] = [this](const std::string& v) {
     return ParseInt(v, &backend_.cuda.device);
@@ -248,6 +249,31 @@ void Config::Validate() {
     SML_CHECK(g.max_outstanding_packets / g.num_worker_threads <= backend_.udp.pool_size)
         << "window per worker thread exceeds backend.udp.pool_size";
     SML_CHECK(g.max_outstanding_packets <= 16384) << "the software switch has 16384 slots";
+    // Messages of several packets (the reference's backend.rdma.msg_numel, config.cc:185-211):
+    // a whole number of packets per message, a whole number of messages per worker thread.
+    UdpBackendConfig& u = backend_.udp;
+    if (u.msg_numel == 0) u.msg_numel = g.packet_numel;
+    SML_CHECK(u.msg_numel >= g.packet_numel) << "backend.udp.msg_numel cannot be less than general.packet_numel";
+    if (u.msg_numel % g.packet_numel != 0) {
+      uint32_t rounded = u.msg_numel / g.packet_numel * g.packet_numel;
+      SML_LOG(WARNING) << "backend.udp.msg_numel " << u.msg_numel << " is not divisible by general.packet_numel "
+                       << g.packet_numel << "; using " << rounded;
+      u.msg_numel = rounded;
+    }
+    const uint32_t pkts_per_msg = u.msg_numel / g.packet_numel;
+    SML_CHECK(pkts_per_msg <= 64) << "backend.udp.msg_numel: at most 64 packets per message";
+    const uint32_t per_round = g.num_worker_threads * pkts_per_msg;
+    if (g.max_outstanding_packets % per_round != 0) {
+      // the nearer of the two neighbouring multiples, never less than one message per thread
+      uint32_t lower = g.max_outstanding_packets / per_round * per_round, upper = lower + per_round;
+      uint32_t chosen = (lower >= per_round && g.max_outstanding_packets - lower <= upper - g.max_outstanding_packets) ? lower : upper;
+      SML_LOG(WARNING) << "max_outstanding_packets " << g.max_outstanding_packets << " is not divisible by " << per_round
+                       << " (packets per message x worker threads); using " << chosen << " to have exactly "
+                       << chosen / per_round << " outstanding messages per worker thread";
+      g.max_outstanding_packets = chosen;
+      SML_CHECK(g.max_outstanding_packets <= 16384 && g.max_outstanding_packets / g.num_worker_threads <= u.pool_size)
+          << "max_outstanding_packets after rounding to whole messages exceeds the switch pool";
+    }
     SML_CHECK(backend_.udp.switch_pipes <= 8) << "backend.udp.switch_pipes must be between 0 (automatic) and 8";
     if (!backend_.udp.cores.empty()) {
       int ids[256], count = 0;
@@ -338,7 +364,8 @@ std::string Config::ToString() const {
       << "    spawn_switch = " << (u.spawn_switch ? "true" : "false") << "\n"
       << "    pool_size = " << u.pool_size << "\n"
       << "    switch_pipes = " << u.switch_pipes << "\n"
-      << "    cores = " << u.cores << "\n";
+      << "    cores = " << u.cores << "\n"
+      << "    msg_numel = " << u.msg_numel << "\n";
   } else if (g.backend == "cuda") {
     const CudaBackendConfig& c = backend_.cuda;
     o << "[backend.cuda]\n"
@@ -354,7 +381,8 @@ std::string Config::ToString() const {
       << "    launch = " << c.launch << "\n"
       << "    rendezvous_dir = " << c.rendezvous_dir << "\n"
       << "    wait_timeout_ms = " << c.wait_timeout_ms << "\n"
-      << "    numa_bind = " << (c.numa_bind ? "true" : "false") << "\n";
+      << "    numa_bind = " << (c.numa_bind ? "true" : "false") << "\n"
+      << "    p2p_algo = " << c.p2p_algo << "\n";
   }
   for (const auto& kv : ignored_) o << "  (ignored) " << kv.first << " = " << kv.second << "\n";
   return o.str();

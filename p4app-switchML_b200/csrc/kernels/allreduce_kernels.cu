@@ -27,6 +27,7 @@
 #include <stdlib.h>
 
 #include "kernels/allreduce_kernels.h"
+#include "kernels/bulk_copy.cuh"
 #include "kernels/device_sync.cuh"
 #include "kernels/multimem.cuh"
 #include "kernels/quant_tile.cuh"
@@ -180,7 +181,14 @@ static const int kDefaultLoadWarps = 4, kDefaultReduceWarps = 8;  // the rest of
 struct StagedShared {
   int failed;
   volatile unsigned long long stored;  // tiles copied out so far
+  BulkRing ring[2];                    // TMA copy rings of the loader [0] and the storer [1]
+  WarpStreamBarriers ws;               // mbarriers of the quantising loader's per-warp streams
+  char* ring_buffers;                  // dynamic shared memory (nullptr: the job's tensors rule the TMA paths out):
+                                       // [0, kBulkRingBytes) storer ring, then the loader's ring or its warps' rings
 };
+static const int kStreamWarps = 6;     // loader warps of the quantised mode; each owns kWsRingBytes
+static const size_t kLoaderSmemOffset = kBulkRingBytes;
+static const size_t kLoaderSmemBytes = kStreamWarps * kWsRingBytes > kBulkRingBytes ? kStreamWarps * kWsRingBytes : kBulkRingBytes;
 
 struct Role {
   int tid;       // thread index inside the role
@@ -260,6 +268,20 @@ __device__ __forceinline__ void RoleCopy(const Role& role, void* dst, const void
   }
 }
 
+// A local copy by a role: through the TMA unit when the geometry allows it (one thread drives
+// it, see bulk_copy.cuh), else with the role's own loads and stores. `which` picks the ring.
+// The caller synchronises the role afterwards (RoleSignal / role.Sync) and checks `failed`.
+__device__ __forceinline__ void RoleLocalCopy(const RankCtx& ctx, const Role& role, StagedShared* sh, int which,
+                                              void* dst, const void* src, size_t bytes, int esz) {
+  if (sh->ring_buffers != nullptr && BulkCopyable(dst, src, bytes)) {
+    if (role.tid == 0)
+      BulkCopy(&sh->ring[which], sh->ring_buffers + (which == 0 ? kLoaderSmemOffset : 0), static_cast<char*>(dst),
+               static_cast<const char*>(src), bytes, ctx.timeout_ns, reinterpret_cast<volatile int*>(&sh->failed));
+  } else {
+    RoleCopy(role, dst, src, bytes, esz);
+  }
+}
+
 // Checked build (-DSWITCHML_CHECKED): before a tile, a one-shot buffer or a symmetric tensor
 // is touched, its geometry is verified against the sizes of the regions it indexes. A
 // violation stores STATUS_BOUNDS with the channel in the status word, marks the CTA as
@@ -336,6 +358,23 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
     const size_t slot_index = static_cast<size_t>(channel) * S + static_cast<size_t>(k % S);
     return ctx.exp_offset + slot_index * blocks_per_slot * kExpWordBytes;
   };
+  // The quantising loader reads float32 device memory through per-warp TMA streams.
+  static_assert(MODE != MODE_QUANT || kLoadWarps <= kStreamWarps, "every loader warp needs a ring");
+  const bool stream = MODE == MODE_QUANT && ELEM == ELEM_F32 && sh->ring_buffers != nullptr &&
+                      (reinterpret_cast<uintptr_t>(job.in) & 15) == 0;
+  WarpStream ws;
+  if (MODE == MODE_QUANT && warp < kLoadWarps) {
+    ws.ring = stream ? sh->ring_buffers + kLoaderSmemOffset + static_cast<size_t>(warp) * kWsRingBytes : nullptr;
+    ws.full = sh->ws.full[warp];
+    ws.used = 0;
+    ws.timeout_ns = ctx.timeout_ns;
+    ws.failed = failed;
+  }
+  auto publish = [&](const char* tile_in, size_t tile_len_, size_t tile_exp_off, Epoch tag) {
+    if (stream) return StreamTileExponents(ctx, ws, warp, kLoadWarps, lane, tile_in, tile_len_, tile_exp_off, tag);
+    PublishTileExponents<ELEM>(ctx, warp, kLoadWarps, lane, tile_in, tile_len_, tile_exp_off, tag);
+    return true;
+  };
 
   for (unsigned long long k = 0; k < ntiles; ++k) {
     const unsigned long long pos = c0 + k * tile_elems;
@@ -381,9 +420,10 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
           // With a single slot its words are free by now: every rank consumed them before
           // it signalled the payload of the tile before, and the copy-out awaited above
           // came after all those signals.
-          PublishTileExponents<ELEM>(ctx, warp, kLoadWarps, lane, in, len, exp_off, epoch);
+          const bool published = publish(in, len, exp_off, epoch);
           RoleSignal(ctx, role, channel, 0, epoch);
-          if (!RoleWait(ctx, role, channel, 0, epoch, sh)) return;
+          const bool met = RoleWait(ctx, role, channel, 0, epoch, sh);  // every warp takes part, whatever happened
+          if (!published || !met) return;
         } else {
           // They came with the payload signal of the tile before.
           if (!RoleWait(ctx, role, channel, 1, epoch - 1, sh)) return;
@@ -395,18 +435,33 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
         TileScaleFactors(ctx, role.tid, role.nthreads, exp_off, nblocks, epoch, sf, channel, failed);
         role.Sync();
         if (*failed) return;
-        QuantizeRange<ELEM, 8>(role.tid, role.nthreads, in, reinterpret_cast<int*>(my_stage + slot_off), 0, len,
-                               sf, shift);
+        lap(9);
+        int* q = reinterpret_cast<int*>(my_stage + slot_off);
+        bool streamed = true;
+        size_t done = 0;
+        if (stream) {
+          const size_t nchunks = len / (kWsChunk / 4);
+          streamed = StreamQuantize(ws, warp, kLoadWarps, lane, in, 0, nchunks, sf, shift,
+                                    [&](size_t e, int4 r) { *reinterpret_cast<int4*>(q + e) = r; });
+          done = nchunks * (kWsChunk / 4);
+        }
+        QuantizeRange<ELEM, 8>(role.tid, role.nthreads, in, q + done, done, len, sf, shift);
+        lap(10);
         // Exponents of the next tile, one tile ahead of its data. Its words belong to the
         // slot of tile k+1-S, which every rank consumed before it signalled that tile's
         // payload, and all those signals were awaited above (k+1-S <= k-1).
-        if (ahead && k + 1 < ntiles)
-          PublishTileExponents<ELEM>(ctx, warp, kLoadWarps, lane, in + tile_elems * in_esz, tile_len(k + 1),
-                                     exp_offset_of(k + 1), epoch + 1);
+        if (streamed && ahead && k + 1 < ntiles)
+          streamed = publish(in + tile_elems * in_esz, tile_len(k + 1), exp_offset_of(k + 1), epoch + 1);
+        if (!streamed) {
+          role.Sync();  // the other warps are on their way to the signal's barrier: meet them, then leave together
+          return;
+        }
+        lap(11);
       } else {
-        RoleCopy(role, my_stage + slot_off, in, len * in_esz, in_esz);
+        RoleLocalCopy(ctx, role, sh, 0, my_stage + slot_off, in, len * in_esz, in_esz);
       }
       RoleSignal(ctx, role, channel, 1, epoch);
+      if (*failed) return;
       lap(4);
     } else if (which == 1) {
       // ------------------------------ reducer ------------------------------
@@ -546,10 +601,11 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
           unsigned short* o = reinterpret_cast<unsigned short*>(out);
           for (size_t i = role.tid; i < len; i += role.nthreads) o[i] = FloatToBf16(y[i]);
         } else {
-          RoleCopy(role, out, my_stage + slot_off, len * in_esz, in_esz);
+          RoleLocalCopy(ctx, role, sh, 1, out, my_stage + slot_off, len * in_esz, in_esz);
         }
       }
       role.Sync();
+      if (*failed) return;
       if (role.tid == 0) {
         __threadfence_block();
         sh->stored = k + 1;
@@ -807,11 +863,18 @@ __device__ __forceinline__ void RunJob(const RankCtx& ctx, const JobArgs& job, i
 // starts, advance it by the job's count when the kernel ends (on every path, also after a
 // timeout, so that the ranks stay in step). Nothing about epochs is baked into the launch,
 // which is what lets a captured launch be replayed.
-#define SML_EPOCH_PROLOGUE(CTX, CHANNEL)                                  \
+#define SML_EPOCH_PROLOGUE(CTX, JOB, CHANNEL, ALGO)                       \
   __shared__ Epoch s_base;                                                \
   if (threadIdx.x == 0) {                                                 \
     s_state.failed = 0;                                                   \
     s_state.stored = 0;                                                   \
+    s_state.ring_buffers = nullptr;                                       \
+    if (((ALGO) == ALGO_STAGED || (ALGO) == ALGO_PUSH) && (JOB).bulk_copy) { \
+      BulkRingInit(&s_state.ring[0]);                                     \
+      BulkRingInit(&s_state.ring[1]);                                     \
+      WarpStreamInit(&s_state.ws);                                        \
+      s_state.ring_buffers = reinterpret_cast<char*>(s_dyn);              \
+    }                                                                     \
     s_base = (CTX).epoch_words[CHANNEL];                                  \
   }                                                                       \
   __syncthreads();
@@ -819,12 +882,20 @@ __device__ __forceinline__ void RunJob(const RankCtx& ctx, const JobArgs& job, i
   __syncthreads();                                                        \
   if (threadIdx.x == 0) (CTX).epoch_words[CHANNEL] = s_base + (JOB).epochs;
 
+// Dynamic shared memory of the streaming kernels: the two TMA copy rings.
+extern __shared__ __align__(128) unsigned char s_dyn[];
+
+template <int ALGO>
+constexpr size_t DynamicSmemBytes() {
+  return (ALGO == ALGO_STAGED || ALGO == ALGO_PUSH) ? kLoaderSmemOffset + kLoaderSmemBytes : 0;
+}
+
 template <int ELEM, int MODE, int ALGO>
 __global__ void __launch_bounds__(kThreads, 1)
 AllReduceKernel(const RankCtx ctx, const JobArgs job, unsigned long long epc) {
   __shared__ StagedShared s_state;
   __shared__ float s_sf[(MODE == MODE_QUANT && (ALGO == ALGO_STAGED || ALGO == ALGO_PUSH)) ? kMaxBlocksPerSlot : 1];
-  SML_EPOCH_PROLOGUE(ctx, blockIdx.x)
+  SML_EPOCH_PROLOGUE(ctx, job, blockIdx.x, ALGO)
   RunJob<ELEM, MODE, ALGO>(ctx, job, blockIdx.x, epc, s_base, &s_state.failed, s_sf);
   SML_EPOCH_EPILOGUE(ctx, job, blockIdx.x)
 }
@@ -842,7 +913,7 @@ AllReduceEmuKernel(const RankCtx* ctxs, const JobArgs* jobs, unsigned long long 
     s_job = jobs[blockIdx.y];
   }
   __syncthreads();
-  SML_EPOCH_PROLOGUE(s_ctx, blockIdx.x)
+  SML_EPOCH_PROLOGUE(s_ctx, s_job, blockIdx.x, ALGO)
   RunJob<ELEM, MODE, ALGO>(s_ctx, s_job, blockIdx.x, epc, s_base, &s_state.failed, s_sf);
   SML_EPOCH_EPILOGUE(s_ctx, s_job, blockIdx.x)
 }
@@ -926,7 +997,13 @@ __global__ void WaitProbeKernel(const RankCtx ctx) {
 template <int ELEM, int MODE, int ALGO>
 cudaError_t LaunchOne(const RankCtx& ctx, const JobArgs& job, const LaunchPlan& plan,
                       cudaStream_t stream) {
-  AllReduceKernel<ELEM, MODE, ALGO><<<plan.channels, kThreads, 0, stream>>>(ctx, job, plan.elems_per_channel);
+  constexpr size_t dyn = DynamicSmemBytes<ALGO>();
+  if (dyn > 0) {
+    cudaError_t e = cudaFuncSetAttribute(AllReduceKernel<ELEM, MODE, ALGO>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(dyn));
+    if (e != cudaSuccess) return e;
+  }
+  AllReduceKernel<ELEM, MODE, ALGO><<<plan.channels, kThreads, dyn, stream>>>(ctx, job, plan.elems_per_channel);
   return cudaGetLastError();
 }
 
@@ -938,8 +1015,14 @@ cudaError_t LaunchOneEmu(const RankCtx* ctxs, const JobArgs* jobs, int nranks,
   dim3 grid(plan.channels, nranks);
   // Cooperative launch: the runtime refuses the launch unless all CTAs can be resident
   // together, which the cross-"rank" barriers need.
+  constexpr size_t dyn = DynamicSmemBytes<ALGO>();
+  if (dyn > 0) {
+    cudaError_t e = cudaFuncSetAttribute(AllReduceEmuKernel<ELEM, MODE, ALGO>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         static_cast<int>(dyn));
+    if (e != cudaSuccess) return e;
+  }
   return cudaLaunchCooperativeKernel(reinterpret_cast<void*>(AllReduceEmuKernel<ELEM, MODE, ALGO>),
-                                     grid, dim3(kThreads), args, 0, stream);
+                                     grid, dim3(kThreads), args, dyn, stream);
 }
 
 #define SML_DISPATCH(FN, elem, mode, algo, ...)                                             \
@@ -979,6 +1062,15 @@ cudaError_t LaunchOneEmu(const RankCtx* ctxs, const JobArgs* jobs, int nranks,
 
 }  // namespace
 
+bool DeviceMemory(const void* p) {
+  cudaPointerAttributes at;
+  if (cudaPointerGetAttributes(&at, p) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  return at.type == cudaMemoryTypeDevice;
+}
+
 size_t SlotElems(const RankCtx& ctx, int elem_type, int mode) {
   int st_esz = mode == MODE_QUANT ? 4 : (elem_type == ELEM_BF16 ? 2 : 4);
   return ctx.slot_bytes / st_esz;
@@ -996,6 +1088,8 @@ size_t PushTileCapacity(const RankCtx& ctx, int elem_type, int mode) {
     if (cap > by_words) cap = by_words;
   }
   const size_t unit = n * (ctx.block_numel > 128 ? ctx.block_numel : 128);
+  const size_t stream_unit = n * (kWsChunk / 4);  // shards of whole TMA chunks where the slot allows it
+  if (cap >= stream_unit) return cap / stream_unit * stream_unit;
   return cap / unit * unit;
 }
 
@@ -1257,6 +1351,7 @@ extern "C" int switchml_local_allreduce_noalloc(const void* in, void* out,
   job.mode = mode;
   job.algo = ALGO_STAGED;
   job.post_scale = 1.0f;
+  job.bulk_copy = DeviceMemory(in) && DeviceMemory(out);
   LaunchPlan plan = PlanLaunch(ctx, job, 0, kNoAllocChannels);
   job.tile_elems = plan.tile_elems;
   job.epochs = plan.epochs;

@@ -78,6 +78,8 @@ struct JobArgs {
   unsigned epochs;      // how far the job advances the epoch counter of each channel it uses
   int trailing_barrier; // ALGO_ONESHOT: meet once more after reading, so the buffer needs no parity (graph replays)
   int oneshot_parity;
+  int bulk_copy;     // `in` and `out` are ordinary device memory of this GPU: whole-tile copies may go through the
+                     // TMA unit (never set for pinned host or managed memory)
   int out_zero_copy; // ALGO_STAGED / ALGO_PUSH: `out` lies in the symmetric user region (user_* and out_offset are
                      // set): finished shards are broadcast straight into every rank's output, no copy-out
   unsigned long long tile_elems;  // ALGO_STAGED: elements per tile (<= elements of a slot)
@@ -97,6 +99,8 @@ struct LaunchPlan {
   unsigned long long tile_elems;         // ALGO_STAGED: copy into JobArgs::tile_elems
 };
 
+// True if `p` is device memory (cudaMalloc or the virtual-memory API), not pinned host or managed memory.
+bool DeviceMemory(const void* p);
 // Number of elements of a slot for this element type / mode.
 size_t SlotElems(const RankCtx& ctx, int elem_type, int mode);
 // Largest tile of ALGO_PUSH that fits a slot (a multiple of nranks * max(block, 128)

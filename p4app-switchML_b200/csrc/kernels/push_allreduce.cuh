@@ -245,6 +245,23 @@ __device__ void RunPush(const RankCtx& ctx, const JobArgs& job, int channel,
   auto exp_offset_of = [&](unsigned long long k) {
     return ctx.exp_offset + (static_cast<size_t>(channel) * S + static_cast<size_t>(k % S)) * blocks_per_slot * kExpWordBytes;
   };
+  // The quantising loader reads float32 device memory through per-warp TMA streams.
+  static_assert(MODE != MODE_QUANT || kLoadWarps <= kStreamWarps, "every loader warp needs a ring");
+  const bool stream = MODE == MODE_QUANT && ELEM == ELEM_F32 && sh->ring_buffers != nullptr &&
+                      (reinterpret_cast<uintptr_t>(job.in) & 15) == 0;
+  WarpStream ws;
+  if (MODE == MODE_QUANT && warp < kLoadWarps) {
+    ws.ring = stream ? sh->ring_buffers + kLoaderSmemOffset + static_cast<size_t>(warp) * kWsRingBytes : nullptr;
+    ws.full = sh->ws.full[warp];
+    ws.used = 0;
+    ws.timeout_ns = ctx.timeout_ns;
+    ws.failed = failed;
+  }
+  auto publish = [&](const char* tile_in, size_t tile_len_, size_t tile_exp_off, Epoch tag) {
+    if (stream) return StreamTileExponents(ctx, ws, warp, kLoadWarps, lane, tile_in, tile_len_, tile_exp_off, tag);
+    PublishTileExponents<ELEM>(ctx, warp, kLoadWarps, lane, tile_in, tile_len_, tile_exp_off, tag);
+    return true;
+  };
 
   for (unsigned long long k = 0; k < ntiles; ++k) {
     const unsigned long long pos = c0 + k * tile_elems;
@@ -275,9 +292,10 @@ __device__ void RunPush(const RankCtx& ctx, const JobArgs& job, int channel,
       }
       if (MODE == MODE_QUANT) {
         if (k == 0 || !ahead) {
-          PublishTileExponents<ELEM>(ctx, warp, kLoadWarps, lane, in, len, exp_off, epoch);
+          const bool published = publish(in, len, exp_off, epoch);
           RoleSignal(ctx, role, channel, 0, epoch);
-          if (!RoleWait(ctx, role, channel, 0, epoch, sh)) return;
+          const bool met = RoleWait(ctx, role, channel, 0, epoch, sh);  // every warp takes part, whatever happened
+          if (!published || !met) return;
         } else {
           if (!RoleWait(ctx, role, channel, 1, epoch - 1, sh)) return;
         }
@@ -288,23 +306,64 @@ __device__ void RunPush(const RankCtx& ctx, const JobArgs& job, int channel,
         TileScaleFactors(ctx, role.tid, role.nthreads, exp_off, nblocks, epoch, sf, channel, failed);
         role.Sync();
         if (*failed) return;
+        lap(9);
       }
-      for (int d = 1; d < n; d++) {
-        const int p = (me + d) % n;  // start with the right-hand neighbour: spreads the traffic
-        size_t sb, se;
-        ShardRange(len, n, p, unit, &sb, &se);
-        if (sb >= se) continue;
-        char* dst = ctx.stage_peer[p] + slot_off + static_cast<size_t>(PushAreaIndex(me, p)) * recv_bytes;
-        if (MODE == MODE_QUANT) {
-          QuantizeRange<ELEM, kPushUnroll>(role.tid, role.nthreads, in, reinterpret_cast<int*>(dst), sb, se, sf, shift);
-        } else {
-          RoleCopy(role, dst, in + sb * in_esz, (se - sb) * in_esz, in_esz);
+      bool streamed = true;
+      const size_t per = len / n;  // a full tile: n shards of whole chunks
+      if (MODE == MODE_QUANT && stream && len == tile_elems && per % (kWsChunk / 4) == 0) {
+        // All n-1 foreign shards as one run of chunks, the right-hand neighbour's first.
+        const size_t cps = per / (kWsChunk / 4);  // chunks per shard
+        char* const* peers = ctx.stage_peer;
+        streamed = WarpStreamRun(
+            ws, warp, kLoadWarps, lane, cps * (n - 1),
+            [&](size_t c) {
+              const int p = (me + 1 + static_cast<int>(c / cps)) % n;
+              return in + (static_cast<size_t>(p) * per + (c % cps) * (kWsChunk / 4)) * 4;
+            },
+            [&](size_t c, const char* smem) {
+              const int p = (me + 1 + static_cast<int>(c / cps)) % n;
+              const size_t off = (c % cps) * (kWsChunk / 4);  // first element of the chunk inside its shard
+              int4* dst = reinterpret_cast<int4*>(peers[p] + slot_off + static_cast<size_t>(PushAreaIndex(me, p)) * recv_bytes) + off / 4;
+              const float* sfp = sf;
+              float4 x[8];
+#pragma unroll
+              for (int u = 0; u < 8; u++) x[u] = reinterpret_cast<const float4*>(smem)[u * 32 + lane];
+#pragma unroll
+              for (int u = 0; u < 8; u++) {
+                const size_t e = static_cast<size_t>(p) * per + off + static_cast<size_t>(u * 32 + lane) * 4;
+                const float f = sfp[e >> shift];
+                int4 r;
+                r.x = quant::Quantize(x[u].x, f);
+                r.y = quant::Quantize(x[u].y, f);
+                r.z = quant::Quantize(x[u].z, f);
+                r.w = quant::Quantize(x[u].w, f);
+                dst[u * 32 + lane] = r;
+              }
+            });
+      } else {
+        for (int d = 1; d < n; d++) {
+          const int p = (me + d) % n;  // start with the right-hand neighbour: spreads the traffic
+          size_t sb, se;
+          ShardRange(len, n, p, unit, &sb, &se);
+          if (sb >= se) continue;
+          char* dst = ctx.stage_peer[p] + slot_off + static_cast<size_t>(PushAreaIndex(me, p)) * recv_bytes;
+          if (MODE == MODE_QUANT) {
+            QuantizeRange<ELEM, kPushUnroll>(role.tid, role.nthreads, in, reinterpret_cast<int*>(dst), sb, se, sf, shift);
+          } else {
+            RoleCopy(role, dst, in + sb * in_esz, (se - sb) * in_esz, in_esz);
+          }
         }
       }
-      if (MODE == MODE_QUANT && ahead && k + 1 < ntiles)
-        PublishTileExponents<ELEM>(ctx, warp, kLoadWarps, lane, in + tile_elems * in_esz, tile_len(k + 1),
-                                   exp_offset_of(k + 1), epoch + 1);
+      lap(10);
+      if (MODE == MODE_QUANT && streamed && ahead && k + 1 < ntiles)
+        streamed = publish(in + tile_elems * in_esz, tile_len(k + 1), exp_offset_of(k + 1), epoch + 1);
+      if (!streamed) {
+        role.Sync();  // the other warps are on their way to the signal's barrier: meet them, then leave together
+        return;
+      }
+      lap(11);
       RoleSignal(ctx, role, channel, 1, epoch);
+      if (*failed) return;
       lap(4);
     } else if (which == 1) {
       // ------------------------------ reducer ------------------------------
@@ -412,10 +471,11 @@ __device__ void RunPush(const RankCtx& ctx, const JobArgs& job, int channel,
             unsigned short* o = reinterpret_cast<unsigned short*>(out);
             for (size_t i = role.tid; i < se - sb; i += role.nthreads) o[i] = FloatToBf16(y[i]);
           } else {
-            RoleCopy(role, out, src, (se - sb) * in_esz, in_esz);
+            RoleLocalCopy(ctx, role, sh, 1, out, src, (se - sb) * in_esz, in_esz);
           }
         }
         RoleSignal(ctx, role, channel, 3, epoch);  // my result areas of this slot may be refilled
+        if (*failed) return;
       }
       if (role.tid == 0) {
         sh->stored = k + 1;

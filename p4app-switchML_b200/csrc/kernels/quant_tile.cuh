@@ -22,6 +22,7 @@
 
 #include "kernels/allreduce_kernels.h"
 #include "kernels/device_sync.cuh"
+#include "kernels/warp_stream.cuh"
 #include "switchml/quant_math.h"
 
 namespace switchml {
@@ -51,67 +52,60 @@ __device__ __forceinline__ float TileLoadAsFloat(const void* in, size_t i, int e
 // Local exponents of the `len` elements at `in` (one tile), published under `tag` into the
 // exponent words starting at byte offset `exp_off`. Called by all threads of a role of
 // `nwarps` warps; `warp` is the caller's warp index inside the role.
-template <int ELEM>
-__device__ __forceinline__ void PublishTileExponents(const RankCtx& ctx, int warp, int nwarps, int lane,
-                                                     const char* in, size_t len, size_t exp_off, Epoch tag) {
+// One step of the exponent pass: 8 consecutive rows of 128 float32 elements starting at row
+// `row0` of the tile, one float4 per lane and row in `x` (from global or shared memory).
+// Blocks of 32 or 64 elements are groups of 8 or 16 neighbouring lanes of one row; larger
+// blocks are 1, 2, 4 or 8 whole rows, which a step always holds completely because steps
+// start at multiples of 8 rows.
+__device__ __forceinline__ void PublishRows8(const RankCtx& ctx, int lane, const float4* x, size_t row0,
+                                             size_t exp_off, Epoch tag) {
+  constexpr int kRows = 8;
   const size_t B = ctx.block_numel;
-  const size_t nblocks = (len + B - 1) / B;
-  size_t first_block = 0;
-  if (ELEM == ELEM_F32 && (reinterpret_cast<uintptr_t>(in) & 15) == 0) {
-    // The tile as rows of 128 elements, one float4 per lane. A warp takes kRows consecutive
-    // rows per step and issues all their loads before it looks at any value, so that kRows
-    // 16-byte loads per lane are in flight. Blocks of 32 or 64 elements are groups of 8 or
-    // 16 neighbouring lanes of one row; larger blocks are 1, 2, 4 or 8 whole rows, which a
-    // step always holds completely (kRows = 8, steps start at multiples of 8 rows).
-    constexpr int kRows = 8;
-    const size_t whole_blocks = len / B;                          // blocks without a ragged end
-    const size_t nrows = whole_blocks * B / 128 / kRows * kRows;  // rows handled here, in whole steps
-    const float4* p4 = reinterpret_cast<const float4*>(in);
-    for (size_t r0 = static_cast<size_t>(warp) * kRows; r0 < nrows; r0 += static_cast<size_t>(nwarps) * kRows) {
-      float4 x[kRows];
+  float m[kRows];
 #pragma unroll
-      for (int u = 0; u < kRows; u++) x[u] = p4[(r0 + u) * 32 + lane];
-      float m[kRows];
+  for (int u = 0; u < kRows; u++)
+    m[u] = fmaxf(fmaxf(fabsf(x[u].x), fabsf(x[u].y)), fmaxf(fabsf(x[u].z), fabsf(x[u].w)));
+  if (B < 128) {
+    const int g = static_cast<int>(B / 4);  // lanes per block: 8 or 16
+    const size_t per_row = 128 / B;         // blocks per row: 4 or 2
 #pragma unroll
-      for (int u = 0; u < kRows; u++)
-        m[u] = fmaxf(fmaxf(fabsf(x[u].x), fabsf(x[u].y)), fmaxf(fabsf(x[u].z), fabsf(x[u].w)));
-      if (B < 128) {
-        const int g = static_cast<int>(B / 4);  // lanes per block: 8 or 16
-        const size_t per_row = 128 / B;         // blocks per row: 4 or 2
+    for (int u = 0; u < kRows; u++) {
+      float mm = m[u];
+      for (int o = g >> 1; o > 0; o >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, o));
+      if ((lane % g) == 0)
+        ExpPublish(ctx, exp_off + ((row0 + u) * per_row + lane / g) * kExpWordBytes,
+                   ExpWord(tag, quant::LocalExponent(mm)));
+    }
+  } else {
+    const int rows_per_block = static_cast<int>(B / 128);  // 1, 2, 4 or 8
+    // fold the rows of one block into the first of them, then one butterfly per block
 #pragma unroll
-        for (int u = 0; u < kRows; u++) {
-          float mm = m[u];
-          for (int o = g >> 1; o > 0; o >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, o));
-          if ((lane % g) == 0)
-            ExpPublish(ctx, exp_off + ((r0 + u) * per_row + lane / g) * kExpWordBytes,
-                       ExpWord(tag, quant::LocalExponent(mm)));
-        }
-      } else {
-        const int rows_per_block = static_cast<int>(B / 128);  // 1, 2, 4 or 8
-        // fold the rows of one block into the first of them, then one butterfly per block
+    for (int span = 1; span < kRows; span <<= 1) {
+      if (span < rows_per_block) {
 #pragma unroll
-        for (int span = 1; span < kRows; span <<= 1) {
-          if (span < rows_per_block) {
-#pragma unroll
-            for (int u = 0; u + span < kRows; u += 2 * span) m[u] = fmaxf(m[u], m[u + span]);
-          }
-        }
-#pragma unroll
-        for (int u = 0; u < kRows; u++) {
-          if ((u % rows_per_block) != 0) continue;  // warp-uniform
-          float mm = m[u];
-#pragma unroll
-          for (int o = 16; o > 0; o >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, o));
-          if (lane == 0)
-            ExpPublish(ctx, exp_off + ((r0 + u) / rows_per_block) * kExpWordBytes,
-                       ExpWord(tag, quant::LocalExponent(mm)));
-        }
+        for (int u = 0; u + span < kRows; u += 2 * span) m[u] = fmaxf(m[u], m[u + span]);
       }
     }
-    first_block = nrows * 128 / B;
+#pragma unroll
+    for (int u = 0; u < kRows; u++) {
+      if ((u % rows_per_block) != 0) continue;  // warp-uniform
+      float mm = m[u];
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, o));
+      if (lane == 0)
+        ExpPublish(ctx, exp_off + ((row0 + u) / rows_per_block) * kExpWordBytes,
+                   ExpWord(tag, quant::LocalExponent(mm)));
+    }
   }
-  // What is left (bf16 input, unaligned input, the last rows, a ragged last block): one
-  // block per warp.
+}
+
+// The blocks [first_block, nblocks) of a tile, one block per warp and step, any element type
+// and alignment: what the row-wise passes leave over (last rows, a ragged last block).
+template <int ELEM>
+__device__ __forceinline__ void PublishBlocksSlow(const RankCtx& ctx, int warp, int nwarps, int lane, const char* in,
+                                                  size_t len, size_t first_block, size_t exp_off, Epoch tag) {
+  const size_t B = ctx.block_numel;
+  const size_t nblocks = (len + B - 1) / B;
   for (size_t b = first_block + warp; b < nblocks; b += nwarps) {
     const size_t base = b * B;
     const size_t n = len - base < B ? len - base : B;
@@ -127,6 +121,29 @@ __device__ __forceinline__ void PublishTileExponents(const RankCtx& ctx, int war
     }
     if (lane == 0) ExpPublish(ctx, exp_off + b * kExpWordBytes, ExpWord(tag, quant::LocalExponent(m)));
   }
+}
+
+template <int ELEM>
+__device__ __forceinline__ void PublishTileExponents(const RankCtx& ctx, int warp, int nwarps, int lane,
+                                                     const char* in, size_t len, size_t exp_off, Epoch tag) {
+  const size_t B = ctx.block_numel;
+  size_t first_block = 0;
+  if (ELEM == ELEM_F32 && (reinterpret_cast<uintptr_t>(in) & 15) == 0) {
+    // The tile as rows of 128 elements, one float4 per lane. A warp takes 8 consecutive rows
+    // per step and issues all their loads before it looks at any value.
+    constexpr int kRows = 8;
+    const size_t whole_blocks = len / B;                          // blocks without a ragged end
+    const size_t nrows = whole_blocks * B / 128 / kRows * kRows;  // rows handled here, in whole steps
+    const float4* p4 = reinterpret_cast<const float4*>(in);
+    for (size_t r0 = static_cast<size_t>(warp) * kRows; r0 < nrows; r0 += static_cast<size_t>(nwarps) * kRows) {
+      float4 x[kRows];
+#pragma unroll
+      for (int u = 0; u < kRows; u++) x[u] = p4[(r0 + u) * 32 + lane];
+      PublishRows8(ctx, lane, x, r0, exp_off, tag);
+    }
+    first_block = nrows * 128 / B;
+  }
+  PublishBlocksSlow<ELEM>(ctx, warp, nwarps, lane, in, len, first_block, exp_off, tag);
 }
 
 // Scale factors of the tile's blocks from this rank's own copy of the exponent words, which
@@ -191,6 +208,53 @@ __device__ __forceinline__ void QuantizeRange(int tid, int nthreads, const char*
     for (size_t j = tid; j < n; j += nthreads)
       q[j] = quant::Quantize(TileLoadAsFloat(in, begin + j, ELEM), sf[(begin + j) >> shift]);
   }
+}
+
+// ---- the same two passes fed by the TMA unit (float32 input, 16-byte aligned, device memory) ----
+
+// A tile's exponent pass: whole chunks of 1024 elements stream through the warps' rings, the
+// rest goes the slow way. False if a wait ran out.
+__device__ __forceinline__ bool StreamTileExponents(const RankCtx& ctx, WarpStream& ws, int warp, int nwarps, int lane,
+                                                    const char* in, size_t len, size_t exp_off, Epoch tag) {
+  const size_t nchunks = len / (kWsChunk / 4);
+  const bool ok = WarpStreamRun(
+      ws, warp, nwarps, lane, nchunks, [&](size_t c) { return in + c * kWsChunk; },
+      [&](size_t c, const char* smem) {
+        float4 x[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) x[u] = reinterpret_cast<const float4*>(smem)[u * 32 + lane];
+        PublishRows8(ctx, lane, x, c * 8, exp_off, tag);
+      });
+  if (!ok) return false;
+  PublishBlocksSlow<ELEM_F32>(ctx, warp, nwarps, lane, in, len, nchunks * (kWsChunk / 4) / ctx.block_numel, exp_off, tag);
+  return true;
+}
+
+// Quantise the elements [begin, end) of a tile (both multiples of 1024 apart from the tile's
+// ragged end): whole chunks stream through the warps' rings; `store(e, q)` receives the four
+// quantised values of elements e..e+3 (tile-relative). The ragged end is left to the caller
+// (QuantizeRange on [begin + whole chunks, end)). False if a wait ran out.
+template <typename Store>
+__device__ __forceinline__ bool StreamQuantize(WarpStream& ws, int warp, int nwarps, int lane, const char* in,
+                                               size_t begin, size_t nchunks, const float* sf, int shift, Store store) {
+  return WarpStreamRun(
+      ws, warp, nwarps, lane, nchunks, [&](size_t c) { return in + begin * 4 + c * kWsChunk; },
+      [&](size_t c, const char* smem) {
+        float4 x[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) x[u] = reinterpret_cast<const float4*>(smem)[u * 32 + lane];
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+          const size_t e = begin + c * (kWsChunk / 4) + static_cast<size_t>(u * 32 + lane) * 4;
+          const float f = sf[e >> shift];
+          int4 r;
+          r.x = quant::Quantize(x[u].x, f);
+          r.y = quant::Quantize(x[u].y, f);
+          r.z = quant::Quantize(x[u].z, f);
+          r.w = quant::Quantize(x[u].w, f);
+          store(e, r);
+        }
+      });
 }
 
 }  // namespace kernels

@@ -380,6 +380,23 @@ static void TestSoftSwitch() {
   sw.Process(fwd.data(), fwd.size(), &out);
   EXPECT(out.empty() && sw.counters().malformed == malformed + 2);
   EXPECT(sw.counters().forwarded == 1 && sw.counters().flooded == 1);
+  // A message of two packets on slots 12 and 13: the first says "more follow" and leaves the
+  // exponent register alone whatever its header holds; the last carries the exponents.
+  sw.SetDropProbabilities(0, 0);
+  out.clear();
+  for (int w = 0; w < 3; w++) {
+    auto more = MakePacket(w, 12, 24, 99, {1, 2, 3, 4}, 42);
+    more[offsetof(WireHeader, type)] = WIRE_DATA_MORE;
+    sw.Process(more.data(), more.size(), &out);
+  }
+  EXPECT(out.size() == 3 && PayloadAt(out[0], 3) == 12);
+  if (out.size() == 3) EXPECT(static_cast<int8_t>(out[0].bytes[offsetof(WireHeader, exponent)]) == -128);
+  out.clear();
+  send(0, 13, 25, 3, {1, 1, 1, 1});
+  send(1, 13, 25, 9, {1, 1, 1, 1});
+  send(2, 13, 25, 5, {1, 1, 1, 1});
+  EXPECT(out.size() == 3);
+  if (out.size() == 3) EXPECT(static_cast<int8_t>(out[0].bytes[offsetof(WireHeader, exponent)]) == 9);
   // Single worker: every packet completes its slot at once.
   sw.SetDropProbabilities(0, 0);
   sw.Reset(1, 1, 4);

@@ -53,6 +53,9 @@ struct UdpBackendConfig {
   uint32_t switch_pipes = 0;                // data-plane threads of the in-process switch on ports switch_port, +1, ...;
                                             // 0 = one per worker thread, at most 8
   std::string cores = "";                   // e.g. "0-3" or "0,2,4,6": pin worker thread t to the t-th core
+  uint32_t msg_numel = 0;                   // elements of a message: several packets that share one slot of the
+                                            // window, one timer and ONE exponent (carried by the message's last
+                                            // packet); 0 = one packet per message (= packet_numel)
 };
 
 struct CudaBackendConfig {

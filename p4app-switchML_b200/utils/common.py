@@ -29,6 +29,7 @@ class WireType(IntEnum):
     ECHO_REQUEST = 3    # anyone -> switch
     ECHO_REPLY = 4      # switch -> the sender
     FORWARD = 5         # worker -> worker(s) through the switch
+    DATA_MORE = 6       # worker -> switch: a packet of a message whose last packet (DATA) carries the exponent
 
 
 class WorkerType(IntEnum):

@@ -18,7 +18,7 @@ def rank_data(rank, numel, dtype="float32", seed=0):
 
 
 def udp_worker(rank, n, ctl_port, udp_port, numel, dtype, threads, packet_numel, drop, q, jobs=2,
-               timeout_ms=10.0):
+               timeout_ms=10.0, msg_numel=0):
     """One SwitchML worker over the software switch; reports its result through `q`."""
     try:
         import numpy as np
@@ -27,7 +27,7 @@ def udp_worker(rank, n, ctl_port, udp_port, numel, dtype, threads, packet_numel,
         cfg = sml.make_config("udp", rank=rank, num_workers=n, packet_numel=packet_numel,
                               num_worker_threads=threads, max_outstanding_packets=32 * threads,
                               controller_port=ctl_port, switch_port=udp_port, worker_port=0,
-                              timeout=timeout_ms)
+                              timeout=timeout_ms, msg_numel=msg_numel)
         assert ctx.start(cfg), "start failed"
         if drop and rank == 0:
             # the operator CLI path: tell the switch to lose packets both ways

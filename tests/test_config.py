@@ -93,3 +93,20 @@ def test_api_reference_is_up_to_date():
     script = os.path.join(root, "p4app-switchML_b200", "docs", "make_api_reference.py")
     r = subprocess.run([sys.executable, script, "--check"], capture_output=True, text=True)
     assert r.returncode == 0, r.stdout + r.stderr
+
+
+def test_udp_message_size_is_validated_and_rounded():
+    """[backend.udp] msg_numel follows the rules of the reference's backend.rdma.msg_numel
+    (client_lib/src/config.cc:185-211): not below a packet, rounded down to whole packets, and
+    max_outstanding_packets moved to the nearest whole number of messages per worker thread."""
+    from switchml_b200.utils.config import make_config, check_config
+    base = dict(packet_numel=64, num_worker_threads=2, max_outstanding_packets=64)
+    assert "msg_numel = 64" in check_config(make_config("udp", **base))          # default: one packet
+    dump = check_config(make_config("udp", msg_numel=300, **base))
+    assert "msg_numel = 256" in dump and "max_outstanding_packets = 64" in dump  # 4 packets, 8 messages a thread
+    dump = check_config(make_config("udp", msg_numel=192, **base))               # 3 packets: 64 is not a multiple of 6
+    assert "max_outstanding_packets = 66" in dump
+    with pytest.raises(Exception):
+        check_config(make_config("udp", msg_numel=32, **base))
+    with pytest.raises(Exception):
+        check_config(make_config("udp", msg_numel=64 * 65, **base))

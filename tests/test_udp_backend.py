@@ -13,11 +13,12 @@ from _workers import udp_worker, rank_data
 from switchml_b200.ops.oracle import quant_allreduce_oracle
 
 
-def _run(n, ports, numel, dtype="float32", threads=1, packet_numel=64, drop=0.0, jobs=2):
+def _run(n, ports, numel, dtype="float32", threads=1, packet_numel=64, drop=0.0, jobs=2, msg_numel=0):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     procs = [ctx.Process(target=udp_worker,
-                         args=(r, n, ports[0], ports[1], numel, dtype, threads, packet_numel, drop, q, jobs))
+                         args=(r, n, ports[0], ports[1], numel, dtype, threads, packet_numel, drop, q, jobs, 10.0,
+                               msg_numel))
              for r in range(n)]
     for p in procs:
         p.start()
@@ -55,6 +56,47 @@ def test_three_workers_four_threads_float64_check(ports):
     for r in range(3):
         assert np.max(np.abs(res[r][0][0] - exact)) < 1e-5
     assert np.array_equal(res[0][0][0], res[1][0][0]) and np.array_equal(res[1][0][0], res[2][0][0])
+
+
+def _oracle_per_thread_slice(inputs, threads, block):
+    """Worker threads take contiguous slices (numel / threads, the first numel % threads one
+    longer, reference schedulers/fifo_scheduler.cc:92-109) and cut THEIR slice into blocks."""
+    numel = inputs[0].size
+    base, rem = divmod(numel, threads)
+    out, lo = [], 0
+    for t in range(threads):
+        hi = lo + base + (1 if t < rem else 0)
+        out.append(quant_allreduce_oracle([x[lo:hi] for x in inputs], block_numel=block))
+        lo = hi
+    return np.concatenate(out)
+
+
+def test_messages_of_several_packets_share_one_exponent(ports):
+    """[backend.udp] msg_numel = 4 packets: the window, the timers and the exponent work per
+    message (the reference's backend.rdma.msg_numel), so the result equals the oracle with a
+    quantisation block of msg_numel elements, and the switch counts one message per four packets."""
+    numel = 40000 + 13
+    res = _run(2, ports, numel, threads=2, packet_numel=64, msg_numel=256, jobs=2)
+    for j in range(2):
+        inputs = [rank_data(r, numel, seed=j) for r in range(2)]
+        want = _oracle_per_thread_slice(inputs, 2, 256)
+        for r in range(2):
+            assert np.array_equal(res[r][0][j], want), "rank %d job %d" % (r, j)
+    rows = [l.split() for l in res[0][1]["switch_tables"]["qp"].splitlines()[1:]]
+    assert rows and all(int(r[2]) == 4 * int(r[3]) for r in rows if int(r[3]) > 100), rows  # rx_pkts = 4 x rx_msgs
+    sent = sum(res[0][1]["total_pkts_sent"])
+    assert sent % 4 == 0 and sent >= 4 * 2 * (numel // 256), "statistics count packets, four per message"
+
+
+def test_message_loss_is_recovered_packet_by_packet(ports):
+    numel = 1 << 15
+    res = _run(3, ports, numel, threads=2, packet_numel=64, msg_numel=512, drop=0.02, jobs=2)
+    for j in range(2):
+        inputs = [rank_data(r, numel, seed=j) for r in range(3)]
+        want = _oracle_per_thread_slice(inputs, 2, 512)
+        for r in range(3):
+            assert np.array_equal(res[r][0][j], want), "rank %d job %d" % (r, j)
+    assert sum(sum(res[r][1]["timeouts"]) for r in range(3)) > 0
 
 
 def test_int32_exact(ports):
