@@ -6,12 +6,14 @@
 For float32 and int32 tensors of 2^10 .. 2^28 elements (values U(-1,1) seeded per rank),
 SUM, 10 warm-up + 100 timed iterations, it reports ATE/s (= numel / time per job) and
 bus GB/s (= bytes/time * 2(n-1)/n) for
-    nccl            torch.distributed.all_reduce on the NCCL backend
-    sml-float       this library, float_sum mode, ordinary device tensors (staged)
-    sml-float-symm  same, tensors in the symmetric heap (zero-copy, in place)
-    sml-quant       this library, int32_quant mode (exact, order independent)
+    nccl            torch.distributed.all_reduce on the NCCL backend, float32, in place
+    nccl-int32      the same on int32 tensors
+    sml-float       this library, float_sum mode, ordinary device tensors
+    sml-float-symm  same, tensors in the symmetric heap (reduced where they lie)
+    sml-quant       this library, int32_quant mode (exact, order independent), float32 tensors
     sml-int32       int32 tensors
-All times are CUDA-event times on the launching stream, maximum over ranks.
+All times are CUDA-event times on the launching stream, maximum over ranks. `--markdown FILE`
+writes the table (microseconds per allreduce, and this library's time relative to NCCL's).
 """
 import argparse
 import json
@@ -47,6 +49,34 @@ def timed(fn, iters, warmup, world):
     return ms
 
 
+def markdown_table(results, world, iters, warmup):
+    """Microseconds per allreduce by size and implementation; in brackets NCCL's time divided by
+    this library's (above 1 = faster than NCCL), against NCCL on the same element type."""
+    impls = []
+    for r in results:
+        if r["impl"] not in impls:
+            impls.append(r["impl"])
+    by = {(r["impl"], r["numel"]): r for r in results}
+    sizes = sorted({r["numel"] for r in results})
+    lines = ["%d GPUs, SUM, %d warm-up + %d timed iterations (a quarter of that above 2^26), device time, slowest rank"
+             % (world, warmup, iters), "", "| elements | " + " | ".join(impls) + " |", "|---|" + "---|" * len(impls)]
+    for n in sizes:
+        cells = []
+        for impl in impls:
+            r = by.get((impl, n))
+            if r is None:
+                cells.append("")
+                continue
+            base = by.get(("nccl-int32" if r["dtype"] == "int32" else "nccl", n))
+            ratio = "" if base is None or impl.startswith("nccl") else " (%.2fx)" % (base["us"] / r["us"])
+            cells.append("%.1f%s" % (r["us"], ratio))
+        lines.append("| 2^%d | " % (n.bit_length() - 1) + " | ".join(cells) + " |")
+    big = [by.get((impl, sizes[-1])) for impl in impls]
+    lines += ["", "Largest size: " + ", ".join("%s %.3g ATE/s, bus %.0f GB/s" % (r["impl"], r["ate_per_s"], r["bus_gbs"])
+                                               for r in big if r)]
+    return "\n".join(lines) + "\n"
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--min-log2", type=int, default=10)
@@ -54,7 +84,8 @@ def main():
     ap.add_argument("--step-log2", type=int, default=2)
     ap.add_argument("--iters", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--impls", default="nccl,sml-float,sml-float-symm,sml-quant,sml-int32")
+    ap.add_argument("--impls", default="nccl,nccl-int32,sml-float,sml-float-symm,sml-quant,sml-int32")
+    ap.add_argument("--markdown", default="", help="write the results as a markdown table to this file")
     ap.add_argument("--transport", default="auto")
     ap.add_argument("--channels", type=int, default=0)
     ap.add_argument("--slot-bytes", type=int, default=0, help="0 = library default")
@@ -88,7 +119,7 @@ def main():
                 opts["channels"] = a.channels
             assert ctx.start(sml.make_config("cuda", rank=rank, num_workers=world, **opts))
         for numel in sizes:
-            dtype = torch.int32 if impl == "sml-int32" else torch.float32
+            dtype = torch.int32 if impl.endswith("int32") else torch.float32
             g = torch.Generator(device="cuda").manual_seed(99 + rank)
             if impl == "sml-float-symm":
                 ctx.symmetric_reset()
@@ -102,20 +133,16 @@ def main():
             else:
                 x.copy_(torch.rand(numel, generator=g, device="cuda") * 2 - 1)
             jobs = []
-            if impl == "nccl":
+            if not is_sml:
+                y.copy_(x)
+
                 def fn():
-                    y.copy_(x)            # keep values bounded: reduce a fresh copy each time
-                    dist.all_reduce(y)
-                def copy_only():
-                    y.copy_(x)
+                    dist.all_reduce(y)    # in place, like the reference's benchmark script
             else:
                 def fn():
                     jobs.append(ctx.all_reduce_async(x, y))
-                copy_only = None
             iters = a.iters if numel <= (1 << 26) else max(20, a.iters // 4)
             ms = timed(fn, iters, a.warmup, world)
-            if copy_only is not None and world > 1:
-                ms -= timed(copy_only, iters, a.warmup, world)  # charge NCCL only for the collective
             for j in jobs:
                 assert j.wait() == 3, j.error()
                 j.release()
@@ -133,6 +160,9 @@ def main():
         with open(a.out, "w") as f:
             for r in results:
                 f.write(json.dumps(r) + "\n")
+    if rank == 0 and a.markdown:
+        with open(a.markdown, "w") as f:
+            f.write(markdown_table(results, world, a.iters, a.warmup))
     if world > 1:
         dist.destroy_process_group()
 

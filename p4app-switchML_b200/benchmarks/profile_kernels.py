@@ -43,6 +43,8 @@ def main():
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--ranks", type=int, default=4)
     ap.add_argument("--log2-numel", type=int, default=24)
+    ap.add_argument("--algo", default="staged", choices=["staged", "push"],
+                    help="streamed aggregation: whole tiles through the slots, or shards pushed to their owners")
     a = ap.parse_args()
     if a.kernel == "local_copy":
         import switchml_b200 as sml
@@ -70,10 +72,10 @@ def main():
             xs = [torch.rand(numel, device="cuda") * 2 - 1 for _ in range(a.ranks)]
         outs = [torch.empty_like(x) for x in xs]
         mode = "quant" if a.kernel == "allreduce_quant" else "sum"
-        ms = timed(lambda: emulated_allreduce(xs, mode=mode, block_numel=256, slot_bytes=262144,
+        ms = timed(lambda: emulated_allreduce(xs, mode=mode, algo=a.algo, block_numel=256, slot_bytes=262144,
                                               slots_per_channel=4, outputs=outs), a.iters)
         # includes allocation of the staging regions; the kernel itself is what ncu captures
-        print("%s: %d ranks x %d elements, %.3f ms per call (with staging setup)" % (a.kernel, a.ranks, numel, ms))
+        print("%s (%s): %d ranks x %d elements, %.3f ms per call (with staging setup)" % (a.kernel, a.algo, a.ranks, numel, ms))
     else:
         from switchml_b200.ops.wgrad import wgrad_gemm
         K, M, N = (32, 4096, 25088) if a.kernel == "wgrad_fc6" else (8192, 4096, 1024)

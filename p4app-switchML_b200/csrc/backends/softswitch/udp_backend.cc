@@ -49,6 +49,7 @@ class UdpTransport : public SlotTransport {
 
   void BeginSlice(const JobSlice& js, uint64_t, int batch) override {
     job_tag_ = static_cast<uint8_t>(js.job->id_ & 0xff);
+    foreign_tags_ = 0;
     batch_ = batch;
     timers_.reset(new TimeoutQueue(batch, cfg_.general_.timeout, cfg_.general_.timeout_threshold,
                                    cfg_.general_.timeout_threshold_increment));
@@ -130,8 +131,22 @@ class UdpTransport : public SlotTransport {
       const int index = static_cast<int>(pool_index & ~kSetBit) - tid_ * window_ * pkts_per_msg_;
       const int phys = index >= 0 ? index / pkts_per_msg_ : -1, j = index >= 0 ? index % pkts_per_msg_ : 0;
       bool ok = ntohl(h.magic) == kWireMagic && (h.type == WIRE_RESULT || h.type == WIRE_RESULT_RETX) &&
-                n == sizeof(h) + numel * 4u && numel == packet_numel_ && phys >= 0 && phys < window_ &&
-                h.job_tag == job_tag_;
+                n == sizeof(h) + numel * 4u && numel == packet_numel_ && phys >= 0 && phys < window_;
+      if (ok && h.job_tag != job_tag_) {
+        // The switch stamps a result with the tag of the first packet that reached the slot, so
+        // the workers' job counters must agree. A result that fits in every other respect but
+        // carries another tag, again and again, means they do not (one worker submitted a job
+        // that the others never saw): say so instead of retransmitting in silence.
+        int ss = (phys - shift_ % window_ + window_) % window_;
+        if (ss < static_cast<int>(slots.size()) && !answered(ss) &&
+            slots[ss].pkt_id * static_cast<uint32_t>(pkts_per_msg_) + static_cast<uint32_t>(j) == ntohl(h.pkt_id) &&
+            ++foreign_tags_ == 16) {
+          SML_LOG(ERROR) << "worker thread " << tid_ << ": results for the packets of job tag " << int(job_tag_)
+                         << " keep arriving with tag " << int(h.job_tag)
+                         << ": the workers have not submitted the same sequence of jobs";
+        }
+        ok = false;
+      }
       int s = -1;
       if (ok) {
         s = (phys - shift_ % window_ + window_) % window_;
@@ -181,6 +196,7 @@ class UdpTransport : public SlotTransport {
   int batch_ = 0;
   int shift_ = 0;
   uint8_t job_tag_ = 0;
+  uint64_t foreign_tags_ = 0;  // results that matched a waiting packet in everything but the job tag
   std::vector<uint8_t> set_bits_;
   std::vector<uint8_t> answered_;
   std::vector<uint64_t> missing_;  // per slot: packets of the current message without a result yet

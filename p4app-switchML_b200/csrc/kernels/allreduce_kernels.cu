@@ -181,6 +181,7 @@ static const int kDefaultLoadWarps = 4, kDefaultReduceWarps = 8;  // the rest of
 struct StagedShared {
   int failed;
   volatile unsigned long long stored;  // tiles copied out so far
+  unsigned long long done[3];          // tiles that loader / reducer / storer have finished: the signaler warp tells the peers
   BulkRing ring[2];                    // TMA copy rings of the loader [0] and the storer [1]
   WarpStreamBarriers ws;               // mbarriers of the quantising loader's per-warp streams
   char* ring_buffers;                  // dynamic shared memory (nullptr: the job's tensors rule the TMA paths out):
@@ -234,6 +235,46 @@ __device__ __forceinline__ bool RoleWait(const RankCtx& ctx, const Role& role, i
   }
   role.Sync();
   return *reinterpret_cast<volatile int*>(&sh->failed) == 0;
+}
+
+// A role has finished tile number `tiles_done` (counted from 1): its data is where the peers
+// will read it. Telling them takes a system-scope fence, which on a busy link waits tens of
+// microseconds for the role's posted stores to be acknowledged; the role does not wait for
+// that itself but leaves a note in shared memory for the signaler warp and goes on with the
+// next tile. All threads of the role call this.
+__device__ __forceinline__ void RoleDone(const Role& role, StagedShared* sh, int which, unsigned long long tiles_done) {
+  role.Sync();
+  if (role.tid == 0)
+    asm volatile("st.release.cta.shared::cta.u64 [%0], %1;" ::"r"(BulkSmemAddr(&sh->done[which])), "l"(tiles_done) : "memory");
+}
+
+// The signaler warp: turns the roles' notes into flag stores. For every role whose count has
+// grown it fences at system scope (everything the role wrote before its note, which this warp
+// acquired, is ordered before the flag) and stores the epoch of the newest finished tile into
+// the role's phase on every rank; waits are ">=", so the newest epoch answers for all. Ends
+// when every signalling role has finished `ntiles` tiles or the CTA failed.
+__device__ __forceinline__ void RunSignaler(const RankCtx& ctx, StagedShared* sh, int channel, Epoch base,
+                                            unsigned long long ntiles, int nroles) {
+  const int lane = threadIdx.x & 31;
+  unsigned long long told[3] = {0, 0, 0};
+  volatile int* failed = reinterpret_cast<volatile int*>(&sh->failed);
+  for (;;) {
+    bool all = true;
+#pragma unroll
+    for (int r = 0; r < 3; r++) {
+      if (r >= nroles) continue;
+      unsigned long long d;
+      asm volatile("ld.acquire.cta.shared::cta.u64 %0, [%1];" : "=l"(d) : "r"(BulkSmemAddr(&sh->done[r])) : "memory");
+      if (d > told[r]) {
+        __threadfence_system();
+        if (lane < ctx.nranks) StoreReleaseSys(FlagPtr(ctx.stage_peer[lane], channel, r + 1, ctx.rank), base + d);
+        told[r] = d;
+      }
+      if (told[r] < ntiles) all = false;
+    }
+    if (all || *failed) return;
+    __nanosleep(40);
+  }
 }
 
 // Byte-wise identical copy by the threads of one role.
@@ -303,7 +344,8 @@ template <int ELEM, int MODE, int kLoadWarps = kDefaultLoadWarps, int kReduceWar
           int kUnrollLink = kDefaultUnrollLink>
 __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
                           unsigned long long elems_per_channel, Epoch base, StagedShared* sh, float* s_sf) {
-  constexpr int kStoreWarps = kThreads / 32 - kLoadWarps - kReduceWarps;
+  constexpr int kStoreWarps = kThreads / 32 - kLoadWarps - kReduceWarps - 1;  // the last warp tells the peers
+  static_assert(kStoreWarps >= 1, "the storer needs a warp");
   constexpr int kUnrollInt = 4 * kUnrollLink;  // 4-byte integer lanes in flight per thread
   const int in_esz = ELEM == ELEM_BF16 ? 2 : 4;
   const int st_esz = MODE == MODE_QUANT ? 4 : in_esz;
@@ -321,9 +363,13 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
   char* my_stage = ctx.stage_peer[ctx.rank];
   const size_t blocks_per_slot = ctx.slot_bytes / 4 / ctx.block_numel;
   const int shift = 31 - __clz(ctx.block_numel);  // block_numel is a power of two
-  // With two or more slots the exponents of tile k+1 travel while tile k is quantised, so the
-  // agreement never costs a wait of its own; a single slot leaves no room to run ahead.
-  const bool ahead = S >= 2;
+  // The exponents of tile k+A travel while tile k is quantised (A = 2 with four or more slots,
+  // 1 with two or three), so the agreement never costs a wait of its own and, with A = 2, the
+  // loaders of different ranks do not march in lockstep either: what tile k needs was signalled
+  // two tiles ago. A single slot leaves no room to run ahead. The words of tile k+A belong to
+  // the slot of tile k+A-S, which every rank consumed before it signalled that tile's payload
+  // (phase 1); the loader has awaited phase 1 of tile k-A by then, and S >= 2A.
+  const unsigned long long A = S >= 4 ? 2 : (S >= 2 ? 1 : 0);
   // The output lies in symmetric memory: the owner of a shard broadcasts the finished values
   // straight into every rank's output and nothing is copied out of the slot.
   const bool direct_out = job.out_zero_copy != 0;
@@ -335,8 +381,11 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
     which = 0; role.tid = threadIdx.x; role.nthreads = kLoadWarps * 32; role.bar_id = 1;
   } else if (warp < kLoadWarps + kReduceWarps) {
     which = 1; role.tid = threadIdx.x - kLoadWarps * 32; role.nthreads = kReduceWarps * 32; role.bar_id = 2;
-  } else {
+  } else if (warp < kLoadWarps + kReduceWarps + kStoreWarps) {
     which = 2; role.tid = threadIdx.x - (kLoadWarps + kReduceWarps) * 32; role.nthreads = kStoreWarps * 32; role.bar_id = 3;
+  } else {
+    RunSignaler(ctx, sh, channel, base, ntiles, 2);  // loader (phase 1) and reducer (phase 2)
+    return;
   }
   volatile int* failed = reinterpret_cast<volatile int*>(&sh->failed);
   // Channel 0 keeps a coarse time budget of its roles (ns waiting for others / ns doing
@@ -415,18 +464,20 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
         if (*failed) return;
       }
       if (MODE == MODE_QUANT) {
-        if (k == 0 || !ahead) {
-          // Nobody has published this tile's exponents yet: do it now and meet (phase 0).
-          // With a single slot its words are free by now: every rank consumed them before
-          // it signalled the payload of the tile before, and the copy-out awaited above
-          // came after all those signals.
-          const bool published = publish(in, len, exp_off, epoch);
+        if (k == 0 || A == 0) {
+          // Nobody has published the exponents of this tile (of the first A tiles, at the start
+          // of a job) yet: do it now and meet (phase 0). With a single slot its words are free
+          // by now: every rank consumed them before it signalled the payload of the tile
+          // before, and the copy-out awaited above came after all those signals.
+          bool published = publish(in, len, exp_off, epoch);
+          for (unsigned long long t = 1; published && t < A && t < ntiles; t++)
+            published = publish(in + t * tile_elems * in_esz, tile_len(t), exp_offset_of(t), epoch + t);
           RoleSignal(ctx, role, channel, 0, epoch);
           const bool met = RoleWait(ctx, role, channel, 0, epoch, sh);  // every warp takes part, whatever happened
           if (!published || !met) return;
-        } else {
-          // They came with the payload signal of the tile before.
-          if (!RoleWait(ctx, role, channel, 1, epoch - 1, sh)) return;
+        } else if (k >= A) {
+          // They came with the payload signal of tile k-A.
+          if (!RoleWait(ctx, role, channel, 1, epoch - A, sh)) return;
         }
       }
       lap(3);
@@ -447,11 +498,9 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
         }
         QuantizeRange<ELEM, 8>(role.tid, role.nthreads, in, q + done, done, len, sf, shift);
         lap(10);
-        // Exponents of the next tile, one tile ahead of its data. Its words belong to the
-        // slot of tile k+1-S, which every rank consumed before it signalled that tile's
-        // payload, and all those signals were awaited above (k+1-S <= k-1).
-        if (streamed && ahead && k + 1 < ntiles)
-          streamed = publish(in + tile_elems * in_esz, tile_len(k + 1), exp_offset_of(k + 1), epoch + 1);
+        // Exponents of tile k+A, ahead of its data.
+        if (streamed && A > 0 && k + A < ntiles)
+          streamed = publish(in + A * tile_elems * in_esz, tile_len(k + A), exp_offset_of(k + A), epoch + A);
         if (!streamed) {
           role.Sync();  // the other warps are on their way to the signal's barrier: meet them, then leave together
           return;
@@ -460,7 +509,7 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
       } else {
         RoleLocalCopy(ctx, role, sh, 0, my_stage + slot_off, in, len * in_esz, in_esz);
       }
-      RoleSignal(ctx, role, channel, 1, epoch);
+      RoleDone(role, sh, 0, k + 1);
       if (*failed) return;
       lap(4);
     } else if (which == 1) {
@@ -588,7 +637,7 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
           BroadcastVec(ctx, ctx.stage_peer, ctx.stage_mc, slot_off + v * 16, r);
         }
       }
-      RoleSignal(ctx, role, channel, 2, epoch);
+      RoleDone(role, sh, 1, k + 1);
       lap(6);
     } else {
       // ------------------------------ storer ------------------------------
@@ -868,6 +917,7 @@ __device__ __forceinline__ void RunJob(const RankCtx& ctx, const JobArgs& job, i
   if (threadIdx.x == 0) {                                                 \
     s_state.failed = 0;                                                   \
     s_state.stored = 0;                                                   \
+    s_state.done[0] = s_state.done[1] = s_state.done[2] = 0;              \
     s_state.ring_buffers = nullptr;                                       \
     if (((ALGO) == ALGO_STAGED || (ALGO) == ALGO_PUSH) && (JOB).bulk_copy) { \
       BulkRingInit(&s_state.ring[0]);                                     \

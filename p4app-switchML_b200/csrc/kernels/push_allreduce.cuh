@@ -22,10 +22,10 @@
 //     done with tile k - S: phase 2 >= e(k - S) from everybody;
 //   * a reducer may overwrite a peer's result area once that peer's storer is done with
 //     tile k - S: phase 3 >= e(k - S) from everybody;
-//   * MODE_QUANT: the exponent words of tile k+1 (slot (k+1) % S) are published while tile k
-//     is pushed; their previous user is tile k+1-S, consumed by every loader before its
-//     phase-1 signal and by every reducer before its phase-2 signal of that tile, so the
-//     loader awaits phase 2 >= e(k + 1 - S) instead of e(k - S).
+//   * MODE_QUANT: the exponent words of tile k+A (slot (k+A) % S; A = 2 with four or more
+//     slots, else 1, none with a single slot) are published while tile k is pushed; their
+//     previous user is tile k+A-S, consumed by every loader before its phase-1 signal of that
+//     tile; the publishing loader has awaited phase 1 >= e(k - A) by then, and S >= 2A.
 // Between jobs nothing extra is needed: a rank's kernel ends after its storer has seen
 // every peer's phase 2 for every tile (their reducers are done with all receive areas), and
 // a result is pushed only after the peer's loader of the new job has signalled, i.e. after
@@ -193,7 +193,8 @@ __device__ void RunPush(const RankCtx& ctx, const JobArgs& job, int channel,
                         unsigned long long elems_per_channel, Epoch base, StagedShared* sh, float* s_sf) {
   constexpr int kLoadWarps = MODE == MODE_QUANT ? 6 : 5;
   constexpr int kReduceWarps = MODE == MODE_QUANT ? 7 : 7;
-  constexpr int kStoreWarps = kThreads / 32 - kLoadWarps - kReduceWarps;
+  constexpr int kStoreWarps = kThreads / 32 - kLoadWarps - kReduceWarps - 1;  // the last warp tells the peers
+  static_assert(kStoreWarps >= 1, "the storer needs a warp");
   const int in_esz = ELEM == ELEM_BF16 ? 2 : 4;
   const int st_esz = MODE == MODE_QUANT ? 4 : in_esz;   // what travels on the reduce leg
   const int res_esz = MODE == MODE_QUANT ? 4 : in_esz;  // what travels on the result leg
@@ -212,7 +213,7 @@ __device__ void RunPush(const RankCtx& ctx, const JobArgs& job, int channel,
   char* my_stage = ctx.stage_peer[me];
   const size_t blocks_per_slot = ctx.slot_bytes / 4 / ctx.block_numel;
   const int shift = 31 - __clz(ctx.block_numel);
-  const bool ahead = S >= 2;
+  const unsigned long long A = S >= 4 ? 2 : (S >= 2 ? 1 : 0);  // exponents travel A tiles ahead of the data (see RunStaged)
   const bool direct_out = job.out_zero_copy != 0;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -222,8 +223,12 @@ __device__ void RunPush(const RankCtx& ctx, const JobArgs& job, int channel,
     which = 0; role.tid = threadIdx.x; role.nthreads = kLoadWarps * 32; role.bar_id = 1;
   } else if (warp < kLoadWarps + kReduceWarps) {
     which = 1; role.tid = threadIdx.x - kLoadWarps * 32; role.nthreads = kReduceWarps * 32; role.bar_id = 2;
-  } else {
+  } else if (warp < kLoadWarps + kReduceWarps + kStoreWarps) {
     which = 2; role.tid = threadIdx.x - (kLoadWarps + kReduceWarps) * 32; role.nthreads = kStoreWarps * 32; role.bar_id = 3;
+  } else {
+    // loader (phase 1), reducer (phase 2) and, unless results go straight into the outputs, storer (phase 3)
+    RunSignaler(ctx, sh, channel, base, ntiles, direct_out ? 2 : 3);
+    return;
   }
   volatile int* failed = reinterpret_cast<volatile int*>(&sh->failed);
   const bool timed = channel == 0 && role.tid == 0;
@@ -286,18 +291,19 @@ __device__ void RunPush(const RankCtx& ctx, const JobArgs& job, int channel,
     if (which == 0) {
       // ------------------------------ loader ------------------------------
       // Room in the peers' slots (see the flow-control notes above).
-      const unsigned long long need = MODE == MODE_QUANT && ahead ? k + 1 : k;
-      if (need >= static_cast<unsigned long long>(S)) {
-        if (!RoleWait(ctx, role, channel, 2, base + (need - S) + 1, sh)) return;
+      if (k >= static_cast<unsigned long long>(S)) {
+        if (!RoleWait(ctx, role, channel, 2, epoch - S, sh)) return;
       }
       if (MODE == MODE_QUANT) {
-        if (k == 0 || !ahead) {
-          const bool published = publish(in, len, exp_off, epoch);
+        if (k == 0 || A == 0) {
+          bool published = publish(in, len, exp_off, epoch);
+          for (unsigned long long t = 1; published && t < A && t < ntiles; t++)
+            published = publish(in + t * tile_elems * in_esz, tile_len(t), exp_offset_of(t), epoch + t);
           RoleSignal(ctx, role, channel, 0, epoch);
           const bool met = RoleWait(ctx, role, channel, 0, epoch, sh);  // every warp takes part, whatever happened
           if (!published || !met) return;
-        } else {
-          if (!RoleWait(ctx, role, channel, 1, epoch - 1, sh)) return;
+        } else if (k >= A) {
+          if (!RoleWait(ctx, role, channel, 1, epoch - A, sh)) return;
         }
       }
       lap(3);
@@ -355,14 +361,14 @@ __device__ void RunPush(const RankCtx& ctx, const JobArgs& job, int channel,
         }
       }
       lap(10);
-      if (MODE == MODE_QUANT && streamed && ahead && k + 1 < ntiles)
-        streamed = publish(in + tile_elems * in_esz, tile_len(k + 1), exp_offset_of(k + 1), epoch + 1);
+      if (MODE == MODE_QUANT && streamed && A > 0 && k + A < ntiles)
+        streamed = publish(in + A * tile_elems * in_esz, tile_len(k + A), exp_offset_of(k + A), epoch + A);
       if (!streamed) {
         role.Sync();  // the other warps are on their way to the signal's barrier: meet them, then leave together
         return;
       }
       lap(11);
-      RoleSignal(ctx, role, channel, 1, epoch);
+      RoleDone(role, sh, 0, k + 1);
       if (*failed) return;
       lap(4);
     } else if (which == 1) {
@@ -452,7 +458,7 @@ __device__ void RunPush(const RankCtx& ctx, const JobArgs& job, int channel,
           }
         }
       }
-      RoleSignal(ctx, role, channel, 2, epoch);
+      RoleDone(role, sh, 1, k + 1);
       lap(6);
     } else {
       // ------------------------------ storer ------------------------------
@@ -474,7 +480,7 @@ __device__ void RunPush(const RankCtx& ctx, const JobArgs& job, int channel,
             RoleLocalCopy(ctx, role, sh, 1, out, src, (se - sb) * in_esz, in_esz);
           }
         }
-        RoleSignal(ctx, role, channel, 3, epoch);  // my result areas of this slot may be refilled
+        RoleDone(role, sh, 2, k + 1);  // my result areas of this slot may be refilled
         if (*failed) return;
       }
       if (role.tid == 0) {

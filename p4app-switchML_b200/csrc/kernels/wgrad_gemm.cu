@@ -51,7 +51,7 @@ constexpr int kEpiBytes = kTileM * kEpiCols * 4;  // 16 KiB
 constexpr int kEpiBufs = 2;
 constexpr int kTmemCols = 512;
 constexpr int kThreads = 384;  // 12 warps; warps 8-11 idle unless the reduce is fused
-constexpr uint32_t kSpinLimit = 1u << 28;  // try_wait polls before a wait gives up
+constexpr unsigned long long kMbarBudgetNs = 2000000000ull;  // an mbarrier wait gives up after two seconds
 
 struct __align__(1024) SharedStorage {
   uint8_t stage[kStages][kStageBytes];
@@ -81,10 +81,12 @@ __device__ __forceinline__ void MbarExpectTx(uint64_t* bar, uint32_t bytes) {
                : "memory");
 }
 
-// Bounded wait for the phase with the given parity. False = gave up or aborted.
+// Bounded wait for the phase with the given parity: the budget is time on %globaltimer, not a
+// number of polls. False = gave up or aborted.
 __device__ __forceinline__ bool MbarWait(uint64_t* bar, uint32_t parity, volatile int* abort) {
   uint32_t addr = SmemAddr(bar);
-  for (uint32_t i = 0; i < kSpinLimit; i++) {
+  unsigned long long start = 0;
+  for (uint32_t i = 0;; i++) {
     uint32_t done;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -92,7 +94,13 @@ __device__ __forceinline__ bool MbarWait(uint64_t* bar, uint32_t parity, volatil
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(done) : "r"(addr), "r"(parity) : "memory");
     if (done) return true;
-    if ((i & 1023) == 1023 && *abort) return false;
+    if ((i & 1023) == 1023) {
+      if (*abort) return false;
+      unsigned long long now;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+      if (start == 0) start = now;
+      else if (now - start > kMbarBudgetNs) break;
+    }
   }
   *abort = 1;
   return false;
@@ -205,27 +213,31 @@ __device__ __forceinline__ bool WaitFlags(const unsigned long long* flags, int n
 }
 
 // Cross-GPU reduction of the tiles this rank owns (tile index mod nranks == rank), shared
-// by all warps of all CTAs through one work counter: an item is a quarter tile (32 rows).
+// by all warps of all CTAs through one work counter: an item is `rows_per_item` rows of a tile
+// (a power of two between 2 and 32, chosen by the host so that every warp of the grid gets a
+// few items: a small output is then spread over all SMs instead of a handful of warps that
+// each walk thousands of vectors one switch round trip at a time).
 // Called by whole warps. Items are handed out in tile order, the order in which the GEMM
 // produces them, so a warp rarely waits long for the flags of its item.
 __device__ __forceinline__ bool ReduceWork(const WgradFusedArgs& fused, int M, int N, int tiles_n,
-                                           int num_tiles, volatile int* abort) {
+                                           int num_tiles, int rows_per_item, volatile int* abort) {
   const int lane = threadIdx.x & 31;
   const int owned = (num_tiles - fused.rank + fused.nranks - 1) / fused.nranks;
-  const int items = owned * 4;
+  const int per_tile = kTileM / rows_per_item;
+  const int items = owned * per_tile;
   char* mc = fused.out_mc;
   for (;;) {
     int item = 0;
     if (lane == 0) item = atomicAdd(fused.work_counter, 1);
     item = __shfl_sync(0xffffffffu, item, 0);
     if (item >= items) return true;
-    const long long tile = static_cast<long long>(item >> 2) * fused.nranks + fused.rank;
+    const long long tile = static_cast<long long>(item / per_tile) * fused.nranks + fused.rank;
     if (!WaitFlags(fused.flags_peer[fused.rank] + static_cast<size_t>(tile) * 8, fused.nranks, fused.epoch,
                    fused.timeout_ns, abort))
       return false;
-    const int m0 = static_cast<int>(tile / tiles_n) * kTileM + (item & 3) * 32;
+    const int m0 = static_cast<int>(tile / tiles_n) * kTileM + (item % per_tile) * rows_per_item;
     const int n0 = static_cast<int>(tile % tiles_n) * kTileN;
-    const int rows = min(32, M - m0), cols = min(kTileN, N - n0);
+    const int rows = min(rows_per_item, M - m0), cols = min(kTileN, N - n0);
     if (rows <= 0) continue;
     const int vec_per_row = cols / 4;  // N is a multiple of 8: rows are whole float4s
     const int total = rows * vec_per_row;
@@ -256,7 +268,7 @@ __device__ __forceinline__ bool ReduceWork(const WgradFusedArgs& fused, int M, i
 template <bool kFused>
 __global__ void __launch_bounds__(kThreads, 1)
 WgradGemmKernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                const __grid_constant__ CUtensorMap map_d, int M, int N, int K, WgradFusedArgs fused,
+                const __grid_constant__ CUtensorMap map_d, int M, int N, int K, WgradFusedArgs fused, int rows_per_item,
                 int* error_flag) {
   extern __shared__ uint8_t smem_raw[];
   SharedStorage& sh = *reinterpret_cast<SharedStorage*>(
@@ -399,7 +411,7 @@ WgradGemmKernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     // Every warp that has nothing (more) to do for the GEMM helps with the cross-GPU
     // reduction: warps 8-11 and 3 from the start, the others when their role is finished.
     __syncwarp();
-    ReduceWork(fused, M, N, tiles_n, num_tiles, &sh.abort);
+    ReduceWork(fused, M, N, tiles_n, num_tiles, rows_per_item, &sh.abort);
   }
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -688,7 +700,14 @@ extern "C" int switchml_wgrad_gemm(const void* dy, const void* x, float* dw, int
       cudaFuncSetAttribute(WgradGemmKernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
       attr_f = true;
     }
-    WgradGemmKernel<true><<<grid, kThreads, smem, stream>>>(map_a, map_b, map_d, M, N, K, *fused, error_flag);
+    // One CTA on every SM even when there are fewer tiles: the others only reduce. Work items
+    // of the reduction: a few per warp of the grid, between 2 and 32 rows of a tile each.
+    grid = sms;
+    const long long owned_rows = static_cast<long long>((tiles + fused->nranks - 1) / fused->nranks) * kTileM;
+    const long long warps = static_cast<long long>(grid) * (kThreads / 32);
+    int rows_per_item = 32;
+    while (rows_per_item > 2 && owned_rows / rows_per_item < 2 * warps) rows_per_item >>= 1;
+    WgradGemmKernel<true><<<grid, kThreads, smem, stream>>>(map_a, map_b, map_d, M, N, K, *fused, rows_per_item, error_flag);
     e = cudaGetLastError();
   } else {
     static bool attr_p = false;
@@ -696,7 +715,7 @@ extern "C" int switchml_wgrad_gemm(const void* dy, const void* x, float* dw, int
       cudaFuncSetAttribute(WgradGemmKernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
       attr_p = true;
     }
-    WgradGemmKernel<false><<<grid, kThreads, smem, stream>>>(map_a, map_b, map_d, M, N, K, none, error_flag);
+    WgradGemmKernel<false><<<grid, kThreads, smem, stream>>>(map_a, map_b, map_d, M, N, K, none, 32, error_flag);
     e = cudaGetLastError();
   }
   return e == cudaSuccess ? 0 : -4;

@@ -43,6 +43,30 @@ def test_single_rank_roundtrip(ctx, launch, mode):
     # (float_sum with one worker is a plain copy kernel, or nothing at all in place)
 
 
+def test_inline_jobs_on_unordered_streams_do_not_overlap(ctx):
+    """launch = inline enqueues every job on its caller's stream, but all jobs of a context share
+    the staging slots, the flags and the per-channel epochs: a job submitted on another stream
+    than its predecessor must be ordered after it by the backend itself. Many quantised jobs on
+    two streams that nothing else orders, each checked against the oracle."""
+    assert ctx.start(sml.make_config("cuda", packet_numel=256, mode="int32_quant", launch="inline"))
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    numel = (1 << 21) + 77
+    xs = [torch.randn(numel, device="cuda") * (3.0 ** i) for i in range(6)]
+    ys = [torch.empty_like(x) for x in xs]
+    torch.cuda.synchronize()
+    jobs = []
+    for rounds in range(3):
+        for i, (x, y) in enumerate(zip(xs, ys)):
+            jobs.append(ctx.all_reduce_async(x, y, stream=streams[i % 2]))
+    for j in jobs:
+        assert j.wait() == sml.JobStatus.FINISHED, j.error()
+    torch.cuda.synchronize()
+    for x, y in zip(xs, ys):
+        want = quant_allreduce_oracle([x.cpu().numpy()], 256)
+        assert np.array_equal(y.cpu().numpy(), want)
+    assert ctx.get_stats()["jobs_failed"] == 0
+
+
 def test_stream_ordering_without_host_sync(ctx):
     assert ctx.start(sml.make_config("cuda", packet_numel=256, mode="float_sum", launch="worker"))
     side = torch.cuda.Stream()

@@ -139,7 +139,7 @@ def _random_quant_cases(worker_counts, cases, seed):
         algo = ("staged", "push", "staged", "oneshot", "push")[case % 5]
         numel = int(rng.integers(1, 40000 if algo == "oneshot" else 400000))
         slot_bytes = int(rng.choice([8, 16, 64])) * 4 * block
-        slots = int(rng.choice([1, 2, 2, 3]))
+        slots = int(rng.choice([1, 2, 3, 4, 5]))
         channels = int(rng.choice([0, 1, 3, 7]))
         xs = []
         for r in range(n):
