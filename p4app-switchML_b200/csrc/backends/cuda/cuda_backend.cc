@@ -160,6 +160,7 @@ class CudaBackend : public CudaBackendInterface {
   unsigned long long epoch_base_ = 0;
   int oneshot_parity_ = 0;
   unsigned long long launched_jobs_ = 0;
+  uint64_t oneshot_limit_ = 0;  // messages up to this many bytes take the one-barrier kernel
   unsigned long long kernel_launches_ = 0;  // kernels of this library enqueued so far (under launch_mu_)
 
   std::shared_ptr<EventPool> events_ = std::make_shared<EventPool>();
@@ -228,7 +229,11 @@ void CudaBackend::SetupWorker() {
   ctx_.slots_per_channel = c.slots_per_channel;
   ctx_.block_numel = static_cast<int>(g.packet_numel);
   ctx_.quant_base = quant::QuantBase(n_);
-  ctx_.oneshot_bytes = (c.oneshot_max_bytes + 255) / 256 * 256;
+  // The one-barrier kernel sends every rank's whole message to every rank, n-1 times the
+  // traffic of the streaming algorithms: the fewer the ranks, the longer it stays the faster
+  // one. The configured limit is the one for eight workers.
+  oneshot_limit_ = c.oneshot_max_bytes * 8 / static_cast<uint64_t>(n_ < 2 ? 2 : n_);
+  ctx_.oneshot_bytes = (oneshot_limit_ + 255) / 256 * 256;
   ctx_.timeout_ns = static_cast<unsigned long long>(c.wait_timeout_ms * 1e6);
   size_t bytes = kernels::StagingBytes(ctx_.slot_bytes, ctx_.slots_per_channel, ctx_.block_numel,
                                        max_channels_, ctx_.oneshot_bytes, n_, &ctx_.data_offset,
@@ -436,11 +441,13 @@ void CudaBackend::LaunchJob(const std::shared_ptr<Job>& job, cudaStream_t stream
   // Peer-memory transport moves large messages with posted stores only, unless told otherwise.
   const bool push = n_ > 1 && !ctx_.use_multimem && c.p2p_algo == "push" &&
                     kernels::PushTileCapacity(ctx_, a.elem_type, a.mode) > 0;
-  if (bytes <= c.oneshot_max_bytes && !(a.mode == kernels::MODE_SUM && heap_ok)) {
+  // (Tensors of the symmetric heap are reduced where they lie when the switch can do it;
+  // over plain peer memory small ones are quicker through the one-barrier kernel.)
+  if (bytes <= oneshot_limit_ && !(a.mode == kernels::MODE_SUM && heap_ok && ctx_.use_multimem)) {
     a.algo = kernels::ALGO_ONESHOT;
     a.oneshot_parity = oneshot_parity_;
     if (!capturing) oneshot_parity_ ^= 1;
-  } else if (push && bytes > c.oneshot_max_bytes) {
+  } else if (push) {
     a.algo = kernels::ALGO_PUSH;
     if (out_in_heap) {  // results go straight into every rank's output
       a.out_zero_copy = 1;

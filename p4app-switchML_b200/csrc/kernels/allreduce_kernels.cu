@@ -709,8 +709,17 @@ __device__ void RunOneShot(const RankCtx& ctx, const JobArgs& job, int channel,
     char* mc = ctx.stage_mc + off;
     char* out = static_cast<char*>(job.out) + c0 * esz;
     if (ELEM == ELEM_I32) {
-      for (size_t i = threadIdx.x; i < len; i += blockDim.x)
-        reinterpret_cast<int*>(out)[i] = MultimemLdReduceAddS32(mc + i * 4);
+      // one 32-bit lane per instruction: keep eight of them in flight per thread
+      constexpr int kInts = 8;
+      size_t i = threadIdx.x;
+      for (; i + (kInts - 1) * blockDim.x < len; i += kInts * blockDim.x) {
+        int v[kInts];
+#pragma unroll
+        for (int u = 0; u < kInts; u++) v[u] = MultimemLdReduceAddS32(mc + (i + u * blockDim.x) * 4);
+#pragma unroll
+        for (int u = 0; u < kInts; u++) reinterpret_cast<int*>(out)[i + u * blockDim.x] = v[u];
+      }
+      for (; i < len; i += blockDim.x) reinterpret_cast<int*>(out)[i] = MultimemLdReduceAddS32(mc + i * 4);
     } else {
       const size_t vec_elems = 16 / esz;
       const size_t nfull = len / vec_elems;
@@ -800,7 +809,38 @@ __device__ void RunOneShot(const RankCtx& ctx, const JobArgs& job, int channel,
       }
     }
   } else {
-    for (size_t i = threadIdx.x; i < len; i += blockDim.x) {
+    // Whole 16-byte vectors first, four in flight per thread and source (the buffers are
+    // vector aligned; the output may not be), then what is left element by element.
+    size_t first = 0;
+    if (Aligned16(out)) {
+      const size_t vec_elems = 16 / esz, nvec = len / vec_elems;
+      constexpr int U = 4;
+      const size_t stride = blockDim.x;
+      size_t v = threadIdx.x;
+      for (; v + (U - 1) * stride < nvec; v += U * stride) {
+        VecAcc<ELEM> acc[U];
+#pragma unroll
+        for (int u = 0; u < U; u++) acc[u].Init(*reinterpret_cast<const uint4*>(mine + buf_off(0) + (v + u * stride) * 16));
+        for (int s = 1; s < ctx.nranks; s++) {
+          const char* src = mine + buf_off(s);
+          uint4 t[U];
+#pragma unroll
+          for (int u = 0; u < U; u++) t[u] = *reinterpret_cast<const uint4*>(src + (v + u * stride) * 16);
+#pragma unroll
+          for (int u = 0; u < U; u++) acc[u].Add(t[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < U; u++) *reinterpret_cast<uint4*>(out + (v + u * stride) * 16) = acc[u].Finish(job.post_scale);
+      }
+      for (; v < nvec; v += stride) {
+        VecAcc<ELEM> acc;
+        acc.Init(*reinterpret_cast<const uint4*>(mine + buf_off(0) + v * 16));
+        for (int s = 1; s < ctx.nranks; s++) acc.Add(*reinterpret_cast<const uint4*>(mine + buf_off(s) + v * 16));
+        *reinterpret_cast<uint4*>(out + v * 16) = acc.Finish(job.post_scale);
+      }
+      first = nvec * vec_elems;
+    }
+    for (size_t i = first + threadIdx.x; i < len; i += blockDim.x) {
       if (ELEM == ELEM_I32) {
         unsigned acc = 0;
         for (int s = 0; s < ctx.nranks; s++) acc += reinterpret_cast<const unsigned*>(mine + buf_off(s))[i];
@@ -1187,10 +1227,12 @@ LaunchPlan PlanLaunch(const RankCtx& ctx, const JobArgs& job, int requested_chan
     int ch = requested_channels > 0 ? requested_channels : max_channels;
     if (ch > max_channels) ch = max_channels;
     // Tile: a slot for big jobs; for smaller ones shrink it so that the job still spreads
-    // over all channels, but not below 16 Ki elements (barrier cost would dominate).
+    // over all channels and every channel has about four tiles to pipeline (loader, reducer
+    // and storer then work on different tiles at the same time), but not below 16 Ki elements
+    // (the cost of meeting the peers would dominate).
     unsigned long long unit = static_cast<unsigned long long>(ctx.nranks) *
                               (ctx.block_numel > 128 ? ctx.block_numel : 128);
-    unsigned long long tile = (numel + ch - 1) / ch;
+    unsigned long long tile = (numel + 4ull * ch - 1) / (4ull * ch);
     if (tile < 16384) tile = 16384;
     tile = (tile + unit - 1) / unit * unit;
     if (tile > slot_elems) tile = slot_elems;
@@ -1206,7 +1248,8 @@ LaunchPlan PlanLaunch(const RankCtx& ctx, const JobArgs& job, int requested_chan
     // Whole quantisation blocks per channel; a few CTAs are enough for small messages.
     unsigned long long unit = ctx.block_numel > 128 ? ctx.block_numel : 128;
     unsigned long long units = (numel + unit - 1) / unit;
-    int ch = requested_channels > 0 ? requested_channels : 64;
+    // A few CTAs are enough for small messages; from 256 Ki elements on every SM takes part.
+    int ch = requested_channels > 0 ? requested_channels : (numel >= (256u << 10) ? max_channels : 64);
     if (ch > max_channels) ch = max_channels;
     unsigned long long per = (units + ch - 1) / ch;
     unsigned long long min_per = (4096 + unit - 1) / unit;  // at least 4 Ki elements per CTA

@@ -65,7 +65,7 @@ struct CudaBackendConfig {
   uint32_t channels = 0;                  // CTAs per kernel; 0 = pick from message size
   uint64_t slot_bytes = 524288;           // staging bytes per slot per channel
   uint32_t slots_per_channel = 4;         // ring depth (the switch keeps 2 sets per slot; here the loader may run further ahead)
-  uint64_t oneshot_max_bytes = 1048576;   // messages up to this size take the one-barrier kernel
+  uint64_t oneshot_max_bytes = 4194304;   // messages up to this size take the one-barrier kernel
   uint64_t symm_heap_mb = 0;              // user symmetric heap for zero-copy tensors
   bool average = false;                   // fold 1/num_workers into the result
   std::string launch = "worker";          // worker: launcher thread pulls the FIFO; inline: caller launches
