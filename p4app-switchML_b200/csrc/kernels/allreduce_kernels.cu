@@ -3,17 +3,22 @@
 // ALGO_STAGED — the streaming pipeline. A job is cut into contiguous per-channel ranges
 // (the analogue of the reference scheduler's static per-thread slices,
 // schedulers/fifo_scheduler.cc:92-109); a channel (one CTA on every rank) walks its range
-// in tiles of one staging slot. Per tile:
-//   MODE_QUANT   A  block max-abs -> exponent, published to the peers          [barrier 0]
-//                   global exponent = max over ranks (multimem.ld_reduce.max.s32 through
-//                   the switch, or peer loads); quantise own tile into the slot [barrier 1]
+// in tiles of at most one staging slot. Per tile:
+//   MODE_QUANT   A  the block exponents were agreed one or two tiles earlier through tagged
+//                   atomic maxima (quant_tile.cuh); quantise own tile into the slot  [phase 1]
 //                B  owner of shard r: integer sum over ranks of its shard
 //                   (multimem.ld_reduce.add.s32 / peer loads), dequantise, broadcast
-//                   (multimem.st / peer stores) as float32                      [barrier 2]
+//                   (multimem.st / peer stores) into the slot, or into the outputs
+//                   themselves when they lie in symmetric memory                     [phase 2]
 //                C  copy the finished tile from the slot to the output
-//   MODE_SUM     copy-in [barrier 1], B with a float/int add, [barrier 2], copy-out.
-// The barrier after B is also the acknowledgement that lets the slot be reused, the role
-// of the "other set" bitmap clear in the switch (p4/bitmap_checker.p4:82-123).
+//   MODE_SUM     copy-in [phase 1], B with a float/int add, [phase 2], copy-out.
+// The signal after B is also the acknowledgement that lets the slot be reused, the role
+// of the "other set" bitmap clear in the switch (p4/bitmap_checker.p4:82-123). Whole-tile
+// copies go through the TMA unit (bulk_copy.cuh), the quantising loader reads through
+// per-warp TMA streams (warp_stream.cuh), and a signaler warp tells the peers so that no
+// role waits for its own system-scope fence.
+//
+// ALGO_PUSH — peer memory without multicast: see push_allreduce.cuh.
 //
 // ALGO_ONESHOT — for small messages: every rank pushes its input into a per-source buffer
 // on every rank (one multimem.st, or n peer stores), one barrier, then each rank reduces
@@ -170,13 +175,13 @@ __device__ __forceinline__ void ShardRange(size_t len, int nranks, int rank, siz
 // Warp-specialised streaming pipeline. The 16 warps of a channel split into three roles
 // that walk the channel's tiles independently, so that for different tiles the local
 // HBM copies and the NVLink phase run at the same time:
-//   loader  (warps 0-3)   copy-in (SUM) / exponents + quantise (QUANT)  -> signals phase 1
-//   reducer (warps 4-11)  waits phase 1, reduces + broadcasts its shard  -> signals phase 2
-//   storer  (warps 12-15) waits phase 2, copies the finished tile out    -> frees the slot
+//   loader   (warps 0-3; 0-5 when it quantises)  copy-in / quantise, exponents ahead -> phase 1
+//   reducer  (the next 8 warps)   waits phase 1, reduces + broadcasts its shard    -> phase 2
+//   storer   (all but the last of the rest)  waits phase 2, copies the tile out    -> frees the slot
+//   signaler (the last warp)      fences and stores the flags for loader and reducer
 // A role synchronises internally with its own named barrier; the loader may run ahead of
 // the storer by the number of slots of the channel.
-// Measured on 8 GPUs (1 GiB float32): 4/8/4 warps 2.51 ms, 6/6/4 2.62 ms, 3/10/3 2.76 ms.
-static const int kDefaultLoadWarps = 4, kDefaultReduceWarps = 8;  // the rest of the 16 warps store
+static const int kDefaultLoadWarps = 4, kDefaultReduceWarps = 8;  // of the 16 warps; one signals, the rest store
 
 struct StagedShared {
   int failed;
@@ -349,7 +354,8 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
   constexpr int kUnrollInt = 4 * kUnrollLink;  // 4-byte integer lanes in flight per thread
   const int in_esz = ELEM == ELEM_BF16 ? 2 : 4;
   const int st_esz = MODE == MODE_QUANT ? 4 : in_esz;
-  const size_t slot_elems = ctx.slot_bytes / st_esz;
+  const size_t slot_elems = ctx.slot_bytes / st_esz;  // what the checked build verifies tiles against
+  (void)slot_elems;
   const size_t vec_elems = 16 / st_esz;
   const size_t unit = MODE == MODE_QUANT ? static_cast<size_t>(ctx.block_numel) : 128;
   const int S = ctx.slots_per_channel;
