@@ -491,7 +491,12 @@ void CudaBackend::LaunchJob(const std::shared_ptr<Job>& job, cudaStream_t stream
            static_cast<unsigned long long>(t.numel), DataTypeName(user.data_type));
   SML_NVTX_PUSH(range);
   bool plain_copy = n_ == 1 && a.mode == kernels::MODE_SUM && a.post_scale == 1.0f && !nothing_to_do;
-  if (t.numel > 0 && plain_copy) e = kernels::LaunchLocalCopy(t.in_ptr, t.out_ptr, bytes, stream);
+  // One worker in the exact mode: one pass that rounds every value to its block's grid.
+  const bool local_quant = n_ == 1 && a.mode == kernels::MODE_QUANT && a.elem_type == kernels::ELEM_F32 && t.numel > 0 &&
+                           ((reinterpret_cast<uintptr_t>(t.in_ptr) | reinterpret_cast<uintptr_t>(t.out_ptr)) & 15) == 0;
+  if (local_quant)
+    e = kernels::LaunchLocalQuant(t.in_ptr, t.out_ptr, t.numel, ctx_.block_numel, ctx_.quant_base, a.post_scale, stream);
+  else if (t.numel > 0 && plain_copy) e = kernels::LaunchLocalCopy(t.in_ptr, t.out_ptr, bytes, stream);
   else if (t.numel > 0 && !nothing_to_do) e = kernels::LaunchAllReduce(job_ctx, a, plan, stream);
   if (t.numel > 0 && !nothing_to_do && e == cudaSuccess) kernel_launches_ += widened ? 3 : 1;
   SML_NVTX_POP();

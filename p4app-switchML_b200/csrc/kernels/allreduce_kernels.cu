@@ -1037,6 +1037,82 @@ __global__ void __launch_bounds__(kThreads) LocalCopyKernel(const char* in, char
   }
 }
 
+// The exact mode with a single worker: nothing to exchange, so the round trip through the
+// fixed-point grid (block maximum -> exponent -> int32 -> float32, exactly what one worker
+// contributes and receives) is one pass over the data: every warp takes chunks of 1024
+// elements, 8 float4 per lane, finds its blocks' maxima with shuffles and writes the result.
+// Bit-identical to the streaming kernels and to the CPU oracle.
+__global__ void __launch_bounds__(kThreads)
+LocalQuantKernel(const float* in, float* out, size_t numel, int block_numel, float quant_base, float post_scale) {
+  const int lane = threadIdx.x & 31;
+  const size_t warp = (static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const size_t nwarps = (static_cast<size_t>(gridDim.x) * blockDim.x) >> 5;
+  const size_t B = block_numel;
+  const size_t whole = numel / B * B;     // elements in blocks without a ragged end
+  const size_t nchunks = whole / 1024;    // 1024 is a multiple of every block size
+  const float4* in4 = reinterpret_cast<const float4*>(in);
+  float4* out4 = reinterpret_cast<float4*>(out);
+  for (size_t c = warp; c < nchunks; c += nwarps) {
+    float4 x[8];
+    float m[8];
+#pragma unroll
+    for (int u = 0; u < 8; u++) x[u] = in4[c * 256 + u * 32 + lane];
+#pragma unroll
+    for (int u = 0; u < 8; u++) m[u] = fmaxf(fmaxf(fabsf(x[u].x), fabsf(x[u].y)), fmaxf(fabsf(x[u].z), fabsf(x[u].w)));
+    if (B < 128) {
+      const int g = static_cast<int>(B / 4);  // lanes per block
+#pragma unroll
+      for (int u = 0; u < 8; u++)
+        for (int o = g >> 1; o > 0; o >>= 1) m[u] = fmaxf(m[u], __shfl_xor_sync(0xffffffffu, m[u], o));
+    } else {
+      const int rows = static_cast<int>(B / 128);  // rows of 128 elements per block: 1, 2, 4 or 8
+#pragma unroll
+      for (int span = 1; span < 8; span <<= 1) {
+        if (span < rows) {
+#pragma unroll
+          for (int u = 0; u + span < 8; u += 2 * span) m[u] = fmaxf(m[u], m[u + span]);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 8; u++) {
+        if ((u % rows) != 0) continue;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m[u] = fmaxf(m[u], __shfl_xor_sync(0xffffffffu, m[u], o));
+      }
+      // hand every block's maximum back to all of its rows
+#pragma unroll
+      for (int span = 4; span >= 1; span >>= 1) {
+        if (span < rows) {
+#pragma unroll
+          for (int u = 0; u + span < 8; u += 2 * span) m[u + span] = m[u];
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 8; u++) {
+      const float f = quant::ScaleFactorFromBase(quant::LocalExponent(m[u]), quant_base);
+      float4 y;
+      y.x = quant::Dequantize(quant::Quantize(x[u].x, f), f) * post_scale;
+      y.y = quant::Dequantize(quant::Quantize(x[u].y, f), f) * post_scale;
+      y.z = quant::Dequantize(quant::Quantize(x[u].z, f), f) * post_scale;
+      y.w = quant::Dequantize(quant::Quantize(x[u].w, f), f) * post_scale;
+      out4[c * 256 + u * 32 + lane] = y;
+    }
+  }
+  // What is left: fewer than 1024 elements of whole blocks and a ragged last block, one
+  // block per warp.
+  const size_t nblocks = (numel + B - 1) / B;
+  for (size_t b = nchunks * (1024 / B) + warp; b < nblocks; b += nwarps) {
+    const size_t base = b * B, n = numel - base < B ? numel - base : B;
+    float mx = 0.f;
+    for (size_t i = lane; i < n; i += 32) mx = fmaxf(mx, fabsf(in[base + i]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    const float f = quant::ScaleFactorFromBase(quant::LocalExponent(mx), quant_base);
+    for (size_t i = lane; i < n; i += 32) out[base + i] = quant::Dequantize(quant::Quantize(in[base + i], f), f) * post_scale;
+  }
+}
+
 // uint8 -> int32 (zero extended) and back (low byte kept, i.e. the sum modulo 256): uint8
 // tensors make the trip as int32. 16 elements per thread and step when the byte side is
 // 16-byte aligned (the int32 side is scratch memory and always is), else one by one.
@@ -1301,6 +1377,18 @@ cudaError_t LaunchLocalCopy(const void* in, void* out, size_t bytes, cudaStream_
   if (bytes == 0 || in == out) return cudaSuccess;
   int blocks = 148 * 4;
   LocalCopyKernel<<<blocks, kThreads, 0, stream>>>(static_cast<const char*>(in), static_cast<char*>(out), bytes);
+  return cudaGetLastError();
+}
+
+cudaError_t LaunchLocalQuant(const void* in, void* out, size_t numel, int block_numel, float quant_base,
+                             float post_scale, cudaStream_t stream) {
+  if (numel == 0) return cudaSuccess;
+  if ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15) return cudaErrorInvalidValue;
+  size_t want = (numel / 1024 + kThreads / 32 - 1) / (kThreads / 32);  // one chunk per warp and turn
+  if (want < 1) want = 1;
+  const int blocks = static_cast<int>(want < 148 * 4 ? want : 148 * 4);
+  LocalQuantKernel<<<blocks, kThreads, 0, stream>>>(static_cast<const float*>(in), static_cast<float*>(out), numel,
+                                                   block_numel, quant_base, post_scale);
   return cudaGetLastError();
 }
 

@@ -132,6 +132,10 @@ cudaError_t LaunchAllReduceEmulated(const RankCtx* ctxs_dev, const JobArgs* jobs
                                     cudaStream_t stream);
 // Single worker, plain sum, out of place: copy `bytes` bytes with one kernel.
 cudaError_t LaunchLocalCopy(const void* in, void* out, size_t bytes, cudaStream_t stream);
+// Single worker, exact mode, float32, both pointers 16-byte aligned: the quantise / dequantise round
+// trip in one pass (bit-identical to what the streaming kernels give one worker).
+cudaError_t LaunchLocalQuant(const void* in, void* out, size_t numel, int block_numel, float quant_base,
+                             float post_scale, cudaStream_t stream);
 // uint8 tensors travel as int32: zero-extend `numel` bytes into int32 scratch, and keep the
 // low byte of every int32 on the way back (the sum modulo 256).
 cudaError_t LaunchWidenU8(const void* in, void* out, size_t numel, cudaStream_t stream);

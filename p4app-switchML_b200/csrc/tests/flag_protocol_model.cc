@@ -29,6 +29,9 @@
 //     ones, writes its output and pushes the result into the result areas of its peers (phase
 //     2), after phase 3 >= e(k-S) from everybody; the storer copies the received results out
 //     (phase 3);
+//   * on the GPU a role leaves a note in shared memory and a signaler warp fences and stores the
+//     flags for it; the note is released and acquired at CTA scope, so for the ordering of
+//     memory it is as if the role signalled itself, which is what the model does;
 //   * each channel keeps the epoch it has reached in a word of its own and advances it when a
 //     job ends, so consecutive jobs need no host-side epoch bookkeeping.
 // The arithmetic is switchml/quant_math.h, so the result must equal the CPU oracle bit for bit.

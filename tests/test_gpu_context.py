@@ -39,8 +39,30 @@ def test_single_rank_roundtrip(ctx, launch, mode):
     st = ctx.get_stats()
     assert st["jobs_finished"] == 5 and st["jobs_failed"] == 0
     if mode == "int32_quant":
-        assert st["backend"]["tiles"] > 0   # a single worker still goes through the slot pipeline
+        assert st["backend"]["kernel_launches"] >= 4   # a single worker still runs a kernel per float job: the round trip
+                                                       # through the fixed-point grid changes the values
     # (float_sum with one worker is a plain copy kernel, or nothing at all in place)
+
+
+@pytest.mark.parametrize("block", [32, 64, 128, 512, 1024])
+def test_single_worker_exact_mode_is_one_pass_and_bit_exact(ctx, block):
+    """One worker in int32_quant mode takes the single-pass kernel (aligned float32) or the
+    streaming kernel (anything else); both must give the oracle's bits, in and out of place."""
+    assert ctx.start(sml.make_config("cuda", packet_numel=block, mode="int32_quant", launch="inline"))
+    g = torch.Generator(device="cuda").manual_seed(block)
+    numel = 21 * 1024 + 3 * block + 17
+    base = torch.randn(numel + 4, device="cuda", generator=g) * torch.logspace(-20, 20, numel + 4, device="cuda")
+    base[5 * block:7 * block] = 0.0
+    for x in (base[:numel], base[1:1 + numel]):            # 16-byte aligned, and 4-byte aligned only
+        want = quant_allreduce_oracle([x.cpu().numpy()], block)
+        y = torch.empty(numel + 4, device="cuda")[x.storage_offset():x.storage_offset() + numel]
+        job = ctx.all_reduce_async(x.contiguous() if x.storage_offset() == 0 else x, y)
+        assert job.wait() == sml.JobStatus.FINISHED, job.error()
+        assert np.array_equal(y.cpu().numpy().view(np.uint32), want.view(np.uint32)), (block, x.storage_offset())
+    z = base[:numel].clone()
+    want = quant_allreduce_oracle([z.cpu().numpy()], block)
+    ctx.all_reduce(z)
+    assert np.array_equal(z.cpu().numpy().view(np.uint32), want.view(np.uint32))
 
 
 def test_inline_jobs_on_unordered_streams_do_not_overlap(ctx):
