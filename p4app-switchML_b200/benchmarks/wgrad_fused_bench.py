@@ -9,6 +9,8 @@ GPU, 4096 x 1024). For each it reports
     gemm          the tcgen05 GEMM alone (no communication)
     gemm+reduce   GEMM, then the in-place zero-copy allreduce of dW (two kernels)
     fused         one kernel: tiles are reduced through the NVSwitch as they are produced
+    gather        (where the operands are small next to the gradient) the ranks exchange dY and
+                  X, every rank computes the tiles it owns over all of them and broadcasts them
     cublas+nccl   torch.mm (fp32 output) followed by NCCL all_reduce, the library baseline
 and the roofline of the fused kernel: the slower of FLOPs at the measured bf16 peak and
 dW bytes x (1 + 1/n) at 770 GB/s per direction. CUDA-event times, maximum over ranks.
@@ -48,6 +50,7 @@ def main():
     for name, K, M, N in shapes:
         ctx.symmetric_reset()
         fw = FusedWgrad(ctx, M, N, scale=1.0 / world, policy="fused")
+        fg = FusedWgrad(ctx, M, N, scale=1.0 / world, policy="gather") if K * (M + N) * 2 * world <= M * N * 4 else None
         dy = torch.randn(K, M, device="cuda", dtype=torch.bfloat16)
         x = torch.randn(K, N, device="cuda", dtype=torch.bfloat16)
         plain = torch.empty(M, N, device="cuda")
@@ -67,14 +70,16 @@ def main():
         t_two = time_cuda(gemm_then_reduce, 20, 3, world)
         t_fused = time_cuda(lambda: fw.run(dy, x), 20, 3, world)
         t_lib = time_cuda(cublas_nccl, 20, 3, world)
+        t_gather = time_cuda(lambda: fg.run(dy, x), 20, 3, world) if fg is not None and fg.fused else None
         torch.cuda.synchronize()
-        assert int(fw.error.item()) == 0
+        assert int(fw.error.item()) == 0 and (fg is None or int(fg.error.item()) == 0)
         flops = 2.0 * K * M * N
         link_bytes = M * N * 4 * (1 + 1.0 / world) if world > 1 else 0
         roof_ms = max(flops / (PEAK_TFLOPS * 1e12), link_bytes / (LINK_GBS * 1e9)) * 1e3
         if rank == 0:
             print(json.dumps({"shape": name, "K": K, "M": M, "N": N, "n_gpus": world, "fused_in_kernel": fw.fused,
                               "gemm_ms": t_gemm, "gemm_then_reduce_ms": t_two, "fused_ms": t_fused,
+                              "gather_ms": t_gather, "gather_roofline_ms": M * N * 4 / (LINK_GBS * 1e9) * 1e3,
                               "cublas_nccl_ms": t_lib, "roofline_ms": roof_ms,
                               "fused_fraction_of_roofline": roof_ms / t_fused}), flush=True)
     ctx.stop()

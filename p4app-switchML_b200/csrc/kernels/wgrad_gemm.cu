@@ -265,11 +265,92 @@ __device__ __forceinline__ bool ReduceWork(const WgradFusedArgs& fused, int M, i
   }
 }
 
-template <bool kFused>
+// Gather mode: the tiles this rank owns are complete sums already; hand them to every rank.
+// Same work items as ReduceWork; an item waits for this rank's own flag of the tile only.
+__device__ __forceinline__ bool BroadcastWork(const WgradFusedArgs& fused, const float* dw, int M, int N, int tiles_n,
+                                              int num_tiles, int rows_per_item, volatile int* abort) {
+  const int lane = threadIdx.x & 31;
+  const int owned = (num_tiles - fused.rank + fused.nranks - 1) / fused.nranks;
+  const int per_tile = kTileM / rows_per_item;
+  const int items = owned * per_tile;
+  char* mc = fused.out_mc;
+  const char* local = reinterpret_cast<const char*>(dw);
+  for (;;) {
+    int item = 0;
+    if (lane == 0) item = atomicAdd(fused.work_counter, 1);
+    item = __shfl_sync(0xffffffffu, item, 0);
+    if (item >= items) return true;
+    const long long tile = static_cast<long long>(item / per_tile) * fused.nranks + fused.rank;
+    if (!WaitFlags(fused.flags_peer[fused.rank] + static_cast<size_t>(tile) * 8 + fused.rank, 1, fused.epoch,
+                   fused.timeout_ns, abort))
+      return false;
+    const int m0 = static_cast<int>(tile / tiles_n) * kTileM + (item % per_tile) * rows_per_item;
+    const int n0 = static_cast<int>(tile % tiles_n) * kTileN;
+    const int rows = min(rows_per_item, M - m0), cols = min(kTileN, N - n0);
+    if (rows <= 0) continue;
+    const int vec_per_row = cols / 4;
+    const int total = rows * vec_per_row;
+    for (int idx = lane; idx < total; idx += 32 * 8) {
+      float4 v[8];
+      size_t off[8];
+#pragma unroll
+      for (int u = 0; u < 8; u++) {
+        int id = idx + u * 32;
+        if (id < total) {
+          int r = id / vec_per_row, cv = id % vec_per_row;
+          off[u] = (static_cast<size_t>(m0 + r) * N + n0 + cv * 4) * 4;
+          v[u] = __ldcg(reinterpret_cast<const float4*>(local + off[u]));
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 8; u++) {
+        int id = idx + u * 32;
+        if (id < total) {
+          if (fused.scale != 1.0f) { v[u].x *= fused.scale; v[u].y *= fused.scale; v[u].z *= fused.scale; v[u].w *= fused.scale; }
+          MultimemStoreF32x4(mc + off[u], v[u]);
+        }
+      }
+    }
+  }
+}
+
+// Gather mode, first step: this rank's dY (bytes_a) and X (bytes_b) into slab `rank` of the
+// gather buffer of every rank; the last CTA to finish tells the peers (flag entry `flag_entry`).
+__global__ void __launch_bounds__(512) WgradGatherKernel(const char* dy, const char* x, WgradFusedArgs fused,
+                                                         size_t bytes_a, size_t bytes_b, size_t flag_entry) {
+  const size_t tid = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const size_t nthreads = static_cast<size_t>(gridDim.x) * blockDim.x;
+  char* dst_a = fused.gather_mc + static_cast<size_t>(fused.rank) * bytes_a;
+  char* dst_b = fused.gather_mc + static_cast<size_t>(fused.nranks) * bytes_a + static_cast<size_t>(fused.rank) * bytes_b;
+  for (size_t v = tid; v < bytes_a / 16; v += nthreads) {
+    float4 w = *reinterpret_cast<const float4*>(dy + v * 16);
+    MultimemStoreF32x4(dst_a + v * 16, w);
+  }
+  for (size_t v = tid; v < bytes_b / 16; v += nthreads) {
+    float4 w = *reinterpret_cast<const float4*>(x + v * 16);
+    MultimemStoreF32x4(dst_b + v * 16, w);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    const int arrived = atomicAdd(fused.gather_counter, 1);
+    if (arrived == static_cast<int>(gridDim.x) - 1) {
+      *fused.gather_counter = 0;  // for the next call
+      __threadfence_system();
+      for (int p = 0; p < fused.nranks; p++)
+        StoreReleaseSys(fused.flags_peer[p] + flag_entry * 8 + fused.rank, fused.epoch);
+    }
+  }
+}
+
+// kMode 0: plain GEMM; 1: every finished tile is reduced across the ranks; 2: gather mode (owned tiles over the
+// gathered operands, broadcast).
+template <int kMode>
 __global__ void __launch_bounds__(kThreads, 1)
 WgradGemmKernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                const __grid_constant__ CUtensorMap map_d, int M, int N, int K, WgradFusedArgs fused, int rows_per_item,
-                int* error_flag) {
+                const __grid_constant__ CUtensorMap map_d, const float* dw, int M, int N, int K, WgradFusedArgs fused,
+                int rows_per_item, int* error_flag) {
+  constexpr bool kFused = kMode != 0;
   extern __shared__ uint8_t smem_raw[];
   SharedStorage& sh = *reinterpret_cast<SharedStorage*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -279,6 +360,9 @@ WgradGemmKernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   const int tiles_n = (N + kTileN - 1) / kTileN;
   const int num_tiles = tiles_m * tiles_n;
   const int k_blocks = (K + kTileK - 1) / kTileK;
+  // The tiles this CTA walks: all of them in turn, or (gather mode) those this rank owns.
+  const int my_tiles = kMode == 2 ? (num_tiles - fused.rank + fused.nranks - 1) / fused.nranks : num_tiles;
+  auto tile_of = [&](int t) { return kMode == 2 ? t * fused.nranks + fused.rank : t; };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; s++) {
@@ -304,9 +388,17 @@ WgradGemmKernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
-    if (lane == 0) {
+    bool operands_in = true;
+    if (kMode == 2) {
+      // every rank's slab of the operands must have landed in this rank's gather buffer
+      operands_in = WaitFlags(fused.flags_peer[fused.rank] + static_cast<size_t>(num_tiles + 148) * 8, fused.nranks, fused.epoch,
+                              fused.timeout_ns, &sh.abort);
+      asm volatile("fence.proxy.async.global;" ::: "memory");
+    }
+    if (lane == 0 && operands_in) {
       uint32_t it = 0;
-      for (int tile = blockIdx.x; tile < num_tiles && !sh.abort; tile += gridDim.x) {
+      for (int t = blockIdx.x; t < my_tiles && !sh.abort; t += gridDim.x) {
+        const int tile = tile_of(t);
         const int m0 = (tile / tiles_n) * kTileM, n0 = (tile % tiles_n) * kTileN;
         for (int kb = 0; kb < k_blocks; kb++, it++) {
           const int s = it % kStages;
@@ -327,7 +419,7 @@ WgradGemmKernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     // ------------------------------ MMA issuer ------------------------------
     if (lane == 0) {
       uint32_t it = 0, local_tile = 0;
-      for (int tile = blockIdx.x; tile < num_tiles && !sh.abort; tile += gridDim.x, local_tile++) {
+      for (int t = blockIdx.x; t < my_tiles && !sh.abort; t += gridDim.x, local_tile++) {
         const int acc = local_tile & 1;
         const uint32_t acc_phase = (local_tile >> 1) & 1;
         if (!MbarWait(&sh.acc_empty[acc], acc_phase ^ 1, &sh.abort)) break;
@@ -361,7 +453,8 @@ WgradGemmKernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const int row = q * 32 + lane;        // row of the tile held by this thread
     const int epi_tid = threadIdx.x - 128;
     uint32_t local_tile = 0, stores = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, local_tile++) {
+    for (int t = blockIdx.x; t < my_tiles; t += gridDim.x, local_tile++) {
+      const int tile = tile_of(t);
       const int m0 = (tile / tiles_n) * kTileM, n0 = (tile % tiles_n) * kTileN;
       const int acc = local_tile & 1;
       const uint32_t acc_phase = (local_tile >> 1) & 1;
@@ -399,8 +492,12 @@ WgradGemmKernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
           asm volatile("fence.proxy.async.global;" ::: "memory");
           __threadfence_system();
-          for (int p = 0; p < fused.nranks; p++)
-            StoreReleaseSys(fused.flags_peer[p] + static_cast<size_t>(tile) * 8 + fused.rank, fused.epoch);
+          if (kMode == 2) {  // only this rank's broadcasting warps wait for it
+            StoreReleaseSys(fused.flags_peer[fused.rank] + static_cast<size_t>(tile) * 8 + fused.rank, fused.epoch);
+          } else {
+            for (int p = 0; p < fused.nranks; p++)
+              StoreReleaseSys(fused.flags_peer[p] + static_cast<size_t>(tile) * 8 + fused.rank, fused.epoch);
+          }
         }
       }
     }
@@ -411,7 +508,8 @@ WgradGemmKernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     // Every warp that has nothing (more) to do for the GEMM helps with the cross-GPU
     // reduction: warps 8-11 and 3 from the start, the others when their role is finished.
     __syncwarp();
-    ReduceWork(fused, M, N, tiles_n, num_tiles, rows_per_item, &sh.abort);
+    if (kMode == 2) BroadcastWork(fused, dw, M, N, tiles_n, num_tiles, rows_per_item, &sh.abort);
+    else ReduceWork(fused, M, N, tiles_n, num_tiles, rows_per_item, &sh.abort);
   }
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -674,9 +772,17 @@ extern "C" int switchml_wgrad_gemm(const void* dy, const void* x, float* dw, int
   if ((M % 8) || (N % 8)) return -2;
   if ((reinterpret_cast<uintptr_t>(dy) | reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(dw)) & 15)
     return -2;
+  const bool gather = fused && fused->nranks > 1 && fused->mode == 1;
+  if (gather && (!fused->gather_local || !fused->gather_mc || !fused->gather_counter || !fused->out_mc || !fused->work_counter ||
+                 fused->nranks > 8))
+    return -1;
+  // Gather mode multiplies the gathered operands: nranks * K rows, read from this rank's gather buffer.
+  const int k_rows = gather ? fused->nranks * K : K;
+  const void* a_base = gather ? static_cast<const void*>(fused->gather_local) : dy;
+  const void* b_base = gather ? static_cast<const void*>(fused->gather_local + static_cast<size_t>(k_rows) * M * 2) : x;
   CUtensorMap map_a, map_b, map_d;
-  if (!MakeMap(&map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, dy, K, M, kTileK, kAtomMN) ||
-      !MakeMap(&map_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, x, K, N, kTileK, kAtomMN) ||
+  if (!MakeMap(&map_a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a_base, k_rows, M, kTileK, kAtomMN) ||
+      !MakeMap(&map_b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, b_base, k_rows, N, kTileK, kAtomMN) ||
       !MakeMap(&map_d, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, dw, M, N, kTileM, kEpiCols))
     return -3;
   int dev = 0;
@@ -684,6 +790,7 @@ extern "C" int switchml_wgrad_gemm(const void* dy, const void* x, float* dw, int
   if (dev >= 0 && dev < 64 && g_sm_count[dev] == 0)
     cudaDeviceGetAttribute(&g_sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
   int sms = (dev >= 0 && dev < 64 && g_sm_count[dev] > 0) ? g_sm_count[dev] : 148;
+  if (sms > 148) sms = 148;  // the flag array has room for 148 closing flags
   int tiles = ((M + kTileM - 1) / kTileM) * ((N + kTileN - 1) / kTileN);
   int grid = tiles < sms ? tiles : sms;
   size_t smem = sizeof(SharedStorage) + 1024;
@@ -697,25 +804,38 @@ extern "C" int switchml_wgrad_gemm(const void* dy, const void* x, float* dw, int
     // every rank and fully resident: one CTA per SM at most.
     static bool attr_f = false;
     if (!attr_f) {
-      cudaFuncSetAttribute(WgradGemmKernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+      cudaFuncSetAttribute(WgradGemmKernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+      cudaFuncSetAttribute(WgradGemmKernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
       attr_f = true;
     }
-    // One CTA on every SM even when there are fewer tiles: the others only reduce. Work items
-    // of the reduction: a few per warp of the grid, between 2 and 32 rows of a tile each.
+    // One CTA on every SM even when there are fewer tiles: the others only reduce (or broadcast).
+    // Work items of that: a few per warp of the grid, between 2 and 32 rows of a tile each.
     grid = sms;
     const long long owned_rows = static_cast<long long>((tiles + fused->nranks - 1) / fused->nranks) * kTileM;
     const long long warps = static_cast<long long>(grid) * (kThreads / 32);
     int rows_per_item = 32;
     while (rows_per_item > 2 && owned_rows / rows_per_item < 2 * warps) rows_per_item >>= 1;
-    WgradGemmKernel<true><<<grid, kThreads, smem, stream>>>(map_a, map_b, map_d, M, N, K, *fused, rows_per_item, error_flag);
+    if (gather) {
+      const size_t bytes_a = static_cast<size_t>(K) * M * 2, bytes_b = static_cast<size_t>(K) * N * 2;
+      size_t vecs = (bytes_a + bytes_b) / 16;
+      int gblocks = static_cast<int>((vecs + 511) / 512);
+      if (gblocks > sms) gblocks = sms;
+      if (gblocks < 1) gblocks = 1;
+      WgradGatherKernel<<<gblocks, 512, 0, stream>>>(static_cast<const char*>(dy), static_cast<const char*>(x), *fused,
+                                                    bytes_a, bytes_b, static_cast<size_t>(tiles) + 148);
+      if (cudaGetLastError() != cudaSuccess) return -4;
+      WgradGemmKernel<2><<<grid, kThreads, smem, stream>>>(map_a, map_b, map_d, dw, M, N, k_rows, *fused, rows_per_item, error_flag);
+    } else {
+      WgradGemmKernel<1><<<grid, kThreads, smem, stream>>>(map_a, map_b, map_d, dw, M, N, K, *fused, rows_per_item, error_flag);
+    }
     e = cudaGetLastError();
   } else {
     static bool attr_p = false;
     if (!attr_p) {
-      cudaFuncSetAttribute(WgradGemmKernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+      cudaFuncSetAttribute(WgradGemmKernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
       attr_p = true;
     }
-    WgradGemmKernel<false><<<grid, kThreads, smem, stream>>>(map_a, map_b, map_d, M, N, K, none, 32, error_flag);
+    WgradGemmKernel<0><<<grid, kThreads, smem, stream>>>(map_a, map_b, map_d, dw, M, N, K, none, 32, error_flag);
     e = cudaGetLastError();
   }
   return e == cudaSuccess ? 0 : -4;

@@ -41,6 +41,22 @@ typedef struct WgradFusedArgs {
   unsigned long long timeout_ns;
   float scale; /* multiplied into the reduced gradient (1/nranks for the mean) */
   int* work_counter; /* one int in this rank's device memory, zeroed (in stream order) before every fused call */
+  /* mode 0 (default): every rank multiplies its own operands and the switch adds the ranks' results.
+   * mode 1, "gather": the sum over ranks of dY_r^T X_r is ONE product over the concatenated K
+   * dimension. Every rank first copies its dY and X into slab `rank` of a gather buffer on all
+   * ranks (multimem.st; (nranks-1) * K * (M+N) * 2 bytes leave each GPU), then computes only the
+   * tiles it owns (tile index mod nranks == rank) over all nranks * K rows and broadcasts them
+   * (multimem.st) while the tensor cores go on. The link carries the gradient once instead of
+   * (1 + 1/n) times in each direction plus the switch's reduction: the better plan whenever
+   * the operands are small next to the gradient (VGG's fully connected layers: K = batch).
+   * `gather_local` / `gather_mc`: this rank's and the multicast address of a buffer of
+   * nranks * K * (M + N) bf16 in the symmetric region (same offset on every rank), laid out as
+   * [nranks * K, M] followed by [nranks * K, N]; `gather_counter`: one zero-initialised int in
+   * this rank's device memory (the kernel leaves it zero). */
+  int mode;
+  char* gather_local;
+  char* gather_mc;
+  int* gather_counter;
 } WgradFusedArgs;
 
 int switchml_wgrad_gemm(const void* dy, const void* x, float* dw, int M, int N, int K,

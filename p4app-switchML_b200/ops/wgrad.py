@@ -21,7 +21,9 @@ class _FusedArgs(ctypes.Structure):
     _fields_ = [("rank", ctypes.c_int), ("nranks", ctypes.c_int),
                 ("flags_peer", ctypes.c_void_p * 8), ("out_mc", ctypes.c_void_p),
                 ("epoch", ctypes.c_ulonglong), ("timeout_ns", ctypes.c_ulonglong),
-                ("scale", ctypes.c_float), ("work_counter", ctypes.c_void_p)]
+                ("scale", ctypes.c_float), ("work_counter", ctypes.c_void_p),
+                ("mode", ctypes.c_int), ("gather_local", ctypes.c_void_p), ("gather_mc", ctypes.c_void_p),
+                ("gather_counter", ctypes.c_void_p)]
 
 
 def _lib():
@@ -113,9 +115,18 @@ class FusedWgrad:
         self.counter = torch.zeros(1, dtype=torch.int32, device=self.grad.device)
         self.args.work_counter = self.counter.data_ptr()
         self.fused = self.nranks > 1 and bool(mc)
-        # "fused": always reduce inside the GEMM kernel; "split": GEMM, then the in-place
-        # zero-copy reduction; "auto": fused for short reductions (K < 256, e.g. VGG fc6/fc7),
-        # split for long ones, where the two-CTA GEMM plus a separate reduction measured faster.
+        self._symm = (local, mc)
+        self.gather_buf = None     # [nranks * K * (M + N)] bf16 in the symmetric heap, made on first use
+        self.gather_k = 0
+        self.gather_counter = torch.zeros(1, dtype=torch.int32, device=self.grad.device)
+        self.args.gather_counter = self.gather_counter.data_ptr()
+        # "gather": the ranks exchange their (small) operands, every rank computes the tiles it
+        # owns over all of them and broadcasts them: the gradient crosses the link once;
+        # "fused": every rank multiplies its own operands and finished tiles are reduced through
+        # the switch inside the GEMM kernel; "split": GEMM, then the in-place reduction as a
+        # second kernel; "auto": gather when the operands of all ranks are less than a quarter of
+        # the gradient (VGG's fully connected layers, K = batch), else split, which measured
+        # faster than the fused reduction for long K.
         self.policy = policy
         torch.cuda.synchronize()
 
@@ -136,7 +147,19 @@ class FusedWgrad:
             _PENDING.append(ev)
             return out
         K = dy.shape[0]
-        in_kernel = self.fused and (self.policy == "fused" or (self.policy == "auto" and K < 256))
+        operand_bytes = self.nranks * K * (self.M + self.N) * 2
+        gather = self.fused and (self.policy == "gather" or
+                                 (self.policy == "auto" and 4 * operand_bytes <= self.M * self.N * 4))
+        in_kernel = gather or (self.fused and self.policy == "fused")
+        if gather and (self.gather_buf is None or self.gather_k != K):
+            # every rank gets here with the same shapes in the same order, so the symmetric
+            # allocations stay in step
+            self.gather_buf = self.ctx.symmetric_empty(self.nranks * K * (self.M + self.N), torch.bfloat16)
+            self.gather_k = K
+            local, mc = self._symm
+            self.args.gather_local = self.gather_buf.data_ptr()
+            self.args.gather_mc = mc + (self.gather_buf.data_ptr() - local)
+        self.args.mode = 1 if gather else 0
         if in_kernel:
             self.args.epoch += 1
             self.counter.zero_()  # work queue of the in-kernel reduction starts at zero

@@ -139,8 +139,9 @@ def cuda_worker(rank, n, ctl_port, transport, mode, q, heap_mb=64, launch="inlin
         # tcgen05 weight-gradient GEMM with the cross-GPU reduce fused into the kernel
         if mode == "float_sum":
             from switchml_b200.ops.wgrad import FusedWgrad
-            for (K, M, N) in ((256, 384, 520), (64, 1024, 2048), (1024, 128, 256)):
-                fw = FusedWgrad(ctx, M, N, scale=1.0 / n, policy="fused" if M != 128 else "split")
+            for (K, M, N, policy) in ((256, 384, 520, "fused"), (64, 1024, 2048, "fused"), (1024, 128, 256, "split"),
+                                      (32, 1024, 2048, "gather"), (200, 384, 520, "gather"), (64, 2048, 4096, "auto")):
+                fw = FusedWgrad(ctx, M, N, scale=1.0 / n, policy=policy)
                 report["fused_in_kernel"] = fw.fused
                 for it in range(3):
                     g = torch.Generator(device="cuda").manual_seed(1000 * rank + it)
