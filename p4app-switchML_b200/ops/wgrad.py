@@ -154,11 +154,17 @@ class FusedWgrad:
         if gather and (self.gather_buf is None or self.gather_k != K):
             # every rank gets here with the same shapes in the same order, so the symmetric
             # allocations stay in step
-            self.gather_buf = self.ctx.symmetric_empty(self.nranks * K * (self.M + self.N), torch.bfloat16)
-            self.gather_k = K
-            local, mc = self._symm
-            self.args.gather_local = self.gather_buf.data_ptr()
-            self.args.gather_mc = mc + (self.gather_buf.data_ptr() - local)
+            try:
+                self.gather_buf = self.ctx.symmetric_empty(self.nranks * K * (self.M + self.N), torch.bfloat16)
+            except MemoryError:
+                # the heap is used up (it is never freed piecemeal); every rank sees the same heap,
+                # so every rank falls back to the two-kernel path for this shape
+                self.gather_buf, gather, in_kernel = None, False, self.fused and self.policy == "fused"
+            else:
+                self.gather_k = K
+                local, mc = self._symm
+                self.args.gather_local = self.gather_buf.data_ptr()
+                self.args.gather_mc = mc + (self.gather_buf.data_ptr() - local)
         self.args.mode = 1 if gather else 0
         if in_kernel:
             self.args.epoch += 1
