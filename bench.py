@@ -330,9 +330,9 @@ def bench_allreduce(args):
     quant = None
     if dtype == torch.float32 and args.quant_steps > 0:
         ctx = start_context("int32_quant", 0)
-        # bit-for-bit against the CPU oracle on a small odd-sized tensor with zero blocks
+        # bit-for-bit against the CPU oracle on an odd-sized tensor with zero blocks
         from switchml_b200.ops.oracle import quant_allreduce_oracle
-        small = (1 << 20) + 1
+        small = (1 << 22) + 1  # above the one-barrier kernel's limit at every worker count: the streaming path
         rng = [np.random.RandomState(77 + r) for r in range(world)]
         ins = [(r_.rand(small).astype(np.float32) * 2 - 1) * np.float32(10.0 ** (i - 2)) for i, r_ in enumerate(rng)]
         for a in ins:
