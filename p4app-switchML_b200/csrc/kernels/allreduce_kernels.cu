@@ -528,8 +528,11 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
       // Where finished values go: this tile's place in the slot, or in the output itself.
       char* const* dst_peer = direct_out ? job.user_peer : ctx.stage_peer;
       char* dst_mc = direct_out ? job.user_mc : ctx.stage_mc;
-      const size_t dst_off = direct_out ? job.out_offset + pos * in_esz : slot_off;
-      const bool narrow = MODE == MODE_QUANT && ELEM == ELEM_BF16 && direct_out;  // results leave as bf16
+      // bf16 jobs of the exact mode get their results as bf16: into the output itself, or into
+      // the second part of the slot, behind the int32 payload of a full tile.
+      const size_t narrow_area = job.tile_elems * 4;
+      const bool narrow = MODE == MODE_QUANT && ELEM == ELEM_BF16 && (direct_out || job.tile_elems * 6 <= ctx.slot_bytes);
+      const size_t dst_off = direct_out ? job.out_offset + pos * in_esz : (narrow ? slot_off + narrow_area : slot_off);
       // An empty shard (short last tile) must not touch anything: rounding its bounds to
       // whole vectors would make it overlap the last vector of the previous rank's shard.
       if (sb >= se) {
@@ -651,7 +654,9 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
       lap(7);
       if (!direct_out) {
         char* out = static_cast<char*>(job.out) + pos * in_esz;
-        if (MODE == MODE_QUANT && ELEM == ELEM_BF16) {
+        if (MODE == MODE_QUANT && ELEM == ELEM_BF16 && job.tile_elems * 6 <= ctx.slot_bytes) {
+          RoleLocalCopy(ctx, role, sh, 1, out, my_stage + slot_off + job.tile_elems * 4, len * 2, 2);  // bf16 results
+        } else if (MODE == MODE_QUANT && ELEM == ELEM_BF16) {
           const float* y = reinterpret_cast<const float*>(my_stage + slot_off);
           unsigned short* o = reinterpret_cast<unsigned short*>(out);
           for (size_t i = role.tid; i < len; i += role.nthreads) o[i] = FloatToBf16(y[i]);
@@ -1244,6 +1249,12 @@ bool DeviceMemory(const void* p) {
 }
 
 size_t SlotElems(const RankCtx& ctx, int elem_type, int mode) {
+  if (mode == MODE_QUANT && elem_type == ELEM_BF16) {
+    // int32 payload and, behind it, the bf16 results (they travel as bf16: half the return leg)
+    const size_t unit = static_cast<size_t>(ctx.nranks) * (ctx.block_numel > 128 ? ctx.block_numel : 128);
+    const size_t cap = ctx.slot_bytes / 6 / unit * unit;
+    return cap > 0 ? cap : unit;  // a slot of one unit (the configured minimum) keeps float32 results instead
+  }
   int st_esz = mode == MODE_QUANT ? 4 : (elem_type == ELEM_BF16 ? 2 : 4);
   return ctx.slot_bytes / st_esz;
 }
@@ -1252,9 +1263,10 @@ size_t PushTileCapacity(const RankCtx& ctx, int elem_type, int mode) {
   const size_t n = ctx.nranks;
   if (n < 2) return 0;
   const size_t in_esz = elem_type == ELEM_BF16 ? 2 : 4;
-  const size_t leg = mode == MODE_QUANT ? 4 : in_esz;  // bytes per element on either leg
+  const size_t leg_in = mode == MODE_QUANT ? 4 : in_esz;                                // reduce leg
+  const size_t leg_out = mode == MODE_QUANT ? (elem_type == ELEM_BF16 ? 2 : 4) : in_esz;  // result leg
   // (n-1) receive areas + (n-1) result areas of tile/n elements each
-  size_t cap = ctx.slot_bytes * n / (2 * (n - 1) * leg);
+  size_t cap = ctx.slot_bytes * n / ((n - 1) * (leg_in + leg_out));
   if (mode == MODE_QUANT) {
     const size_t by_words = ctx.slot_bytes / 4;  // one exponent word per block of the slot
     if (cap > by_words) cap = by_words;

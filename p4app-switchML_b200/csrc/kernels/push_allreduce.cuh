@@ -197,7 +197,7 @@ __device__ void RunPush(const RankCtx& ctx, const JobArgs& job, int channel,
   static_assert(kStoreWarps >= 1, "the storer needs a warp");
   const int in_esz = ELEM == ELEM_BF16 ? 2 : 4;
   const int st_esz = MODE == MODE_QUANT ? 4 : in_esz;   // what travels on the reduce leg
-  const int res_esz = MODE == MODE_QUANT ? 4 : in_esz;  // what travels on the result leg
+  const int res_esz = MODE == MODE_QUANT ? (ELEM == ELEM_BF16 ? 2 : 4) : in_esz;  // what travels on the result leg (bf16 jobs: bf16)
   const size_t unit = MODE == MODE_QUANT ? static_cast<size_t>(ctx.block_numel) : 128;
   const int S = ctx.slots_per_channel;
   const int n = ctx.nranks, me = ctx.rank;
@@ -395,7 +395,7 @@ __device__ void RunPush(const RankCtx& ctx, const JobArgs& job, int channel,
         const size_t t = role.tid, nt = role.nthreads;
         const uintptr_t both = reinterpret_cast<uintptr_t>(own) | reinterpret_cast<uintptr_t>(out);
         if (MODE == MODE_QUANT) {
-          const bool narrow = ELEM == ELEM_BF16 && direct_out;  // a bf16 output written where it lies
+          const bool narrow = ELEM == ELEM_BF16;  // bf16 jobs receive bf16: in their output, or in the result areas
           const size_t ngroups = (both & (ELEM == ELEM_BF16 ? 7 : 15)) == 0 ? cnt / 4 : 0;
           constexpr int U = 4;
           size_t g = t;
@@ -472,11 +472,7 @@ __device__ void RunPush(const RankCtx& ctx, const JobArgs& job, int channel,
           if (sb >= se) continue;
           const char* src = my_stage + result_off + static_cast<size_t>(PushAreaIndex(p, me)) * res_bytes;
           char* out = static_cast<char*>(job.out) + (pos + sb) * in_esz;
-          if (MODE == MODE_QUANT && ELEM == ELEM_BF16) {
-            const float* y = reinterpret_cast<const float*>(src);
-            unsigned short* o = reinterpret_cast<unsigned short*>(out);
-            for (size_t i = role.tid; i < se - sb; i += role.nthreads) o[i] = FloatToBf16(y[i]);
-          } else {
+          {
             RoleLocalCopy(ctx, role, sh, 1, out, src, (se - sb) * in_esz, in_esz);
           }
         }
