@@ -61,7 +61,7 @@ def _declare(l):
         "sml_oracle_int_allreduce": (None, [c.POINTER(vp), i32, u64, vp]),
         "sml_static_slice": (None, [u64, i32, i32, c.POINTER(u64), c.POINTER(u64)]),
         "sml_emu_allreduce": (i32, [i32, c.POINTER(vp), c.POINTER(vp), u64, i32, i32, i32, i32, u64,
-                                    i32, i32, c.c_float, i32]),
+                                    i32, i32, c.c_float, i32, i32]),
         "sml_convert_u8": (i32, [i32, vp, vp, u64, vp]),
         "sml_controller_start": (vp, [c.c_char_p, i32, i32]),
         "sml_controller_start_pipes": (vp, [c.c_char_p, i32, i32, i32]),

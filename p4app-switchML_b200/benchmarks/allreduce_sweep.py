@@ -89,6 +89,8 @@ def main():
     ap.add_argument("--transport", default="auto")
     ap.add_argument("--channels", type=int, default=0)
     ap.add_argument("--slot-bytes", type=int, default=0, help="0 = library default")
+    ap.add_argument("--exponent-lookahead", type=int, default=-1, help="-1 = library default")
+    ap.add_argument("--signal-fence", default="", help="sc | release; empty = library default")
     ap.add_argument("--out", default="")
     a = ap.parse_args()
 
@@ -117,6 +119,10 @@ def main():
                 opts["slot_bytes"] = a.slot_bytes
             if a.channels:
                 opts["channels"] = a.channels
+            if a.exponent_lookahead >= 0:
+                opts["exponent_lookahead"] = a.exponent_lookahead
+            if a.signal_fence:
+                opts["signal_fence"] = a.signal_fence
             assert ctx.start(sml.make_config("cuda", rank=rank, num_workers=world, **opts))
         for numel in sizes:
             dtype = torch.int32 if impl.endswith("int32") else torch.float32

@@ -147,6 +147,7 @@ class CudaBackend : public CudaBackendInterface {
   cudaStream_t comm_stream_ = nullptr;
   int* dev_status_ = nullptr;
   unsigned long long* dev_counters_ = nullptr;
+  unsigned long long* dev_trace_ = nullptr;  // kTraceWords, only with [backend.cuda] trace
   unsigned long long* dev_epochs_ = nullptr;  // per-channel epochs, advanced by the kernels themselves
   int* host_status_ = nullptr;  // pinned ring of status words
 
@@ -227,6 +228,9 @@ void CudaBackend::SetupWorker() {
   ctx_.nranks = n_;
   ctx_.slot_bytes = c.slot_bytes;
   ctx_.slots_per_channel = c.slots_per_channel;
+  ctx_.sc_fence = c.signal_fence == "sc" ? 1 : 0;
+  ctx_.exp_ring = kernels::ExpRingDepth(static_cast<int>(c.slots_per_channel));
+  ctx_.exp_lookahead = kernels::ExpLookahead(static_cast<int>(c.slots_per_channel), static_cast<int>(c.exponent_lookahead));
   ctx_.block_numel = static_cast<int>(g.packet_numel);
   ctx_.quant_base = quant::QuantBase(n_);
   // The one-barrier kernel sends every rank's whole message to every rank, n-1 times the
@@ -277,6 +281,11 @@ void CudaBackend::SetupWorker() {
   SML_CUDA_CHECK(cudaHostGetDevicePointer(reinterpret_cast<void**>(&dev_status_), host_status_, 0));
   ctx_.status = dev_status_;
   ctx_.counters = dev_counters_;
+  if (c.trace) {
+    SML_CUDA_CHECK(cudaMalloc(&dev_trace_, kernels::kTraceWords * sizeof(unsigned long long)));
+    SML_CUDA_CHECK(cudaMemset(dev_trace_, 0, kernels::kTraceWords * sizeof(unsigned long long)));
+  }
+  ctx_.trace = dev_trace_;
   ctx_.epoch_words = dev_epochs_;
   epoch_base_ = 0;
   oneshot_parity_ = 0;
@@ -320,11 +329,13 @@ void CudaBackend::CleanupWorker() {
   order_event_ = nullptr;
   order_valid_ = false;
   if (dev_counters_) cudaFree(dev_counters_);
+  if (dev_trace_) cudaFree(dev_trace_);
   if (dev_epochs_) cudaFree(dev_epochs_);
   dev_epochs_ = nullptr;
   if (host_status_) cudaFreeHost(host_status_);
   dev_status_ = nullptr;
   dev_counters_ = nullptr;
+  dev_trace_ = nullptr;
   host_status_ = nullptr;
   fds_.Close();
   client_.Close();
@@ -694,7 +705,27 @@ std::string CudaBackend::ExtraStatsJson() {
     << ",\"loader_scale_factors\":" << c[9] << ",\"loader_payload\":" << c[10] << ",\"loader_exponents_ahead\":" << c[11]
     << ",\"loader_signal\":" << c[4]
     << ",\"reducer_wait\":" << c[5] << ",\"reducer_work\":" << c[6] << ",\"storer_wait\":" << c[7]
-    << ",\"storer_work\":" << c[8] << "}}";
+    << ",\"storer_work\":" << c[8] << "}";
+  if (dev_trace_) {
+    // The last job's timeline on channel 0, in ns after the kernel's start: for each role, when its
+    // waits for a tile were over and when it had finished the tile (0 = the job had no such tile).
+    std::vector<unsigned long long> t(kernels::kTraceWords);
+    cudaMemcpy(t.data(), dev_trace_, t.size() * sizeof(t[0]), cudaMemcpyDeviceToHost);
+    const unsigned long long t0 = t[6 * kernels::kTraceTiles];
+    static const char* names[6] = {"loader_began", "loader_finished", "reducer_began", "reducer_finished",
+                                   "storer_began", "storer_finished"};
+    o << ",\"channel0_trace_ns\":{";
+    for (int row = 0; row < 6; row++) {
+      o << (row ? "," : "") << "\"" << names[row] << "\":[";
+      for (int k = 0; k < kernels::kTraceTiles; k++) {
+        unsigned long long v = t[row * kernels::kTraceTiles + k];
+        o << (k ? "," : "") << (v > t0 ? v - t0 : 0);
+      }
+      o << "]";
+    }
+    o << "}";
+  }
+  o << "}";
   return o.str();
 }
 
@@ -738,7 +769,7 @@ int ConvertU8OnDevice(bool widen, const void* in, void* out, unsigned long long 
 int EmulatedAllReduce(int nranks, void* const* in_ptrs, void* const* out_ptrs,
                       unsigned long long numel, int elem_type, int mode, int algo, int block_numel,
                       size_t slot_bytes, int slots_per_channel, int channels, float post_scale,
-                      int repeats, std::string* error) {
+                      int repeats, int exponent_lookahead, std::string* error) {
   using namespace kernels;
   auto fail = [&](const std::string& m, int code) {
     if (error) *error = m;
@@ -763,6 +794,9 @@ int EmulatedAllReduce(int nranks, void* const* in_ptrs, void* const* out_ptrs,
   proto.nranks = nranks;
   proto.slot_bytes = slot_bytes;
   proto.slots_per_channel = slots_per_channel;
+  proto.sc_fence = 0;
+  proto.exp_ring = ExpRingDepth(slots_per_channel);
+  proto.exp_lookahead = ExpLookahead(slots_per_channel, exponent_lookahead < 0 ? kDefaultExpLookahead : exponent_lookahead);
   proto.block_numel = block_numel;
   proto.quant_base = quant::QuantBase(nranks);
   proto.oneshot_bytes = oneshot_bytes;

@@ -49,11 +49,11 @@ Backend* CreateCudaBackend(Context& context, Config& config);
 
 // Stand-alone multi-rank emulation on one GPU (no Context needed): `nranks` virtual
 // ranks, all memory on the current device, one cooperative kernel. in/out are arrays of
-// `nranks` device pointers. Returns 0 or a negative error / positive kernels::Status.
+// `nranks` device pointers. `exponent_lookahead` < 0 takes the default. Returns 0 or a negative error / positive kernels::Status.
 int EmulatedAllReduce(int nranks, void* const* in_ptrs, void* const* out_ptrs,
                       unsigned long long numel, int elem_type, int mode, int algo, int block_numel,
                       size_t slot_bytes, int slots_per_channel, int channels, float post_scale,
-                      int repeats, std::string* error);
+                      int repeats, int exponent_lookahead, std::string* error);
 
 // True if the kernels were compiled with -DSWITCHML_CHECKED (geometry checks before every
 // tile; a violation sets STATUS_BOUNDS instead of touching memory).

@@ -255,10 +255,12 @@ void sml_static_slice(uint64_t numel, int parts, int index, uint64_t* offset, ui
 
 int sml_emu_allreduce(int nranks, void* const* in_ptrs, void* const* out_ptrs, uint64_t numel,
                       int elem_type, int mode, int algo, int block_numel, uint64_t slot_bytes,
-                      int slots_per_channel, int channels, float post_scale, int repeats) {
+                      int slots_per_channel, int channels, float post_scale, int repeats,
+                      int exponent_lookahead) {
   std::string err;
   int r = EmulatedAllReduce(nranks, in_ptrs, out_ptrs, numel, elem_type, mode, algo, block_numel,
-                            slot_bytes, slots_per_channel, channels, post_scale, repeats, &err);
+                            slot_bytes, slots_per_channel, channels, post_scale, repeats,
+                            exponent_lookahead, &err);
   if (r != 0) g_error = err;
   return r;
 }

@@ -120,6 +120,9 @@ bool Config::LoadFromString(const std::string& text, const std::string& origin) 
   opts["backend.cuda.rendezvous_dir"] = SML_OPT_STRING(backend_.cuda.rendezvous_dir);
   opts["backend.cuda.p2p_algo"] = SML_OPT_STRING(backend_.cuda.p2p_algo);
   opts["backend.cuda.numa_bind"] = SML_OPT_BOOL(backend_.cuda.numa_bind);
+  opts["backend.cuda.trace"] = SML_OPT_BOOL(backend_.cuda.trace);
+  opts["backend.cuda.signal_fence"] = SML_OPT_STRING(backend_.cuda.signal_fence);
+  opts["backend.cuda.exponent_lookahead"] = SML_OPT_UNSIGNED(backend_.cuda.exponent_lookahead);
   opts["backend.cuda.wait_timeout_ms"] = [this](const std::string& v) {
     return ParseDouble(v, &backend_.cuda.wait_timeout_ms);
   };
@@ -301,6 +304,9 @@ void Config::Validate() {
     SML_CHECK(c.slots_per_channel >= 1 && c.slots_per_channel <= 8)
         << "backend.cuda.slots_per_channel must be in [1,8]";
     SML_CHECK(c.channels <= 512) << "backend.cuda.channels must be at most 512";
+    SML_CHECK(c.signal_fence == "sc" || c.signal_fence == "release")
+        << "backend.cuda.signal_fence must be sc | release";
+    SML_CHECK(c.exponent_lookahead <= 4) << "backend.cuda.exponent_lookahead must be in [0,4]";
     // A slot is cut into num_workers shards of whole quantisation blocks, so its length
     // must be a multiple of num_workers * packet_numel elements (4 bytes each); keep the
     // shards 16-byte vectorisable as well.
@@ -382,7 +388,10 @@ std::string Config::ToString() const {
       << "    rendezvous_dir = " << c.rendezvous_dir << "\n"
       << "    wait_timeout_ms = " << c.wait_timeout_ms << "\n"
       << "    numa_bind = " << (c.numa_bind ? "true" : "false") << "\n"
-      << "    p2p_algo = " << c.p2p_algo << "\n";
+      << "    p2p_algo = " << c.p2p_algo << "\n"
+      << "    exponent_lookahead = " << c.exponent_lookahead << "\n"
+      << "    signal_fence = " << c.signal_fence << "\n"
+      << "    trace = " << (c.trace ? "true" : "false") << "\n";
   }
   for (const auto& kv : ignored_) o << "  (ignored) " << kv.first << " = " << kv.second << "\n";
   return o.str();

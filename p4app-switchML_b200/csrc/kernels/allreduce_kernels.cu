@@ -210,7 +210,7 @@ __device__ __forceinline__ void RoleSignal(const RankCtx& ctx, const Role& role,
                                            int phase, Epoch epoch) {
   role.Sync();
   if (role.tid < ctx.nranks) {
-    __threadfence_system();
+    if (ctx.sc_fence) __threadfence_system();
     StoreReleaseSys(FlagPtr(ctx.stage_peer[role.tid], channel, phase, ctx.rank), epoch);
   }
 }
@@ -264,16 +264,24 @@ __device__ __forceinline__ void RunSignaler(const RankCtx& ctx, StagedShared* sh
   unsigned long long told[3] = {0, 0, 0};
   volatile int* failed = reinterpret_cast<volatile int*>(&sh->failed);
   for (;;) {
+    // All notes first, then one fence for whatever is new: the fence is the expensive part
+    // (it drains behind the SM's stores in flight) and covers every role's writes at once.
+    unsigned long long d[3] = {0, 0, 0};
+    bool news = false;
+#pragma unroll
+    for (int r = 0; r < 3; r++) {
+      if (r >= nroles) continue;
+      asm volatile("ld.acquire.cta.shared::cta.u64 %0, [%1];" : "=l"(d[r]) : "r"(BulkSmemAddr(&sh->done[r])) : "memory");
+      news |= d[r] > told[r];
+    }
+    if (news && ctx.sc_fence) __threadfence_system();
     bool all = true;
 #pragma unroll
     for (int r = 0; r < 3; r++) {
       if (r >= nroles) continue;
-      unsigned long long d;
-      asm volatile("ld.acquire.cta.shared::cta.u64 %0, [%1];" : "=l"(d) : "r"(BulkSmemAddr(&sh->done[r])) : "memory");
-      if (d > told[r]) {
-        __threadfence_system();
-        if (lane < ctx.nranks) StoreReleaseSys(FlagPtr(ctx.stage_peer[lane], channel, r + 1, ctx.rank), base + d);
-        told[r] = d;
+      if (d[r] > told[r]) {
+        if (lane < ctx.nranks) StoreReleaseSys(FlagPtr(ctx.stage_peer[lane], channel, r + 1, ctx.rank), base + d[r]);
+        told[r] = d[r];
       }
       if (told[r] < ntiles) all = false;
     }
@@ -369,13 +377,16 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
   char* my_stage = ctx.stage_peer[ctx.rank];
   const size_t blocks_per_slot = ctx.slot_bytes / 4 / ctx.block_numel;
   const int shift = 31 - __clz(ctx.block_numel);  // block_numel is a power of two
-  // The exponents of tile k+A travel while tile k is quantised (A = 2 with four or more slots,
-  // 1 with two or three), so the agreement never costs a wait of its own and, with A = 2, the
-  // loaders of different ranks do not march in lockstep either: what tile k needs was signalled
-  // two tiles ago. A single slot leaves no room to run ahead. The words of tile k+A belong to
-  // the slot of tile k+A-S, which every rank consumed before it signalled that tile's payload
-  // (phase 1); the loader has awaited phase 1 of tile k-A by then, and S >= 2A.
-  const unsigned long long A = S >= 4 ? 2 : (S >= 2 ? 1 : 0);
+  // The exponents of tile k+A travel while tile k is quantised, so the agreement never costs a
+  // wait of its own: what tile k needs was signalled A tiles ago, with the payload of tile k-A.
+  // That signal is slow to arrive while a reducer saturates the link (its fence drains behind
+  // the bulk stores), so A tiles have to cover it: with A = 2 the loaders of four GPUs waited
+  // 300 us per pair of tiles for it. The exponent words have a ring of E slots of their own. The
+  // words of tile k+A were last used by tile k+A-E, which every rank consumed before it signalled
+  // that tile's payload (phase 1); the loader has awaited phase 1 of tile k-A by then, and
+  // E >= 2A. A single data slot leaves no room to run ahead (A = 0).
+  const unsigned long long A = static_cast<unsigned long long>(ctx.exp_lookahead);
+  const int E = ctx.exp_ring;
   // The output lies in symmetric memory: the owner of a shard broadcasts the finished values
   // straight into every rank's output and nothing is copied out of the slot.
   const bool direct_out = job.out_zero_copy != 0;
@@ -398,11 +409,16 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
   // its own work) in counters[3 + 2*role], [4 + 2*role]: a built-in pipeline profile.
   const bool timed = channel == 0 && role.tid == 0;
   unsigned long long t_mark = timed ? GlobalTimerNs() : 0;
+  unsigned long long cur_tile = 0;  // for the trace
+  if (timed && which == 0 && ctx.trace) ctx.trace[6 * kTraceTiles] = t_mark;
   auto lap = [&](int idx) {
     if (timed) {
       unsigned long long now = GlobalTimerNs();
       atomicAdd(ctx.counters + idx, now - t_mark);
       t_mark = now;
+      // idx 3/5/7: the role's waits for this tile are over; 4/6/8: the tile is finished
+      if (ctx.trace && idx >= 3 && idx <= 8 && cur_tile < kTraceTiles)
+        ctx.trace[(which * 2 + ((idx - 3) & 1)) * kTraceTiles + cur_tile] = now;
     }
   };
   auto tile_len = [&](unsigned long long k) {
@@ -410,8 +426,8 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
     return static_cast<size_t>(c1 - pos < tile_elems ? c1 - pos : tile_elems);
   };
   auto exp_offset_of = [&](unsigned long long k) {
-    const size_t slot_index = static_cast<size_t>(channel) * S + static_cast<size_t>(k % S);
-    return ctx.exp_offset + slot_index * blocks_per_slot * kExpWordBytes;
+    const size_t ring_index = static_cast<size_t>(channel) * E + static_cast<size_t>(k % E);
+    return ctx.exp_offset + ring_index * blocks_per_slot * kExpWordBytes;
   };
   // The quantising loader reads float32 device memory through per-warp TMA streams.
   static_assert(MODE != MODE_QUANT || kLoadWarps <= kStreamWarps, "every loader warp needs a ring");
@@ -432,6 +448,7 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
   };
 
   for (unsigned long long k = 0; k < ntiles; ++k) {
+    cur_tile = k;
     const unsigned long long pos = c0 + k * tile_elems;
     const Epoch epoch = base + k + 1;
     const size_t len = tile_len(k);
@@ -444,6 +461,7 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
                        slot_off >= ctx.data_offset && slot_off + ctx.slot_bytes <= ctx.stage_bytes &&
                        (MODE != MODE_QUANT ||
                         (blocks_per_slot * S <= static_cast<size_t>(kMaxBlocksPerSlot) &&
+                         E >= 1 && 2 * A <= static_cast<unsigned long long>(E) &&
                          exp_off + blocks_per_slot * kExpWordBytes <= ctx.oneshot_offset)) &&
                        (!direct_out || job.out_offset + (pos + len) * in_esz <= job.user_bytes));
     float* sf = s_sf + static_cast<size_t>(slot) * blocks_per_slot;
@@ -472,9 +490,9 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
       if (MODE == MODE_QUANT) {
         if (k == 0 || A == 0) {
           // Nobody has published the exponents of this tile (of the first A tiles, at the start
-          // of a job) yet: do it now and meet (phase 0). With a single slot its words are free
-          // by now: every rank consumed them before it signalled the payload of the tile
-          // before, and the copy-out awaited above came after all those signals.
+          // of a job) yet: do it now and meet (phase 0). Without lookahead the words are free
+          // by now: their last user is E tiles back, and every rank consumed that tile before it
+          // signalled its payload, which the meeting of the tile before this one came after.
           bool published = publish(in, len, exp_off, epoch);
           for (unsigned long long t = 1; published && t < A && t < ntiles; t++)
             published = publish(in + t * tile_elems * in_esz, tile_len(t), exp_offset_of(t), epoch + t);
@@ -585,15 +603,25 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
               MultimemStore4(out_mc + (i + u * n) * 4, bits);
             }
           }
-          for (; i < se; i += n) {
-            int v = MultimemLdReduceAddS32(mc + i * 4);
-            unsigned bits = static_cast<unsigned>(v);
-            if (MODE == MODE_QUANT) {
-              float y = quant::Dequantize(v, sf[i >> shift]);
-              if (job.post_scale != 1.0f) y *= job.post_scale;
-              bits = __float_as_uint(y);
+          if (i < se) {
+            // The remainder, fewer than kUnrollInt * n words: all of them in flight at once (one
+            // trip through the switch instead of one per word and thread).
+            int v[kUnrollInt];
+#pragma unroll
+            for (int u = 0; u < kUnrollInt; u++)
+              if (i + u * n < se) v[u] = MultimemLdReduceAddS32(mc + (i + u * n) * 4);
+#pragma unroll
+            for (int u = 0; u < kUnrollInt; u++) {
+              if (i + u * n < se) {
+                unsigned bits = static_cast<unsigned>(v[u]);
+                if (MODE == MODE_QUANT) {
+                  float y = quant::Dequantize(v[u], sf[(i + u * n) >> shift]);
+                  if (job.post_scale != 1.0f) y *= job.post_scale;
+                  bits = __float_as_uint(y);
+                }
+                MultimemStore4(out_mc + (i + u * n) * 4, bits);
+              }
             }
-            MultimemStore4(out_mc + i * 4, bits);
           }
         } else {
           size_t v0 = sb / 4, v1 = (se + 3) / 4;
@@ -626,8 +654,15 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
 #pragma unroll
             for (int u = 0; u < kUnrollLink; u++) finish(v + u * n, r[u]);
           }
-          for (; v < v1; v += n)
-            finish(v, ReduceVec<ELEM_I32>(ctx, ctx.stage_peer, ctx.stage_mc, slot_off + v * 16, 1.0f));
+          if (v < v1) {  // the remainder in one go, see above
+            uint4 r[kUnrollLink];
+#pragma unroll
+            for (int u = 0; u < kUnrollLink; u++)
+              if (v + u * n < v1) r[u] = ReduceVec<ELEM_I32>(ctx, ctx.stage_peer, ctx.stage_mc, slot_off + (v + u * n) * 16, 1.0f);
+#pragma unroll
+            for (int u = 0; u < kUnrollLink; u++)
+              if (v + u * n < v1) finish(v + u * n, r[u]);
+          }
         }
       } else {
         size_t v0 = sb / vec_elems, v1 = (se + vec_elems - 1) / vec_elems;
@@ -641,9 +676,14 @@ __device__ void RunStaged(const RankCtx& ctx, const JobArgs& job, int channel,
           for (int u = 0; u < kUnrollLink; u++)
             BroadcastVec(ctx, ctx.stage_peer, ctx.stage_mc, slot_off + (v + u * n) * 16, r[u]);
         }
-        for (; v < v1; v += n) {
-          uint4 r = ReduceVec<ELEM>(ctx, ctx.stage_peer, ctx.stage_mc, slot_off + v * 16, job.post_scale);
-          BroadcastVec(ctx, ctx.stage_peer, ctx.stage_mc, slot_off + v * 16, r);
+        if (v < v1) {  // the remainder in one go, see above
+          uint4 r[kUnrollLink];
+#pragma unroll
+          for (int u = 0; u < kUnrollLink; u++)
+            if (v + u * n < v1) r[u] = ReduceVec<ELEM>(ctx, ctx.stage_peer, ctx.stage_mc, slot_off + (v + u * n) * 16, job.post_scale);
+#pragma unroll
+          for (int u = 0; u < kUnrollLink; u++)
+            if (v + u * n < v1) BroadcastVec(ctx, ctx.stage_peer, ctx.stage_mc, slot_off + (v + u * n) * 16, r[u]);
         }
       }
       RoleDone(role, sh, 1, k + 1);
@@ -910,9 +950,17 @@ __device__ void RunZeroCopy(const RankCtx& ctx, const JobArgs& job, int channel,
       for (int u = 0; u < kUnrollLink; u++)
         BroadcastVec(ctx, peers, job.user_mc, out_base + (v + u * blockDim.x) * 16, r[u]);
     }
-    for (; v < nvec; v += blockDim.x) {
-      uint4 r = ReduceVec<ELEM>(ctx, peers, job.user_mc, in_base + v * 16, job.post_scale);
-      BroadcastVec(ctx, peers, job.user_mc, out_base + v * 16, r);
+    if (v < nvec) {
+      // The remainder, fewer than kUnrollLink * blockDim.x vectors: all in flight at once.
+      uint4 r[kUnrollLink];
+#pragma unroll
+      for (int u = 0; u < kUnrollLink; u++)
+        if (v + u * blockDim.x < nvec)
+          r[u] = ReduceVec<ELEM>(ctx, peers, job.user_mc, in_base + (v + u * blockDim.x) * 16, job.post_scale);
+#pragma unroll
+      for (int u = 0; u < kUnrollLink; u++)
+        if (v + u * blockDim.x < nvec)
+          BroadcastVec(ctx, peers, job.user_mc, out_base + (v + u * blockDim.x) * 16, r[u]);
     }
     (void)inplace;
     // Ragged end: plain peer loads and stores, element by element.
@@ -1285,7 +1333,7 @@ size_t StagingBytes(size_t slot_bytes, int slots_per_channel, int block_numel, i
   size_t off = align(flags);
   *exp_offset = off;
   size_t blocks_per_slot = slot_bytes / 4 / block_numel;
-  off = align(off + size_t(max_channels) * slots_per_channel * blocks_per_slot * kExpWordBytes);
+  off = align(off + size_t(max_channels) * ExpRingDepth(slots_per_channel) * blocks_per_slot * kExpWordBytes);
   *oneshot_offset = off;
   off = align(off + 3 * size_t(nranks) * oneshot_bytes);  // two alternating sets + one for captured launches
   *data_offset = off;
@@ -1444,7 +1492,7 @@ namespace {
 const int kNoAllocChannels = 8;
 const int kNoAllocSlots = 2;
 const size_t kNoAllocSlotBytes = 32768;
-const size_t kNoAllocAuxOffset = 768u << 10;  // counters and status word behind the staging
+const size_t kNoAllocAuxOffset = 896u << 10;  // counters and status word behind the staging (at most 772 KiB, with blocks of 32)
 
 // Scratch of the allocation-free entry point. In host code this name is only a handle for
 // cudaGetSymbolAddress, never a device address.
@@ -1528,6 +1576,9 @@ extern "C" int switchml_local_allreduce_noalloc(const void* in, void* out,
   ctx.stage_peer[0] = scratch;
   ctx.slot_bytes = kNoAllocSlotBytes;
   ctx.slots_per_channel = kNoAllocSlots;
+  ctx.sc_fence = 1;
+  ctx.exp_ring = ExpRingDepth(kNoAllocSlots);
+  ctx.exp_lookahead = ExpLookahead(kNoAllocSlots, kDefaultExpLookahead);
   ctx.block_numel = block_numel;
   ctx.oneshot_bytes = 256;
   ctx.timeout_ns = 1000000000ull;

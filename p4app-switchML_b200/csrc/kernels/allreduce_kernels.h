@@ -20,6 +20,9 @@ static const int kMaxRanks = 8;
 static const int kMaxChannels = 512;
 static const int kNumPhases = 4;
 static const int kThreads = 512;            // threads per CTA of every aggregation kernel
+static const int kExpRing = 8;              // exponent slots per channel, at least (a slot per data slot if those are more)
+static const int kTraceTiles = 64;          // tiles per job that the per-tile trace remembers
+static const int kTraceWords = 6 * kTraceTiles + 1;  // [role][began, finished][tile] in ns of %globaltimer, then the job's start
 static const int kFlagWordsPerChannel = kNumPhases * kMaxRanks;
 // Layout of a rank's symmetric staging region (byte offsets from its base).
 static const size_t kFlagBytes = size_t(kMaxChannels) * kFlagWordsPerChannel * 8;  // 128 KiB of 64-bit epochs
@@ -56,6 +59,10 @@ struct RankCtx {
   size_t oneshot_offset;         // start of the one-shot buffers
   size_t slot_bytes;             // bytes of one data slot
   int slots_per_channel;
+  int sc_fence;                  // 1: a sequentially consistent system fence before every flag store (signal_fence = sc);
+                                 // 0: the flag's release store alone orders the data before it
+  int exp_ring;                  // exponent slots per channel: a ring of its own, ExpRingDepth(slots_per_channel)
+  int exp_lookahead;             // how many tiles the exponents travel ahead of their data (2 * lookahead <= ring)
   int block_numel;               // quantisation block (= packet_numel)
   float quant_base;              // quant::QuantBase(nranks): scale factor at exponent 0
   size_t oneshot_bytes;          // capacity of one rank's one-shot buffer (per parity)
@@ -63,6 +70,8 @@ struct RankCtx {
   unsigned long long timeout_ns; // budget of every wait
   int* status;                   // device-visible status word (0 = ok)
   unsigned long long* counters;  // [0] tiles processed, [1] wait iterations, [2] timeouts
+  unsigned long long* trace;     // nullptr, or kTraceWords words in this rank's device memory: when channel 0's roles
+                                 // began and finished each of a job's first kTraceTiles tiles ([backend.cuda] trace)
   unsigned long long* epoch_words;  // [kMaxChannels] in this rank's device memory: the epoch each channel has
                                  // reached. Kept on the device so that a captured launch can be replayed.
 };
@@ -98,6 +107,22 @@ struct LaunchPlan {
   unsigned long long tiles;              // staged tiles summed over channels (stats)
   unsigned long long tile_elems;         // ALGO_STAGED: copy into JobArgs::tile_elems
 };
+
+// The exponent words of a channel form a ring of their own: they are 1/128 of the data, so
+// the ring can be deeper than the data slots and the exponents can run further ahead.
+inline int ExpRingDepth(int slots_per_channel) { return slots_per_channel > kExpRing ? slots_per_channel : kExpRing; }
+// Tiles by which exponents run ahead of their data: `wanted` clamped to half the ring; none
+// with a single data slot (every tile then meets over its own exponents first).
+inline int ExpLookahead(int slots_per_channel, int wanted) {
+  if (slots_per_channel < 2 || wanted < 0) return 0;
+  const int most = ExpRingDepth(slots_per_channel) / 2;
+  return wanted > most ? most : wanted;
+}
+// Default: none. Every tile's exponents are published right before it is quantised, so the
+// quantising pass finds the tile in L2 (with lookahead the exponent pass runs A tiles ahead and
+// its data is evicted again: all channels together touch 74 MB per tile step), and the loaders
+// have time for the extra meeting: they are several times faster than the reducers.
+static const int kDefaultExpLookahead = 0;
 
 // True if `p` is device memory (cudaMalloc or the virtual-memory API), not pinned host or managed memory.
 bool DeviceMemory(const void* p);

@@ -59,7 +59,7 @@ __device__ __forceinline__ bool ChannelBarrier(const RankCtx& ctx, int channel, 
   __syncthreads();  // everything this CTA wrote precedes the signal
   if (threadIdx.x < ctx.nranks) {
     int peer = threadIdx.x;
-    __threadfence_system();
+    if (ctx.sc_fence) __threadfence_system();
     if (signal) StoreReleaseSys(FlagPtr(ctx.stage_peer[peer], channel, phase, ctx.rank), epoch);
     const Epoch* mine = FlagPtr(ctx.stage_peer[ctx.rank], channel, phase, peer);
     unsigned long long start = GlobalTimerNs();

@@ -22,10 +22,10 @@
 //     done with tile k - S: phase 2 >= e(k - S) from everybody;
 //   * a reducer may overwrite a peer's result area once that peer's storer is done with
 //     tile k - S: phase 3 >= e(k - S) from everybody;
-//   * MODE_QUANT: the exponent words of tile k+A (slot (k+A) % S; A = 2 with four or more
-//     slots, else 1, none with a single slot) are published while tile k is pushed; their
-//     previous user is tile k+A-S, consumed by every loader before its phase-1 signal of that
-//     tile; the publishing loader has awaited phase 1 >= e(k - A) by then, and S >= 2A.
+//   * MODE_QUANT: the exponent words of tile k+A (slot (k+A) % E of a ring of E exponent slots;
+//     A tiles of lookahead, none with a single data slot) are published while tile k is pushed;
+//     their previous user is tile k+A-E, consumed by every loader before its phase-1 signal of
+//     that tile; the publishing loader has awaited phase 1 >= e(k - A) by then, and E >= 2A.
 // Between jobs nothing extra is needed: a rank's kernel ends after its storer has seen
 // every peer's phase 2 for every tile (their reducers are done with all receive areas), and
 // a result is pushed only after the peer's loader of the new job has signalled, i.e. after
@@ -213,7 +213,8 @@ __device__ void RunPush(const RankCtx& ctx, const JobArgs& job, int channel,
   char* my_stage = ctx.stage_peer[me];
   const size_t blocks_per_slot = ctx.slot_bytes / 4 / ctx.block_numel;
   const int shift = 31 - __clz(ctx.block_numel);
-  const unsigned long long A = S >= 4 ? 2 : (S >= 2 ? 1 : 0);  // exponents travel A tiles ahead of the data (see RunStaged)
+  const unsigned long long A = static_cast<unsigned long long>(ctx.exp_lookahead);  // exponents travel A tiles ahead of the data (see RunStaged)
+  const int E = ctx.exp_ring;
   const bool direct_out = job.out_zero_copy != 0;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -233,11 +234,16 @@ __device__ void RunPush(const RankCtx& ctx, const JobArgs& job, int channel,
   volatile int* failed = reinterpret_cast<volatile int*>(&sh->failed);
   const bool timed = channel == 0 && role.tid == 0;
   unsigned long long t_mark = timed ? GlobalTimerNs() : 0;
+  unsigned long long cur_tile = 0;  // for the trace
+  if (timed && which == 0 && ctx.trace) ctx.trace[6 * kTraceTiles] = t_mark;
   auto lap = [&](int idx) {
     if (timed) {
       unsigned long long now = GlobalTimerNs();
       atomicAdd(ctx.counters + idx, now - t_mark);
       t_mark = now;
+      // idx 3/5/7: the role's waits for this tile are over; 4/6/8: the tile is finished
+      if (ctx.trace && idx >= 3 && idx <= 8 && cur_tile < kTraceTiles)
+        ctx.trace[(which * 2 + ((idx - 3) & 1)) * kTraceTiles + cur_tile] = now;
     }
   };
   auto tile_len = [&](unsigned long long k) {
@@ -248,7 +254,7 @@ __device__ void RunPush(const RankCtx& ctx, const JobArgs& job, int channel,
     return ctx.data_offset + (static_cast<size_t>(channel) * S + static_cast<size_t>(k % S)) * ctx.slot_bytes;
   };
   auto exp_offset_of = [&](unsigned long long k) {
-    return ctx.exp_offset + (static_cast<size_t>(channel) * S + static_cast<size_t>(k % S)) * blocks_per_slot * kExpWordBytes;
+    return ctx.exp_offset + (static_cast<size_t>(channel) * E + static_cast<size_t>(k % E)) * blocks_per_slot * kExpWordBytes;
   };
   // The quantising loader reads float32 device memory through per-warp TMA streams.
   static_assert(MODE != MODE_QUANT || kLoadWarps <= kStreamWarps, "every loader warp needs a ring");
@@ -269,6 +275,7 @@ __device__ void RunPush(const RankCtx& ctx, const JobArgs& job, int channel,
   };
 
   for (unsigned long long k = 0; k < ntiles; ++k) {
+    cur_tile = k;
     const unsigned long long pos = c0 + k * tile_elems;
     const Epoch epoch = base + k + 1;
     const size_t len = tile_len(k);
@@ -283,6 +290,7 @@ __device__ void RunPush(const RankCtx& ctx, const JobArgs& job, int channel,
                        (MODE != MODE_QUANT ||
                         (blocks_per_slot * S <= static_cast<size_t>(kMaxBlocksPerSlot) &&
                          tile_elems / ctx.block_numel <= blocks_per_slot &&
+                         E >= 1 && 2 * A <= static_cast<unsigned long long>(E) &&
                          exp_off + blocks_per_slot * kExpWordBytes <= ctx.oneshot_offset)) &&
                        (!direct_out || job.out_offset + (pos + len) * in_esz <= job.user_bytes));
     float* sf = s_sf + static_cast<size_t>(slot) * blocks_per_slot;

@@ -13,10 +13,11 @@
 //   * tile k of a job uses epoch e(k) = base + k + 1 and slot k mod S; a signal is a release
 //     store of the epoch into the sender's column of every peer's pad, a wait polls the local
 //     pad with acquire loads and a time budget;
-//   * exponents: one 64-bit word per block and slot on every rank; a rank publishes
-//     (epoch << 8 | exponent + 128) with an atomic MAX into the word of ALL ranks, for tile k+A
-//     while it handles the payload of tile k (A = 2 with S >= 4, 1 with S >= 2; with a single
-//     slot every tile meets in phase 0). After the awaited signal each rank reads only its OWN word; a foreign tag is a
+//   * exponents: one 64-bit word per block on every rank, in a ring of E >= 8 exponent slots per
+//     channel that is independent of the data slots (tile k uses exponent slot k mod E); a
+//     rank publishes (epoch << 8 | exponent + 128) with an atomic MAX into the word of ALL
+//     ranks, for tile k+A while it handles the payload of tile k (A <= E/2 tiles of lookahead;
+//     with a single data slot or A = 0 every tile meets in phase 0). After the awaited signal each rank reads only its OWN word; a foreign tag is a
 //     protocol violation. The loader hands the scale factors to its reducer through a per-slot
 //     array that the phase-1 signal (which the reducer awaits from its own rank too) covers;
 //   * "staged" (with NVLink multicast): the loader quantises its tile into its own slot
@@ -60,7 +61,13 @@ const int kPhases = 4;
 struct Geometry {
   int ranks, channels, slots, block, tile;  // tile: elements, a multiple of ranks * block
   bool push;                                // false: staged through whole-tile slots, true: shards pushed to owners
+  int lookahead;                            // tiles by which exponents run ahead of their data, as configured
   int blocks() const { return tile / block; }
+  int ring() const { return slots > 8 ? slots : 8; }  // exponent slots per channel (kernels::ExpRingDepth)
+  size_t A() const {                                  // kernels::ExpLookahead
+    if (slots < 2 || lookahead < 0) return 0;
+    return static_cast<size_t>(std::min(lookahead, ring() / 2));
+  }
   int shard() const { return tile / ranks; }  // elements of the largest shard
 };
 
@@ -68,7 +75,7 @@ struct RankMemory {
   std::vector<std::atomic<uint64_t>> flags;      // [channel][phase][src]
   std::vector<int32_t> data;                     // staged: [channel][slot][tile]: quantised values, then results (as bits)
                                                  // push:   [channel][slot][2 * (ranks-1) * shard]: receive areas, result areas
-  std::vector<std::atomic<uint64_t>> exp_words;  // [channel][slot][blocks]: tagged exponents, atomic MAX from every rank
+  std::vector<std::atomic<uint64_t>> exp_words;  // [channel][exponent slot][blocks]: tagged exponents, atomic MAX from every rank
   std::vector<float> scale;                      // [channel][slot][blocks]: loader -> reducer of the same rank
   std::vector<uint64_t> epoch_words;             // [channel], touched only between jobs
   std::vector<std::atomic<uint64_t>> stored;     // [channel]: tiles the storer has copied out in this job
@@ -77,7 +84,7 @@ struct RankMemory {
   RankMemory(const Geometry& g)
       : flags(static_cast<size_t>(g.channels) * kPhases * g.ranks),
         data(static_cast<size_t>(g.channels) * g.slots * (g.push ? 2 * (g.ranks - 1) * g.shard() : g.tile)),
-        exp_words(static_cast<size_t>(g.channels) * g.slots * g.blocks()),
+        exp_words(static_cast<size_t>(g.channels) * g.ring() * g.blocks()),
         scale(static_cast<size_t>(g.channels) * g.slots * g.blocks()), epoch_words(g.channels, 0), stored(g.channels) {
     for (auto& f : flags) f.store(0);
     for (auto& w : exp_words) w.store(0);
@@ -101,7 +108,7 @@ struct Model {
     return Data(dst, channel, k) + (g.ranks - 1 + (src < dst ? src : src - 1)) * g.shard();
   }
   std::atomic<uint64_t>* ExpWords(int rank, int channel, size_t k) {
-    return mem[rank]->exp_words.data() + SlotIndex(channel, k) * g.blocks();
+    return mem[rank]->exp_words.data() + (static_cast<size_t>(channel) * g.ring() + k % g.ring()) * g.blocks();
   }
   float* Scale(int rank, int channel, size_t k) { return mem[rank]->scale.data() + SlotIndex(channel, k) * g.blocks(); }
   void Signal(int me, int channel, int phase, uint64_t epoch) {
@@ -172,7 +179,7 @@ void Loader(Model& m, int me, int c, const float* in, size_t numel) {
   ChannelRange r = RangeOf(g, numel, c);
   const uint64_t base = m.mem[me]->epoch_words[c];
   const size_t ntiles = (r.end - r.begin + g.tile - 1) / g.tile;
-  const size_t A = g.slots >= 4 ? 2 : (g.slots >= 2 ? 1 : 0);  // exponents travel A tiles ahead of the data
+  const size_t A = g.A();  // exponents travel A tiles ahead of the data
   const size_t S = g.slots;
   for (size_t k = 0; k < ntiles; k++) {
     const uint64_t epoch = base + k + 1;
@@ -319,9 +326,10 @@ int RunFlagProtocolModel() {
   int failures = 0;
   uint32_t seed = 99;
   auto next = [&] { seed = seed * 1664525u + 1013904223u; return seed; };
-  const Geometry geometries[] = {{2, 2, 2, 64, 256, false}, {3, 2, 1, 64, 384, false}, {4, 3, 4, 32, 256, false},
-                                 {2, 2, 2, 64, 256, true},  {3, 1, 1, 64, 384, true},  {4, 3, 4, 32, 256, true},
-                                 {2, 1, 5, 64, 256, true},  {2, 2, 3, 64, 256, false}};
+  const Geometry geometries[] = {{2, 2, 2, 64, 256, false, 4}, {3, 2, 1, 64, 384, false, 4}, {4, 3, 4, 32, 256, false, 4},
+                                 {2, 2, 2, 64, 256, true, 4},  {3, 1, 1, 64, 384, true, 4},  {4, 3, 4, 32, 256, true, 4},
+                                 {2, 1, 5, 64, 256, true, 3},  {2, 2, 3, 64, 256, false, 1}, {3, 2, 4, 64, 384, false, 2},
+                                 {2, 2, 8, 64, 256, true, 2},  {2, 2, 2, 64, 256, false, 0}, {2, 1, 3, 64, 256, true, 0}};
   for (const Geometry& g : geometries) {
     Model m;
     m.g = g;

@@ -73,6 +73,9 @@ struct CudaBackendConfig {
   double wait_timeout_ms = 10000.0;       // budget of every device-side wait for a peer
   bool numa_bind = false;                 // keep the launcher and completion threads on the GPU's NUMA node
   std::string p2p_algo = "push";          // peer-memory transport, large messages: push (posted stores only) | staged
+  uint32_t exponent_lookahead = 0;        // int32_quant: tiles by which the block exponents run ahead of their data (0..ring/2)
+  std::string signal_fence = "release";   // sc: fence.sc.sys before every flag store | release: the flag's st.release.sys alone
+  bool trace = false;                     // channel 0 timestamps every tile of its roles; GetStats shows the last job's timeline
 };
 
 class Config {

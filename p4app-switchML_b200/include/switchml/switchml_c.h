@@ -78,10 +78,12 @@ void sml_static_slice(uint64_t numel, int parts, int index, uint64_t* offset, ui
 int sml_convert_u8(int widen, const void* in, void* out, uint64_t numel, void* stream);
 
 /* `nranks` virtual ranks on the current CUDA device in one cooperative kernel.
- * elem_type 0 f32 / 1 i32 / 2 bf16; mode 0 sum / 1 quant; algo 0 staged / 1 one-shot. */
+ * elem_type 0 f32 / 1 i32 / 2 bf16; mode 0 sum / 1 quant; algo 0 staged / 1 one-shot / 3 push;
+ * exponent_lookahead: tiles by which the exponents run ahead of the data (< 0: the default). */
 int sml_emu_allreduce(int nranks, void* const* in_ptrs, void* const* out_ptrs, uint64_t numel,
                       int elem_type, int mode, int algo, int block_numel, uint64_t slot_bytes,
-                      int slots_per_channel, int channels, float post_scale, int repeats);
+                      int slots_per_channel, int channels, float post_scale, int repeats,
+                      int exponent_lookahead);
 
 /* Stand-alone controller / software switch (what rank 0 otherwise hosts in-process). */
 void* sml_controller_start(const char* ip, int port, int udp_port);

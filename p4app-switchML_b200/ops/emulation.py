@@ -16,9 +16,11 @@ ALGO = {"staged": 0, "oneshot": 1, "push": 3}
 
 
 def emulated_allreduce(inputs, mode="quant", algo="staged", block_numel=256, slot_bytes=131072,
-                       slots_per_channel=2, channels=0, post_scale=1.0, repeats=1, outputs=None):
+                       slots_per_channel=2, channels=0, post_scale=1.0, repeats=1, outputs=None,
+                       exponent_lookahead=-1):
     """Allreduce `inputs` (a list of equally sized 1-D CUDA tensors, one per virtual rank,
-    all on the current device). Returns the list of per-rank outputs."""
+    all on the current device). Returns the list of per-rank outputs. `exponent_lookahead`:
+    tiles by which the exact mode's exponents run ahead of their data (-1: the library's default)."""
     import torch
     n = len(inputs)
     x0 = inputs[0]
@@ -35,7 +37,8 @@ def emulated_allreduce(inputs, mode="quant", algo="staged", block_numel=256, slo
     outs = (ctypes.c_void_p * n)(*[o.data_ptr() for o in outputs])
     torch.cuda.synchronize()
     rc = lib().sml_emu_allreduce(n, ins, outs, x0.numel(), elem, MODE[mode], ALGO[algo], block_numel,
-                                 slot_bytes, slots_per_channel, channels, float(post_scale), repeats)
+                                 slot_bytes, slots_per_channel, channels, float(post_scale), repeats,
+                                 int(exponent_lookahead))
     if rc != 0:
         raise NativeError("emulated allreduce failed (%d): %s" % (rc, last_error()))
     return outputs

@@ -73,7 +73,7 @@ def cuda_worker(rank, n, ctl_port, transport, mode, q, heap_mb=64, launch="inlin
         cfg = sml.make_config("cuda", rank=rank, num_workers=n, packet_numel=256, device=rank,
                               controller_port=ctl_port, transport=transport, mode=mode,
                               symm_heap_mb=heap_mb, launch=launch, wait_timeout_ms=20000,
-                              slot_bytes=65536)
+                              slot_bytes=65536, trace=True)
         assert ctx.start(cfg), "start failed"
         report = {"multimem": ctx.uses_multimem(), "cases": 0}
         sizes = [1, 255, 4097, 65536, 70001, (1 << 20) + 3, 5 * (1 << 20)]
@@ -205,7 +205,21 @@ def cuda_worker(rank, n, ctl_port, transport, mode, q, heap_mb=64, launch="inlin
                 for p, rp in zip(model.parameters(), ref_model.parameters()):
                     assert torch.allclose(p.grad, rp.grad, rtol=1e-4, atol=1e-6), "DDP gradient != sum of local gradients"
                 report["cases"] += 1
+        # the per-tile trace of channel 0: one streamed job, then its timeline must be ordered
+        x = torch.from_numpy(rank_data(rank, 6 << 20, "float32", seed=5)).cuda()
+        job = ctx.all_reduce_async(x, torch.empty_like(x))
+        assert job.wait(60000) == sml.JobStatus.FINISHED, job.error()
         report["stats"] = ctx.get_stats()
+        tr = report["stats"]["backend"]["channel0_trace_ns"]
+        tiles = sum(1 for v in tr["loader_finished"] if v)
+        assert tiles >= 2, "a 24 MiB job has several tiles per channel"
+        for role in ("loader", "reducer", "storer"):
+            began, finished = tr[role + "_began"][:tiles], tr[role + "_finished"][:tiles]
+            assert all(0 < b <= f for b, f in zip(began, finished)), role + ": a tile finished before it began"
+            assert all(finished[k] <= began[k + 1] for k in range(tiles - 1)), role + ": tiles out of order"
+        assert all(l <= r for l, r in zip(tr["loader_finished"][:tiles], tr["reducer_finished"][:tiles])), \
+            "a tile was reduced before it was loaded"
+        report["cases"] += 1
         ctx.stop()
         q.put((rank, "ok", report))
     except Exception:

@@ -59,6 +59,22 @@ def test_quant_block_sizes_and_reuse(block, algo):
         assert np.array_equal(o.cpu().numpy(), want)
 
 
+@pytest.mark.parametrize("algo", ["staged", "push"])
+@pytest.mark.parametrize("slots", [2, 4])
+@pytest.mark.parametrize("lookahead", [0, 1, 2, 3, 4])
+def test_quant_exponent_lookahead(lookahead, slots, algo):
+    """The exponents of a tile travel `lookahead` tiles ahead of its data through a ring of
+    exponent slots of its own (8 deep, whatever the number of data slots): every setting gives
+    the oracle's bits, over many tiles per channel and several jobs on the same staging."""
+    xs = _inputs(3, 200003, seed=11 + lookahead)
+    outs = emulated_allreduce([x.cuda() for x in xs], mode="quant", algo=algo, block_numel=64,
+                              slot_bytes=3 * 4 * 128 * 4, slots_per_channel=slots, channels=2,
+                              repeats=2, exponent_lookahead=lookahead)
+    want = quant_allreduce_oracle([x.numpy() for x in xs], 64)
+    for o in outs:
+        assert np.array_equal(o.cpu().numpy(), want)
+
+
 @pytest.mark.parametrize("algo", ["staged", "oneshot", "push"])
 @pytest.mark.parametrize("n", [2, 8])
 def test_int32_wrapping_sum(n, algo):
