@@ -37,6 +37,8 @@ def test_window_is_rounded_to_thread_multiple():
     "[general]\nbackend = rdma\n",                                          # NIC backends do not exist here
     "[general]\nbackend = udp\npacket_numel = 128\n",                       # udp wants 64 or 256
     "[general]\nbackend = cuda\npacket_numel = 100\n",                      # cuda wants a power of two
+    "[general]\nbackend = cuda\npacket_numel = 256\n[backend.cuda]\nexponent_lookahead = 5\n",   # ring of 8: at most 4
+    "[general]\nbackend = cuda\npacket_numel = 256\n[backend.cuda]\nsignal_fence = none\n",     # sc | release
     "[general]\nbogus_key = 1\n",
     "[general]\nrank = minus one\n",
     "[general\nrank = 1\n",
@@ -58,6 +60,15 @@ def test_cuda_section_and_slot_rounding():
     assert "mode = float_sum" in dump and "transport = p2p" in dump
     # multiple of num_workers * max(packet_numel,128) * 4 = 4096
     assert "slot_bytes = 98304" in dump
+
+
+def test_cuda_signalling_keys():
+    """Defaults: flags are announced by their release store alone, exponents are agreed right
+    before their tile; both can be set back, and the trace is off unless asked for."""
+    dump = check_config(sml.make_config("cuda", packet_numel=256))
+    assert "signal_fence = release" in dump and "exponent_lookahead = 0" in dump and "trace = false" in dump
+    dump = check_config(sml.make_config("cuda", packet_numel=256, signal_fence="sc", exponent_lookahead=4, trace=True))
+    assert "signal_fence = sc" in dump and "exponent_lookahead = 4" in dump and "trace = true" in dump
 
 
 def test_make_config_routes_keys():
