@@ -78,3 +78,20 @@ def test_reference_arm_imports_nothing_of_this_repository():
     record = json.loads(lines[0])
     assert record["impl"] == "reference" and "unavailable" in record
     assert lines[-1] == "LOADED []"
+
+
+def test_sweep_table_compares_each_element_type_with_its_own_nccl_column():
+    spec = importlib.util.spec_from_file_location(
+        "sweep_under_test", os.path.join(ROOT, "p4app-switchML_b200", "benchmarks", "allreduce_sweep.py"))
+    sweep = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(sweep)
+
+    def rec(impl, numel, us, dtype="float32"):
+        return {"impl": impl, "numel": numel, "us": us, "dtype": dtype, "ate_per_s": numel / us * 1e6, "bus_gbs": 1.0}
+    table = sweep.markdown_table([rec("nccl", 1024, 20.0), rec("nccl-int32", 1024, 10.0, "int32"),
+                                  rec("sml-float", 1024, 10.0), rec("sml-int32", 1024, 20.0, "int32"),
+                                  rec("nccl", 4096, 30.0), rec("sml-float", 4096, 60.0)], 4, 100, 10)
+    lines = table.splitlines()
+    assert lines[2] == "| elements | nccl | nccl-int32 | sml-float | sml-int32 |"
+    assert lines[4] == "| 2^10 | 20.0 | 10.0 | 10.0 (2.00x) | 20.0 (0.50x) |"   # float against nccl, int32 against nccl-int32
+    assert lines[5] == "| 2^12 | 30.0 |  | 60.0 (0.50x) |  |"
